@@ -1,0 +1,149 @@
+/*
+ * ltq — B200 (sm_100a) CUDA implementation of l-ten's uint8 quantized
+ * fully-connected forward path, behind a C ABI.
+ *
+ * Every pointer named *_dev is device memory on `device`; everything else is
+ * host memory.  All entry points return 0 on success or a negative ltq_status;
+ * ltq_last_error() gives the message of the calling thread's last failure.
+ * No exception crosses this boundary and no entry point has a CPU fallback:
+ * without a usable CUDA device every compute call fails with
+ * LTQ_ERR_CUDA.
+ *
+ * `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ * stream, which keeps ordering with l-ten's own synchronous CUDA calls).
+ * Work is enqueued on it and the call returns without synchronising unless
+ * stated otherwise.
+ *
+ * Reference interfaces are cited as file:line inside the l-ten project.
+ */
+#ifndef LTQ_H
+#define LTQ_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LTQ_VERSION 1
+
+/* Mirrors `struct QuantizationParams`, l-ten/math_fns.h:12-16 (same layout:
+ * float at 0, uint8 at 4, size 8): real = scale * (q - zero_point). */
+typedef struct ltq_qparams {
+    float scale;
+    uint8_t zero_point;
+} ltq_qparams;
+
+typedef enum ltq_status {
+    LTQ_OK = 0,
+    LTQ_ERR_INVALID_ARG = -1,   /* null pointer, bad size, bad enum */
+    LTQ_ERR_UNSUPPORTED = -2,   /* alpha != 1 / beta != 0 (l-ten/math_fns.cpp:1331-1334), K*255^2 overflow */
+    LTQ_ERR_CUDA = -3,          /* a CUDA runtime/driver call failed; message has the CUDA error string */
+    LTQ_ERR_DEVICE_TIMEOUT = -4,/* a bounded device-side wait gave up (status word read back on request) */
+    LTQ_ERR_NO_MEMORY = -5,
+    LTQ_ERR_TOO_LARGE = -6      /* size beyond a documented fixed limit */
+} ltq_status;
+
+/* What the epilogue writes (out_dev element type follows). */
+typedef enum ltq_out_mode {
+    LTQ_OUT_U8 = 0,  /* (uchar)(rm*acc + z_out), rm = s_a*s_w/s_out — the reference's only mode, l-ten/math_fns.cpp:1436,1474 */
+    LTQ_OUT_F32 = 1, /* (s_a*s_w) * (float)acc — what Dequantize would recover, without the uint8 round trip */
+    LTQ_OUT_I32 = 2  /* acc itself: sum (a-z_a)(w-z_w) + bias, l-ten/math_fns.cpp:1469-1473 */
+} ltq_out_mode;
+
+/* Epilogue flags (bit-or). */
+#define LTQ_FLAG_RELU 1u     /* acc = max(acc,0) before scaling; no counterpart in the reference (its relu is float-only) */
+#define LTQ_FLAG_SATURATE 2u /* U8 cast clamps to [0,255]. Default (flag clear) reproduces the reference build's cast:
+                                truncate toward zero, keep the low byte when out of range */
+/* Kernel selection override, for tests and profiling (default: by shape). */
+#define LTQ_FLAG_FORCE_SIMT 0x100u  /* generic dp4a tile kernel */
+#define LTQ_FLAG_FORCE_TC 0x200u    /* tcgen05 kernel (needs K % 16 == 0) */
+#define LTQ_FLAG_FORCE_SKINNY 0x400u/* weight-streaming kernel (needs M <= 16, K % 16 == 0) */
+
+int ltq_version(void);
+const char *ltq_last_error(void);
+/* Number of kernels this library has launched since load (all threads). */
+uint64_t ltq_kernel_launches(void);
+
+/* ---- quantisation helpers (replace l-ten/utils.h:23-27 for device data) -------------------------------------- */
+
+/* GetMinMax, l-ten/utils.cpp:198-226.  minmax_dev[0]=min, [1]=max (floats, device).  len >= 1. */
+int ltq_get_min_max(const float *data_dev, uint64_t len, float *minmax_dev, int device, void *stream);
+
+/* ComputeQuantizationParams, l-ten/utils.cpp:266-286.  Pure host arithmetic on two scalars.
+ * Returns LTQ_ERR_INVALID_ARG when the widened range is empty (min = max = 0), where the reference divides by 0. */
+int ltq_compute_qparams(float min_val, float max_val, ltq_qparams *qp);
+
+/* Same rule evaluated on the device from minmax_dev into qp_dev (no host round trip). */
+int ltq_compute_qparams_dev(const float *minmax_dev, ltq_qparams *qp_dev, int device, void *stream);
+
+/* Quantize(float*, uint8_t*, len, qp), l-ten/utils.cpp:243-254. */
+int ltq_quantize_u8(const float *data_dev, uint8_t *q_dev, uint64_t len, const ltq_qparams *qp, int device,
+                    void *stream);
+/* Quantize(float*, int*, len, qp), l-ten/utils.cpp:228-241 (bias: scale s_in*s_wt, zero point 0). */
+int ltq_quantize_i32(const float *data_dev, int32_t *q_dev, uint64_t len, const ltq_qparams *qp, int device,
+                     void *stream);
+/* Dequantize(float*, uint8_t*, len, qp), l-ten/utils.cpp:256-264. */
+int ltq_dequantize(float *data_dev, const uint8_t *q_dev, uint64_t len, const ltq_qparams *qp, int device,
+                   void *stream);
+
+/* Activation quantise step fused with the per-row sums the GEMM epilogue needs: q = Quantize(x) over [M,K] and
+ * asum[i] = sum_k q[i,k] (the col_vector of l-ten/math_fns.cpp:1372-1380 before its -z_w factor).
+ * Exactly one of qp (host) / qp_dev (device, e.g. from ltq_compute_qparams_dev) must be non-NULL. */
+int ltq_quantize_rows_u8(const float *x_dev, uint64_t M, uint64_t K, const ltq_qparams *qp, const ltq_qparams *qp_dev,
+                         uint8_t *q_dev, int32_t *asum_dev, int device, void *stream);
+
+/* Per-row sums of a uint8 [rows, cols] matrix into int32 [rows] (row_vector / col_vector of
+ * l-ten/math_fns.cpp:1362-1380 before their -z factors). */
+int ltq_row_sums_u8(const uint8_t *m_dev, uint64_t rows, uint64_t cols, int32_t *sums_dev, int device, void *stream);
+
+/* ---- the reference kernel call, argument for argument ---------------------------------------------------------- */
+
+/* quantized_matmul, l-ten/math_fns.h:104 / l-ten/math_fns.cpp:1311-1478, all four transpose variants.
+ * A, B, C, bias, workspace are device pointers; qparams is a HOST array of 3 (A-operand, B-operand, output).
+ * workspace_dev holds at least (M + N) int32 and receives [-z_A*sum_k B(j,.) (N) | -z_B*sum_k A(i,.) (M)] exactly as
+ * the reference leaves it.  alpha != 1 or beta != 0 -> LTQ_ERR_UNSUPPORTED (reference: LTEN_ERR).
+ * C = (uchar)(rm * acc + z_C) with the reference build's truncating, wrapping cast. */
+int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                         const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, uint8_t *C_dev,
+                         const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int device,
+                         void *stream);
+
+/* ---- layer handle: what FullyConnected_q (l-ten/layers.h:69-106) keeps between calls ------------------------- */
+
+typedef struct ltq_layer ltq_layer;
+
+/* FullyConnected_q::init, l-ten/fully_connected.cpp:295-320, device side.  The handle owns only derived state
+ * (weight row sums, tensor maps, the activation-sum workspace that l-ten keeps in workspace_); weights and bias stay
+ * the caller's. */
+int ltq_layer_create(ltq_layer **layer, int device, uint64_t in_features, uint64_t out_features);
+int ltq_layer_destroy(ltq_layer *layer);
+
+/* Bind device weights uint8 [N,K] (K contiguous: the {1,1,N,K} tensor of l-ten/fully_connected.cpp:303) and
+ * optional int32 bias [N]; computes sum_k W[j,k] once (the reference recomputes it on every call,
+ * l-ten/math_fns.cpp:1362-1370).  Call again whenever the weight bytes change or move.  Synchronises `stream`. */
+int ltq_layer_set_weights(ltq_layer *layer, const uint8_t *w_dev, const int32_t *bias_dev, void *stream);
+
+/* set_qparams_in / set_qparams_out / set_qparams_params, l-ten/layers.h:89-91, fully_connected.cpp:440-446. */
+int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_qparams *qp_wt,
+                          const ltq_qparams *qp_out);
+
+/* FullyConnected_q::forward's compute, l-ten/fully_connected.cpp:364-395, with all leading dims folded into M.
+ *   x_dev     uint8 [M,K]
+ *   asum_dev  int32 [M] row sums of x (from ltq_quantize_rows_u8), or NULL: computed here into the layer's workspace
+ *   qp_in_dev optional DEVICE qparams overriding the layer's input qparams (dynamic activation quantisation
+ *             without a host round trip); NULL = use the value set by ltq_layer_set_qparams
+ *   out_dev   uint8 / float / int32 [M,N] by out_mode
+ * Kernel choice: M <= 16 -> weight-streaming kernel; otherwise the tcgen05 kernel when K % 16 == 0; else the
+ * generic kernel. */
+int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
+                      const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream);
+
+/* Reads (and clears) the layer's device status word: LTQ_OK, or LTQ_ERR_DEVICE_TIMEOUT when a bounded wait inside a
+ * kernel ran out since the last check.  Synchronises `stream`. */
+int ltq_layer_check(ltq_layer *layer, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LTQ_H */

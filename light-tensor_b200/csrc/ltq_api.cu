@@ -1,0 +1,396 @@
+// C-ABI entry points of libltq (declared in include/ltq.h): argument checking, kernel selection and the layer handle.
+// Nothing here computes on the host beyond scalar set-up; every data path is a CUDA kernel and every entry point fails
+// with LTQ_ERR_CUDA when no device is usable.
+#include <stdarg.h>
+#include <string.h>
+
+#include <cmath>
+#include <mutex>
+#include <new>
+
+#include "ltq_common.cuh"
+#include "ltq_gemm_tc.cuh"
+#include "ltq_gemv.cuh"
+
+namespace ltq {
+
+std::atomic<uint64_t> g_launches{0};
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+
+namespace {
+
+constexpr int MAX_DEVICES = 64;
+
+struct DeviceState {
+    int sms = 0;
+    uint32_t *status = nullptr;  // device word: 0, or the code of the first bounded wait that expired
+};
+DeviceState g_dev[MAX_DEVICES];
+std::mutex g_dev_mu;
+
+// Per-device constants and the status word, created on first use with that device current.
+int device_state(int device, DeviceState **out)
+{
+    LTQ_REQUIRE(device >= 0 && device < MAX_DEVICES, LTQ_ERR_INVALID_ARG, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    DeviceState &d = g_dev[device];
+    if (!d.status) {
+        int sms = 0;
+        LTQ_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+        int major = 0;
+        LTQ_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        LTQ_REQUIRE(major == 10, LTQ_ERR_CUDA, "device %d has compute capability %d.x; this library is built for sm_100a only",
+                    device, major);
+        uint32_t *p = nullptr;
+        LTQ_CUDA_TRY(cudaMalloc(&p, 256));
+        LTQ_CUDA_TRY(cudaMemset(p, 0, 256));
+        d.sms = sms;
+        d.status = p;
+    }
+    *out = &d;
+    return LTQ_OK;
+}
+
+Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *bias, const ltq_qparams &qa,
+                       const ltq_qparams &qb, const ltq_qparams &qc, uint64_t K, int out_mode, unsigned flags)
+{
+    Epilogue e;
+    e.bsum = bsum;
+    e.asum = asum;
+    e.bias = bias;
+    e.qpA_dev = nullptr;
+    e.sA = qa.scale;
+    e.sB = qb.scale;
+    e.sC = qc.scale;
+    e.zA = qa.zero_point;
+    e.zB = qb.zero_point;
+    e.zC = qc.zero_point;
+    e.K = (uint32_t)K;
+    e.out_mode = out_mode;
+    e.flags = flags & (LTQ_FLAG_RELU | LTQ_FLAG_SATURATE);
+    return e;
+}
+
+enum Path { PATH_SIMT, PATH_TC, PATH_SKINNY };
+
+// Kernel choice for the FullyConnected_q layout (A [M,K], B [N,K]).
+int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B, unsigned flags, Path *path)
+{
+    const bool tc_ok = tc_shape_ok(M, N, K, A, B), sk_ok = gemv_shape_ok(M, N, K, A, B);
+    if (flags & LTQ_FLAG_FORCE_SIMT) {
+        *path = PATH_SIMT;
+    } else if (flags & LTQ_FLAG_FORCE_TC) {
+        LTQ_REQUIRE(tc_ok, LTQ_ERR_UNSUPPORTED, "tcgen05 kernel needs K %% 16 == 0 and 16-byte aligned operands (M=%llu N=%llu K=%llu)",
+                    (unsigned long long)M, (unsigned long long)N, (unsigned long long)K);
+        *path = PATH_TC;
+    } else if (flags & LTQ_FLAG_FORCE_SKINNY) {
+        LTQ_REQUIRE(sk_ok, LTQ_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, K %% 16 == 0 and 16-byte aligned operands (M=%llu K=%llu)",
+                    (unsigned long long)M, (unsigned long long)K);
+        *path = PATH_SKINNY;
+    } else if (sk_ok) {
+        *path = PATH_SKINNY;
+    } else if (tc_ok) {
+        *path = PATH_TC;
+    } else {
+        *path = PATH_SIMT;
+    }
+    return LTQ_OK;
+}
+
+}  // namespace
+}  // namespace ltq
+
+using namespace ltq;
+
+struct ltq_layer {
+    int device = 0;
+    uint64_t K = 0, N = 0;
+    const uint8_t *w = nullptr;
+    const int32_t *bias = nullptr;
+    int32_t *wsum = nullptr;       // [N] sum_k W[j,k]
+    int32_t *asum_ws = nullptr;    // activation row sums when the caller supplies none; grows with M like
+    uint64_t asum_cap = 0;         // FullyConnected_q::workspace_ (l-ten/fully_connected.cpp:366-371)
+    ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
+    TcOperandMap map_w[3];         // weight tensor maps for 64-, 128- and 256-column tiles, built on demand
+    DeviceState *dev = nullptr;
+};
+
+extern "C" {
+
+int ltq_version(void) { return LTQ_VERSION; }
+const char *ltq_last_error(void) { return ltq::g_err; }
+uint64_t ltq_kernel_launches(void) { return g_launches.load(); }
+
+// ---- helpers ----------------------------------------------------------------------------------------------------------
+int ltq_get_min_max(const float *data_dev, uint64_t len, float *minmax_dev, int device, void *stream)
+{
+    LTQ_REQUIRE(data_dev && minmax_dev && len >= 1, LTQ_ERR_INVALID_ARG, "Invalid argument");  // l-ten/utils.cpp:204-207
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_min_max(data_dev, len, minmax_dev, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_compute_qparams(float min_val, float max_val, ltq_qparams *qp)
+{
+    LTQ_REQUIRE(qp, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    // l-ten/utils.cpp:266-286, float arithmetic in the same order.
+    min_val = std::fmin(min_val, 0.f);
+    max_val = std::fmax(max_val, 0.f);
+    volatile float range = max_val - min_val;
+    LTQ_REQUIRE(range > 0.f, LTQ_ERR_INVALID_ARG, "empty value range [%g, %g]: scale would be 0", min_val, max_val);
+    volatile float scale = range / 255.f;
+    volatile float ratio = min_val / scale;
+    volatile float zp = 0.f - ratio;
+    qp->scale = scale;
+    qp->zero_point = (uint8_t)std::round((float)zp);
+    return LTQ_OK;
+}
+
+int ltq_compute_qparams_dev(const float *minmax_dev, ltq_qparams *qp_dev, int device, void *stream)
+{
+    LTQ_REQUIRE(minmax_dev && qp_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_qparams_from_minmax(minmax_dev, qp_dev, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_quantize_u8(const float *data_dev, uint8_t *q_dev, uint64_t len, const ltq_qparams *qp, int device, void *stream)
+{
+    LTQ_REQUIRE(data_dev && q_dev && qp, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (len == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_quantize_u8(data_dev, q_dev, len, *qp, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_quantize_i32(const float *data_dev, int32_t *q_dev, uint64_t len, const ltq_qparams *qp, int device, void *stream)
+{
+    LTQ_REQUIRE(data_dev && q_dev && qp, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (len == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_quantize_i32(data_dev, q_dev, len, *qp, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_dequantize(float *data_dev, const uint8_t *q_dev, uint64_t len, const ltq_qparams *qp, int device, void *stream)
+{
+    LTQ_REQUIRE(data_dev && q_dev && qp, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (len == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_dequantize(data_dev, q_dev, len, *qp, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_quantize_rows_u8(const float *x_dev, uint64_t M, uint64_t K, const ltq_qparams *qp, const ltq_qparams *qp_dev,
+                         uint8_t *q_dev, int32_t *asum_dev, int device, void *stream)
+{
+    LTQ_REQUIRE(x_dev && q_dev && asum_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE((qp != nullptr) != (qp_dev != nullptr), LTQ_ERR_INVALID_ARG,
+                "exactly one of qp (host) and qp_dev (device) must be given");
+    if (M == 0) return LTQ_OK;
+    LTQ_REQUIRE(K >= 1, LTQ_ERR_INVALID_ARG, "K must be >= 1");
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_quantize_rows(x_dev, M, K, qp, qp_dev, q_dev, asum_dev, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_row_sums_u8(const uint8_t *m_dev, uint64_t rows, uint64_t cols, int32_t *sums_dev, int device, void *stream)
+{
+    LTQ_REQUIRE(m_dev && sums_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (rows == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_row_sums(m_dev, rows, cols, sums_dev, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+// ---- GEMM dispatch shared by the stateless call and the layer ------------------------------------------------------
+static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
+                       const Epilogue &epi, void *out, unsigned flags, ltq_layer *layer, cudaStream_t stream)
+{
+    Path path;
+    int rc = choose_path(M, N, K, A, B, flags, &path);
+    if (rc != LTQ_OK) return rc;
+    switch (path) {
+        case PATH_SKINNY:
+            LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->sms, stream));
+            break;
+        case PATH_TC: {
+            const int bn = tc_pick_bn(M, N, dev->sms);
+            TcOperandMap map_a, tmp_b;
+            int er = tc_make_map(&map_a, A, M, K, 128);
+            LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation operand (CUresult %d)", er);
+            TcOperandMap *map_b = &tmp_b;
+            if (layer) map_b = &layer->map_w[bn == 64 ? 0 : (bn == 128 ? 1 : 2)];
+            if (!map_b->matches(B, N, K, bn)) {
+                er = tc_make_map(map_b, B, N, K, bn);
+                LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
+            }
+            LTQ_CUDA_TRY(launch_gemm_tc(map_a, *map_b, bn, M, N, K, epi, out, dev->status, dev->sms, stream));
+            break;
+        }
+        default:
+            LTQ_CUDA_TRY(launch_gemm_simt(false, true, M, N, K, A, B, epi, out, stream));
+    }
+    return LTQ_OK;
+}
+
+int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                         const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, uint8_t *C_dev,
+                         const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int device,
+                         void *stream)
+{
+    LTQ_REQUIRE(alpha == 1 && beta == 0, LTQ_ERR_UNSUPPORTED,
+                "Support for alpha != 1 and beta != 0 not implemented");  // l-ten/math_fns.cpp:1331-1334
+    LTQ_REQUIRE(A_dev && B_dev && C_dev && qparams && workspace_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (M == 0 || N == 0) return LTQ_OK;
+    // l-ten/math_fns.cpp:1433-1434 asserts that K*zA*zB fits an int.
+    const uint64_t bc = K * (uint64_t)qparams[0].zero_point * (uint64_t)qparams[1].zero_point;
+    LTQ_REQUIRE(bc <= 0x7FFFFFFFull, LTQ_ERR_UNSUPPORTED, "K*zA*zB = %llu does not fit an int", (unsigned long long)bc);
+    LTQ_ENTER_DEVICE(device);
+    DeviceState *dev;
+    int rc = device_state(device, &dev);
+    if (rc != LTQ_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool tA = transpose_A != 0, tB = transpose_B != 0;
+    int32_t *bsum = workspace_dev, *asum = workspace_dev + N;
+    if (K == 0) {
+        LTQ_CUDA_TRY(cudaMemsetAsync(workspace_dev, 0, (M + N) * sizeof(int32_t), st));
+    } else {
+        // B is [N,K] when transposed (rows contiguous in K), [K,N] otherwise; A is [M,K] unless transposed ([K,M]).
+        if (tB) LTQ_CUDA_TRY(launch_row_sums(B_dev, N, K, bsum, st));
+        else LTQ_CUDA_TRY(launch_col_sums(B_dev, K, N, bsum, st));
+        if (!tA) LTQ_CUDA_TRY(launch_row_sums(A_dev, M, K, asum, st));
+        else LTQ_CUDA_TRY(launch_col_sums(A_dev, K, M, asum, st));
+    }
+    Epilogue epi = make_epilogue(bsum, asum, bias_dev, qparams[0], qparams[1], qparams[2], K, LTQ_OUT_U8, 0);
+    if (!tA && tB && K > 0) {
+        rc = run_fc_gemm(dev, M, N, K, A_dev, B_dev, epi, C_dev, 0, nullptr, st);
+        if (rc != LTQ_OK) return rc;
+    } else {
+        LTQ_CUDA_TRY(launch_gemm_simt(tA, tB, M, N, K, A_dev, B_dev, epi, C_dev, st));
+    }
+    // Leave the workspace as the reference does: sums already multiplied by the other operand's -zero_point.
+    LTQ_CUDA_TRY(launch_scale_i32(bsum, N, -(int32_t)qparams[0].zero_point, st));
+    LTQ_CUDA_TRY(launch_scale_i32(asum, M, -(int32_t)qparams[1].zero_point, st));
+    return LTQ_OK;
+}
+
+// ---- layer handle -----------------------------------------------------------------------------------------------------
+int ltq_layer_create(ltq_layer **layer, int device, uint64_t in_features, uint64_t out_features)
+{
+    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    *layer = nullptr;
+    LTQ_REQUIRE(in_features >= 1 && out_features >= 1, LTQ_ERR_INVALID_ARG, "feature counts must be >= 1");
+    LTQ_REQUIRE(in_features < (1ull << 31) && out_features < (1ull << 31), LTQ_ERR_TOO_LARGE,
+                "feature counts must be below 2^31");
+    LTQ_ENTER_DEVICE(device);
+    DeviceState *dev;
+    int rc = device_state(device, &dev);
+    if (rc != LTQ_OK) return rc;
+    ltq_layer *l = new (std::nothrow) ltq_layer;
+    LTQ_REQUIRE(l, LTQ_ERR_NO_MEMORY, "out of host memory");
+    l->device = device;
+    l->K = in_features;
+    l->N = out_features;
+    l->dev = dev;
+    cudaError_t e = cudaMalloc(&l->wsum, out_features * sizeof(int32_t));
+    if (e != cudaSuccess) {
+        delete l;
+        set_error("cudaMalloc of %llu weight sums failed: %s", (unsigned long long)out_features, cudaGetErrorString(e));
+        return LTQ_ERR_NO_MEMORY;
+    }
+    *layer = l;
+    return LTQ_OK;
+}
+
+int ltq_layer_destroy(ltq_layer *layer)
+{
+    if (!layer) return LTQ_OK;
+    LTQ_ENTER_DEVICE(layer->device);
+    cudaFree(layer->wsum);
+    cudaFree(layer->asum_ws);
+    delete layer;
+    return LTQ_OK;
+}
+
+int ltq_layer_set_weights(ltq_layer *layer, const uint8_t *w_dev, const int32_t *bias_dev, void *stream)
+{
+    LTQ_REQUIRE(layer && w_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_ENTER_DEVICE(layer->device);
+    layer->w = w_dev;
+    layer->bias = bias_dev;
+    for (auto &m : layer->map_w) m = TcOperandMap();
+    LTQ_CUDA_TRY(launch_row_sums(w_dev, layer->N, layer->K, layer->wsum, (cudaStream_t)stream));
+    LTQ_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    return LTQ_OK;
+}
+
+int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_qparams *qp_wt, const ltq_qparams *qp_out)
+{
+    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (qp_in) layer->qp_in = *qp_in;
+    if (qp_wt) layer->qp_wt = *qp_wt;
+    if (qp_out) layer->qp_out = *qp_out;
+    return LTQ_OK;
+}
+
+int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
+                      const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream)
+{
+    LTQ_REQUIRE(layer && x_dev && out_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE(layer->w, LTQ_ERR_INVALID_ARG, "ltq_layer_set_weights has not been called");
+    LTQ_REQUIRE(out_mode == LTQ_OUT_U8 || out_mode == LTQ_OUT_F32 || out_mode == LTQ_OUT_I32, LTQ_ERR_INVALID_ARG,
+                "unknown out_mode %d", out_mode);
+    LTQ_REQUIRE(M < (1ull << 31), LTQ_ERR_TOO_LARGE, "M must be below 2^31");
+    if (M == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(layer->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!asum_dev) {
+        if (M > layer->asum_cap) {
+            // Same policy as the reference's workspace: reallocate only when the batch grows.
+            int32_t *p = nullptr;
+            cudaError_t e = cudaMalloc(&p, M * sizeof(int32_t));
+            if (e != cudaSuccess) {
+                set_error("cudaMalloc of %llu activation sums failed: %s", (unsigned long long)M, cudaGetErrorString(e));
+                return LTQ_ERR_NO_MEMORY;
+            }
+            if (layer->asum_ws) {
+                LTQ_CUDA_TRY(cudaStreamSynchronize(st));
+                cudaFree(layer->asum_ws);
+            }
+            layer->asum_ws = p;
+            layer->asum_cap = M;
+        }
+        LTQ_CUDA_TRY(launch_row_sums(x_dev, M, layer->K, layer->asum_ws, st));
+        asum_dev = layer->asum_ws;
+    }
+    Epilogue epi = make_epilogue(layer->wsum, asum_dev, layer->bias, layer->qp_in, layer->qp_wt, layer->qp_out, layer->K,
+                                 out_mode, flags);
+    epi.qpA_dev = qp_in_dev;
+    return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi, out_dev, flags, layer, st);
+}
+
+int ltq_layer_check(ltq_layer *layer, void *stream)
+{
+    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_ENTER_DEVICE(layer->device);
+    uint32_t code = 0;
+    LTQ_CUDA_TRY(cudaMemcpyAsync(&code, layer->dev->status, sizeof code, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    LTQ_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    if (code) {
+        LTQ_CUDA_TRY(cudaMemsetAsync(layer->dev->status, 0, sizeof code, (cudaStream_t)stream));
+        set_error("a bounded device-side wait expired (code 0x%x: role %u, slot %u)", code, code >> 8, code & 0xFF);
+        return LTQ_ERR_DEVICE_TIMEOUT;
+    }
+    return LTQ_OK;
+}
+
+}  // extern "C"

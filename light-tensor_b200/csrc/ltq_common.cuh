@@ -1,0 +1,160 @@
+// Shared declarations for the ltq CUDA library: error plumbing, launch counting and the epilogue arithmetic that every
+// GEMM kernel applies to its raw uint8 x uint8 int32 dot products.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <atomic>
+
+#include "../../include/ltq.h"
+
+namespace ltq {
+
+// ---- host-side error state ---------------------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(uint64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+#define LTQ_CUDA_TRY(expr)                                                                                   \
+    do {                                                                                                     \
+        cudaError_t e__ = (expr);                                                                            \
+        if (e__ != cudaSuccess) {                                                                            \
+            ::ltq::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__);   \
+            return LTQ_ERR_CUDA;                                                                             \
+        }                                                                                                    \
+    } while (0)
+
+#define LTQ_REQUIRE(cond, status, ...)        \
+    do {                                      \
+        if (!(cond)) {                        \
+            ::ltq::set_error(__VA_ARGS__);    \
+            return (status);                  \
+        }                                     \
+    } while (0)
+
+// Makes `device` current for the lifetime of the guard and restores the caller's device afterwards (l-ten itself never
+// calls cudaSetDevice, so the caller's current device must not move under it).
+struct DeviceGuard {
+    int prev = -1;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int device)
+    {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) err = cudaSetDevice(device);
+    }
+    ~DeviceGuard()
+    {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+#define LTQ_ENTER_DEVICE(device)                                                                             \
+    ::ltq::DeviceGuard guard__(device);                                                                      \
+    if (guard__.err != cudaSuccess) {                                                                        \
+        ::ltq::set_error("cannot select CUDA device %d: %s", (device), cudaGetErrorString(guard__.err));     \
+        return LTQ_ERR_CUDA;                                                                                 \
+    }
+
+// ---- epilogue ------------------------------------------------------------------------------------------------------
+// Everything a kernel needs to turn raw = sum_k A[i,k]*B[j,k] into an output element.
+//   acc = raw - zA*bsum[j] - zB*asum[i] + K*zA*zB (+ bias[j])            l-ten/math_fns.cpp:1433-1473
+// in wrapping 32-bit arithmetic (the reference's int additions wrap the same way on its x86 build).
+struct Epilogue {
+    const int32_t *bsum;          // [N] raw sums over K of the B operand (weights for the FC layer)
+    const int32_t *asum;          // [M] raw sums over K of the A operand (activations)
+    const int32_t *bias;          // [N] or nullptr
+    const ltq_qparams *qpA_dev;   // optional device-resident override of (sA, zA)
+    float sA, sB, sC;
+    int32_t zA, zB, zC;
+    uint32_t K;
+    int out_mode;                 // ltq_out_mode
+    unsigned flags;               // LTQ_FLAG_RELU | LTQ_FLAG_SATURATE
+};
+
+// Per-launch constants derived once per thread.
+struct EpilogueConsts {
+    uint32_t neg_zA, neg_zB, bc;  // -zA, -zB, K*zA*zB (mod 2^32)
+    float rm, sAB, zCf;
+};
+
+__device__ __forceinline__ EpilogueConsts epilogue_consts(const Epilogue &e)
+{
+    float sA = e.sA;
+    int32_t zA = e.zA;
+    if (e.qpA_dev) {
+        sA = e.qpA_dev->scale;
+        zA = e.qpA_dev->zero_point;
+    }
+    EpilogueConsts c;
+    c.neg_zA = (uint32_t)(-zA);
+    c.neg_zB = (uint32_t)(-e.zB);
+    c.bc = e.K * (uint32_t)zA * (uint32_t)e.zB;
+    c.sAB = __fmul_rn(sA, e.sB);
+    c.rm = __fdiv_rn(c.sAB, e.sC);  // l-ten/math_fns.cpp:1436: float, left to right
+    c.zCf = (float)e.zC;
+    return c;
+}
+
+// Row part of the correction: -zB*asum[i] + K*zA*zB.
+__device__ __forceinline__ uint32_t epilogue_row_term(const Epilogue &e, const EpilogueConsts &c, uint64_t i)
+{
+    return c.neg_zB * (uint32_t)e.asum[i] + c.bc;
+}
+// Column part: -zA*bsum[j] (+ bias[j]).
+__device__ __forceinline__ uint32_t epilogue_col_term(const Epilogue &e, const EpilogueConsts &c, uint64_t j)
+{
+    uint32_t t = c.neg_zA * (uint32_t)e.bsum[j];
+    if (e.bias) t += (uint32_t)e.bias[j];
+    return t;
+}
+
+__device__ __forceinline__ int32_t epilogue_acc(uint32_t raw, uint32_t row_term, uint32_t col_term, bool relu)
+{
+    int32_t acc = (int32_t)(raw + row_term + col_term);
+    if (relu && acc < 0) acc = 0;
+    return acc;
+}
+
+// (unsigned char)(rm*acc + zC), l-ten/math_fns.cpp:1474: int->float rounds to nearest, multiply and add are separate
+// roundings (the reference is built without FMA), the cast truncates toward zero.  Out of range the reference's x86
+// code converts to int32 and keeps the low byte (and yields 0 once |t| >= 2^31); `saturate` clamps instead.
+__device__ __forceinline__ uint8_t epilogue_u8(int32_t acc, const EpilogueConsts &c, bool saturate)
+{
+    float t = __fadd_rn(__fmul_rn(c.rm, __int2float_rn(acc)), c.zCf);
+    if (saturate) {
+        if (!(t > 0.f)) return 0;
+        if (t >= 255.f) return 255;
+        return (uint8_t)__float2int_rz(t);
+    }
+    if (!(t > -2147483648.f && t < 2147483648.f)) return 0;
+    return (uint8_t)(__float2int_rz(t) & 0xFF);
+}
+
+__device__ __forceinline__ float epilogue_f32(int32_t acc, const EpilogueConsts &c)
+{
+    return __fmul_rn(c.sAB, __int2float_rn(acc));
+}
+
+// ---- kernel launchers implemented in the other translation units --------------------------------------------------
+// Generic dp4a tile kernel: any M, N, K and any transpose combination.
+cudaError_t launch_gemm_simt(bool tA, bool tB, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
+                             const Epilogue &epi, void *out, cudaStream_t stream);
+
+// Operand sums. rows x cols uint8, contiguous along cols: sums[r] = sum_c m[r*cols + c].
+cudaError_t launch_row_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream);
+// Same matrix read the other way: sums[c] = sum_r m[r*cols + c].
+cudaError_t launch_col_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream);
+// v[i] *= factor (wrapping), used to leave the reference's pre-multiplied workspace behind.
+cudaError_t launch_scale_i32(int32_t *v, uint64_t n, int32_t factor, cudaStream_t stream);
+
+cudaError_t launch_min_max(const float *data, uint64_t len, float *minmax, cudaStream_t stream);
+cudaError_t launch_qparams_from_minmax(const float *minmax, ltq_qparams *qp, cudaStream_t stream);
+cudaError_t launch_quantize_u8(const float *x, uint8_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream);
+cudaError_t launch_quantize_i32(const float *x, int32_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream);
+cudaError_t launch_dequantize(float *x, const uint8_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream);
+cudaError_t launch_quantize_rows(const float *x, uint64_t M, uint64_t K, const ltq_qparams *qp_host,
+                                 const ltq_qparams *qp_dev, uint8_t *q, int32_t *asum, cudaStream_t stream);
+
+}  // namespace ltq

@@ -1,0 +1,108 @@
+// Generic uint8 x uint8 -> int32 GEMM on CUDA cores (dp4a) with the full fused epilogue.
+//
+// This is the kernel for shapes the tensor-core kernel does not take: operands whose K stride is not 16-byte aligned
+// and the transposed layouts of quantized_matmul (l-ten/math_fns.cpp:1336-1467) that only Conv2d_q-style callers use.
+// It also serves as the on-device cross-check of the tcgen05 kernel at sizes the CPU oracle cannot reach.
+//
+// 64x64 output tile per 256-thread CTA, 32-deep K slices staged in shared memory as packed 4-byte K groups, each
+// thread owning a 4x4 register tile (16 dp4a per 8 shared loads).
+#include "ltq_common.cuh"
+
+namespace ltq {
+
+constexpr int TM = 64, TN = 64, TK = 32;
+constexpr int LDW = TK / 4 + 1;  // words per staged row, +1 to stagger banks
+
+// Element (r, k) of an operand stored either k-contiguous ([rows, K]) or r-contiguous ([K, rows]).
+__device__ __forceinline__ uint8_t fetch(const uint8_t *__restrict__ p, bool k_contig, uint64_t rows, uint64_t K,
+                                         uint64_t r, uint64_t k)
+{
+    if (r >= rows || k >= K) return 0;
+    return k_contig ? p[r * K + k] : p[k * rows + r];
+}
+
+__device__ __forceinline__ void stage(uint32_t (*dst)[LDW], const uint8_t *__restrict__ p, bool k_contig,
+                                      uint64_t rows, uint64_t K, uint64_t r0, uint64_t k0)
+{
+    uint8_t *d = reinterpret_cast<uint8_t *>(dst);
+    for (int e = threadIdx.x; e < TM * TK; e += 256) {
+        // Walk memory in its contiguous direction so that neighbouring threads touch neighbouring bytes.
+        int r, k;
+        if (k_contig) {
+            r = e / TK;
+            k = e % TK;
+        } else {
+            k = e / TM;
+            r = e % TM;
+        }
+        d[r * (LDW * 4) + k] = fetch(p, k_contig, rows, K, r0 + r, k0 + k);
+    }
+}
+
+__global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, uint64_t M, uint64_t N, uint64_t K,
+                                                        const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
+                                                        Epilogue epi, void *__restrict__ out)
+{
+    __shared__ uint32_t As[TM][LDW];
+    __shared__ uint32_t Bs[TN][LDW];
+    const uint64_t m0 = (uint64_t)blockIdx.x * TM, n0 = (uint64_t)blockIdx.y * TN;
+    const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+
+    int32_t acc[4][4] = {};
+    for (uint64_t k0 = 0; k0 < K; k0 += TK) {
+        stage(As, A, a_kc, M, K, m0, k0);
+        stage(Bs, B, b_kc, N, K, n0, k0);
+        __syncthreads();
+#pragma unroll
+        for (int kw = 0; kw < TK / 4; kw++) {
+            uint32_t a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[ty + 16 * i][kw];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Bs[tx + 16 * j][kw];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = (int32_t)__dp4a(a[i], b[j], (uint32_t)acc[i][j]);
+        }
+        __syncthreads();
+    }
+
+    const EpilogueConsts c = epilogue_consts(epi);
+    const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint64_t row = m0 + ty + 16 * i;
+        if (row >= M) continue;
+        const uint32_t rt = epilogue_row_term(epi, c, row);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint64_t col = n0 + tx + 16 * j;
+            if (col >= N) continue;
+            const int32_t v = epilogue_acc((uint32_t)acc[i][j], rt, epilogue_col_term(epi, c, col), relu);
+            const uint64_t o = row * N + col;
+            if (epi.out_mode == LTQ_OUT_U8)
+                static_cast<uint8_t *>(out)[o] = epilogue_u8(v, c, sat);
+            else if (epi.out_mode == LTQ_OUT_F32)
+                static_cast<float *>(out)[o] = epilogue_f32(v, c);
+            else
+                static_cast<int32_t *>(out)[o] = v;
+        }
+    }
+}
+
+cudaError_t launch_gemm_simt(bool tA, bool tB, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
+                             const Epilogue &epi, void *out, cudaStream_t stream)
+{
+    if (M == 0 || N == 0) return cudaSuccess;
+    // quantized_matmul's layouts: A is [M,K] unless transposed ([K,M]); B is [K,N] unless transposed ([N,K]).
+    const bool a_kc = !tA, b_kc = tB;
+    const uint64_t gx = (M + TM - 1) / TM, gy = (N + TN - 1) / TN;
+    if (gy > 65535 || gx > 0x7FFFFFFFull) return cudaErrorInvalidConfiguration;
+    dim3 grid((unsigned)gx, (unsigned)gy);
+    gemm_simt_kernel<<<grid, 256, 0, stream>>>(a_kc, b_kc, M, N, K, A, B, epi, out);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace ltq

@@ -1,0 +1,486 @@
+// uint8 x uint8 -> int32 GEMM on the 5th-generation tensor cores (tcgen05, kind::i8) for sm_100a, with the fused
+// zero-point / bias / ReLU / dequantise / requantise epilogue of l-ten's quantized_matmul
+// (l-ten/math_fns.cpp:1433-1474).  FullyConnected_q's layout only: A = activations [M,K], B = weights [N,K], both
+// K-contiguous (transpose_A = false, transpose_B = true in l-ten/fully_connected.cpp:389-393).
+//
+// One persistent CTA per SM, 192 threads, three roles:
+//   warp 0      TMA producer  : cp.async.bulk.tensor.2d (no multicast) -> 128B-swizzled smem ring, mbarrier tx counts
+//   warp 1      MMA issuer    : one thread issues tcgen05.mma.cta_group::1.kind::i8 (128 x BN x 32), u8 x u8 -> s32,
+//                               accumulators in TMEM, double buffered (2 x BN columns) so the epilogue of tile t overlaps
+//                               the main loop of tile t+1; tcgen05.commit releases smem stages / publishes accumulators
+//   warps 2..5  epilogue      : tcgen05.ld 32 lanes x 32 columns at a time, correction terms, conversion, 16-byte stores
+//
+// Every wait on an mbarrier is bounded (wall-clock limit read from %globaltimer): on expiry the kernel records a code
+// in a device status word, stops issuing work, drains and frees its TMEM, and returns.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "ltq_common.cuh"
+#include "ltq_gemm_tc.cuh"
+
+namespace ltq {
+
+namespace {
+
+constexpr int BM = 128;          // UMMA M (TMEM lanes)
+constexpr int BK = 128;          // bytes (= elements) of K per smem stage: one 128-byte swizzle atom wide
+constexpr int UMMA_K = 32;       // kind::i8
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
+
+template <int BN>
+struct Cfg {
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // power of two >= 32
+    // ring + 1024 B alignment slack + column terms (2 x BN x 4) + barriers
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 2 * BN * 4 + 256;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false after WAIT_LIMIT_NS, or at once when another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                          uint32_t *status, uint32_t code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0u, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], u8 x u8 -> s32.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread = lane, register = column).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major operand tile laid out by TMA with the 128-byte swizzle: rows of 128
+// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell), layout type 2
+// (SWIZZLE_128B).  The tile base is 1024-byte aligned, so base_offset is 0; stepping K by 32 bytes inside the atom is a
+// plain +2 on the (address >> 4) field.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // bits [0,14)
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
+    d |= (uint64_t)1 << 46;                               // version
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::i8: D = S32 (2 at bit 4), A = B = unsigned 8-bit (0 at bits 7 and 10), both K-major
+// (0 at bits 15, 16), no saturation (bit 3 clear: wrapping like the reference), N >> 3 at bit 17, M >> 4 at bit 24.
+template <int BN>
+__device__ __forceinline__ constexpr uint32_t make_idesc()
+{
+    return (2u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+}  // namespace
+
+// OUT: 0 = uint8, 1 = float, 2 = int32 (ltq_out_mode).
+template <int BN, int OUT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
+               uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
+{
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // 128B-swizzled tiles need a 1024-byte aligned base.
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;
+    uint8_t *after = smem_raw + (ring - raw) + C::STAGES * C::STAGE_BYTES;
+    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                 // [2][BN] column terms
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * BN * 4);     // full[S] empty[S] tfull[2] tempty[2]
+    uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * C::STAGES + 4);  // [0] tmem base, [1] abort flag
+    volatile uint32_t *abort_flag = s_misc + 1;
+
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * C::STAGES;
+    const uint32_t tfull0 = empty0 + 8 * C::STAGES, tempty0 = tfull0 + 16;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tempty0 + 8 * s, 4);  // one arrival per epilogue warp
+        }
+        s_misc[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(s_misc), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_misc[0];
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                const int32_t m0 = (int32_t)((t / tiles_n) * BM), n0 = (int32_t)((t % tiles_n) * BN);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
+                    if (!ok) break;
+                    const uint32_t a_dst = ring + st * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
+                    mbar_expect_tx(full0 + 8 * st, C::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, full0 + 8 * st, (int32_t)(kb * BK), m0);
+                    tma_load_2d(b_dst, &map_b, full0 + 8 * st, (int32_t)(kb * BK), n0);
+                    if (++st == C::STAGES) { st = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc<BN>();
+            uint32_t st = 0, ph = 0, as = 0, aph = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                ok = mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    ok = mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_src = ring + st * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
+                    const uint64_t a_desc = make_smem_desc(a_src), b_desc = make_smem_desc(b_src);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // +32 bytes of K per step: +2 in the descriptor's 16-byte address units
+                        umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | (uint32_t)k) != 0u);
+                    }
+                    umma_commit(empty0 + 8 * st);  // frees the smem stage once these MMAs have read it
+                    if (++st == C::STAGES) { st = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(tfull0 + 8 * as);  // accumulator complete
+                if (++as == 2) { as = 0; aph ^= 1; }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 = 128 threads) ----------------
+        const uint32_t q = (uint32_t)warp & 3u;       // TMEM lane quarter this warp may read
+        const uint32_t et = threadIdx.x - 64;         // 0..127
+        const EpilogueConsts c = epilogue_consts(epi);
+        const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
+        using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
+        OutT *o = static_cast<OutT *>(out);
+        // 16-byte stores need every row start aligned: row pitch and base both multiples of 16 bytes.
+        const bool vec_ok = (((uint64_t)N * sizeof(OutT)) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+        uint32_t as = 0, aph = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const uint32_t m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+            // column terms of this tile -> smem (shared by all 128 rows)
+            uint32_t *col = s_col + as * BN;
+            for (uint32_t j = et; j < (uint32_t)BN; j += 128) {
+                const uint32_t gj = n0 + j;
+                col[j] = gj < N ? epilogue_col_term(epi, c, gj) : 0u;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const uint32_t row = m0 + q * 32 + lane;
+            const uint32_t rt = row < M ? epilogue_row_term(epi, c, row) : 0u;
+
+            if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * BN;
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ch++) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    const uint32_t c0 = n0 + ch * 32;
+                    if (row < M && c0 < N) {
+                        OutT *dst = o + (uint64_t)row * N + c0;
+                        const int valid = (N - c0) < 32u ? (int)(N - c0) : 32;
+                        if (OUT == 0) {
+                            uint32_t p[8];
+#pragma unroll
+                            for (int g = 0; g < 8; g++) {
+                                uint32_t w = 0;
+#pragma unroll
+                                for (int b = 0; b < 4; b++) {
+                                    const int j = g * 4 + b;
+                                    const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
+                                    w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
+                                }
+                                p[g] = w;
+                            }
+                            if (vec_ok && valid == 32) {
+                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+                                d4[0] = make_uint4(p[0], p[1], p[2], p[3]);
+                                d4[1] = make_uint4(p[4], p[5], p[6], p[7]);
+                            } else {
+                                for (int j = 0; j < valid; j++)
+                                    reinterpret_cast<uint8_t *>(dst)[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
+                                v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
+                            }
+                            if (vec_ok && valid == 32) {
+                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                                for (int g = 0; g < 8; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (j < valid) reinterpret_cast<uint32_t *>(dst)[j] = v[j];
+                            }
+                        }
+                    }
+                }
+                // all of this warp's reads of the accumulator are done -> hand the buffer back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * as);
+            }
+            if (++as == 2) { as = 0; aph ^= 1; }
+        }
+    }
+
+    // Teardown: nobody leaves before every role is done with TMEM and shared memory.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0 && lane == 0 && *abort_flag) {
+        // After a timeout bulk copies issued by this thread may still be in flight towards this CTA's shared memory.
+        // They complete within microseconds of being issued; hold the CTA for a bounded 2 ms before it exits.
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+template <int BN, int OUT>
+cudaError_t launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
+                       const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+{
+    using C = Cfg<BN>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    const uint64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
+    gemm_tc_kernel<BN, OUT><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, (uint32_t)M, (uint32_t)N,
+                                                                          (uint32_t)K, epi, out, status);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <int BN>
+cudaError_t launch_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
+                       const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+{
+    switch (epi.out_mode) {
+        case LTQ_OUT_U8: return launch_cfg<BN, 0>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case LTQ_OUT_F32: return launch_cfg<BN, 1>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        default: return launch_cfg<BN, 2>(ma, mb, M, N, K, epi, out, status, sms, stream);
+    }
+}
+
+}  // namespace
+
+bool tc_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B)
+{
+    return M >= 1 && N >= 1 && K >= 16 && (K % 16 == 0) && M < (1ull << 31) && N < (1ull << 31) &&
+           K < (1ull << 31) && (((uintptr_t)A & 15) == 0) && (((uintptr_t)B & 15) == 0) && encode_fn() != nullptr;
+}
+
+int tc_pick_bn(uint64_t M, uint64_t N, int sms)
+{
+    // Widest tile that still gives every SM a tile; problems too small for that get narrower tiles (more CTAs).
+    const uint64_t tm = (M + BM - 1) / BM, s = (uint64_t)sms;
+    if (tm * ((N + 255) / 256) >= s) return 256;
+    if (tm * ((N + 127) / 128) >= s) return 128;
+    if (N <= 64) return 64;
+    return tm * ((N + 127) / 128) >= s / 2 ? 128 : 64;
+}
+
+int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(m->opaque), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                    const_cast<uint8_t *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)r;
+    m->base = base;
+    m->rows = rows;
+    m->K = K;
+    m->box_rows = box_rows;
+    return 0;
+}
+
+cudaError_t launch_gemm_tc(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
+                           uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+{
+    const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(map_a.opaque);
+    const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(map_b.opaque);
+    switch (bn) {
+        case 256: return launch_out<256>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case 128: return launch_out<128>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case 64: return launch_out<64>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace ltq

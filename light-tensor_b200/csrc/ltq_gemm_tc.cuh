@@ -1,0 +1,32 @@
+// Host-visible interface of the tcgen05 GEMM (ltq_gemm_tc.cu), kept free of <cuda.h> so the API layer can hold tensor
+// maps inside its layer handle without seeing driver types.
+#pragma once
+#include "ltq_common.cuh"
+
+namespace ltq {
+
+// A TMA tensor map (CUtensorMap is 128 bytes, 64-byte aligned) over a K-contiguous uint8 matrix [rows, K], tiled in
+// boxes of box_rows x 128 bytes with the 128-byte swizzle, plus the facts it was built from so a cached map can be
+// checked against the next call.
+struct TcOperandMap {
+    alignas(64) unsigned char opaque[128];
+    const void *base = nullptr;
+    uint64_t rows = 0, K = 0;
+    int box_rows = 0;
+    bool matches(const void *b, uint64_t r, uint64_t k, int br) const
+    {
+        return base == b && rows == r && K == k && box_rows == br;
+    }
+};
+
+// True when the tensor-core kernel can take the problem: K a multiple of 16 (TMA row pitch), 16-byte aligned bases,
+// extents below 2^31, and the driver exports cuTensorMapEncodeTiled.
+bool tc_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B);
+// Output-tile width (64, 128 or 256 columns) for a problem on a device with `sms` SMs.
+int tc_pick_bn(uint64_t M, uint64_t N, int sms);
+// Encodes a map; box_rows is 128 for the A operand and the tile width for the B operand. 0 on success.
+int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows);
+cudaError_t launch_gemm_tc(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
+                           uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream);
+
+}  // namespace ltq

@@ -1,0 +1,373 @@
+// Quantisation helpers on the device: min/max, qparams, float->uint8 / int32, uint8->float, and the operand sums the
+// GEMM epilogue folds in.  All of them are single-pass, HBM-bound streaming kernels: 16-byte loads, grids sized in
+// multiples of the SM count, no shared-memory staging needed.
+//
+// Arithmetic follows l-ten/utils.cpp:198-286 operation for operation (IEEE divide, separate add, clamp, round half away
+// from zero); the file is compiled with -fmad=false so nothing is contracted.
+#include "ltq_common.cuh"
+
+namespace ltq {
+
+static int sm_count()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// ---- min / max ------------------------------------------------------------------------------------------------------
+// Order-preserving map float -> uint32 so that atomicMin/atomicMax on integers order floats.
+__device__ __forceinline__ uint32_t f2ord(float f)
+{
+    uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float ord2f(uint32_t u)
+{
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+}
+
+// slot[0] = min over ord(x); slot[1] = min over ~ord(x) (i.e. the max, complemented) so both start from 0xFFFFFFFF and a
+// single byte-fill initialises them.
+__global__ void __launch_bounds__(256) minmax_reduce_kernel(const float *__restrict__ x, uint64_t len, uint32_t *slot)
+{
+    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    // 16-byte body when the base pointer allows it, scalar head/tail otherwise.
+    const uint64_t mis = ((16 - ((uintptr_t)x & 15)) & 15) / 4;
+    const uint64_t head = mis < len ? mis : len;
+    const uint64_t nvec = (len - head) / 4;
+    const float4 *xv = reinterpret_cast<const float4 *>(x + head);
+    auto upd = [&](float v) {
+        if (v == v) {  // comparisons with NaN are false in the reference, so NaNs never replace min/max
+            uint32_t o = f2ord(v);
+            lo = o < lo ? o : lo;
+            hi = o > hi ? o : hi;
+        }
+    };
+    for (uint64_t i = tid; i < nvec; i += nth) {
+        float4 v = __ldg(xv + i);
+        upd(v.x); upd(v.y); upd(v.z); upd(v.w);
+    }
+    for (uint64_t i = tid; i < head; i += nth) upd(x[i]);
+    for (uint64_t i = head + nvec * 4 + tid; i < len; i += nth) upd(x[i]);
+
+    for (int o = 16; o; o >>= 1) {
+        lo = min(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, o));
+        hi = max(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, o));
+    }
+    __shared__ uint32_t slo[8], shi[8];
+    if ((threadIdx.x & 31) == 0) {
+        slo[threadIdx.x >> 5] = lo;
+        shi[threadIdx.x >> 5] = hi;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        lo = slo[threadIdx.x];
+        hi = shi[threadIdx.x];
+        for (int o = 4; o; o >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xFFu, lo, o));
+            hi = max(hi, __shfl_xor_sync(0xFFu, hi, o));
+        }
+        if (threadIdx.x == 0) {
+            if (lo != 0xFFFFFFFFu) atomicMin(slot, lo);
+            if (hi != 0u) atomicMin(slot + 1, ~hi);
+        }
+    }
+}
+
+// Decodes the two slots in place into floats {min, max}.  An input with no comparable element (all NaN) keeps the
+// reference's seed, data[0].
+__global__ void minmax_decode_kernel(uint32_t *slot, const float *x)
+{
+    uint32_t a = slot[0], b = slot[1];
+    float mn = (a == 0xFFFFFFFFu) ? x[0] : ord2f(a);
+    float mx = (b == 0xFFFFFFFFu) ? x[0] : ord2f(~b);
+    reinterpret_cast<float *>(slot)[0] = mn;
+    reinterpret_cast<float *>(slot)[1] = mx;
+}
+
+cudaError_t launch_min_max(const float *data, uint64_t len, float *minmax, cudaStream_t stream)
+{
+    cudaError_t e = cudaMemsetAsync(minmax, 0xFF, 8, stream);
+    if (e != cudaSuccess) return e;
+    uint64_t want = (len / 4 + 255) / 256;
+    uint64_t cap = (uint64_t)sm_count() * 8;
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    minmax_reduce_kernel<<<blocks, 256, 0, stream>>>(data, len, reinterpret_cast<uint32_t *>(minmax));
+    minmax_decode_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<uint32_t *>(minmax), data);
+    count_launch(2);
+    return cudaGetLastError();
+}
+
+// ---- qparams from min/max, l-ten/utils.cpp:266-286 -------------------------------------------------------------
+__global__ void qparams_kernel(const float *minmax, ltq_qparams *qp)
+{
+    float mn = fminf(minmax[0], 0.f);
+    float mx = fmaxf(minmax[1], 0.f);
+    float scale = __fdiv_rn(__fsub_rn(mx, mn), 255.f);
+    float zp = __fsub_rn(0.f, __fdiv_rn(mn, scale));
+    qp->scale = scale;
+    // An all-zero tensor gives scale 0 and zp NaN in the reference (undefined cast); 0 is written here.
+    qp->zero_point = (zp == zp) ? (uint8_t)(int)roundf(zp) : (uint8_t)0;
+}
+
+cudaError_t launch_qparams_from_minmax(const float *minmax, ltq_qparams *qp, cudaStream_t stream)
+{
+    qparams_kernel<<<1, 1, 0, stream>>>(minmax, qp);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---- Quantize / Dequantize, l-ten/utils.cpp:228-264 -------------------------------------------------------------
+__device__ __forceinline__ uint32_t quant_u8(float x, float scale, float zpf)
+{
+    float v = __fadd_rn(zpf, __fdiv_rn(x, scale));
+    v = fmaxf(0.f, fminf(255.f, v));
+    return (uint32_t)(int)roundf(v);
+}
+
+__device__ __forceinline__ int32_t quant_i32(float x, float scale, float zpf)
+{
+    float v = __fadd_rn(zpf, __fdiv_rn(x, scale));
+    // std::max((float)INT_MIN, std::min((float)INT_MAX, v)); (float)INT_MAX == 2^31.
+    float t = (v < 2147483648.f) ? v : 2147483648.f;
+    t = (-2147483648.f < t) ? t : -2147483648.f;
+    float r = roundf(t);
+    // (int)2^31 is out of range for the reference's conversion, which then yields INT_MIN on x86; NaN likewise.
+    if (!(r < 2147483648.f)) return INT32_MIN;
+    return (int32_t)r;
+}
+
+__global__ void __launch_bounds__(256) quantize_u8_kernel(const float *__restrict__ x, uint8_t *__restrict__ q,
+                                                          uint64_t len, float scale, float zpf)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    const bool aligned = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
+    uint64_t nvec = aligned ? len / 4 : 0;
+    for (uint64_t i = tid; i < nvec; i += nth) {
+        float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+        uint32_t p = quant_u8(v.x, scale, zpf) | (quant_u8(v.y, scale, zpf) << 8) | (quant_u8(v.z, scale, zpf) << 16) |
+                     (quant_u8(v.w, scale, zpf) << 24);
+        reinterpret_cast<uint32_t *>(q)[i] = p;
+    }
+    for (uint64_t i = nvec * 4 + tid; i < len; i += nth) q[i] = (uint8_t)quant_u8(x[i], scale, zpf);
+}
+
+__global__ void __launch_bounds__(256) quantize_i32_kernel(const float *__restrict__ x, int32_t *__restrict__ q,
+                                                           uint64_t len, float scale, float zpf)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = tid; i < len; i += nth) q[i] = quant_i32(x[i], scale, zpf);
+}
+
+__global__ void __launch_bounds__(256) dequantize_kernel(float *__restrict__ x, const uint8_t *__restrict__ q,
+                                                         uint64_t len, float scale, int zp)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    const bool aligned = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
+    uint64_t nvec = aligned ? len / 4 : 0;
+    for (uint64_t i = tid; i < nvec; i += nth) {
+        uint32_t p = __ldg(reinterpret_cast<const uint32_t *>(q) + i);
+        float4 v;
+        v.x = __fmul_rn(scale, (float)((int)(p & 0xFF) - zp));
+        v.y = __fmul_rn(scale, (float)((int)((p >> 8) & 0xFF) - zp));
+        v.z = __fmul_rn(scale, (float)((int)((p >> 16) & 0xFF) - zp));
+        v.w = __fmul_rn(scale, (float)((int)(p >> 24) - zp));
+        reinterpret_cast<float4 *>(x)[i] = v;
+    }
+    for (uint64_t i = nvec * 4 + tid; i < len; i += nth) x[i] = __fmul_rn(scale, (float)((int)q[i] - zp));
+}
+
+static int stream_grid(uint64_t work_items)
+{
+    uint64_t want = (work_items + 255) / 256;
+    uint64_t cap = (uint64_t)sm_count() * 8;
+    return (int)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+cudaError_t launch_quantize_u8(const float *x, uint8_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream)
+{
+    quantize_u8_kernel<<<stream_grid(len / 4 + 1), 256, 0, stream>>>(x, q, len, qp.scale, (float)(int)qp.zero_point);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_quantize_i32(const float *x, int32_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream)
+{
+    quantize_i32_kernel<<<stream_grid(len), 256, 0, stream>>>(x, q, len, qp.scale, (float)(int)qp.zero_point);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize(float *x, const uint8_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream)
+{
+    dequantize_kernel<<<stream_grid(len / 4 + 1), 256, 0, stream>>>(x, q, len, qp.scale, (int)qp.zero_point);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---- activation quantise + row sums -------------------------------------------------------------------------------
+// TPR threads cooperate on one row (TPR = 32: a warp; TPR = 256: the whole CTA).  Reads fp32 once, writes uint8 once
+// and one int32 per row: 5 bytes per element of HBM traffic, the minimum for this step.
+template <int TPR>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float *__restrict__ x, uint64_t M, uint64_t K,
+                                                            float scale_h, float zpf_h,
+                                                            const ltq_qparams *__restrict__ qp_dev,
+                                                            uint8_t *__restrict__ q, int32_t *__restrict__ asum)
+{
+    float scale = scale_h, zpf = zpf_h;
+    if (qp_dev) {
+        scale = qp_dev->scale;
+        zpf = (float)(int)qp_dev->zero_point;
+    }
+    constexpr int ROWS_PER_CTA = 256 / TPR;
+    const int lane = threadIdx.x % TPR;
+    const int sub = threadIdx.x / TPR;
+    __shared__ int32_t warp_part[8];
+    for (uint64_t row = (uint64_t)blockIdx.x * ROWS_PER_CTA + sub; ; row += (uint64_t)gridDim.x * ROWS_PER_CTA) {
+        // All threads of a CTA leave together when TPR == 256 (row is uniform); with TPR == 32 a warp leaves alone.
+        if (row >= M) break;
+        const float *xr = x + row * K;
+        uint8_t *qr = q + row * K;
+        const bool aligned = (((uintptr_t)xr & 15) == 0) && (((uintptr_t)qr & 3) == 0);
+        const uint64_t nvec = aligned ? K / 4 : 0;
+        int32_t s = 0;
+        for (uint64_t i = lane; i < nvec; i += TPR) {
+            float4 v = __ldg(reinterpret_cast<const float4 *>(xr) + i);
+            uint32_t a = quant_u8(v.x, scale, zpf), b = quant_u8(v.y, scale, zpf), c = quant_u8(v.z, scale, zpf),
+                     d = quant_u8(v.w, scale, zpf);
+            s += (int32_t)(a + b + c + d);
+            reinterpret_cast<uint32_t *>(qr)[i] = a | (b << 8) | (c << 16) | (d << 24);
+        }
+        for (uint64_t i = nvec * 4 + lane; i < K; i += TPR) {
+            uint32_t a = quant_u8(xr[i], scale, zpf);
+            s += (int32_t)a;
+            qr[i] = (uint8_t)a;
+        }
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        if (TPR == 32) {
+            if (lane == 0) asum[row] = s;
+        } else {
+            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = s;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int32_t t = 0;
+                for (int w = 0; w < 8; w++) t += warp_part[w];
+                asum[row] = t;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+cudaError_t launch_quantize_rows(const float *x, uint64_t M, uint64_t K, const ltq_qparams *qp_host,
+                                 const ltq_qparams *qp_dev, uint8_t *q, int32_t *asum, cudaStream_t stream)
+{
+    float scale = qp_host ? qp_host->scale : 0.f;
+    float zpf = qp_host ? (float)(int)qp_host->zero_point : 0.f;
+    const uint64_t cap = (uint64_t)sm_count() * 8;
+    if (K <= 2048) {
+        uint64_t want = (M + 7) / 8;
+        int blocks = (int)(want > cap ? cap : want);
+        quantize_rows_kernel<32><<<blocks, 256, 0, stream>>>(x, M, K, scale, zpf, qp_dev, q, asum);
+    } else {
+        int blocks = (int)(M > cap ? cap : M);
+        quantize_rows_kernel<256><<<blocks, 256, 0, stream>>>(x, M, K, scale, zpf, qp_dev, q, asum);
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---- operand sums ---------------------------------------------------------------------------------------------------
+// One warp per row, 16-byte loads, bytes summed four at a time with dp4a against 0x01010101.
+__global__ void __launch_bounds__(256) row_sums_kernel(const uint8_t *__restrict__ m, uint64_t rows, uint64_t cols,
+                                                       int32_t *__restrict__ sums)
+{
+    const int lane = threadIdx.x & 31;
+    const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+    for (uint64_t r = warp; r < rows; r += nwarps) {
+        const uint8_t *p = m + r * cols;
+        const uint64_t mis = (16 - ((uintptr_t)p & 15)) & 15;
+        const uint64_t head = mis < cols ? mis : cols;
+        const uint64_t nvec = (cols - head) / 16;
+        const uint4 *pv = reinterpret_cast<const uint4 *>(p + head);
+        uint32_t s = 0;
+        for (uint64_t i = lane; i < nvec; i += 32) {
+            uint4 v = __ldg(pv + i);
+            s = __dp4a(v.x, 0x01010101u, s);
+            s = __dp4a(v.y, 0x01010101u, s);
+            s = __dp4a(v.z, 0x01010101u, s);
+            s = __dp4a(v.w, 0x01010101u, s);
+        }
+        for (uint64_t i = lane; i < head; i += 32) s += p[i];
+        for (uint64_t i = head + nvec * 16 + lane; i < cols; i += 32) s += p[i];
+        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        if (lane == 0) sums[r] = (int32_t)s;
+    }
+}
+
+// Sums down the columns of a row-major matrix: thread per column, coalesced across threads, rows split over
+// blockIdx.y with an atomic combine (sums must be zeroed first).
+__global__ void __launch_bounds__(256) col_sums_kernel(const uint8_t *__restrict__ m, uint64_t rows, uint64_t cols,
+                                                       int32_t *__restrict__ sums)
+{
+    const uint64_t c = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    int32_t s = 0;
+    for (uint64_t r = blockIdx.y; r < rows; r += gridDim.y) s += m[r * cols + c];
+    atomicAdd(sums + c, s);
+}
+
+__global__ void __launch_bounds__(256) scale_i32_kernel(int32_t *v, uint64_t n, int32_t factor)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = tid; i < n; i += nth) v[i] = (int32_t)((uint32_t)v[i] * (uint32_t)factor);
+}
+
+cudaError_t launch_row_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream)
+{
+    uint64_t want = (rows + 7) / 8;
+    uint64_t cap = (uint64_t)sm_count() * 8;
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    row_sums_kernel<<<blocks, 256, 0, stream>>>(m, rows, cols, sums);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_col_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream)
+{
+    cudaError_t e = cudaMemsetAsync(sums, 0, cols * sizeof(int32_t), stream);
+    if (e != cudaSuccess) return e;
+    uint64_t bx = (cols + 255) / 256;
+    uint64_t by = (uint64_t)sm_count() * 4 / bx;
+    if (by < 1) by = 1;
+    if (by > rows) by = rows ? rows : 1;
+    if (by > 65535) by = 65535;
+    dim3 grid((unsigned)bx, (unsigned)by);
+    col_sums_kernel<<<grid, 256, 0, stream>>>(m, rows, cols, sums);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scale_i32(int32_t *v, uint64_t n, int32_t factor, cudaStream_t stream)
+{
+    scale_i32_kernel<<<stream_grid(n), 256, 0, stream>>>(v, n, factor);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace ltq

@@ -1,0 +1,21 @@
+"""ltq -- thin Python binding over libltq.so, the sm_100a CUDA library behind include/ltq.h.
+
+Everything here goes through the C ABI with raw device pointers (``torch`` is used only to own device memory and
+streams).  There is no fallback: if the shared library is missing or no CUDA device is usable, calls raise.
+
+Names mirror the l-ten reference so that tests read like its own:
+``GetMinMax / ComputeQuantizationParams / Quantize / Dequantize`` (l-ten/utils.h:23-27), ``quantized_matmul``
+(l-ten/math_fns.h:104) and ``FullyConnected_q`` (l-ten/layers.h:69-106).
+"""
+from ._binding import (LtqError, QParams, lib, lib_path, last_error, kernel_launches, OUT_U8, OUT_F32, OUT_I32,
+                       FLAG_RELU, FLAG_SATURATE, FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FORCE_SKINNY, DECLARED_SYMBOLS)
+from .ops import (GetMinMax, ComputeQuantizationParams, compute_qparams_dev, Quantize, QuantizeInt32, Dequantize,
+                  quantize_rows, row_sums, quantized_matmul)
+from .layer import FullyConnected_q, LayerHandle
+
+__all__ = [
+    "LtqError", "QParams", "lib", "lib_path", "last_error", "kernel_launches", "OUT_U8", "OUT_F32", "OUT_I32",
+    "FLAG_RELU", "FLAG_SATURATE", "FLAG_FORCE_SIMT", "FLAG_FORCE_TC", "FLAG_FORCE_SKINNY", "DECLARED_SYMBOLS",
+    "GetMinMax", "ComputeQuantizationParams", "compute_qparams_dev", "Quantize", "QuantizeInt32", "Dequantize",
+    "quantize_rows", "row_sums", "quantized_matmul", "FullyConnected_q", "LayerHandle",
+]

@@ -1,0 +1,185 @@
+"""GPU: layer-level parity on the benchmark configurations -- golden fixtures for the MNIST-shaped MLP and the 1024^3
+linear, the CPU oracle on sampled rows plus cross-kernel agreement at 4096^3, the skinny sweep in full."""
+import hashlib
+
+import numpy as np
+import pytest
+
+from helpers import ltq_qp, qp_of
+
+pytestmark = pytest.mark.gpu
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def test_mlp_chain_matches_golden(cuda, golden):
+    """784-512-512-10, batch 64: FullyConnected_q with the reference's method names, chained uint8 -> uint8, then
+    Dequantize, as tests/nn_tests.cpp:930-963 drives it."""
+    import ltq
+    from ltq import workloads
+    g = golden("fc_mlp.npz")
+    x, layers = workloads.mlp_mnist(seed=0, batch=64)
+    qp_in = ltq_qp(g["l0.qp"][0])
+    xq = ltq.Quantize(cuda.from_numpy(x).cuda(), qp_in)
+    np.testing.assert_array_equal(xq.cpu().numpy(), g["x_q"])
+    h = xq.view(1, 64, 784)
+    for li, (w, b) in enumerate(layers):
+        N, K = w.shape
+        qps = [ltq_qp(r) for r in g[f"l{li}.qp"]]
+        fc = ltq.FullyConnected_q(K, N, True)
+        fc.init()
+        # quantisation set-up on the device, then written through get_all_weights() like tests/nn_tests.cpp:818-826
+        wq = ltq.Quantize(cuda.from_numpy(w).cuda(), qps[1])
+        bq = ltq.QuantizeInt32(cuda.from_numpy(b).cuda(), ltq.QParams(np.float32(qps[0].scale) * np.float32(qps[1].scale), 0))
+        np.testing.assert_array_equal(wq.cpu().numpy(), g[f"l{li}.w_q"])
+        np.testing.assert_array_equal(bq.cpu().numpy(), g[f"l{li}.b_q"])
+        ws = fc.get_all_weights()
+        ws[0].copy_(wq.cpu().view(1, 1, N, K))
+        ws[1].copy_(bq.cpu())
+        fc.set_qparams_in(qps[0])
+        fc.set_qparams_out(qps[2])
+        fc.set_qparams_params([qps[1]], 1)
+        fc.to("cuda", 0)
+        h = fc.forward(h)
+        assert tuple(h.shape) == (1, 64, N) and h.dtype == cuda.uint8
+        np.testing.assert_array_equal(h.cpu().numpy().reshape(64, N), g[f"l{li}.y"])
+    logits = ltq.Dequantize(h, qps[2])
+    np.testing.assert_array_equal(logits.cpu().numpy().reshape(64, 10), g["logits"])
+
+
+def test_leading_dims_fold_into_m(cuda, oracle):
+    import ltq
+    rng = np.random.default_rng(11)
+    K, N = 64, 48
+    x = rng.integers(0, 256, (3, 5, 7, K), dtype=np.uint8)
+    w = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    fc = ltq.FullyConnected_q(K, N)
+    fc.init()
+    fc.get_all_weights()[0].copy_(cuda.from_numpy(w).view(1, 1, N, K))
+    qps = (ltq.QParams(0.1, 5), ltq.QParams(0.2, 9), ltq.QParams(90.0, 100))
+    fc.set_qparams_in(qps[0]); fc.set_qparams_out(qps[2]); fc.set_qparams_params([qps[1]], 1)
+    fc.to("cuda", 0)
+    y = fc.forward(cuda.from_numpy(x).cuda())
+    assert tuple(y.shape) == (3, 5, 7, N)
+    want, _ = oracle.port.quantized_matmul(x.reshape(-1, K), w, 105, N, K,
+                                           [oracle.qp(q.scale, q.zero_point) for q in qps])
+    np.testing.assert_array_equal(y.cpu().numpy().reshape(105, N), want)
+
+
+@pytest.mark.parametrize("path", ["auto", "simt"])
+def test_linear_1024_matches_golden(cuda, golden, path):
+    import ltq
+    from ltq import workloads
+    g = golden("linear_1024.npz")
+    wl = workloads.linear_u8(seed=2)
+    qa, qw = ltq.QParams(*wl["qp_a"]), ltq.QParams(*wl["qp_w"])
+    bq = ltq.QuantizeInt32(cuda.from_numpy(wl["bias"]).cuda(), ltq.QParams(np.float32(qa.scale) * np.float32(qw.scale), 0))
+    np.testing.assert_array_equal(bq.cpu().numpy(), g["bias_q"])
+    force = ltq.FLAG_FORCE_SIMT if path == "simt" else 0
+    h = ltq.LayerHandle(0, 1024, 1024)
+    wd, ad = cuda.from_numpy(wl["w"]).cuda(), cuda.from_numpy(wl["a"]).cuda()
+    h.set_weights(wd, bq)
+    for i in range(4):
+        sc, zc = g[f"o{i}.qp"]
+        h.set_qparams(qa, qw, ltq.QParams(np.float32(sc), int(zc)))
+        C = h.forward(ad, ltq.OUT_U8, force).cpu().numpy()
+        np.testing.assert_array_equal(C[::64], g[f"o{i}.rows"])
+        assert sha(C) == str(g[f"o{i}.sha"])
+    # same through the reference-shaped stateless call
+    Cd = cuda.empty((1024, 1024), dtype=cuda.uint8, device="cuda")
+    ws = cuda.empty(2048, dtype=cuda.int32, device="cuda")
+    sc, zc = g["o0.qp"]
+    ltq.quantized_matmul(False, True, 1024, 1024, 1024, 1, ad, wd, 0, Cd, [qa, qw, ltq.QParams(np.float32(sc), int(zc))], bq, ws)
+    assert sha(Cd.cpu().numpy()) == str(g["o0.sha"])
+    h.check()
+
+
+def test_linear_1024_f32_relu_and_int32_vs_oracle(cuda, oracle):
+    """fp32 dequantized output with fused ReLU, and the bit-exact int32 accumulator check."""
+    import ltq
+    from ltq import workloads
+    wl = workloads.linear_u8(seed=2)
+    qa, qw = oracle.qp(*wl["qp_a"]), oracle.qp(*wl["qp_w"])
+    bias_q = oracle.port.quantize_i32(wl["bias"], oracle.qp(np.float32(qa.scale) * np.float32(qw.scale), 0))
+    acc = oracle.port.acc_i32(wl["a"], wl["w"], 1024, 1024, 1024, qa.zero_point, qw.zero_point, bias=bias_q)
+    h = ltq.LayerHandle(0, 1024, 1024)
+    wd, ad = cuda.from_numpy(wl["w"]).cuda(), cuda.from_numpy(wl["a"]).cuda()
+    h.set_weights(wd, cuda.from_numpy(bias_q).cuda())
+    h.set_qparams(ltq.QParams(qa.scale, qa.zero_point), ltq.QParams(qw.scale, qw.zero_point), ltq.QParams(1.0, 0))
+    np.testing.assert_array_equal(h.forward(ad, ltq.OUT_I32).cpu().numpy(), acc)
+    got = h.forward(ad, ltq.OUT_F32, ltq.FLAG_RELU).cpu().numpy()
+    want = oracle.port.epilogue_f32(acc, qa.scale, qw.scale, relu=True)
+    rel = np.abs(got - want) / np.maximum(np.abs(want), 1e-30)
+    assert rel.max() <= 1e-5  # specified tolerance; the kernels in fact match bit for bit:
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    h.check()
+
+
+def test_square_4096_requant(cuda, oracle):
+    """4096^3, activations and weights quantized per tensor by min/max on the device, output requantized to uint8 with
+    qparams from the fp32 product's min/max.  Checks: (1) 96 sampled rows against the CPU oracle, bit for bit;
+    (2) the tcgen05 kernel and the dp4a kernel agree on the whole 16 Mi-element output; (3) linearity-free integer
+    identity: the int32 outputs summed per row equal what the operand sums predict."""
+    import ltq
+    from ltq import workloads
+    x, w = workloads.square_4096(seed=3)
+    xd, wd = cuda.from_numpy(x).cuda(), cuda.from_numpy(w).cuda()
+    qx = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(xd)))
+    qw = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(wd)))
+    xq, asum = ltq.quantize_rows(xd, qp=qx)
+    wq = ltq.Quantize(wd, qw)
+    ref32 = xd @ wd.t()
+    qo = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(ref32)))
+    del ref32
+    h = ltq.LayerHandle(0, 4096, 4096)
+    h.set_weights(wq, None)
+    h.set_qparams(qx, qw, qo)
+    out_tc = h.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_TC, asum=asum)
+    out_simt = h.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_SIMT, asum=asum)
+    h.check()
+    assert cuda.equal(out_tc, out_simt)
+    rows = np.sort(np.random.default_rng(0).choice(4096, 96, replace=False))
+    xq_h, wq_h = xq.cpu().numpy(), wq.cpu().numpy()
+    acc = oracle.port.acc_i32(xq_h[rows], wq_h, len(rows), 4096, 4096, qx.zero_point, qw.zero_point)
+    want = oracle.port.epilogue_u8(acc, qx.scale, qw.scale, qo.scale, qo.zero_point)
+    np.testing.assert_array_equal(out_tc.cpu().numpy()[rows], want)
+    # the quantized result tracks the fp32 product to within one output step (what requantisation promises)
+    deq = ltq.Dequantize(out_tc, qo)
+    assert (deq - xd @ wd.t()).abs().max().item() < 6 * qo.scale
+    # integer identity at full size: sum_j acc[i,j] = sum_k (a[i,k]-za) * (colsum_w[k] - N*zw)
+    acc_full = h.forward(xq, ltq.OUT_I32, ltq.FLAG_FORCE_TC, asum=asum).to(cuda.int64).sum(1)
+    colw = wq.to(cuda.int64).sum(0) - 4096 * qw.zero_point
+    pred = ((xq.to(cuda.int64) - qx.zero_point) * colw[None, :]).sum(1)
+    assert cuda.equal(acc_full, pred)
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_skinny_sweep_full_vs_oracle(cuda, oracle, M):
+    """M in {1,4,16}, K=4096, N=11008: weights quantized once, activations quantized per call (dynamic min/max on the
+    device, qparams never leave it), fp32 out.  Entire output compared with the CPU oracle."""
+    import ltq
+    from ltq import workloads
+    x, w = workloads.skinny(seed=4, M=M)
+    xd, wd = cuda.from_numpy(x).cuda(), cuda.from_numpy(w).cuda()
+    qw = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(wd)))
+    wq = ltq.Quantize(wd, qw)
+    qx_dev = ltq.compute_qparams_dev(ltq.GetMinMax(xd))
+    xq, asum = ltq.quantize_rows(xd, qp_dev=qx_dev)
+    h = ltq.LayerHandle(0, 4096, 11008)
+    h.set_weights(wq, None)
+    h.set_qparams(None, qw, None)
+    out = h.forward(xq, ltq.OUT_F32, 0, asum=asum, qp_in_dev=qx_dev).cpu().numpy()
+    h.check()
+    # oracle side
+    oqx = oracle.port.compute_qparams(*oracle.port.get_min_max(x))
+    oqw = oracle.port.compute_qparams(*oracle.port.get_min_max(w))
+    xq_o, wq_o = oracle.port.quantize_u8(x, oqx), oracle.port.quantize_u8(w, oqw)
+    np.testing.assert_array_equal(xq.cpu().numpy(), xq_o)
+    np.testing.assert_array_equal(wq.cpu().numpy(), wq_o)
+    acc = oracle.port.acc_i32(xq_o, wq_o, M, 11008, 4096, oqx.zero_point, oqw.zero_point)
+    want = oracle.port.epilogue_f32(acc, oqx.scale, oqw.scale)
+    rel = np.abs(out - want) / np.maximum(np.abs(want), 1e-30)
+    assert rel.max() <= 1e-5
+    np.testing.assert_array_equal(out.view(np.uint32), want.view(np.uint32))

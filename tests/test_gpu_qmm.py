@@ -1,0 +1,114 @@
+"""GPU: the reference-shaped quantized_matmul entry point and every GEMM kernel against golden vectors and the CPU
+oracle.  int32 and uint8 results are compared bit for bit; float results bit for bit as well (tolerance 0), which is
+inside the 1e-5 relative bound the path is specified to."""
+import numpy as np
+import pytest
+
+from helpers import iter_qmm_cases, ltq_qp, qp_of
+
+pytestmark = pytest.mark.gpu
+
+
+def test_quantized_matmul_small_matches_golden(cuda, golden):
+    import ltq
+    g = golden("qmm_small.npz")
+    n = 0
+    for c in iter_qmm_cases(g):
+        M, N, K = c["M"], c["N"], c["K"]
+        A = cuda.from_numpy(c["A"]).cuda()
+        B = cuda.from_numpy(c["B"]).cuda()
+        bias = None if c["bias"] is None else cuda.from_numpy(c["bias"]).cuda()
+        Cd = cuda.full((M, N), 0xAB, dtype=cuda.uint8, device="cuda")
+        ws = cuda.zeros(M + N, dtype=cuda.int32, device="cuda")
+        ltq.quantized_matmul(c["tA"], c["tB"], M, N, K, 1, A, B, 0, Cd, [ltq_qp(r) for r in c["qp"]], bias, ws)
+        np.testing.assert_array_equal(Cd.cpu().numpy(), c["C"], err_msg=c["key"])
+        np.testing.assert_array_equal(ws.cpu().numpy(), c["ws"], err_msg=c["key"])
+        n += 1
+    assert n >= 100
+
+
+def _run_layer(cuda, ltq, a, w, bias, qps, out_mode, flags, asum=None):
+    N, K = w.shape
+    h = ltq.LayerHandle(0, K, N)
+    wd = cuda.from_numpy(w).cuda()
+    bd = None if bias is None else cuda.from_numpy(bias).cuda()
+    h.set_weights(wd, bd)
+    h.set_qparams(*qps)
+    out = h.forward(cuda.from_numpy(a).cuda(), out_mode, flags, asum=asum)
+    h.check()
+    res = out.cpu().numpy()
+    h.close()
+    return res
+
+
+SHAPES = [
+    # (M, N, K)
+    (1, 8, 16), (1, 11008 // 8, 4096), (4, 100, 4096), (16, 264, 1040), (9, 72, 48), (16, 8, 12032),
+    (17, 10, 784), (64, 512, 784), (64, 10, 512), (128, 256, 128), (130, 300, 400), (256, 512, 1024),
+    (300, 129, 2064), (128, 64, 16), (1, 1, 16), (77, 333, 112),
+]
+
+
+@pytest.mark.parametrize("path", ["simt", "tc", "skinny", "auto"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_kernels_vs_oracle_all_modes(cuda, oracle, shape, path):
+    import ltq
+    M, N, K = shape
+    if path == "skinny" and M > 16:
+        pytest.skip("skinny kernel takes M <= 16")
+    force = {"simt": ltq.FLAG_FORCE_SIMT, "tc": ltq.FLAG_FORCE_TC, "skinny": ltq.FLAG_FORCE_SKINNY, "auto": 0}[path]
+    rng = np.random.default_rng(M * 7919 + N * 31 + K)
+    a = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    w = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    bias = rng.integers(-50000, 50000, N, dtype=np.int32)
+    za, zw, zc = int(rng.integers(0, 256)), int(rng.integers(0, 256)), int(rng.integers(0, 256))
+    sa, sw = np.float32(0.02), np.float32(0.005)
+    acc = oracle.port.acc_i32(a, w, M, N, K, za, zw, bias=bias)
+    # output scale such that results spread over (and beyond) the uint8 range
+    sc = np.float32(max(1e-6, np.abs(acc).max() * float(sa * sw) / 150.0))
+    qps = (ltq.QParams(sa, za), ltq.QParams(sw, zw), ltq.QParams(sc, zc))
+
+    got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_I32, force)
+    np.testing.assert_array_equal(got, acc)
+    got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_I32, force | ltq.FLAG_RELU)
+    np.testing.assert_array_equal(got, np.maximum(acc, 0))
+    for relu in (False, True):
+        for sat in (False, True):
+            fl = force | (ltq.FLAG_RELU if relu else 0) | (ltq.FLAG_SATURATE if sat else 0)
+            got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_U8, fl)
+            want = oracle.port.epilogue_u8(acc, sa, sw, sc, zc, relu=relu, saturate=sat)
+            np.testing.assert_array_equal(got, want)
+        got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_F32, force | (ltq.FLAG_RELU if relu else 0))
+        want = oracle.port.epilogue_f32(acc, sa, sw, relu=relu)
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))  # tolerance: 0 ulp
+    # no bias, caller-provided activation sums
+    asum = cuda.from_numpy(a.astype(np.int64).sum(1).astype(np.int32)).cuda()
+    got = _run_layer(cuda, ltq, a, w, None, qps, ltq.OUT_I32, force, asum=asum)
+    np.testing.assert_array_equal(got, oracle.port.acc_i32(a, w, M, N, K, za, zw))
+
+
+@pytest.mark.parametrize("zs", [(0, 0), (255, 255), (0, 255), (255, 0)])
+def test_extreme_zero_points_and_saturated_inputs(cuda, oracle, zs):
+    import ltq
+    M, N, K = 128, 256, 2048
+    for fill in (0, 255):
+        a = np.full((M, K), fill, np.uint8)
+        w = np.full((N, K), 255 - fill if zs[0] else fill, np.uint8)
+        qps = (ltq.QParams(0.01, zs[0]), ltq.QParams(0.01, zs[1]), ltq.QParams(1.0, 0))
+        for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC):
+            got = _run_layer(cuda, ltq, a, w, None, qps, ltq.OUT_I32, force)
+            np.testing.assert_array_equal(got, oracle.port.acc_i32(a, w, M, N, K, zs[0], zs[1]))
+
+
+def test_int32_wraps_like_the_reference_beyond_k_33025(cuda, oracle):
+    """K * 255^2 exceeds int32 for K > 33025: raw sums wrap mod 2^32 on both sides (no saturation in the MMA)."""
+    import ltq
+    M, N, K = 128, 64, 34048
+    a = np.full((M, K), 255, np.uint8)
+    w = np.full((N, K), 255, np.uint8)
+    a[::3, ::5] = 7
+    qps = (ltq.QParams(0.01, 0), ltq.QParams(0.01, 0), ltq.QParams(1.0, 0))
+    want = oracle.port.acc_i32(a, w, M, N, K, 0, 0)
+    assert (want < 0).any()
+    for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC):
+        np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, None, qps, ltq.OUT_I32, force), want)
