@@ -227,15 +227,29 @@ def run_gpu(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, graph=True):
+        """ms per step over EXACTLY `steps` steps, CUDA events on the launching stream, max over ranks.  The steps are
+        captured once into a CUDA graph (the kernels run for tens of microseconds; launching them one by one from
+        Python would time the interpreter) and the graph is replayed once untimed before the timed replay."""
         for i in range(warmup):
             fn(i)
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(steps):
-            fn(warmup + i)
-        e1.record()
+        if graph:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for i in range(steps):
+                    fn(warmup + i)
+            gr.replay()
+            sync_all()
+            e0.record()
+            gr.replay()
+            e1.record()
+        else:
+            e0.record()
+            for i in range(steps):
+                fn(warmup + i)
+            e1.record()
         sync_all()
         ms = e0.elapsed_time(e1)
         if dist is not None:
@@ -248,9 +262,10 @@ def run_gpu(args):
     launches0 = ltq.kernel_launches()
     if rank == 0:
         sampler.start()
-    ms_step = timed(step, args.steps, args.warmup)
-    launches = (ltq.kernel_launches() - launches0) * args.steps // (args.steps + args.warmup)
-    ms_gemm = timed(gemm_only, args.steps, max(3, args.warmup))
+    ms_step = timed(step, args.steps, args.warmup, graph=not args.no_graph)
+    # kernels per timed region: warm-up steps, the capture pass and (with a graph) two replays all launch the same list
+    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
+    ms_gemm = timed(gemm_only, args.steps, max(3, args.warmup), graph=not args.no_graph)
     clocks = sampler.stop() if rank == 0 else None
     for h in layers:
         h.check()
@@ -275,7 +290,10 @@ def run_gpu(args):
         y = fc.forward(q.view(1, M, K), asum=s)
         host_out.copy_(y.view(M, N), non_blocking=True)
 
-    ms_e2e = timed(e2e_step, max(3, args.steps // 2), 3)
+    if args.no_e2e:
+        ms_e2e = float("nan")
+    else:
+        ms_e2e = timed(e2e_step, max(3, args.steps // 2), 3, graph=False)
     e2e_tops = ops / (ms_e2e * 1e-3) / 1e12 * world
     fc._handle = None
 
@@ -313,7 +331,9 @@ def run_gpu(args):
         "config": {"workload": workload_name(wl), "M_per_gpu": M, "N": N, "K": K, "sharding": "rows (M) per GPU, "
                    "weights replicated, no collective" if world > 1 else "single GPU",
                    "l2": f"rotating {sets} distinct input/weight/output sets, larger than L2 in total",
-                   "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue"},
+                   "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue",
+                   "timing": "CUDA events around one replay of a CUDA graph holding exactly `steps` steps"
+                   if not args.no_graph else "CUDA events around `steps` eager launches"},
         "gemm_only": {"ms": ms_gemm, "tops": gemm_tops},
         "roofline": roof, "cpu_baseline": cpu,
         "e2e": {"value": e2e_tops, "unit": "TOPS", "ms_per_step": ms_e2e, "h2d_bytes_per_step": M * K * 4,
@@ -334,6 +354,8 @@ def main():
     ap.add_argument("--workload", default="square_4096", choices=["square_4096", "skinny"])
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -143,13 +143,25 @@ cudaError_t launch_t(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N,
                      void *out, int sms, cudaStream_t stream)
 {
     const size_t smem = smem_for(M, K);
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<HI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // Attribute and occupancy are looked up once per (device, shared-memory size) and reused: the kernel runs for a few
+    // microseconds, so two runtime queries per launch would cost more than the launch itself.
+    struct Cached { size_t smem = 0; int per_sm = 0; };
+    static Cached cache[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_kernel<HI, OUT>, WARPS * 32, smem);
-    if (e != cudaSuccess) return e;
-    if (per_sm < 1) return cudaErrorInvalidConfiguration;
-    if (per_sm > 4) per_sm = 4;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (cache[dev].smem != smem || cache[dev].per_sm == 0) {
+        e = cudaFuncSetAttribute(gemv_kernel<HI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        int q = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_kernel<HI, OUT>, WARPS * 32, smem);
+        if (e != cudaSuccess) return e;
+        if (q < 1) return cudaErrorInvalidConfiguration;
+        cache[dev].smem = smem;
+        cache[dev].per_sm = q > 4 ? 4 : q;
+    }
+    const int per_sm = cache[dev].per_sm;
     const uint64_t units = (N + UNIT_ROWS - 1) / UNIT_ROWS;
     uint64_t grid = (uint64_t)sms * per_sm;
     if (grid > units) grid = units;
