@@ -109,6 +109,21 @@ int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t 
                          const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int device,
                          void *stream);
 
+/* No counterpart in the reference: the same computation as ltq_quantized_matmul for callers that must not allocate
+ * device memory and therefore have no workspace to pass -- code running inside another framework's pre-planned memory
+ * region, latency-critical loops that cannot take the allocator's lock or an implicit synchronisation, processes
+ * whose device memory is fully reserved.  The (M + N) int32 of scratch live in a fixed array inside the library image
+ * (every GPU that loads the library holds LTQ_STATIC_WS_INTS * 4 bytes until exit), so M + N must not exceed
+ * LTQ_STATIC_WS_INTS (LTQ_ERR_TOO_LARGE otherwise).  The call performs no cudaMalloc / cudaFree and calls no
+ * allocating routine.  The first call on each device looks up the array's device address; make that first call
+ * outside any stream capture.  All calls on a device share the scratch: it holds the previous call's sums on entry
+ * (they are overwritten or cleared before use), and two calls whose kernels overlap on the GPU race on it -- issue
+ * them on one stream, or otherwise order them.  Output C is identical to ltq_quantized_matmul's. */
+#define LTQ_STATIC_WS_INTS (256 * 1024)
+int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                                const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, uint8_t *C_dev,
+                                const ltq_qparams *qparams, const int32_t *bias_dev, int device, void *stream);
+
 /* ---- layer handle: what FullyConnected_q (l-ten/layers.h:69-106) keeps between calls ------------------------- */
 
 typedef struct ltq_layer ltq_layer;

@@ -10,12 +10,12 @@ Names mirror the l-ten reference so that tests read like its own:
 from ._binding import (LtqError, QParams, lib, lib_path, last_error, kernel_launches, OUT_U8, OUT_F32, OUT_I32,
                        FLAG_RELU, FLAG_SATURATE, FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FORCE_SKINNY, DECLARED_SYMBOLS)
 from .ops import (GetMinMax, ComputeQuantizationParams, compute_qparams_dev, Quantize, QuantizeInt32, Dequantize,
-                  quantize_rows, row_sums, quantized_matmul)
+                  quantize_rows, row_sums, quantized_matmul, quantized_matmul_static)
 from .layer import FullyConnected_q, LayerHandle
 
 __all__ = [
     "LtqError", "QParams", "lib", "lib_path", "last_error", "kernel_launches", "OUT_U8", "OUT_F32", "OUT_I32",
     "FLAG_RELU", "FLAG_SATURATE", "FLAG_FORCE_SIMT", "FLAG_FORCE_TC", "FLAG_FORCE_SKINNY", "DECLARED_SYMBOLS",
     "GetMinMax", "ComputeQuantizationParams", "compute_qparams_dev", "Quantize", "QuantizeInt32", "Dequantize",
-    "quantize_rows", "row_sums", "quantized_matmul", "FullyConnected_q", "LayerHandle",
+    "quantize_rows", "row_sums", "quantized_matmul", "quantized_matmul_static", "FullyConnected_q", "LayerHandle",
 ]

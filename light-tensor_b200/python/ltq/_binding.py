@@ -42,6 +42,8 @@ _SIGNATURES = {
     "ltq_row_sums_u8": (_int, [_vp, _u64, _u64, _vp, _int, _vp]),
     "ltq_quantized_matmul": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp, _vp,
                                     _int, _vp]),
+    "ltq_quantized_matmul_static": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp,
+                                           _int, _vp]),
     "ltq_layer_create": (_int, [C.POINTER(_vp), _int, _u64, _u64]),
     "ltq_layer_destroy": (_int, [_vp]),
     "ltq_layer_set_weights": (_int, [_vp, _vp, _vp, _vp]),

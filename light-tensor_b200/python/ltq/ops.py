@@ -113,3 +113,17 @@ def quantized_matmul(transpose_A, transpose_B, M, N, K, alpha, A, B, beta, C_out
                                      beta, C_out.data_ptr(), arr, None if bias is None else bias.data_ptr(),
                                      workspace.data_ptr(), d, _stream(A)))
     return C_out
+
+
+def quantized_matmul_static(transpose_A, transpose_B, M, N, K, alpha, A, B, beta, C_out, qparams, bias):
+    """``quantized_matmul`` without a caller workspace and without any device allocation: for callers that are not
+    allowed to allocate (they run inside a host framework's planned memory, or must stay clear of the allocator's lock).
+    The operand sums go to a fixed scratch array inside the library; M + N is limited to 262144 and calls that overlap
+    on the GPU must be ordered by the caller."""
+    d = _dev(A)
+    assert A.dtype == torch.uint8 and B.dtype == torch.uint8 and C_out.dtype == torch.uint8
+    arr = (QParams * 3)(*qparams)
+    check(lib().ltq_quantized_matmul_static(int(transpose_A), int(transpose_B), M, N, K, alpha, A.data_ptr(),
+                                            B.data_ptr(), beta, C_out.data_ptr(), arr,
+                                            None if bias is None else bias.data_ptr(), d, _stream(A)))
+    return C_out
