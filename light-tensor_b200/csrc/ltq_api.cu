@@ -92,7 +92,7 @@ int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B
                     (unsigned long long)M, (unsigned long long)N, (unsigned long long)K);
         *path = PATH_TC;
     } else if (flags & LTQ_FLAG_FORCE_SKINNY) {
-        LTQ_REQUIRE(sk_ok, LTQ_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, K %% 16 == 0 and 16-byte aligned operands (M=%llu K=%llu)",
+        LTQ_REQUIRE(sk_ok, LTQ_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, K %% 128 == 0, K <= 8192 and 16-byte aligned operands (M=%llu K=%llu)",
                     (unsigned long long)M, (unsigned long long)K);
         *path = PATH_SKINNY;
     } else if (sk_ok) {
@@ -120,6 +120,7 @@ struct ltq_layer {
     uint64_t asum_cap = 0;         // FullyConnected_q::workspace_ (l-ten/fully_connected.cpp:366-371)
     ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
     TcOperandMap map_w[3];         // weight tensor maps for 64-, 128- and 256-column tiles, built on demand
+    GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
     DeviceState *dev = nullptr;
 };
 
@@ -220,7 +221,7 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
     if (rc != LTQ_OK) return rc;
     switch (path) {
         case PATH_SKINNY:
-            LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->sms, stream));
+            LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->status, dev->sms, stream, layer ? &layer->map_w_gemv : nullptr));
             break;
         case PATH_TC: {
             const int bn = tc_pick_bn(M, N, dev->sms);
@@ -328,6 +329,7 @@ int ltq_layer_set_weights(ltq_layer *layer, const uint8_t *w_dev, const int32_t 
     layer->w = w_dev;
     layer->bias = bias_dev;
     for (auto &m : layer->map_w) m = TcOperandMap();
+    layer->map_w_gemv = GemvWeightMaps();
     LTQ_CUDA_TRY(launch_row_sums(w_dev, layer->N, layer->K, layer->wsum, (cudaStream_t)stream));
     LTQ_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
     return LTQ_OK;

@@ -18,6 +18,7 @@
 
 #include "ltq_common.cuh"
 #include "ltq_gemm_tc.cuh"
+#include "ltq_tcgen05.cuh"
 
 namespace ltq {
 
@@ -27,7 +28,6 @@ constexpr int BM = 128;          // UMMA M (TMEM lanes)
 constexpr int BK = 128;          // bytes (= elements) of K per smem stage: one 128-byte swizzle atom wide
 constexpr int UMMA_K = 32;       // kind::i8
 constexpr int NUM_THREADS = 192;
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s per wait
 
 template <int BN>
 struct Cfg {
@@ -39,143 +39,6 @@ struct Cfg {
     // ring + 1024 B alignment slack + column terms (2 x BN x 4) + barriers
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 2 * BN * 4 + 256;
 };
-
-// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_ns()
-{
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait.  Returns false after WAIT_LIMIT_NS, or at once when another role has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code)
-{
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_ns();
-    for (uint32_t spin = 1;; spin++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (global_ns() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                atomicCAS(status, 0u, code);
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t x, int32_t y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols)
-{
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish()
-{
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols)
-{
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem] * B[smem], u8 x u8 -> s32.
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
-        "}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread = lane, register = column).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor for a K-major operand tile laid out by TMA with the 128-byte swizzle: rows of 128
-// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell), layout type 2
-// (SWIZZLE_128B).  The tile base is 1024-byte aligned, so base_offset is 0; stepping K by 32 bytes inside the atom is a
-// plain +2 on the (address >> 4) field.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // bits [0,14)
-    d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset
-    d |= (uint64_t)1 << 46;                               // version
-    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor, kind::i8: D = S32 (2 at bit 4), A = B = unsigned 8-bit (0 at bits 7 and 10), both K-major
-// (0 at bits 15, 16), no saturation (bit 3 clear: wrapping like the reference), N >> 3 at bit 17, M >> 4 at bit 24.
-template <int BN>
-__device__ __forceinline__ constexpr uint32_t make_idesc()
-{
-    return (2u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
 
 }  // namespace
 
@@ -247,34 +110,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc<BN>();
-            uint32_t st = 0, ph = 0, as = 0, aph = 0;
-            bool ok = true;
-            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-                ok = mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as);
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+        constexpr uint32_t idesc = make_idesc_i8(BM, BN);
+        uint32_t st = 0, ph = 0, as = 0, aph = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + as * BN;
+            for (uint32_t kb = 0; kb < num_kb; kb++) {
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + as * BN;
-                for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    ok = mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t a_src = ring + st * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
-                    const uint64_t a_desc = make_smem_desc(a_src), b_desc = make_smem_desc(b_src);
+                const uint32_t a_src = ring + st * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
+                const uint64_t a_desc = make_smem_desc(a_src), b_desc = make_smem_desc(b_src);
+                if (elect_one()) {
+                    // +32 bytes of K per step: +2 in the descriptor's 16-byte address units
+                    umma_i8(d_tmem, a_desc, b_desc, idesc, kb != 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        // +32 bytes of K per step: +2 in the descriptor's 16-byte address units
-                        umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | (uint32_t)k) != 0u);
-                    }
+                    for (int k = 1; k < BK / UMMA_K; k++) umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
                     umma_commit(empty0 + 8 * st);  // frees the smem stage once these MMAs have read it
-                    if (++st == C::STAGES) { st = 0; ph ^= 1; }
                 }
-                if (!ok) break;
-                umma_commit(tfull0 + 8 * as);  // accumulator complete
-                if (++as == 2) { as = 0; aph ^= 1; }
+                __syncwarp();
+                if (++st == C::STAGES) { st = 0; ph ^= 1; }
             }
+            if (!ok) break;
+            if (elect_one()) umma_commit(tfull0 + 8 * as);  // accumulator complete
+            __syncwarp();
+            if (++as == 2) { as = 0; aph ^= 1; }
         }
     } else {
         // ---------------- epilogue (warps 2..5 = 128 threads) ----------------
@@ -467,6 +331,29 @@ int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K,
     m->rows = rows;
     m->K = K;
     m->box_rows = box_rows;
+    m->box_lines = 0;
+    return 0;
+}
+
+int tc_make_map_lines(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows, int box_lines)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    if (K % 128 != 0) return -2;
+    // dim0: the 128 bytes of a line; dim1: matrix rows (pitch K); dim2: lines along K (pitch 128).
+    cuuint64_t dims[3] = {128, (cuuint64_t)rows, (cuuint64_t)(K / 128)};
+    cuuint64_t strides[2] = {(cuuint64_t)K, 128};
+    cuuint32_t box[3] = {128, (cuuint32_t)box_rows, (cuuint32_t)box_lines};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(m->opaque), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                    const_cast<uint8_t *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)r;
+    m->base = base;
+    m->rows = rows;
+    m->K = K;
+    m->box_rows = box_rows;
+    m->box_lines = box_lines;
     return 0;
 }
 

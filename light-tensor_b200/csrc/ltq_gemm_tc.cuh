@@ -13,9 +13,10 @@ struct TcOperandMap {
     const void *base = nullptr;
     uint64_t rows = 0, K = 0;
     int box_rows = 0;
-    bool matches(const void *b, uint64_t r, uint64_t k, int br) const
+    int box_lines = 0;  // 0 for the 2-D form; lines of 128 bytes along K per box for the 3-D form
+    bool matches(const void *b, uint64_t r, uint64_t k, int br, int bl = 0) const
     {
-        return base == b && rows == r && K == k && box_rows == br;
+        return base == b && rows == r && K == k && box_rows == br && box_lines == bl;
     }
 };
 
@@ -26,6 +27,11 @@ bool tc_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *
 int tc_pick_bn(uint64_t M, uint64_t N, int sms);
 // Encodes a map; box_rows is 128 for the A operand and the tile width for the B operand. 0 on success.
 int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows);
+// 3-D view of the same kind of matrix for the weight-streaming kernel (K % 128 == 0): dims {128 B line, rows, K/128
+// lines}, box {128 B, box_rows, box_lines}.  One box lands in shared memory as [line][row][128 B]; with the 128-byte
+// swizzle the 16-byte chunk index is XORed with the low three bits of (line * box_rows + row), so the rows of a box
+// read at the same K offset fall in different banks.  0 on success.
+int tc_make_map_lines(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows, int box_lines);
 cudaError_t launch_gemm_tc(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
                            uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream);
 

@@ -1,200 +1,335 @@
 // Skinny (M <= 16) quantized linear: out[M,N] = epilogue(x[M,K] . W[N,K]^T).  Decode-like shapes are bound by reading
-// the weight matrix once from HBM (N*K bytes against M*N*K MACs), so the kernel is organised around that stream:
+// the weight matrix once from HBM (N*K bytes against M*N*K MACs), so the kernel is a weight-streaming pipeline that
+// keeps the SM's instruction issue out of the data path altogether:
 //
-//  * the whole activation block (<= 16 rows) is staged once per CTA in shared memory, rows padded so that 16-byte
-//    reads by a quarter warp hit distinct banks;
-//  * a CTA takes units of 8 weight rows; its 8 warps split K in interleaved 64-byte pieces, each lane issuing a batch of
-//    independent 16-byte streaming loads (no L1 allocation) before any math, so every SM keeps tens of KB in flight;
-//  * the math is warp-level mma.sync m16n8k32 u8 x u8 -> s32 with the activation rows as the 16-row operand and the 8
-//    weight rows as the 8-column operand.  K is consumed in a permuted order inside each 64-byte piece (the sum over K
-//    does not depend on order), which lets each lane feed the fragments straight from its 16-byte load;
-//  * the 8 per-warp partial 16x8 tiles are combined through shared memory and the fused epilogue
-//    (l-ten/math_fns.cpp:1469-1474) writes the outputs.
+//  * operands are swapped for the tensor core: the WEIGHT rows are the 128-row (M) operand of tcgen05.mma and the
+//    <= 16 activation rows are its 16-column (N) operand, D[weight row, token] accumulating in TMEM.  Such a narrow MMA
+//    is short, but back-to-back MMAs into one accumulator serialise on the pipeline's latency (~120 cycles each), so
+//    the K steps rotate over 4 independent 16-column accumulators that the epilogue adds up;
+//  * one persistent CTA per SM owns a contiguous band of weight rows (N split evenly in units of 8 rows; a band is one
+//    MMA tile of up to 128 rows, of which only the band's rows are loaded - the tile's remaining rows compute on stale
+//    shared memory and are never stored);
+//  * the producer thread issues TMA tensor copies (cp.async.bulk.tensor.3d, no multicast) into a shared-memory ring.
+//    The matrices are described to TMA as {128-byte line, row, line index along K}: a box of R rows x L lines lands as
+//    L consecutive K-major tiles [R rows][128 B] under the 128-byte swizzle, exactly the layout the MMA's shared-memory
+//    descriptors read, while each row contributes L x 128 contiguous bytes of DRAM per box.  The activation block is
+//    fetched the same way, once (rows beyond M are zero-filled by TMA);
+//  * four epilogue warps read the accumulators with tcgen05.ld (thread = weight row, register = token), apply the fused
+//    epilogue (l-ten/math_fns.cpp:1469-1474) and store; for every token the 32 lanes of a warp write 32 consecutive
+//    outputs.  Accumulators are double buffered in TMEM.
+//
+// Every mbarrier wait is bounded (2 s by %globaltimer); on expiry a code is left in the device status word.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "ltq_common.cuh"
 #include "ltq_gemv.cuh"
+#include "ltq_tcgen05.cuh"
 
 namespace ltq {
 
 namespace {
 
-constexpr int WARPS = 8;
-constexpr int UNIT_ROWS = 8;       // weight rows per unit = mma N
-constexpr int PIECE = 64;          // bytes of K a warp covers per step (4 lanes x 16 B per weight row)
-constexpr int BATCH = 8;           // steps whose loads are issued together
+constexpr int THREADS = 192;               // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
+constexpr int LINE = 128;                  // bytes of K per line (one swizzle atom wide)
+constexpr int XROWS = 16;                  // activation rows as seen by the MMA (N = 16), TMEM columns per accumulator
+constexpr int TILE_M = 128;                // MMA M: weight rows per tile (upper bound)
+constexpr int MAX_STAGES = 16;
+constexpr int SMEM_LIMIT = 220 * 1024;
+constexpr int OVERREAD = TILE_M * LINE;    // an MMA reads 128 rows from a tile's start whatever the band holds
+constexpr int NACC = 4;                    // independent partial accumulators per tile (summed in the epilogue)
+constexpr uint32_t TMEM_COLS = 2 * NACC * XROWS;  // two buffers of NACC accumulators of 16 columns = 128
 
-__device__ __forceinline__ void mma_u8(int32_t (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
+struct Plan {
+    uint32_t grid, tiles_per_cta, tiles;   // tiles = grid * tiles_per_cta
+    uint32_t oct_lo, oct_hi;               // a tile holds oct_lo or oct_hi groups of 8 rows (oct_hi <= 16)
+    uint32_t lines;                        // lines per stage (per TMA box)
+    uint32_t stages;
+    uint32_t stage_bytes;                  // lines * oct_hi * 8 * 128
+    size_t smem;
+    bool ok;
+};
 
-__device__ __forceinline__ uint4 ld_stream(const uint8_t *p)
+Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms)
 {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+    Plan p{};
+    const uint64_t octs = (N + 7) / 8;
+    p.grid = (uint32_t)(octs < (uint64_t)sms ? octs : (uint64_t)sms);
+    p.tiles_per_cta = (uint32_t)((octs + (uint64_t)p.grid * 16 - 1) / ((uint64_t)p.grid * 16));
+    p.tiles = p.grid * p.tiles_per_cta;
+    p.oct_lo = (uint32_t)(octs / p.tiles);
+    p.oct_hi = (uint32_t)((octs + p.tiles - 1) / p.tiles);
+    const uint32_t klines = (uint32_t)(K / LINE);
+    const uint32_t line_bytes = p.oct_hi * 8 * LINE;
+    uint32_t L = (20u * 1024u) / line_bytes;
+    L = L < 1 ? 1 : (L > 4 ? 4 : L);
+    if (L > klines) L = klines;
+    p.lines = L;
+    p.stage_bytes = L * line_bytes;
+    // The MMA's over-read past the last tile may run into the activation block that follows the ring; only when that
+    // block is smaller than the over-read is extra slack needed.
+    // Activation block: 8 rows per line when M <= 8 (the MMA still reads 16 rows per line tile; rows 8..15 are then the
+    // next line's rows, whose products land in TMEM columns that are never stored), plus 1 KB so that this over-read of
+    // the last line stays inside the block.
+    const size_t xbytes = (size_t)(M > 8 ? 16 : 8) * K + 1024;
+    const size_t slack = xbytes >= (size_t)OVERREAD ? 0 : (size_t)OVERREAD - xbytes;
+    const size_t fixed = 1024 + xbytes + slack + 512;
+    p.ok = fixed + 2 * (size_t)p.stage_bytes <= (size_t)SMEM_LIMIT && p.oct_hi <= 16 && p.oct_lo >= 1;
+    if (!p.ok) return p;
+    uint32_t s = (uint32_t)(((size_t)SMEM_LIMIT - fixed) / p.stage_bytes);
+    p.stages = s > MAX_STAGES ? MAX_STAGES : s;
+    p.smem = fixed + (size_t)p.stages * p.stage_bytes;
+    return p;
 }
 
 }  // namespace
 
-// HI: rows 8..15 of the activation block are populated (M > 8).
-template <bool HI, int OUT>
-__global__ void __launch_bounds__(WARPS * 32)
-gemv_kernel(const uint8_t *__restrict__ x, const uint8_t *__restrict__ W, uint32_t M, uint32_t N, uint32_t K,
-            uint32_t x_pitch, Epilogue epi, void *__restrict__ out)
+// OUT: 0 = uint8, 1 = float, 2 = int32 (ltq_out_mode).
+template <int OUT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w_lo,
+            const __grid_constant__ CUtensorMap map_w_hi, uint32_t M, uint32_t N, uint32_t K, uint32_t tiles_per_cta,
+            uint32_t tiles, uint32_t oct_lo, uint32_t lines, uint32_t stages, uint32_t stage_bytes, Epilogue epi,
+            void *__restrict__ out, uint32_t *status)
 {
-    extern __shared__ __align__(16) uint8_t smem[];
-    constexpr int XROWS = HI ? 16 : 8;
-    uint8_t *xs = smem;                                                         // [XROWS][x_pitch]
-    int32_t *red = reinterpret_cast<int32_t *>(smem + (size_t)XROWS * x_pitch);  // [2][WARPS][128]
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw0 = smem_u32(smem_raw);
+    const uint32_t ring = (raw0 + 1023u) & ~1023u;                       // [stages][lines][rows][128 B]
+    const uint32_t xs = ring + stages * stage_bytes;                     // [K/128][8 or 16][128 B], then slack if small
+    const uint32_t xrows = M > 8 ? 16u : 8u;                             // rows per line tile of the activation block
+    const uint32_t xbytes = xrows * K + 1024u, slack = xbytes >= (uint32_t)OVERREAD ? 0u : (uint32_t)OVERREAD - xbytes;
+    uint8_t *after = smem_raw + (xs - raw0) + xbytes + slack;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after);                // full[S] empty[S] xbar tfull[2] tempty[2]
+    uint32_t *misc = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 5);  // [0] tmem base, [1] abort flag
+    volatile uint32_t *abort_flag = misc + 1;
 
-    // Stage activations, zero-filling rows >= M and the K tail up to the pitch.
-    for (uint32_t i = threadIdx.x; i < XROWS * (x_pitch / 16); i += blockDim.x) {
-        const uint32_t r = i / (x_pitch / 16), c = (i % (x_pitch / 16)) * 16;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < M && c < K) v = *reinterpret_cast<const uint4 *>(x + (size_t)r * K + c);
-        *reinterpret_cast<uint4 *>(xs + (size_t)r * x_pitch + c) = v;
-    }
-    __syncthreads();
-
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES, xbar = empty0 + 8 * MAX_STAGES;
+    const uint32_t tfull0 = xbar + 8, tempty0 = tfull0 + 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const EpilogueConsts c = epilogue_consts(epi);
-    const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
-    const uint32_t units = (N + UNIT_ROWS - 1) / UNIT_ROWS;
-    const uint8_t *xlo = xs + (size_t)g * x_pitch + 16 * t;
-    const uint8_t *xhi = xs + (size_t)(g + 8) * x_pitch + 16 * t;
+    const uint32_t octs = (N + 7) / 8;
+    const uint32_t klines = K / LINE, chunks = (klines + lines - 1) / lines;
+    const uint32_t t_begin = blockIdx.x * tiles_per_cta, t_end = t_begin + tiles_per_cta;
 
-    int buf = 0;
-    for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x, buf ^= 1) {
-        const uint32_t n = unit * UNIT_ROWS + g;
-        const bool row_ok = n < N;
-        const uint8_t *wrow = W + (size_t)(row_ok ? n : 0) * K + 16 * t;
-        int32_t acc[4] = {0, 0, 0, 0};
-        for (uint32_t k0 = warp * PIECE; k0 < K; k0 += WARPS * PIECE * BATCH) {
-            uint4 w[BATCH];
+    // Producer state lives in thread 0: (tile, K chunk) of the next box, ring slot and its phase.
+    uint32_t p_t = t_begin, p_kc = 0, p_st = 0, p_ph = 0;
+    bool p_x_sent = false;
+    // Issues the next weight box (and, behind the very first one, the activation block).  `fresh`: the ring slot has
+    // never been used, so there is nothing to wait for.
+    auto produce = [&](bool fresh) -> bool {
+        const uint32_t o0 = (uint32_t)(((uint64_t)p_t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(p_t + 1) * octs) / tiles);
+        const uint32_t rows = (o1 - o0) * 8;
+        const CUtensorMap *mw = (o1 - o0) == oct_lo ? &map_w_lo : &map_w_hi;
+        if (!fresh && !mbar_wait(empty0 + 8 * p_st, p_ph ^ 1, abort_flag, status, 0x500u | p_st)) return false;
+        // a box always transfers its full size: lines or rows outside the matrix arrive as zeros
+        mbar_expect_tx(full0 + 8 * p_st, lines * rows * LINE);
+        tma_load_3d(ring + p_st * stage_bytes, mw, full0 + 8 * p_st, 0, (int32_t)(o0 * 8), (int32_t)(p_kc * lines));
+        if (!p_x_sent) {
+            // the activation block rides behind the first weight box: [K/128 lines][8 or 16 rows][128 B]
+            mbar_expect_tx(xbar, xrows * K);
+            tma_load_3d(xs, &map_x, xbar, 0, 0, 0);
+            p_x_sent = true;
+        }
+        if (++p_st == stages) { p_st = 0; p_ph ^= 1; }
+        if (++p_kc == chunks) { p_kc = 0; p_t++; }
+        return true;
+    };
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(xbar, 1);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tempty0 + 8 * s, 4);  // one arrival per epilogue warp
+        }
+        misc[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // Fill the ring before anything else happens in the CTA: the first bytes from HBM are ~1.5 us away and every
+        // set-up step below (TMEM allocation, the CTA-wide barrier) would otherwise add to that.
+        for (uint32_t i = 0; i < stages && p_t < t_end; i++) produce(true);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(misc), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = misc[0];
+
+    if (warp == 0) {
+        // ---------------- TMA producer (continues where the pre-fill stopped) ----------------
+        if (lane == 0) {
+            while (p_t < t_end && produce(false)) {}
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+        constexpr uint32_t idesc = make_idesc_i8(TILE_M, XROWS);
+        uint32_t st = 0, ph = 0, as = 0, aph = 0;
+        bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(xbar, 0, abort_flag, status, 0x600u));
+        for (uint32_t t = t_begin; ok && t < t_end; t++) {
+            const uint32_t o0 = (uint32_t)(((uint64_t)t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(t + 1) * octs) / tiles);
+            const uint32_t line_stride = (o1 - o0) * 8 * LINE;  // bytes between the K-major tiles of one box
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + as * (NACC * XROWS);
+            for (uint32_t kc = 0; kc < chunks; kc++) {
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t l0 = kc * lines, nl = (klines - l0) < lines ? (klines - l0) : lines;
+                for (uint32_t l = 0; l < nl; l++) {
+                    const uint64_t a_desc = make_smem_desc(ring + st * stage_bytes + l * line_stride);
+                    const uint64_t b_desc = make_smem_desc(xs + (l0 + l) * (xrows * LINE));
+                    // one accumulator per K step of a line; the first line overwrites, later lines accumulate
+                    const uint32_t gl = l0 + l, d_line = d_tmem, acc = gl >= 1u;
+                    if (elect_one()) {
 #pragma unroll
-            for (int u = 0; u < BATCH; u++) {
-                const uint32_t k = k0 + u * WARPS * PIECE;
-                // K is a multiple of 16, so a lane's 16 bytes are either wholly inside the row or wholly outside.
-                w[u] = (row_ok && k + 16 * t < K) ? ld_stream(wrow + k) : make_uint4(0, 0, 0, 0);
+                        for (int k = 0; k < LINE / 32; k++)
+                            umma_i8(d_line + k * XROWS, a_desc + 2u * k, b_desc + 2u * k, idesc, acc);
+                    }
+                    __syncwarp();
+                }
+                if (elect_one()) umma_commit(empty0 + 8 * st);
+                __syncwarp();
+                if (++st == stages) { st = 0; ph ^= 1; }
             }
+            if (!ok) break;
+            if (elect_one()) umma_commit(tfull0 + 8 * as);
+            __syncwarp();
+            if (++as == 2) { as = 0; aph ^= 1; }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5): thread = weight row, register = token ----------------
+        const uint32_t q = (uint32_t)warp & 3u;
+        const EpilogueConsts c = epilogue_consts(epi);
+        const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
+        using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
+        OutT *o = static_cast<OutT *>(out);
+        uint32_t rt[XROWS];  // per-token part of the correction; identical for every weight row
 #pragma unroll
-            for (int u = 0; u < BATCH; u++) {
-                const uint32_t k = k0 + u * WARPS * PIECE;
-                if (k < K) {
-                    const uint4 lo = *reinterpret_cast<const uint4 *>(xlo + k);
-                    uint4 hi = make_uint4(0, 0, 0, 0);
-                    if (HI) hi = *reinterpret_cast<const uint4 *>(xhi + k);
-                    mma_u8(acc, lo.x, hi.x, lo.y, hi.y, w[u].x, w[u].y);
-                    mma_u8(acc, lo.z, hi.z, lo.w, hi.w, w[u].z, w[u].w);
+        for (int m = 0; m < XROWS; m++) rt[m] = (uint32_t)m < M ? epilogue_row_term(epi, c, (uint32_t)m) : 0u;
+        uint32_t as = 0, aph = 0;
+        bool ok = true;
+        for (uint32_t t = t_begin; t < t_end; t++) {
+            const uint32_t o0 = (uint32_t)(((uint64_t)t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(t + 1) * octs) / tiles);
+            const uint32_t n = o0 * 8 + q * 32 + lane;
+            const bool valid = (q * 32 + lane) < (o1 - o0) * 8 && n < N;
+            // fetched before waiting, so the global-memory latency passes under the stream
+            const uint32_t ct = valid ? epilogue_col_term(epi, c, n) : 0u;
+            if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
+            if (ok) {
+                tc_fence_after();
+                uint32_t v[XROWS];
+                const uint32_t tacc = tmem_base + ((q * 32u) << 16) + as * (NACC * XROWS);
+                tmem_ld16(tacc, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int a = 1; a < NACC; a++) {
+                    uint32_t w[XROWS];
+                    tmem_ld16(tacc + a * XROWS, w);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int m = 0; m < XROWS; m++) v[m] += w[m];
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * as);  // accumulator buffer may be overwritten
+                if (valid) {
+#pragma unroll
+                    for (int m = 0; m < XROWS; m++) {
+                        if ((uint32_t)m < M) {
+                            const int32_t a = epilogue_acc(v[m], rt[m], ct, relu);
+                            OutT r;
+                            if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
+                            else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
+                            else r = (OutT)a;
+                            o[(size_t)m * N + n] = r;
+                        }
+                    }
                 }
             }
+            if (++as == 2) { as = 0; aph ^= 1; }
         }
-        // Fragment -> [row][col] of the 16x8 partial tile: c0 (g,2t) c1 (g,2t+1) c2 (g+8,2t) c3 (g+8,2t+1).
-        int32_t *mine = red + (buf * WARPS + warp) * 128;
-        mine[g * 8 + 2 * t] = acc[0];
-        mine[g * 8 + 2 * t + 1] = acc[1];
-        if (HI) {
-            mine[(g + 8) * 8 + 2 * t] = acc[2];
-            mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
-        }
-        __syncthreads();  // partials of this unit visible; the other buffer is free again after the previous sync
-        if (threadIdx.x < XROWS * 8) {
-            const uint32_t row = threadIdx.x >> 3, col = unit * UNIT_ROWS + (threadIdx.x & 7);
-            if (row < M && col < N) {
-                uint32_t raw = 0;
-#pragma unroll
-                for (int w8 = 0; w8 < WARPS; w8++) raw += (uint32_t)red[(buf * WARPS + w8) * 128 + threadIdx.x];
-                const int32_t a = epilogue_acc(raw, epilogue_row_term(epi, c, row), epilogue_col_term(epi, c, col), relu);
-                const size_t o = (size_t)row * N + col;
-                if (OUT == 0)
-                    static_cast<uint8_t *>(out)[o] = epilogue_u8(a, c, sat);
-                else if (OUT == 1)
-                    static_cast<float *>(out)[o] = epilogue_f32(a, c);
-                else
-                    static_cast<int32_t *>(out)[o] = a;
-            }
-        }
+    }
+
+    // Teardown: nobody leaves before every role is done with TMEM and shared memory.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0 && lane == 0 && *abort_flag) {
+        // After a timeout, copies issued by the producer may still be landing in this CTA's shared memory; they
+        // complete within microseconds, so hold the CTA for a bounded 2 ms before it exits.
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
 namespace {
 
-uint32_t pitch_for(uint64_t K)
+template <int OUT>
+cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOperandMap &hi, const Plan &p, uint64_t M,
+                     uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, cudaStream_t stream)
 {
-    // Rows 128-byte aligned plus 64: consecutive rows start 16 banks apart, so the two rows a quarter warp reads in one
-    // 16-byte access never collide.
-    return (uint32_t)(((K + 127) / 128) * 128 + 64);
-}
-
-size_t smem_for(uint64_t M, uint64_t K)
-{
-    return (size_t)(M > 8 ? 16 : 8) * pitch_for(K) + 2 * WARPS * 128 * sizeof(int32_t);
-}
-
-template <bool HI, int OUT>
-cudaError_t launch_t(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                     void *out, int sms, cudaStream_t stream)
-{
-    const size_t smem = smem_for(M, K);
-    // Attribute and occupancy are looked up once per (device, shared-memory size) and reused: the kernel runs for a few
-    // microseconds, so two runtime queries per launch would cost more than the launch itself.
-    struct Cached { size_t smem = 0; int per_sm = 0; };
-    static Cached cache[64];
+    // The opt-in shared-memory size is set once per device: the kernel runs for a few microseconds and a runtime
+    // attribute call per launch would cost as much as the launch.
+    static bool attr_done[64] = {false};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-    if (cache[dev].smem != smem || cache[dev].per_sm == 0) {
-        e = cudaFuncSetAttribute(gemv_kernel<HI, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (!attr_done[dev]) {
+        e = cudaFuncSetAttribute(gemv_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT + 2048);
         if (e != cudaSuccess) return e;
-        int q = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&q, gemv_kernel<HI, OUT>, WARPS * 32, smem);
-        if (e != cudaSuccess) return e;
-        if (q < 1) return cudaErrorInvalidConfiguration;
-        cache[dev].smem = smem;
-        cache[dev].per_sm = q > 4 ? 4 : q;
+        attr_done[dev] = true;
     }
-    const int per_sm = cache[dev].per_sm;
-    const uint64_t units = (N + UNIT_ROWS - 1) / UNIT_ROWS;
-    uint64_t grid = (uint64_t)sms * per_sm;
-    if (grid > units) grid = units;
-    gemv_kernel<HI, OUT><<<(unsigned)grid, WARPS * 32, smem, stream>>>(x, W, (uint32_t)M, (uint32_t)N, (uint32_t)K,
-                                                                       pitch_for(K), epi, out);
+    gemv_kernel<OUT><<<p.grid, THREADS, p.smem, stream>>>(
+        *reinterpret_cast<const CUtensorMap *>(mx.opaque), *reinterpret_cast<const CUtensorMap *>(lo.opaque),
+        *reinterpret_cast<const CUtensorMap *>(hi.opaque), (uint32_t)M, (uint32_t)N, (uint32_t)K, p.tiles_per_cta, p.tiles,
+        p.oct_lo, p.lines, p.stages, p.stage_bytes, epi, out, status);
     count_launch();
     return cudaGetLastError();
-}
-
-template <bool HI>
-cudaError_t launch_o(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                     void *out, int sms, cudaStream_t stream)
-{
-    switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_t<HI, 0>(x, W, M, N, K, epi, out, sms, stream);
-        case LTQ_OUT_F32: return launch_t<HI, 1>(x, W, M, N, K, epi, out, sms, stream);
-        default: return launch_t<HI, 2>(x, W, M, N, K, epi, out, sms, stream);
-    }
 }
 
 }  // namespace
 
 bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W)
 {
-    return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 16 && K % 16 == 0 &&
-           smem_for(M, K) <= 200 * 1024 && (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0);
+    return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 128 && K % 128 == 0 && K <= 8192 &&
+           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148).ok;
 }
 
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                        void *out, int sms, cudaStream_t stream)
+                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache)
 {
-    return M > 8 ? launch_o<true>(x, W, M, N, K, epi, out, sms, stream)
-                 : launch_o<false>(x, W, M, N, K, epi, out, sms, stream);
+    const Plan p = make_plan(M, N, K, sms);
+    if (!p.ok) return cudaErrorInvalidConfiguration;
+    TcOperandMap mx;
+    GemvWeightMaps local;
+    // activations: one box holds the whole block, [K/128 lines][8 or 16 rows][128 B]; rows >= M are out of bounds -> zeros
+    if (tc_make_map_lines(&mx, x, M, K, M > 8 ? 16 : 8, (int)(K / LINE)) != 0) return cudaErrorInvalidValue;
+    GemvWeightMaps *wm = cache ? cache : &local;
+    if (!wm->lo.matches(W, N, K, (int)p.oct_lo * 8, (int)p.lines)) {
+        if (tc_make_map_lines(&wm->lo, W, N, K, (int)p.oct_lo * 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
+    }
+    if (!wm->hi.matches(W, N, K, (int)p.oct_hi * 8, (int)p.lines)) {
+        if (tc_make_map_lines(&wm->hi, W, N, K, (int)p.oct_hi * 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
+    }
+    switch (epi.out_mode) {
+        case LTQ_OUT_U8: return launch_t<0>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream);
+        case LTQ_OUT_F32: return launch_t<1>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream);
+        default: return launch_t<2>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream);
+    }
 }
 
 }  // namespace ltq

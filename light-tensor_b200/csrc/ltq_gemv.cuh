@@ -1,14 +1,23 @@
 // Host-visible interface of the skinny (M <= 16) weight-streaming kernel (ltq_gemv.cu).
 #pragma once
 #include "ltq_common.cuh"
+#include "ltq_gemm_tc.cuh"
 
 namespace ltq {
 
-// True when the kernel can take the problem: 1 <= M <= 16, K a multiple of 16 whose activation block fits in shared
-// memory, 16-byte aligned bases.
+// True when the kernel can take the problem: 1 <= M <= 16, K a multiple of 128 and at most 8192 (the activation block and
+// a ring of weight stages must fit in shared memory), 16-byte aligned bases.
 bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W);
 // x uint8 [M,K], W uint8 [N,K], both K-contiguous.
+// Weight tensor maps of the kernel (two box heights, because the row bands of the CTAs differ by at most one group of
+// 8 rows).  A caller that keeps one per weight matrix saves the host-side encoding on every call.
+struct GemvWeightMaps {
+    TcOperandMap lo, hi;
+};
+
+// `status`: device word that receives a code if a bounded wait inside the kernel expires.
+// `cache`: optional storage for the weight tensor maps, reused across calls while W, N, K stay the same.
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                        void *out, int sms, cudaStream_t stream);
+                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache);
 
 }  // namespace ltq

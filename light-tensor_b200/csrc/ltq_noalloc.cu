@@ -21,7 +21,7 @@ static_assert(LTQ_STATIC_WS_INTS_IMPL == LTQ_STATIC_WS_INTS, "header and impleme
 
 // Operand sums: [0, N) sums over K of the B operand, [N, N + M) sums over K of the A operand.
 static __device__ __align__(256) int32_t g_static_ws[LTQ_STATIC_WS_INTS_IMPL];
-// Status word for the bounded waits of the tensor-core kernel (the ordinary path allocates its own).
+// Status word for the bounded waits inside the GEMM kernels (the ordinary path allocates its own).
 static __device__ __align__(256) uint32_t g_static_status[64];
 
 namespace {
@@ -111,7 +111,7 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
     epi.flags = 0;
 
     if (!tA && tB && K > 0 && gemv_shape_ok(M, N, K, A_dev, B_dev)) {
-        LTQ_CUDA_TRY(launch_gemv(A_dev, B_dev, M, N, K, epi, C_dev, sd->sms, st));
+        LTQ_CUDA_TRY(launch_gemv(A_dev, B_dev, M, N, K, epi, C_dev, sd->status, sd->sms, st, nullptr));
     } else if (!tA && tB && K > 0 && tc_shape_ok(M, N, K, A_dev, B_dev)) {
         const int bn = tc_pick_bn(M, N, sd->sms);
         TcOperandMap map_a, map_b;  // encoded on the host into these stack objects; no device memory involved
