@@ -58,6 +58,8 @@ typedef enum ltq_out_mode {
 /* Kernel selection override, for tests and profiling (default: by shape). */
 #define LTQ_FLAG_FORCE_SIMT 0x100u  /* generic dp4a tile kernel */
 #define LTQ_FLAG_FORCE_TC 0x200u    /* tcgen05 kernel (needs K % 16 == 0) */
+#define LTQ_FLAG_FORCE_TC_PAIR 0x800u   /* with the tcgen05 path: the 2-CTA (cta_group::2) 256 x 256 tile kernel */
+#define LTQ_FLAG_FORCE_TC_SINGLE 0x1000u/* with the tcgen05 path: the single-CTA kernel */
 #define LTQ_FLAG_FORCE_SKINNY 0x400u/* weight-streaming kernel (needs M <= 16, K % 128 == 0, K <= 8192) */
 
 int ltq_version(void);

@@ -224,7 +224,10 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
             LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->status, dev->sms, stream, layer ? &layer->map_w_gemv : nullptr));
             break;
         case PATH_TC: {
-            const int bn = tc_pick_bn(M, N, dev->sms);
+            const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
+                              ((flags & LTQ_FLAG_FORCE_TC_PAIR) || tc_pair_preferred(M, N, dev->sms));
+            // the pair kernel's B boxes hold 128 rows (half a 256-column tile), like the 128-column single-CTA tile
+            const int bn = pair ? 128 : tc_pick_bn(M, N, dev->sms);
             TcOperandMap map_a, tmp_b;
             int er = tc_make_map(&map_a, A, M, K, 128);
             LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation operand (CUresult %d)", er);
@@ -234,7 +237,10 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
                 er = tc_make_map(map_b, B, N, K, bn);
                 LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
             }
-            LTQ_CUDA_TRY(launch_gemm_tc(map_a, *map_b, bn, M, N, K, epi, out, dev->status, dev->sms, stream));
+            if (pair)
+                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, *map_b, M, N, K, epi, out, dev->status, dev->sms, stream));
+            else
+                LTQ_CUDA_TRY(launch_gemm_tc(map_a, *map_b, bn, M, N, K, epi, out, dev->status, dev->sms, stream));
             break;
         }
         default:

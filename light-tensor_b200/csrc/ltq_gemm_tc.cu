@@ -242,6 +242,223 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---- CTA-pair variant ---------------------------------------------------------------------------------------------------
+// Large problems: two CTAs of a 2-CTA cluster work on one 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each CTA
+// loads its own 128 rows of A and only HALF of the tile's B rows (128 of 256), so a CTA moves 32 KB per 128-deep K block
+// instead of 48 KB: one third less L2 -> SM traffic, and six stages instead of four fit in shared memory, which is what
+// it takes to cover the L2 round trip at the tensor pipe's rate.  The leader CTA (cluster rank 0) issues the MMAs for
+// both; every barrier that both CTAs must observe is signalled through tcgen05.commit with a two-CTA mask.
+namespace {
+
+constexpr int P_BN = 256;                                 // tile columns (128 B rows held by each CTA)
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = BM * BK, P_B_BYTES = (P_BN / 2) * BK, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 2 * P_BN * 4 + 256;
+
+}  // namespace
+
+template <int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
+                    uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t ring = (raw + 1023u) & ~1023u;
+    uint8_t *after = smem_raw + (ring - raw) + P_STAGES * P_STAGE_BYTES;
+    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                  // [2][P_BN] column terms
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * P_BN * 4);    // full[S] empty[S] tfull[2] tempty[2]
+    uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * P_STAGES + 4);  // [0] tmem base, [1] abort flag
+    volatile uint32_t *abort_flag = s_misc + 1;
+
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * P_STAGES;
+    const uint32_t tfull0 = empty0 + 8 * P_STAGES, tempty0 = tfull0 + 16;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + P_BN - 1) / P_BN;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);    // leader's own arrive.expect_tx; bytes come from both CTAs
+            mbar_init(empty0 + 8 * s, 1);   // the leader's commit, delivered to both CTAs
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(tfull0 + 8 * s, 1);   // the leader's commit, delivered to both CTAs
+            mbar_init(tempty0 + 8 * s, 8);  // four epilogue warps in each of the two CTAs (used in the leader only)
+        }
+        s_misc[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(s_misc), 2 * P_BN);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers exist before anything is signalled across
+    tc_fence_after();
+    const uint32_t tmem_base = s_misc[0];
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs): own A rows, own half of the B rows ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
+                const int32_t m0 = (int32_t)((t / tiles_n) * (2 * BM) + rank * BM);
+                const int32_t n0 = (int32_t)((t % tiles_n) * P_BN + rank * (P_BN / 2));
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
+                    if (!ok) break;
+                    const uint32_t a_dst = ring + st * P_STAGE_BYTES, b_dst = a_dst + P_A_BYTES;
+                    const uint32_t lbar = in_leader_cta(full0 + 8 * st);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * st, 2 * P_STAGE_BYTES);
+                    tma_load_2d_pair(a_dst, &map_a, lbar, (int32_t)(kb * BK), m0);
+                    tma_load_2d_pair(b_dst, &map_b, lbar, (int32_t)(kb * BK), n0);
+                    if (++st == P_STAGES) { st = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only): warp-uniform loop, one elected lane issues ----------------
+        if (rank == 0) {
+            constexpr uint32_t idesc = make_idesc_i8(2 * BM, P_BN);
+            uint32_t st = 0, ph = 0, as = 0, aph = 0;
+            bool ok = true;
+            for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * P_BN;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_src = ring + st * P_STAGE_BYTES, b_src = a_src + P_A_BYTES;
+                    const uint64_t a_desc = make_smem_desc(a_src), b_desc = make_smem_desc(b_src);
+                    if (elect_one()) {
+                        umma_i8_pair(d_tmem, a_desc, b_desc, idesc, kb != 0u);
+#pragma unroll
+                        for (int k = 1; k < BK / UMMA_K; k++)
+                            umma_i8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
+                        umma_commit_pair(empty0 + 8 * st, 3);  // both CTAs may refill the stage
+                    }
+                    __syncwarp();
+                    if (++st == P_STAGES) { st = 0; ph ^= 1; }
+                }
+                if (!ok) break;
+                if (elect_one()) umma_commit_pair(tfull0 + 8 * as, 3);  // accumulators complete in both CTAs
+                __syncwarp();
+                if (++as == 2) { as = 0; aph ^= 1; }
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 of both CTAs): own 128 rows x 256 columns ----------------
+        const uint32_t q = (uint32_t)warp & 3u;
+        const uint32_t et = threadIdx.x - 64;
+        const EpilogueConsts c = epilogue_consts(epi);
+        const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
+        using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
+        OutT *o = static_cast<OutT *>(out);
+        const bool vec_ok = (((uint64_t)N * sizeof(OutT)) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+        uint32_t as = 0, aph = 0;
+        bool ok = true;
+        for (uint32_t t = pair; t < num_tiles; t += num_pairs) {
+            const uint32_t m0 = (t / tiles_n) * (2 * BM) + rank * BM, n0 = (t % tiles_n) * P_BN;
+            uint32_t *col = s_col + as * P_BN;
+            for (uint32_t j = et; j < (uint32_t)P_BN; j += 128) {
+                const uint32_t gj = n0 + j;
+                col[j] = gj < N ? epilogue_col_term(epi, c, gj) : 0u;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const uint32_t row = m0 + q * 32 + lane;
+            const uint32_t rt = row < M ? epilogue_row_term(epi, c, row) : 0u;
+
+            if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * P_BN;
+#pragma unroll 1
+                for (int ch = 0; ch < P_BN / 32; ch++) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    const uint32_t c0 = n0 + ch * 32;
+                    if (row < M && c0 < N) {
+                        OutT *dst = o + (uint64_t)row * N + c0;
+                        const int valid = (N - c0) < 32u ? (int)(N - c0) : 32;
+                        if (OUT == 0) {
+                            uint32_t p[8];
+#pragma unroll
+                            for (int g = 0; g < 8; g++) {
+                                uint32_t w = 0;
+#pragma unroll
+                                for (int b = 0; b < 4; b++) {
+                                    const int j = g * 4 + b;
+                                    const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
+                                    w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
+                                }
+                                p[g] = w;
+                            }
+                            if (vec_ok && valid == 32) {
+                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+                                d4[0] = make_uint4(p[0], p[1], p[2], p[3]);
+                                d4[1] = make_uint4(p[4], p[5], p[6], p[7]);
+                            } else {
+                                for (int j = 0; j < valid; j++)
+                                    reinterpret_cast<uint8_t *>(dst)[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
+                                v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
+                            }
+                            if (vec_ok && valid == 32) {
+                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                                for (int g = 0; g < 8; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (j < valid) reinterpret_cast<uint32_t *>(dst)[j] = v[j];
+                            }
+                        }
+                    }
+                }
+                // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(in_leader_cta(tempty0 + 8 * as));
+            }
+            if (++as == 2) { as = 0; aph ^= 1; }
+        }
+    }
+
+    // Teardown.  The leader's MMAs read the peer's shared memory and both CTAs' barriers receive remote arrivals, so
+    // neither CTA may exit before both are completely done.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0 && lane == 0 && *abort_flag) {
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 2 * P_BN);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------------------
 namespace {
 
@@ -298,6 +515,51 @@ cudaError_t launch_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M,
 }
 
 }  // namespace
+
+namespace {
+
+template <int OUT>
+cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
+                        const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+{
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             P_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + P_BN - 1) / P_BN);
+    const uint64_t pairs = tiles < (uint64_t)(sms / 2) ? tiles : (uint64_t)(sms / 2);
+    gemm_tc_pair_kernel<OUT><<<(unsigned)(2 * pairs), NUM_THREADS, P_SMEM_BYTES, stream>>>(
+        ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi, out, status);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
+{
+    // Worth pairing once 256 x 256 tiles can occupy most CTA pairs of the device.
+    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + P_BN - 1) / P_BN);
+    return tiles * 4 >= (uint64_t)(sms / 2) * 3;
+}
+
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, uint64_t M, uint64_t N,
+                                uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
+                                cudaStream_t stream)
+{
+    const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(map_a.opaque);
+    const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(map_b.opaque);
+    switch (epi.out_mode) {
+        case LTQ_OUT_U8: return launch_pair<0>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case LTQ_OUT_F32: return launch_pair<1>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        default: return launch_pair<2>(ma, mb, M, N, K, epi, out, status, sms, stream);
+    }
+}
 
 bool tc_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B)
 {

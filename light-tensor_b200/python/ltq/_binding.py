@@ -23,6 +23,7 @@ class QParams(C.Structure):
 OUT_U8, OUT_F32, OUT_I32 = 0, 1, 2
 FLAG_RELU, FLAG_SATURATE = 1, 2
 FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FORCE_SKINNY = 0x100, 0x200, 0x400
+FLAG_FORCE_TC_PAIR, FLAG_FORCE_TC_SINGLE = 0x800, 0x1000
 
 _u64, _vp, _int = C.c_uint64, C.c_void_p, C.c_int
 _qp = C.POINTER(QParams)

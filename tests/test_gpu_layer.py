@@ -120,7 +120,7 @@ def test_linear_1024_f32_relu_and_int32_vs_oracle(cuda, oracle):
 def test_square_4096_requant(cuda, oracle):
     """4096^3, activations and weights quantized per tensor by min/max on the device, output requantized to uint8 with
     qparams from the fp32 product's min/max.  Checks: (1) 96 sampled rows against the CPU oracle, bit for bit;
-    (2) the tcgen05 kernel and the dp4a kernel agree on the whole 16 Mi-element output; (3) linearity-free integer
+    (2) both tcgen05 kernels (CTA pair and single CTA) and the dp4a kernel agree on the whole 16 Mi-element output; (3) linearity-free integer
     identity: the int32 outputs summed per row equal what the operand sums predict."""
     import ltq
     from ltq import workloads
@@ -136,10 +136,11 @@ def test_square_4096_requant(cuda, oracle):
     h = ltq.LayerHandle(0, 4096, 4096)
     h.set_weights(wq, None)
     h.set_qparams(qx, qw, qo)
-    out_tc = h.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_TC, asum=asum)
+    out_tc = h.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR, asum=asum)
+    out_single = h.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_SINGLE, asum=asum)
     out_simt = h.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_SIMT, asum=asum)
     h.check()
-    assert cuda.equal(out_tc, out_simt)
+    assert cuda.equal(out_tc, out_simt) and cuda.equal(out_single, out_simt)
     rows = np.sort(np.random.default_rng(0).choice(4096, 96, replace=False))
     xq_h, wq_h = xq.cpu().numpy(), wq.cpu().numpy()
     acc = oracle.port.acc_i32(xq_h[rows], wq_h, len(rows), 4096, 4096, qx.zero_point, qw.zero_point)

@@ -46,18 +46,19 @@ SHAPES = [
     (1, 8, 16), (1, 11008 // 8, 4096), (4, 100, 4096), (16, 264, 1040), (9, 72, 48), (16, 8, 8192), (5, 40, 6144),
     (16, 333, 384), (3, 7, 128), (12, 1001, 1152), (8, 596, 2048),
     (17, 10, 784), (64, 512, 784), (64, 10, 512), (128, 256, 128), (130, 300, 400), (256, 512, 1024),
-    (300, 129, 2064), (128, 64, 16), (1, 1, 16), (77, 333, 112),
+    (300, 129, 2064), (128, 64, 16), (1, 1, 16), (77, 333, 112), (600, 520, 1152), (1024, 768, 512),
 ]
 
 
-@pytest.mark.parametrize("path", ["simt", "tc", "skinny", "auto"])
+@pytest.mark.parametrize("path", ["simt", "tc", "tcpair", "skinny", "auto"])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_kernels_vs_oracle_all_modes(cuda, oracle, shape, path):
     import ltq
     M, N, K = shape
     if path == "skinny" and (M > 16 or K % 128 or K > 8192):
         pytest.skip("skinny kernel takes M <= 16, K % 128 == 0, K <= 8192")
-    force = {"simt": ltq.FLAG_FORCE_SIMT, "tc": ltq.FLAG_FORCE_TC, "skinny": ltq.FLAG_FORCE_SKINNY, "auto": 0}[path]
+    force = {"simt": ltq.FLAG_FORCE_SIMT, "tc": ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_SINGLE,
+             "tcpair": ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR, "skinny": ltq.FLAG_FORCE_SKINNY, "auto": 0}[path]
     rng = np.random.default_rng(M * 7919 + N * 31 + K)
     a = rng.integers(0, 256, (M, K), dtype=np.uint8)
     w = rng.integers(0, 256, (N, K), dtype=np.uint8)
@@ -96,7 +97,8 @@ def test_extreme_zero_points_and_saturated_inputs(cuda, oracle, zs):
         a = np.full((M, K), fill, np.uint8)
         w = np.full((N, K), 255 - fill if zs[0] else fill, np.uint8)
         qps = (ltq.QParams(0.01, zs[0]), ltq.QParams(0.01, zs[1]), ltq.QParams(1.0, 0))
-        for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC):
+        for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_SINGLE,
+                      ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR):
             got = _run_layer(cuda, ltq, a, w, None, qps, ltq.OUT_I32, force)
             np.testing.assert_array_equal(got, oracle.port.acc_i32(a, w, M, N, K, zs[0], zs[1]))
 
@@ -111,5 +113,6 @@ def test_int32_wraps_like_the_reference_beyond_k_33025(cuda, oracle):
     qps = (ltq.QParams(0.01, 0), ltq.QParams(0.01, 0), ltq.QParams(1.0, 0))
     want = oracle.port.acc_i32(a, w, M, N, K, 0, 0)
     assert (want < 0).any()
-    for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC):
+    for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_SINGLE,
+                  ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR):
         np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, None, qps, ltq.OUT_I32, force), want)
