@@ -119,7 +119,8 @@ struct ltq_layer {
     int32_t *asum_ws = nullptr;    // activation row sums when the caller supplies none; grows with M like
     uint64_t asum_cap = 0;         // FullyConnected_q::workspace_ (l-ten/fully_connected.cpp:366-371)
     ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
-    TcOperandMap map_w[3];         // weight tensor maps for 64-, 128- and 256-column tiles, built on demand
+    TcOperandMap map_w[4];         // weight tensor maps of the tensor-core kernels, one per box height, built on demand
+    int map_w_next = 0;
     GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
     DeviceState *dev = nullptr;
 };
@@ -226,19 +227,29 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
         case PATH_TC: {
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
                               ((flags & LTQ_FLAG_FORCE_TC_PAIR) || tc_pair_preferred(M, N, dev->sms));
-            // the pair kernel's B boxes hold 128 rows (half a 256-column tile), like the 128-column single-CTA tile
-            const int bn = pair ? 128 : tc_pick_bn(M, N, dev->sms);
+            // single CTA: B boxes of bn rows (bn = 64, 128, 256); pair: boxes of pbn / 2 rows (96 .. 128)
+            const int pbn = pair ? tc_pair_pick_bn(M, N, dev->sms) : 0;
+            const int bn = pair ? pbn / 2 : tc_pick_bn(M, N, dev->sms);
             TcOperandMap map_a, tmp_b;
             int er = tc_make_map(&map_a, A, M, K, 128);
             LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation operand (CUresult %d)", er);
             TcOperandMap *map_b = &tmp_b;
-            if (layer) map_b = &layer->map_w[bn == 64 ? 0 : (bn == 128 ? 1 : 2)];
+            if (layer) {
+                // one cached map per box height this layer has needed so far
+                map_b = nullptr;
+                for (auto &m : layer->map_w)
+                    if (m.matches(B, N, K, bn)) map_b = &m;
+                if (!map_b) {
+                    map_b = &layer->map_w[layer->map_w_next];
+                    layer->map_w_next = (layer->map_w_next + 1) % 4;
+                }
+            }
             if (!map_b->matches(B, N, K, bn)) {
                 er = tc_make_map(map_b, B, N, K, bn);
                 LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
             }
             if (pair)
-                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, *map_b, M, N, K, epi, out, dev->status, dev->sms, stream));
+                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, *map_b, pbn, M, N, K, epi, out, dev->status, dev->sms, stream));
             else
                 LTQ_CUDA_TRY(launch_gemm_tc(map_a, *map_b, bn, M, N, K, epi, out, dev->status, dev->sms, stream));
             break;

@@ -243,31 +243,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---- CTA-pair variant ---------------------------------------------------------------------------------------------------
-// Large problems: two CTAs of a 2-CTA cluster work on one 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each CTA
-// loads its own 128 rows of A and only HALF of the tile's B rows (128 of 256), so a CTA moves 32 KB per 128-deep K block
+// Large problems: two CTAs of a 2-CTA cluster work on one 256 x PBN output tile with tcgen05.mma.cta_group::2.  Each CTA
+// loads its own 128 rows of A and only HALF of the tile's B rows, so a CTA moves at most 32 KB per 128-deep K block
 // instead of 48 KB: one third less L2 -> SM traffic, and six stages instead of four fit in shared memory, which is what
 // it takes to cover the L2 round trip at the tensor pipe's rate.  The leader CTA (cluster rank 0) issues the MMAs for
 // both; every barrier that both CTAs must observe is signalled through tcgen05.commit with a two-CTA mask.
+// Eight epilogue warps per CTA (two per TMEM lane quarter, splitting the columns) keep the exposed epilogue of a CTA's
+// last tile short.  PBN (256, 240, 224 or 192) is picked per problem so that the last wave of tiles is as full as
+// possible: integer tiles x CTA pairs rarely divide evenly, and a narrower tile can save a whole wave.
 namespace {
 
-constexpr int P_BN = 256;                                 // tile columns (128 B rows held by each CTA)
 constexpr int P_STAGES = 6;
-constexpr int P_A_BYTES = BM * BK, P_B_BYTES = (P_BN / 2) * BK, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 2 * P_BN * 4 + 256;
+constexpr int P_THREADS = 64 + 8 * 32;  // producer warp, MMA warp, 8 epilogue warps
+
+template <int PBN>
+struct PCfg {
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = (PBN / 2) * BK;  // this CTA's half of the tile's B rows
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = P_STAGES * STAGE_BYTES + 1024 + 2 * PBN * 4 + 256;
+    static_assert(B_BYTES % 1024 == 0, "swizzled tiles must stay 1024-byte aligned");
+    static_assert(PBN % 16 == 0 && PBN >= 144 && PBN <= 256, "tile width");
+};
+
+// One chunk of W (32 or 16) accumulator columns of one row: correction terms, conversion, store.
+template <int OUT, int W>
+__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col, const EpilogueConsts &c,
+                                               bool relu, bool sat, void *dst_v, bool vec_ok, int valid)
+{
+    if (OUT == 0) {
+        uint32_t p[W / 4];
+#pragma unroll
+        for (int g = 0; g < W / 4; g++) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int j = g * 4 + b;
+                const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
+                w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
+            }
+            p[g] = w;
+        }
+        if (vec_ok && valid == W) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst_v);
+#pragma unroll
+            for (int g = 0; g < W / 16; g++) d4[g] = make_uint4(p[4 * g], p[4 * g + 1], p[4 * g + 2], p[4 * g + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++)
+                if (j < valid) reinterpret_cast<uint8_t *>(dst_v)[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < W; j++) {
+            const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
+            v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
+        }
+        if (vec_ok && valid == W) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst_v);
+#pragma unroll
+            for (int g = 0; g < W / 4; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++)
+                if (j < valid) reinterpret_cast<uint32_t *>(dst_v)[j] = v[j];
+        }
+    }
+}
 
 }  // namespace
 
-template <int OUT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+template <int PBN, int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
                     uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
+    using C = PCfg<PBN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;
-    uint8_t *after = smem_raw + (ring - raw) + P_STAGES * P_STAGE_BYTES;
-    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                  // [2][P_BN] column terms
-    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * P_BN * 4);    // full[S] empty[S] tfull[2] tempty[2]
+    uint8_t *after = smem_raw + (ring - raw) + P_STAGES * C::STAGE_BYTES;
+    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                  // [2][PBN] column terms
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * PBN * 4);     // full[S] empty[S] tfull[2] tempty[2]
     uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * P_STAGES + 4);  // [0] tmem base, [1] abort flag
     volatile uint32_t *abort_flag = s_misc + 1;
 
@@ -277,7 +334,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + P_BN - 1) / P_BN;
+    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + PBN - 1) / PBN;
     const uint32_t num_tiles = tiles_m * tiles_n;
     const uint32_t num_kb = (K + BK - 1) / BK;
 
@@ -287,15 +344,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(empty0 + 8 * s, 1);   // the leader's commit, delivered to both CTAs
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(tfull0 + 8 * s, 1);   // the leader's commit, delivered to both CTAs
-            mbar_init(tempty0 + 8 * s, 8);  // four epilogue warps in each of the two CTAs (used in the leader only)
+            mbar_init(tfull0 + 8 * s, 1);    // the leader's commit, delivered to both CTAs
+            mbar_init(tempty0 + 8 * s, 16);  // eight epilogue warps in each of the two CTAs (used in the leader only)
         }
         s_misc[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc_pair(smem_u32(s_misc), 2 * P_BN);
+        tmem_alloc_pair(smem_u32(s_misc), 512);
         tmem_relinquish_pair();
     }
     tc_fence_before();
@@ -313,13 +370,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             bool ok = true;
             for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
                 const int32_t m0 = (int32_t)((t / tiles_n) * (2 * BM) + rank * BM);
-                const int32_t n0 = (int32_t)((t % tiles_n) * P_BN + rank * (P_BN / 2));
+                const int32_t n0 = (int32_t)((t % tiles_n) * PBN + rank * (PBN / 2));
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
                     if (!ok) break;
-                    const uint32_t a_dst = ring + st * P_STAGE_BYTES, b_dst = a_dst + P_A_BYTES;
+                    const uint32_t a_dst = ring + st * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
                     const uint32_t lbar = in_leader_cta(full0 + 8 * st);
-                    if (rank == 0) mbar_expect_tx(full0 + 8 * st, 2 * P_STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * st, 2 * C::STAGE_BYTES);
                     tma_load_2d_pair(a_dst, &map_a, lbar, (int32_t)(kb * BK), m0);
                     tma_load_2d_pair(b_dst, &map_b, lbar, (int32_t)(kb * BK), n0);
                     if (++st == P_STAGES) { st = 0; ph ^= 1; }
@@ -329,19 +386,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only): warp-uniform loop, one elected lane issues ----------------
         if (rank == 0) {
-            constexpr uint32_t idesc = make_idesc_i8(2 * BM, P_BN);
+            constexpr uint32_t idesc = make_idesc_i8(2 * BM, PBN);
             uint32_t st = 0, ph = 0, as = 0, aph = 0;
             bool ok = true;
             for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + as * P_BN;
+                const uint32_t d_tmem = tmem_base + as * 256;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_src = ring + st * P_STAGE_BYTES, b_src = a_src + P_A_BYTES;
+                    const uint32_t a_src = ring + st * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
                     const uint64_t a_desc = make_smem_desc(a_src), b_desc = make_smem_desc(b_src);
                     if (elect_one()) {
                         umma_i8_pair(d_tmem, a_desc, b_desc, idesc, kb != 0u);
@@ -360,78 +417,53 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5 of both CTAs): own 128 rows x 256 columns ----------------
-        const uint32_t q = (uint32_t)warp & 3u;
-        const uint32_t et = threadIdx.x - 64;
+        // ---------------- epilogue (warps 2..9 of both CTAs): own 128 rows; two warps share a lane quarter ------------
+        const uint32_t q = (uint32_t)warp & 3u;            // TMEM lane quarter this warp may read
+        const uint32_t h = (uint32_t)(warp - 2) >> 2;      // 0: columns [0,128), 1: columns [128,PBN)
+        const uint32_t et = threadIdx.x - 64;              // 0..255
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
         OutT *o = static_cast<OutT *>(out);
         const bool vec_ok = (((uint64_t)N * sizeof(OutT)) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+        constexpr int COL0 = 128;                          // column split between the two warps of a quarter
         uint32_t as = 0, aph = 0;
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles; t += num_pairs) {
-            const uint32_t m0 = (t / tiles_n) * (2 * BM) + rank * BM, n0 = (t % tiles_n) * P_BN;
-            uint32_t *col = s_col + as * P_BN;
-            for (uint32_t j = et; j < (uint32_t)P_BN; j += 128) {
+            const uint32_t m0 = (t / tiles_n) * (2 * BM) + rank * BM, n0 = (t % tiles_n) * PBN;
+            uint32_t *col = s_col + as * PBN;
+            for (uint32_t j = et; j < (uint32_t)PBN; j += 256) {
                 const uint32_t gj = n0 + j;
                 col[j] = gj < N ? epilogue_col_term(epi, c, gj) : 0u;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             const uint32_t row = m0 + q * 32 + lane;
             const uint32_t rt = row < M ? epilogue_row_term(epi, c, row) : 0u;
 
             if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
             if (ok) {
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * P_BN;
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * 256;
+                const int cb = h ? COL0 : 0, ce = h ? PBN : COL0;
 #pragma unroll 1
-                for (int ch = 0; ch < P_BN / 32; ch++) {
+                for (int cc = cb; cc + 32 <= ce; cc += 32) {
                     uint32_t v[32];
-                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld32(taddr + cc, v);
                     tmem_ld_wait();
-                    const uint32_t c0 = n0 + ch * 32;
-                    if (row < M && c0 < N) {
-                        OutT *dst = o + (uint64_t)row * N + c0;
-                        const int valid = (N - c0) < 32u ? (int)(N - c0) : 32;
-                        if (OUT == 0) {
-                            uint32_t p[8];
-#pragma unroll
-                            for (int g = 0; g < 8; g++) {
-                                uint32_t w = 0;
-#pragma unroll
-                                for (int b = 0; b < 4; b++) {
-                                    const int j = g * 4 + b;
-                                    const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
-                                    w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
-                                }
-                                p[g] = w;
-                            }
-                            if (vec_ok && valid == 32) {
-                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-                                d4[0] = make_uint4(p[0], p[1], p[2], p[3]);
-                                d4[1] = make_uint4(p[4], p[5], p[6], p[7]);
-                            } else {
-                                for (int j = 0; j < valid; j++)
-                                    reinterpret_cast<uint8_t *>(dst)[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
-                                v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
-                            }
-                            if (vec_ok && valid == 32) {
-                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-                                for (int g = 0; g < 8; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (j < valid) reinterpret_cast<uint32_t *>(dst)[j] = v[j];
-                            }
-                        }
-                    }
+                    const uint32_t c0 = n0 + cc;
+                    if (row < M && c0 < N)
+                        epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, o + (uint64_t)row * N + c0, vec_ok,
+                                                (N - c0) < 32u ? (int)(N - c0) : 32);
+                }
+                if ((ce - cb) % 32 != 0) {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
+                    const int cc = ce - 16;
+                    uint32_t v[16];
+                    tmem_ld16(taddr + cc, v);
+                    tmem_ld_wait();
+                    const uint32_t c0 = n0 + cc;
+                    if (row < M && c0 < N)
+                        epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, o + (uint64_t)row * N + c0, vec_ok,
+                                                (N - c0) < 16u ? (int)(N - c0) : 16);
                 }
                 // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)
                 tc_fence_before();
@@ -455,7 +487,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc_pair(tmem_base, 2 * P_BN);
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -518,25 +550,37 @@ cudaError_t launch_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M,
 
 namespace {
 
-template <int OUT>
+template <int PBN, int OUT>
 cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
                         const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
 {
+    using C = PCfg<PBN>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             P_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<PBN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + P_BN - 1) / P_BN);
+    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
     const uint64_t pairs = tiles < (uint64_t)(sms / 2) ? tiles : (uint64_t)(sms / 2);
-    gemm_tc_pair_kernel<OUT><<<(unsigned)(2 * pairs), NUM_THREADS, P_SMEM_BYTES, stream>>>(
+    gemm_tc_pair_kernel<PBN, OUT><<<(unsigned)(2 * pairs), P_THREADS, C::SMEM_BYTES, stream>>>(
         ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi, out, status);
     count_launch();
     return cudaGetLastError();
+}
+
+template <int PBN>
+cudaError_t launch_pair_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
+                            const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+{
+    switch (epi.out_mode) {
+        case LTQ_OUT_U8: return launch_pair<PBN, 0>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case LTQ_OUT_F32: return launch_pair<PBN, 1>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        default: return launch_pair<PBN, 2>(ma, mb, M, N, K, epi, out, status, sms, stream);
+    }
 }
 
 }  // namespace
@@ -544,20 +588,40 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M
 bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
 {
     // Worth pairing once 256 x 256 tiles can occupy most CTA pairs of the device.
-    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + P_BN - 1) / P_BN);
+    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
     return tiles * 4 >= (uint64_t)(sms / 2) * 3;
 }
 
-cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, uint64_t M, uint64_t N,
+int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms)
+{
+    // Time ~ (waves of tiles over the CTA pairs) x (tile width).  Wider tiles reuse operands better, so a narrower one
+    // must win by a clear margin (3 %).
+    const uint64_t tm = (M + 2 * BM - 1) / (2 * BM), pairs = (uint64_t)(sms / 2);
+    int best = 256;
+    double best_cost = 1e30;
+    for (int bn : {256, 240, 224, 192}) {
+        const uint64_t tiles = tm * ((N + bn - 1) / bn);
+        const double cost = (double)((tiles + pairs - 1) / pairs) * bn;
+        if (cost < best_cost * 0.97) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
                                 uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
                                 cudaStream_t stream)
 {
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(map_a.opaque);
     const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(map_b.opaque);
-    switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_pair<0>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        case LTQ_OUT_F32: return launch_pair<1>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        default: return launch_pair<2>(ma, mb, M, N, K, epi, out, status, sms, stream);
+    switch (bn) {
+        case 256: return launch_pair_out<256>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case 240: return launch_pair_out<240>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case 224: return launch_pair_out<224>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case 192: return launch_pair_out<192>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        default: return cudaErrorInvalidValue;
     }
 }
 

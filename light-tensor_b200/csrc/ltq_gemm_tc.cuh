@@ -27,10 +27,12 @@ bool tc_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *
 int tc_pick_bn(uint64_t M, uint64_t N, int sms);
 // Encodes a map; box_rows is 128 for the A operand and the tile width for the B operand. 0 on success.
 int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows);
-// CTA-pair variant (256 x 256 tiles, tcgen05.mma.cta_group::2): both maps use 128-row boxes (map_b: box_rows = 128,
-// each CTA of a pair loads half of the tile's B rows).  tc_pair_preferred says when the problem is large enough.
+// CTA-pair variant (256 x bn tiles, tcgen05.mma.cta_group::2).  tc_pair_preferred says when the problem is large
+// enough; tc_pair_pick_bn picks the tile width (256, 240, 224 or 192) that leaves the fullest last wave.  map_a uses
+// 128-row boxes, map_b boxes of bn / 2 rows (each CTA of a pair loads half of the tile's B rows).
 bool tc_pair_preferred(uint64_t M, uint64_t N, int sms);
-cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, uint64_t M, uint64_t N,
+int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms);
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
                                 uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
                                 cudaStream_t stream);
 // 3-D view of the same kind of matrix for the weight-streaming kernel (K % 128 == 0): dims {128 B line, rows, K/128

@@ -116,3 +116,23 @@ def test_int32_wraps_like_the_reference_beyond_k_33025(cuda, oracle):
     for force in (ltq.FLAG_FORCE_SIMT, ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_SINGLE,
                   ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR):
         np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, None, qps, ltq.OUT_I32, force), want)
+
+
+@pytest.mark.parametrize("shape", [(9472, 448, 256), (9472, 384, 128), (2048, 4096, 128), (9472, 512, 128)])
+def test_pair_kernel_tile_widths(cuda, oracle, shape):
+    """Shapes for which the CTA-pair kernel picks 224-, 192-, 240- and 256-column tiles (fullest last wave)."""
+    import ltq
+    M, N, K = shape
+    rng = np.random.default_rng(N)
+    a = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    w = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    bias = rng.integers(-50000, 50000, N, dtype=np.int32)
+    qps = (ltq.QParams(0.02, 77), ltq.QParams(0.005, 131), ltq.QParams(0.9, 100))
+    acc = oracle.port.acc_i32(a, w, M, N, K, 77, 131, bias=bias)
+    force = ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR
+    np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_I32, force), acc)
+    np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_U8, force),
+                                  oracle.port.epilogue_u8(acc, 0.02, 0.005, 0.9, 100))
+    got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_F32, force | ltq.FLAG_RELU)
+    want = oracle.port.epilogue_f32(acc, 0.02, 0.005, relu=True)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
