@@ -128,8 +128,11 @@ __device__ __forceinline__ uint8_t epilogue_u8(int32_t acc, const EpilogueConsts
         if (t >= 255.f) return 255;
         return (uint8_t)__float2int_rz(t);
     }
-    if (!(t > -2147483648.f && t < 2147483648.f)) return 0;
-    return (uint8_t)(__float2int_rz(t) & 0xFF);
+    // The device conversion saturates: t <= -2^31 gives INT_MIN (low byte 0, as on x86) and NaN gives 0 (x86: 0x80000000,
+    // low byte 0); only t >= 2^31 needs care, where x86 yields 0x80000000 but the device INT_MAX.
+    int32_t r = __float2int_rz(t);
+    r = (t >= 2147483648.f) ? 0 : r;
+    return (uint8_t)(r & 0xFF);
 }
 
 __device__ __forceinline__ float epilogue_f32(int32_t acc, const EpilogueConsts &c)

@@ -268,9 +268,20 @@ struct PCfg {
 
 // One chunk of W (32 or 16) accumulator columns of one row: correction terms, conversion, store.
 template <int OUT, int W>
-__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col, const EpilogueConsts &c,
-                                               bool relu, bool sat, void *dst_v, bool vec_ok, int valid)
+__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
+                                               const EpilogueConsts &c, bool relu, bool sat, void *dst_v, bool vec_ok,
+                                               int valid)
 {
+    // column terms: 16-byte shared loads (the chunk starts at a multiple of 16 columns)
+    uint32_t col[W];
+#pragma unroll
+    for (int g = 0; g < W / 4; g++) {
+        const uint4 t4 = reinterpret_cast<const uint4 *>(col_smem)[g];
+        col[4 * g] = t4.x;
+        col[4 * g + 1] = t4.y;
+        col[4 * g + 2] = t4.z;
+        col[4 * g + 3] = t4.w;
+    }
     if (OUT == 0) {
         uint32_t p[W / 4];
 #pragma unroll

@@ -1,0 +1,337 @@
+// Implementation of lten_q.h on top of libltq and the CUDA runtime.
+#include "lten_q.h"
+
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+namespace lten {
+
+// l-ten/error.h:78-93 + l-ten/utils.cpp:303-322: print, then throw.
+ExceptionInfo::ExceptionInfo(const char *msg, const char *file, const char *func, int line) : msg_(msg)
+{
+    text_ = std::string(msg) + " [" + file + ":" + std::to_string(line) + " " + func + "]";
+}
+
+#define LTEN_ERR(msg)                                                                                          \
+    do {                                                                                                       \
+        fprintf(stderr, "[Error] File: %s Function: %s Line:%d Msg: %s\n", __FILE__, __func__, __LINE__, msg); \
+        throw lten::ExceptionInfo(msg, __FILE__, __func__, __LINE__);                                          \
+    } while (0)
+
+#define LTEN_CUDA(expr)                                           \
+    do {                                                          \
+        cudaError_t e__ = (expr);                                 \
+        if (e__ != cudaSuccess) LTEN_ERR(cudaGetErrorString(e__)); \
+    } while (0)
+
+#define LTQ_CALL(expr)                          \
+    do {                                        \
+        if ((expr) != LTQ_OK) LTEN_ERR(ltq_last_error()); \
+    } while (0)
+
+static size_t dtype_size(dtype t) { return t == UINT8 ? 1 : 4; }
+
+struct Tensor::Impl {
+    void *data = nullptr;
+    bool own = true;
+    uint64_t dims[MAX_DIMS] = {0};
+    int ndims = 0;
+    uint64_t numels = 0;
+    TensorOps ops;
+    ~Impl()
+    {
+        if (!own || !data) return;
+        if (ops.device_type == GPU) {
+            int prev = 0;
+            cudaGetDevice(&prev);
+            cudaSetDevice(ops.device_index);
+            cudaFree(data);
+            cudaSetDevice(prev);
+        } else {
+            free(data);
+        }
+    }
+};
+
+void *Tensor::get_data_ptr() const { return impl_ ? impl_->data : nullptr; }
+uint64_t Tensor::get_numels() const { return impl_ ? impl_->numels : 0; }
+const uint64_t *Tensor::get_sizes() const { return impl_->dims; }
+int Tensor::get_ndims() const { return impl_ ? impl_->ndims : 0; }
+dtype Tensor::get_data_type() const { return impl_->ops.data_type; }
+device Tensor::get_device() const { return impl_->ops.device_type; }
+int Tensor::get_device_index() const { return impl_->ops.device_index; }
+
+Tensor AllocateTensor(const uint64_t *dims_ptr, int ndims, TensorOps *options_ptr)
+{
+    if (ndims < 1 || ndims > MAX_DIMS) LTEN_ERR("Invalid number of dimensions");
+    Tensor t;
+    t.impl_ = std::make_shared<Tensor::Impl>();
+    Tensor::Impl &im = *t.impl_;
+    if (options_ptr) im.ops = *options_ptr;
+    im.ndims = ndims;
+    im.numels = 1;
+    for (int i = 0; i < ndims; i++) {
+        im.dims[i] = dims_ptr[i];
+        im.numels *= dims_ptr[i];
+    }
+    const size_t bytes = im.numels * dtype_size(im.ops.data_type);
+    if (im.ops.device_type == GPU) {
+        int prev = 0;
+        LTEN_CUDA(cudaGetDevice(&prev));
+        LTEN_CUDA(cudaSetDevice(im.ops.device_index));
+        LTEN_CUDA(cudaMalloc(&im.data, bytes ? bytes : 1));
+        LTEN_CUDA(cudaMemset(im.data, 0, bytes));
+        LTEN_CUDA(cudaSetDevice(prev));
+    } else {
+        im.data = calloc(bytes ? bytes : 1, 1);
+        if (!im.data) LTEN_ERR("out of memory");
+    }
+    return t;
+}
+
+Tensor AllocateTensor(const std::initializer_list<uint64_t> &dims, TensorOps *options_ptr)
+{
+    return AllocateTensor(dims.begin(), (int)dims.size(), options_ptr);
+}
+
+Tensor TensorFromBuffer(const uint64_t *dims_ptr, int ndims, void *data_ptr, bool own_memory, TensorOps *options_ptr)
+{
+    if (ndims < 1 || ndims > MAX_DIMS) LTEN_ERR("Invalid number of dimensions");
+    Tensor t;
+    t.impl_ = std::make_shared<Tensor::Impl>();
+    Tensor::Impl &im = *t.impl_;
+    if (options_ptr) im.ops = *options_ptr;
+    im.ndims = ndims;
+    im.numels = 1;
+    for (int i = 0; i < ndims; i++) {
+        im.dims[i] = dims_ptr[i];
+        im.numels *= dims_ptr[i];
+    }
+    im.data = data_ptr;
+    im.own = own_memory;
+    return t;
+}
+
+Tensor TensorFromBuffer(const std::initializer_list<uint64_t> &dims, void *data_ptr, bool own_memory, TensorOps *options_ptr)
+{
+    return TensorFromBuffer(dims.begin(), (int)dims.size(), data_ptr, own_memory, options_ptr);
+}
+
+Tensor Tensor::to(device target_device, int target_device_index) const
+{
+    if (!impl_) LTEN_ERR("Invalid argument");
+    TensorOps ops = impl_->ops;
+    ops.device_type = target_device;
+    ops.device_index = target_device == GPU ? target_device_index : 0;
+    Tensor r = AllocateTensor(impl_->dims, impl_->ndims, &ops);
+    const size_t bytes = impl_->numels * dtype_size(ops.data_type);
+    if (bytes == 0) return r;
+    if (impl_->ops.device_type == CPU && target_device == CPU) {
+        memcpy(r.get_data_ptr(), impl_->data, bytes);
+    } else {
+        // cudaMemcpyDefault resolves host / device / peer copies from the pointers (unified addressing)
+        LTEN_CUDA(cudaMemcpy(r.get_data_ptr(), impl_->data, bytes, cudaMemcpyDefault));
+    }
+    return r;
+}
+
+Tensor Tensor::reshape(const std::initializer_list<uint64_t> &dims) const
+{
+    uint64_t n = 1;
+    for (uint64_t d : dims) n *= d;
+    if (!impl_ || n != impl_->numels) LTEN_ERR("Invalid reshape dimensions");
+    Tensor r = *this;
+    r.impl_ = std::make_shared<Impl>(*impl_);
+    r.impl_->own = false;  // a view; the original handle keeps the storage alive for as long as the caller holds it
+    r.impl_->ndims = (int)dims.size();
+    int i = 0;
+    for (uint64_t d : dims) r.impl_->dims[i++] = d;
+    return r;
+}
+
+// ---- FullyConnected_q ------------------------------------------------------------------------------------------------
+FullyConnected_q::FullyConnected_q(int64_t input_features, int64_t output_features, bool use_bias, dtype)
+    : input_features_((uint64_t)input_features), output_features_((uint64_t)output_features), use_bias_(use_bias)
+{
+}
+
+FullyConnected_q::FullyConnected_q(const FullyConnected_q &o) : Module(o) { *this = o; }
+
+FullyConnected_q &FullyConnected_q::operator=(const FullyConnected_q &o)
+{
+    if (this == &o) return *this;
+    if (o.weight_ptr_ || o.handle_) LTEN_ERR("FullyConnected_q can only be copied before init()");
+    input_features_ = o.input_features_;
+    output_features_ = o.output_features_;
+    use_bias_ = o.use_bias_;
+    qparams_in_ = o.qparams_in_;
+    qparams_out_ = o.qparams_out_;
+    qparams_wt_ = o.qparams_wt_;
+    out_mode_ = o.out_mode_;
+    flags_ = o.flags_;
+    is_training_ = o.is_training_;
+    return *this;
+}
+
+FullyConnected_q::~FullyConnected_q()
+{
+    ltq_layer_destroy(handle_);
+    delete weight_ptr_;
+    delete bias_ptr_;
+}
+
+// l-ten/fully_connected.cpp:295-320: uint8 weights {1,1,N,K}, int32 bias {N}, on the CPU, left for the quantisation
+// set-up code to fill.
+bool FullyConnected_q::init()
+{
+    TensorOps options;
+    options.data_type = UINT8;
+    weight_ptr_ = new Tensor;
+    *weight_ptr_ = AllocateTensor({1, 1, output_features_, input_features_}, &options);
+    if (use_bias_) {
+        bias_ptr_ = new Tensor;
+        options.data_type = INT32;
+        *bias_ptr_ = AllocateTensor({output_features_}, &options);
+    }
+    return true;
+}
+
+std::vector<Tensor *> FullyConnected_q::get_all_weights()
+{
+    std::vector<Tensor *> weights;
+    weights.push_back(weight_ptr_);
+    if (use_bias_) weights.push_back(bias_ptr_);
+    return weights;
+}
+
+void FullyConnected_q::set_qparams_params(QuantizationParams *qparams, int count)
+{
+    if (qparams && count) qparams_wt_ = qparams[0];  // l-ten/fully_connected.cpp:440-446: only [0] is kept
+}
+
+void FullyConnected_q::set_output(ltq_out_mode mode, bool relu, bool saturate)
+{
+    out_mode_ = mode;
+    flags_ = (relu ? LTQ_FLAG_RELU : 0u) | (saturate ? LTQ_FLAG_SATURATE : 0u);
+}
+
+void FullyConnected_q::to(device target_device, int target_device_index)
+{
+    if (!weight_ptr_) LTEN_ERR("init() has not been called");
+    *weight_ptr_ = weight_ptr_->to(target_device, target_device_index);
+    if (bias_ptr_) *bias_ptr_ = bias_ptr_->to(target_device, target_device_index);
+    ltq_layer_destroy(handle_);
+    handle_ = nullptr;
+    if (target_device == GPU) {
+        LTQ_CALL(ltq_layer_create(&handle_, target_device_index, input_features_, output_features_));
+        LTQ_CALL(ltq_layer_set_weights(handle_, static_cast<const uint8_t *>(weight_ptr_->get_data_ptr()),
+                                       bias_ptr_ ? static_cast<const int32_t *>(bias_ptr_->get_data_ptr()) : nullptr,
+                                       nullptr));
+    }
+}
+
+Tensor FullyConnected_q::forward(Tensor &input)
+{
+    // the reference's checks, messages and order: l-ten/fully_connected.cpp:330-348
+    const int ndims = input.get_ndims();
+    if (ndims < 3) LTEN_ERR("FullyConnected_q requires tensors with at least 3 dimensions");
+    if (input.get_device() != weight_ptr_->get_device() || input.get_device_index() != weight_ptr_->get_device_index() ||
+        input.get_data_type() != weight_ptr_->get_data_type())
+        LTEN_ERR("Input tensor device type or data type are not the same as this layer's parameters");
+    uint64_t dims[MAX_DIMS];
+    memcpy(dims, input.get_sizes(), sizeof(uint64_t) * ndims);
+    if (dims[ndims - 1] != input_features_) LTEN_ERR("Last dimension must be equal to the number of input features");
+    if (input.get_device() != GPU)
+        LTEN_ERR("FullyConnected_q: this build computes on GPU tensors only; call to(GPU, index) first");
+    dims[ndims - 1] = output_features_;
+
+    TensorOps options;
+    options.data_type = out_mode_ == LTQ_OUT_U8 ? UINT8 : (out_mode_ == LTQ_OUT_F32 ? FLOAT32 : INT32);
+    options.device_type = GPU;
+    options.device_index = input.get_device_index();
+    Tensor result = AllocateTensor(dims, ndims, &options);
+
+    uint64_t rows = 1;  // every leading dimension folds into M: parameters are per tensor, rows are independent
+    for (int d = 0; d < ndims - 1; d++) rows *= dims[d];
+    LTQ_CALL(ltq_layer_set_qparams(handle_, &qparams_in_, &qparams_wt_, &qparams_out_));
+    LTQ_CALL(ltq_layer_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), nullptr, rows, nullptr,
+                               out_mode_, flags_, result.get_data_ptr(), nullptr));
+    return result;
+}
+
+}  // namespace lten
+
+// ---- free functions ----------------------------------------------------------------------------------------------------
+namespace {
+
+// -1: host memory; otherwise the CUDA device that owns the pointer.
+int device_of(const void *p)
+{
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return (a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged) ? a.device : -1;
+}
+
+void fail(const char *msg, const char *func)
+{
+    fprintf(stderr, "[Error] Function: %s Msg: %s\n", func, msg);
+    throw lten::ExceptionInfo(msg, __FILE__, func, 0);
+}
+
+#define FREE_LTQ_CALL(expr) \
+    do {                    \
+        if ((expr) != LTQ_OK) fail(ltq_last_error(), __func__); \
+    } while (0)
+
+}  // namespace
+
+void ComputeQuantizationParams(float min_val, float max_val, QuantizationParams *qp)
+{
+    FREE_LTQ_CALL(ltq_compute_qparams(min_val, max_val, qp));
+}
+
+void GetMinMax(float *data, uint64_t len, float *min_val, float *max_val)
+{
+    if (!data || !min_val || !max_val) fail("Invalid argument", __func__);  // l-ten/utils.cpp:204-207
+    const int dev = device_of(data);
+    if (dev < 0) fail("GetMinMax: host data is not computed by this build; pass a device pointer", __func__);
+    float *mm = nullptr, h[2];
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(dev);
+    if (cudaMalloc(&mm, 2 * sizeof(float)) != cudaSuccess) fail("cudaMalloc failed", __func__);
+    const int rc = ltq_get_min_max(data, len, mm, dev, nullptr);
+    const cudaError_t ce = cudaMemcpy(h, mm, sizeof h, cudaMemcpyDeviceToHost);
+    cudaFree(mm);
+    cudaSetDevice(prev);
+    if (rc != LTQ_OK) fail(ltq_last_error(), __func__);
+    if (ce != cudaSuccess) fail(cudaGetErrorString(ce), __func__);
+    *min_val = h[0];
+    *max_val = h[1];
+}
+
+void Quantize(float *data, uint8_t *q_data, uint64_t len, QuantizationParams *qp)
+{
+    const int dev = device_of(data);
+    if (dev < 0 || device_of(q_data) != dev) fail("Quantize: both buffers must be on the same CUDA device", __func__);
+    FREE_LTQ_CALL(ltq_quantize_u8(data, q_data, len, qp, dev, nullptr));
+}
+
+void Quantize(float *data, int *q_data, uint64_t len, QuantizationParams *qp)
+{
+    const int dev = device_of(data);
+    if (dev < 0 || device_of(q_data) != dev) fail("Quantize: both buffers must be on the same CUDA device", __func__);
+    FREE_LTQ_CALL(ltq_quantize_i32(data, q_data, len, qp, dev, nullptr));
+}
+
+void Dequantize(float *data, uint8_t *q_data, uint64_t len, QuantizationParams *qp)
+{
+    const int dev = device_of(q_data);
+    if (dev < 0 || device_of(data) != dev) fail("Dequantize: both buffers must be on the same CUDA device", __func__);
+    FREE_LTQ_CALL(ltq_dequantize(data, q_data, len, qp, dev, nullptr));
+}

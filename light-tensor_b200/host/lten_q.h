@@ -1,0 +1,141 @@
+// C++ host side of the quantized fully-connected path: a self-contained mirror of the part of l-ten's public surface
+// that this path touches, driving libltq (include/ltq.h) for everything that computes.
+//
+//   lten::Tensor / TensorOps / AllocateTensor / TensorFromBuffer      l-ten/tensor.h:33-81,1478-1482, tensorimpl.h:46-63
+//   lten::Module, lten::FullyConnected_q                              l-ten/layers.h:14-31,69-106
+//   QuantizationParams                                                l-ten/math_fns.h:12-16
+//   GetMinMax / ComputeQuantizationParams / Quantize / Dequantize     l-ten/utils.h:23-27
+//
+// Same names, argument meaning and error behaviour (LTEN_ERR prints to stderr and throws lten::ExceptionInfo,
+// l-ten/error.h:78-93), so code written against l-ten's quantized layer compiles against this header.  What differs:
+// FullyConnected_q::to(GPU, idx) works, forward() takes GPU tensors, and the free functions take DEVICE pointers
+// (classified with cudaPointerGetAttributes).  There is no CPU compute path: forward() on a CPU tensor and the free
+// functions on host buffers throw; only ComputeQuantizationParams, which works on two scalars, runs on the host.
+#ifndef LTEN_Q_H
+#define LTEN_Q_H
+
+#include <stdint.h>
+
+#include <initializer_list>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/ltq.h"
+
+typedef ltq_qparams QuantizationParams;  // same layout as l-ten/math_fns.h:12-16
+
+namespace lten {
+
+enum device { CPU, GPU };
+enum dtype { FLOAT32, INT32, UINT8 };
+enum { MAX_DIMS = 16 };
+
+class ExceptionInfo : public std::exception {
+public:
+    ExceptionInfo(const char *msg, const char *file, const char *func, int line);
+    const char *what() const noexcept override { return text_.c_str(); }
+    const char *get_message() const { return msg_.c_str(); }
+
+private:
+    std::string msg_, text_;
+};
+
+struct TensorOps {
+    dtype data_type = FLOAT32;
+    device device_type = CPU;
+    int device_index = 0;
+    bool alloc_gradient_buffer = false;
+};
+
+// Value handle over reference-counted storage (the role of intrusive_ptr<TensorImplBase> in l-ten).
+class Tensor {
+public:
+    Tensor() {}
+    void *get_data_ptr() const;
+    uint64_t get_numels() const;
+    const uint64_t *get_sizes() const;
+    int get_ndims() const;
+    dtype get_data_type() const;
+    device get_device() const;
+    int get_device_index() const;
+    // Copies to the target device (synchronous cudaMemcpy, as l-ten/tensorimpl.cpp:311-412 does).
+    Tensor to(device target_device, int target_device_index = 0) const;
+    Tensor reshape(const std::initializer_list<uint64_t> &dims) const;
+    bool defined() const { return impl_ != nullptr; }
+
+private:
+    struct Impl;
+    std::shared_ptr<Impl> impl_;
+    friend Tensor AllocateTensor(const uint64_t *, int, TensorOps *);
+    friend Tensor TensorFromBuffer(const uint64_t *, int, void *, bool, TensorOps *);
+};
+
+Tensor AllocateTensor(const std::initializer_list<uint64_t> &dims, TensorOps *options_ptr = nullptr);
+Tensor AllocateTensor(const uint64_t *dims_ptr, int ndims, TensorOps *options_ptr = nullptr);
+Tensor TensorFromBuffer(const std::initializer_list<uint64_t> &dims, void *data_ptr, bool own_memory = false,
+                        TensorOps *options_ptr = nullptr);
+Tensor TensorFromBuffer(const uint64_t *dims_ptr, int ndims, void *data_ptr, bool own_memory = false,
+                        TensorOps *options_ptr = nullptr);
+
+class Module {
+public:
+    Module() {}
+    virtual ~Module() {}
+    virtual bool init() = 0;
+    virtual std::vector<Tensor *> get_all_weights() = 0;
+    virtual void clear_gradients() = 0;
+    virtual void to(device target_device, int target_device_index = 0) = 0;
+    void train(bool is_training) { is_training_ = is_training; }
+    virtual void set_qparams_in(QuantizationParams) {}
+    virtual void set_qparams_out(QuantizationParams) {}
+    virtual void set_qparams_params(QuantizationParams *, int) {}
+
+protected:
+    bool is_training_ = true;
+};
+
+class FullyConnected_q : public Module {
+public:
+    FullyConnected_q(int64_t input_features, int64_t output_features, bool use_bias = false, dtype data_type = FLOAT32);
+    FullyConnected_q(const FullyConnected_q &other);             // copyable before init(), as register_module needs
+    FullyConnected_q &operator=(const FullyConnected_q &other);  // (l-ten/net.h:37-76)
+    ~FullyConnected_q();
+
+    bool init();
+    Tensor forward(Tensor &input);
+    Tensor *get_weights() { return weight_ptr_; }
+    Tensor *get_bias() { return bias_ptr_; }
+    void clear_gradients() {}
+    std::vector<Tensor *> get_all_weights();
+    void to(device target_device, int target_device_index = 0);
+    bool is_using_bias() { return use_bias_; }
+
+    void set_qparams_in(QuantizationParams qparams_in) { qparams_in_ = qparams_in; }
+    void set_qparams_out(QuantizationParams qparams_out) { qparams_out_ = qparams_out; }
+    void set_qparams_params(QuantizationParams *qparams, int count);
+
+    // Additive: what the fused epilogue writes.  Defaults reproduce the reference (uint8, no ReLU, wrapping cast).
+    void set_output(ltq_out_mode mode, bool relu = false, bool saturate = false);
+
+private:
+    uint64_t input_features_, output_features_;
+    Tensor *weight_ptr_ = nullptr, *bias_ptr_ = nullptr;
+    bool use_bias_;
+    QuantizationParams qparams_in_{1.f, 0}, qparams_out_{1.f, 0}, qparams_wt_{1.f, 0};
+    ltq_layer *handle_ = nullptr;  // created by to(GPU), never by the constructor
+    ltq_out_mode out_mode_ = LTQ_OUT_U8;
+    unsigned flags_ = 0;
+};
+
+}  // namespace lten
+
+// l-ten/utils.h:23-27 with device pointers (both buffers of a call on the same device).  Results that the reference
+// returns through host scalars (min, max, the parameters) come back to the host.
+void GetMinMax(float *data, uint64_t len, float *min_val, float *max_val);
+void Quantize(float *data, int *q_data, uint64_t len, QuantizationParams *qp);
+void Quantize(float *data, uint8_t *q_data, uint64_t len, QuantizationParams *qp);
+void Dequantize(float *data, uint8_t *q_data, uint64_t len, QuantizationParams *qp);
+void ComputeQuantizationParams(float min_val, float max_val, QuantizationParams *qp);
+
+#endif  // LTEN_Q_H
