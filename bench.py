@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the uint8 quantized fully-connected forward path (libltq, sm_100a).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_mnist|mlp_block]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_block|mlp_mnist] [--shard rows|cols]
     python bench.py --impl reference ...      # the reference's own CPU code on the host cores
 
 One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch: activation quantise
@@ -164,24 +164,105 @@ def workload_name(wl):
 # ---------------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------------------
-def run_gpu(args):
-    import torch
+# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/ (same command lines as the bench, fewer steps).
+NCU_TRAFFIC = {"gemm_tc_pair_kernel": 34.5e6, "gemv_kernel": 45.3e6}
+
+
+class Harness:
+    """Device set-up, barriers, CUDA-graph timing and clock sampling shared by the workloads."""
+
+    def __init__(self, args):
+        import torch
+        self.torch = torch
+        self.args = args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback (use --impl reference)")
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+        self.sampler = ClockSampler(self.local)
+
+    def sync_all(self):
+        self.torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False):
+        """ms per step over EXACTLY `steps` steps, CUDA events on the launching stream, max over ranks.  The steps are
+        captured once into a CUDA graph (the kernels run for tens of microseconds; launching them one by one from
+        Python would time the interpreter) and the graph is replayed once untimed before the timed replay.  With
+        `sample_clocks` nvidia-smi runs through the warm-up, the timed replay and ~0.4 s of further replays of the same
+        graph (the timed region alone is too short to catch more than a sample or two)."""
+        torch = self.torch
+        if sample_clocks and self.rank == 0:
+            self.sampler.start()
+        for i in range(warmup):
+            fn(i)
+        self.sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gr = None
+        if graph:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for i in range(steps):
+                    fn(warmup + i)
+            gr.replay()
+            self.sync_all()
+            e0.record()
+            gr.replay()
+            e1.record()
+        else:
+            e0.record()
+            for i in range(steps):
+                fn(warmup + i)
+            e1.record()
+        self.sync_all()
+        ms = e0.elapsed_time(e1)
+        if sample_clocks:
+            t_end = time.time() + 0.4
+            while time.time() < t_end:
+                if gr is not None:
+                    gr.replay()
+                else:
+                    fn(0)
+                torch.cuda.synchronize()
+            self.clocks = self.sampler.stop() if self.rank == 0 else None
+        if self.dist is not None:
+            t = torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    def finish(self, line):
+        if self.rank == 0:
+            print(json.dumps(line))
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+def base_line(h, args, value, unit, ms_step, scaling, config, **extra):
+    line = {"metric": "int8_fc_tops", "value": value, "unit": unit, "n_gpus": h.world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling,
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": config}
+    line.update(extra)
+    return line
+
+
+def run_linear(args):
+    """square_4096 (default) and skinny: one quantized linear per step."""
     import ltq
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback (use --impl reference)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    ltq.lib()
+    h = Harness(args)
+    torch, dev, world = h.torch, h.dev, h.world
     pk = peaks()
-
     wl = args.workload
     if wl == "skinny":
         M, K, N = args.m, 4096, 11008
@@ -191,7 +272,7 @@ def run_gpu(args):
         M = K = N = 4096
         out_mode, out_dtype = ltq.OUT_U8, torch.uint8
         sets = 4       # 4 x (64 MB fp32 activations + 16 MB weights + outputs) = 448 MB > 126 MB L2
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    g = torch.Generator(device=dev).manual_seed(1234 + h.rank)
     xs = [torch.randn((M, K), generator=g, device=dev) for _ in range(sets)]
     w32 = [torch.randn((N, K), generator=g, device=dev) * 0.02 for _ in range(sets)]
     layers, qps_x = [], []
@@ -199,13 +280,13 @@ def run_gpu(args):
         qw = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(w32[i])))
         wq = ltq.Quantize(w32[i], qw)
         qx = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(xs[i])))
-        h = ltq.LayerHandle(local, K, N)
-        h.set_weights(wq, None)
+        lh = ltq.LayerHandle(h.local, K, N)
+        lh.set_weights(wq, None)
         # output qparams calibrated from the fp32 product of a row sample (static, as the reference calibrates)
         ref = xs[i][:256] @ w32[i].t()
         qo = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(ref)))
-        h.set_qparams(qx, qw, qo)
-        layers.append(h)
+        lh.set_qparams(qx, qw, qo)
+        layers.append(lh)
         qps_x.append(qx)
     del w32
     xq = [torch.empty((M, K), dtype=torch.uint8, device=dev) for _ in range(sets)]
@@ -221,128 +302,200 @@ def run_gpu(args):
         s = i % sets
         layers[s].forward(xq[s], out_mode, 0, asum=asum[s], out=outs[s])
 
-    def sync_all():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup, graph=True):
-        """ms per step over EXACTLY `steps` steps, CUDA events on the launching stream, max over ranks.  The steps are
-        captured once into a CUDA graph (the kernels run for tens of microseconds; launching them one by one from
-        Python would time the interpreter) and the graph is replayed once untimed before the timed replay."""
-        for i in range(warmup):
-            fn(i)
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if graph:
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                for i in range(steps):
-                    fn(warmup + i)
-            gr.replay()
-            sync_all()
-            e0.record()
-            gr.replay()
-            e1.record()
-        else:
-            e0.record()
-            for i in range(steps):
-                fn(warmup + i)
-            e1.record()
-        sync_all()
-        ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps
-
-    sampler = ClockSampler(local)
     launches0 = ltq.kernel_launches()
-    if rank == 0:
-        sampler.start()
-    ms_step = timed(step, args.steps, args.warmup, graph=not args.no_graph)
-    # kernels per timed region: warm-up steps, the capture pass and (with a graph) two replays all launch the same list
+    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    # kernels per timed region: warm-up steps and the capture pass each launch the same list; replays re-run it
     launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
-    ms_gemm = timed(gemm_only, args.steps, max(3, args.warmup), graph=not args.no_graph)
-    clocks = sampler.stop() if rank == 0 else None
-    for h in layers:
-        h.check()
+    ms_gemm = h.timed(gemm_only, args.steps, max(3, args.warmup), graph=not args.no_graph)
+    for lh in layers:
+        lh.check()
 
     ops = 2.0 * M * N * K
     tops = ops / (ms_step * 1e-3) / 1e12 * world
     gemm_tops = ops / (ms_gemm * 1e-3) / 1e12
 
     # ---- end to end through the FullyConnected_q mirror with host buffers -----------------------------------------
-    fc = ltq.FullyConnected_q(K, N, False)
-    fc.init()
-    fc.weight_ptr_ = layers[0]._keep[0].view(1, 1, N, K)  # device weights already quantized above
-    fc._handle = layers[0]
-    fc.set_output(out_mode)
-    host_x = [torch.randn((M, K)).pin_memory() for _ in range(2)]
-    host_out = torch.empty((M, N), dtype=out_dtype).pin_memory()
-    dev_x = torch.empty((M, K), device=dev)
-
-    def e2e_step(i):
-        dev_x.copy_(host_x[i % 2], non_blocking=True)
-        q, s = ltq.quantize_rows(dev_x, qp=qps_x[0], q=xq[0], asum=asum[0])
-        y = fc.forward(q.view(1, M, K), asum=s)
-        host_out.copy_(y.view(M, N), non_blocking=True)
-
-    if args.no_e2e:
-        ms_e2e = float("nan")
-    else:
-        ms_e2e = timed(e2e_step, max(3, args.steps // 2), 3, graph=False)
-    e2e_tops = ops / (ms_e2e * 1e-3) / 1e12 * world
-    fc._handle = None
-
-    if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
-
     esize = 4 if out_mode == ltq.OUT_F32 else 1
+    e2e = None
+    if not args.no_e2e:
+        fc = ltq.FullyConnected_q(K, N, False)
+        fc.init()
+        fc.weight_ptr_ = layers[0]._keep[0].view(1, 1, N, K)  # device weights already quantized above
+        fc._handle = layers[0]
+        fc.set_output(out_mode)
+        host_x = [torch.randn((M, K)).pin_memory() for _ in range(2)]
+        host_out = torch.empty((M, N), dtype=out_dtype).pin_memory()
+        dev_x = torch.empty((M, K), device=dev)
+
+        def e2e_step(i):
+            dev_x.copy_(host_x[i % 2], non_blocking=True)
+            q, s = ltq.quantize_rows(dev_x, qp=qps_x[0], q=xq[0], asum=asum[0])
+            y = fc.forward(q.view(1, M, K), asum=s)
+            host_out.copy_(y.view(M, N), non_blocking=True)
+
+        ms_e2e = h.timed(e2e_step, max(3, args.steps // 2), 3, graph=False)
+        fc._handle = None
+        e2e = {"value": ops / (ms_e2e * 1e-3) / 1e12 * world, "unit": "TOPS", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * esize}
+
     if wl == "skinny":
-        alg_bytes = N * K + M * K + esize * M * N + 4 * N + 4 * M  # weights + acts + out + wsum + asum
+        alg_bytes = N * K + M * K + esize * M * N + 8 * N + 4 * M  # weights + acts + out + (wsum, bias) + asum
         achieved = alg_bytes / (ms_gemm * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "traffic": None, "kernel": "gemv_kernel",
-                "peak_source": f"{pk['source']} HBM copy", "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS}
+                "frac": achieved / pk["hbm_gbs"], "traffic": NCU_TRAFFIC["gemv_kernel"], "kernel": "gemv_kernel",
+                "algorithmic_bytes": alg_bytes, "ms": ms_gemm, "peak_source": f"{pk['source']} HBM copy",
+                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS}
     else:
         int8_peak = 2.0 * pk["bf16_sustained"]  # no INT8 figure is measured on this pool: 2 x measured bf16 (sustained)
         roof = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
-                "frac": gemm_tops / int8_peak, "traffic": None, "kernel": "gemm_tc_kernel<256,u8>",
-                "peak_source": f"2 x {pk['source']} bf16 sustained ({pk['bf16_sustained']} TFLOP/s); burst would be "
-                               f"{2 * pk['bf16']}", "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS}
+                "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC["gemm_tc_pair_kernel"],
+                "kernel": "gemm_tc_pair_kernel<240,u8>", "algorithmic_ops": ops, "ms": ms_gemm,
+                "peak_source": f"2 x {pk['source']} bf16 sustained ({pk['bf16_sustained']} TFLOP/s); 2 x burst would "
+                               f"be {2 * pk['bf16']}", "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS}
 
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if h.rank == 0 and world == 1 and not args.no_cpu_baseline:
         rows = 16 if wl == "skinny" else 512
         secs, kind, m, n, k = cpu_forward_seconds(wl, rows)
         cpu = {"value": 2.0 * m * n * k / secs / 1e12, "unit": "TOPS", "cores": 1, "kind": kind,
                "seconds": secs, "sample": f"FullyConnected_q::forward on {m} rows of the workload (N={n}, K={k}), "
                f"1 thread of {os.cpu_count()} host cores; the reference path is single-threaded by construction"}
 
-    line = {
-        "metric": "int8_fc_tops", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": workload_name(wl), "M_per_gpu": M, "N": N, "K": K, "sharding": "rows (M) per GPU, "
-                   "weights replicated, no collective" if world > 1 else "single GPU",
-                   "l2": f"rotating {sets} distinct input/weight/output sets, larger than L2 in total",
-                   "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue",
-                   "timing": "CUDA events around one replay of a CUDA graph holding exactly `steps` steps"
-                   if not args.no_graph else "CUDA events around `steps` eager launches"},
-        "gemm_only": {"ms": ms_gemm, "tops": gemm_tops},
-        "roofline": roof, "cpu_baseline": cpu,
-        "e2e": {"value": e2e_tops, "unit": "TOPS", "ms_per_step": ms_e2e, "h2d_bytes_per_step": M * K * 4,
-                "d2h_bytes_per_step": M * N * esize},
-        "gpu_launches": int(launches), "clocks": clocks,
-    }
-    print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    cfg = {"workload": workload_name(wl), "M_per_gpu": M, "N": N, "K": K,
+           "sharding": "rows (M) per GPU, weights replicated, no collective" if world > 1 else "single GPU",
+           "l2": f"rotating {sets} distinct input/weight/output sets, larger than L2 in total",
+           "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue",
+           "timing": "CUDA events around one replay of a CUDA graph holding exactly `steps` steps"
+           if not args.no_graph else "CUDA events around `steps` eager launches"}
+    h.finish(base_line(h, args, tops, "TOPS", ms_step, "weak", cfg, gemm_only={"ms": ms_gemm, "tops": gemm_tops},
+                       roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches),
+                       clocks=getattr(h, "clocks", None)))
+
+
+def run_mlp_block(args):
+    """8192 -> 32768 -> 8192 quantized MLP block with ReLU over M_total tokens (configs[4]), sharded over the ranks by
+    activation rows (no collective) or by weight columns (all-gather of output slices over NCCL + relayout).  Total work
+    is fixed, so scaling is strong."""
+    import ltq
+    from ltq import sharded
+    h = Harness(args)
+    torch, dev, world, rank = h.torch, h.dev, h.world, h.rank
+    Mt, K1, N1, N2 = args.m_total, args.d_model, 4 * args.d_model, args.d_model
+    g = torch.Generator(device=dev).manual_seed(77)          # weights identical on every rank
+    w1 = torch.randn((N1, K1), generator=g, device=dev) * 0.01
+    w2 = torch.randn((N2, N1), generator=g, device=dev) * 0.01
+    qw1 = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(w1)))
+    qw2 = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(w2)))
+    w1q, w2q = ltq.Quantize(w1, qw1), ltq.Quantize(w2, qw2)
+    # static calibration on a row sample, as the reference calibrates offline: input range and hidden (post-ReLU) range
+    gs = torch.Generator(device=dev).manual_seed(78)
+    sample = torch.randn((256, K1), generator=gs, device=dev)
+    qx = ltq.ComputeQuantizationParams(-5.5, 5.5)            # N(0,1) activations: fixed calibrated range
+    hid = torch.relu(sample @ w1.t())
+    qh = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(hid)))
+    del w1, w2, hid, sample
+    if args.shard == "rows":
+        r0, r1 = sharded.shard_range(Mt, rank, world)
+        M = r1 - r0
+        l1 = sharded.RowShardedLinear(w1q, None, qx, qw1, qh)
+        l2 = sharded.RowShardedLinear(w2q, None, qh, qw2, ltq.QParams(1.0, 0))
+    else:
+        M = Mt
+        l1 = sharded.ColShardedLinear(w1q, None, N1, qx, qw1, qh)
+        l2 = sharded.ColShardedLinear(w2q, None, N2, qh, qw2, ltq.QParams(1.0, 0))
+        del w1q, w2q
+    gx = torch.Generator(device=dev).manual_seed(1000 + (rank if args.shard == "rows" else 0))
+    x = torch.randn((M, K1), generator=gx, device=dev)
+    xq = torch.empty((M, K1), dtype=torch.uint8, device=dev)
+    asum = torch.empty(M, dtype=torch.int32, device=dev)
+    if args.shard == "rows":
+        hq = torch.empty((M, N1), dtype=torch.uint8, device=dev)
+        y = torch.empty((M, N2), dtype=torch.float32, device=dev)
+
+        def step(i):
+            ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
+            l1.layer.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=hq)
+            l2.layer.forward(hq, ltq.OUT_F32, 0, out=y)
+    else:
+        n1l, n2l = N1 // world, N2 // world
+        loc1 = torch.empty((M, n1l), dtype=torch.uint8, device=dev)
+        gat1 = torch.empty((world, M, n1l), dtype=torch.uint8, device=dev)
+        hq = torch.empty((M, N1), dtype=torch.uint8, device=dev)
+        loc2 = torch.empty((M, n2l), dtype=torch.float32, device=dev)
+        gat2 = torch.empty((world, M, n2l), dtype=torch.float32, device=dev)
+        y = torch.empty((M, N2), dtype=torch.float32, device=dev)
+
+        def step(i):
+            ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
+            hh = l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, out=hq, gathered=gat1, local=loc1)
+            l2.forward(hh, ltq.OUT_F32, 0, out=y, gathered=gat2, local=loc2)
+
+    launches0 = ltq.kernel_launches()
+    # NCCL collectives are not captured here: the column-sharded step is timed over eager launches
+    use_graph = (not args.no_graph) and args.shard == "rows"
+    ms_step = h.timed(step, args.steps, args.warmup, graph=use_graph, sample_clocks=True)
+    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
+    ops = 2.0 * Mt * (K1 * N1 + N1 * N2)
+    tops = ops / (ms_step * 1e-3) / 1e12
+    cfg = {"workload": f"mlp_block (configs[4]): {K1}->{N1}->{N2} with ReLU, {Mt} tokens in total, uint8 hidden "
+                       "activations via fused requant, fp32 output",
+           "sharding": {"rows": "activation rows split over the ranks, weights replicated, no collective",
+                        "cols": "weight columns split over the ranks, all-gather of output slices (NCCL) + relayout "
+                                "after each layer"}[args.shard],
+           "M_per_gpu": M, "l2": "operands far larger than L2 (x, hidden and output are each >= 0.25 GB per rank)",
+           "step": "quantize_rows + layer 1 (uint8, ReLU) + layer 2 (fp32)",
+           "timing": "CUDA graph replay" if use_graph else "eager launches (NCCL inside the step)"}
+    h.finish(base_line(h, args, tops, "TOPS", ms_step, "strong", cfg, samples_per_s=Mt / (ms_step * 1e-3),
+                       gpu_launches=int(launches), clocks=getattr(h, "clocks", None), e2e=None, roofline=None,
+                       cpu_baseline=None))
+
+
+def run_mlp_mnist(args):
+    """MNIST-shaped 784-512-512-10 MLP, batch 64 (configs[0]): three launches per batch; every rank is an independent
+    replica with its own batch stream."""
+    import ltq
+    from ltq import workloads
+    h = Harness(args)
+    torch, dev, world = h.torch, h.dev, h.world
+    x, layers = workloads.mlp_mnist(seed=0, batch=64)
+    xd = torch.from_numpy(x).to(dev)
+    acts = [xd]
+    for (w, b) in layers:
+        acts.append(torch.relu(acts[-1] @ torch.from_numpy(w).to(dev).t() + torch.from_numpy(b).to(dev)))
+    qa = [ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(a.contiguous()))) for a in acts]
+    hs = []
+    for li, (w, b) in enumerate(layers):
+        wd = torch.from_numpy(w).to(dev)
+        qw = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(wd)))
+        wq = ltq.Quantize(wd, qw)
+        bq = ltq.QuantizeInt32(torch.from_numpy(b).to(dev), ltq.QParams(np.float32(qa[li].scale) * np.float32(qw.scale), 0))
+        lh = ltq.LayerHandle(h.local, w.shape[1], w.shape[0])
+        lh.set_weights(wq, bq)
+        lh.set_qparams(qa[li], qw, qa[li + 1])
+        hs.append(lh)
+    xq = torch.empty((64, 784), dtype=torch.uint8, device=dev)
+    asum = torch.empty(64, dtype=torch.int32, device=dev)
+    h1 = torch.empty((64, 512), dtype=torch.uint8, device=dev)
+    h2 = torch.empty((64, 512), dtype=torch.uint8, device=dev)
+    y = torch.empty((64, 10), dtype=torch.float32, device=dev)
+
+    def step(i):
+        ltq.quantize_rows(xd, qp=qa[0], q=xq, asum=asum)
+        hs[0].forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=h1)
+        hs[1].forward(h1, ltq.OUT_U8, ltq.FLAG_RELU, out=h2)
+        hs[2].forward(h2, ltq.OUT_F32, 0, out=y)
+
+    launches0 = ltq.kernel_launches()
+    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
+    ops = 2.0 * 64 * (784 * 512 + 512 * 512 + 512 * 10)
+    cfg = {"workload": "mlp_mnist (configs[0]): 784-512-512-10, batch 64, uint8 hidden activations with fused ReLU, "
+                       "fp32 logits", "sharding": "independent replicas, one batch stream per GPU",
+           "l2": "the whole model (0.67 MB) is L2-resident by nature; this configuration is launch-latency bound",
+           "step": "quantize_rows + 3 quantized linears (6 kernels)", "timing": "CUDA graph replay"}
+    h.finish(base_line(h, args, ops / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
+                       samples_per_s=64 * world / (ms_step * 1e-3), gpu_launches=int(launches),
+                       clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))
 
 
 def main():
@@ -351,8 +504,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ltq", choices=["ltq", "reference"])
-    ap.add_argument("--workload", default="square_4096", choices=["square_4096", "skinny"])
+    ap.add_argument("--workload", default="square_4096", choices=["square_4096", "skinny", "mlp_block", "mlp_mnist"])
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
+    ap.add_argument("--m-total", type=int, default=65536, help="tokens of the mlp_block workload (all ranks together)")
+    ap.add_argument("--d-model", type=int, default=8192, help="width of the mlp_block workload (hidden = 4x)")
+    ap.add_argument("--shard", default="rows", choices=["rows", "cols"], help="mlp_block partitioning")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
@@ -360,8 +516,12 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "mlp_block":
+        run_mlp_block(args)
+    elif args.workload == "mlp_mnist":
+        run_mlp_mnist(args)
     else:
-        run_gpu(args)
+        run_linear(args)
 
 
 if __name__ == "__main__":

@@ -99,6 +99,13 @@ int ltq_quantize_rows_u8(const float *x_dev, uint64_t M, uint64_t K, const ltq_q
  * l-ten/math_fns.cpp:1362-1380 before their -z factors). */
 int ltq_row_sums_u8(const uint8_t *m_dev, uint64_t rows, uint64_t cols, int32_t *sums_dev, int device, void *stream);
 
+/* Column (N) sharding support; no counterpart in the reference, which has no multi-device code at all.  After an
+ * all-gather of per-rank output slices [M, N/parts] the data sits as [parts][M][part_row_bytes]; this writes the
+ * row-major [M][parts * part_row_bytes] that the next layer (or the caller) expects.  Element type does not matter:
+ * part_row_bytes = (N / parts) * sizeof(element). */
+int ltq_interleave_column_blocks(const void *gathered_dev, void *out_dev, uint64_t parts, uint64_t M,
+                                 uint64_t part_row_bytes, int device, void *stream);
+
 /* ---- the reference kernel call, argument for argument ---------------------------------------------------------- */
 
 /* quantized_matmul, l-ten/math_fns.h:104 / l-ten/math_fns.cpp:1311-1478, all four transpose variants.

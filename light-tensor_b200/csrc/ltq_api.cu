@@ -213,6 +213,16 @@ int ltq_row_sums_u8(const uint8_t *m_dev, uint64_t rows, uint64_t cols, int32_t 
     return LTQ_OK;
 }
 
+int ltq_interleave_column_blocks(const void *gathered_dev, void *out_dev, uint64_t parts, uint64_t M,
+                                 uint64_t part_row_bytes, int device, void *stream)
+{
+    LTQ_REQUIRE(gathered_dev && out_dev && gathered_dev != out_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (parts == 0 || M == 0 || part_row_bytes == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(launch_interleave_blocks(gathered_dev, out_dev, parts, M, part_row_bytes, (cudaStream_t)stream));
+    return LTQ_OK;
+}
+
 // ---- GEMM dispatch shared by the stateless call and the layer ------------------------------------------------------
 static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
                        const Epilogue &epi, void *out, unsigned flags, ltq_layer *layer, cudaStream_t stream)

@@ -338,6 +338,41 @@ __global__ void __launch_bounds__(256) scale_i32_kernel(int32_t *v, uint64_t n, 
     for (uint64_t i = tid; i < n; i += nth) v[i] = (int32_t)((uint32_t)v[i] * (uint32_t)factor);
 }
 
+// After an all-gather of column slices the output sits as [G][M][W bytes] (one plane per rank).  This puts it back into
+// the row-major [M][G * W] the next layer reads: dst[m][g * W + w] = src[g][m][w].  16-byte copies when W allows.
+__global__ void __launch_bounds__(256) interleave_blocks_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                               uint64_t G, uint64_t M, uint64_t W)
+{
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
+    if (W % 16 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+        const uint64_t wv = W / 16, total = G * M * wv;
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+        uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+        for (uint64_t i = tid; i < total; i += nth) {
+            // walk the destination in order (coalesced stores); reads are contiguous runs of W bytes
+            const uint64_t m = i / (G * wv), r = i % (G * wv), g = r / wv, w = r % wv;
+            d4[i] = __ldg(s4 + (g * M + m) * wv + w);
+        }
+    } else {
+        const uint64_t total = G * M * W;
+        for (uint64_t i = tid; i < total; i += nth) {
+            const uint64_t m = i / (G * W), r = i % (G * W), g = r / W, w = r % W;
+            dst[i] = src[(g * M + m) * W + w];
+        }
+    }
+}
+
+cudaError_t launch_interleave_blocks(const void *src, void *dst, uint64_t G, uint64_t M, uint64_t W, cudaStream_t stream)
+{
+    const uint64_t work = G * M * ((W + 15) / 16);
+    uint64_t want = (work + 255) / 256, cap = (uint64_t)sm_count() * 16;
+    int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+    interleave_blocks_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), G, M, W);
+    count_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_row_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream)
 {
     uint64_t want = (rows + 7) / 8;

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "ltq_dequantize": (_int, [_vp, _vp, _u64, _qp, _int, _vp]),
     "ltq_quantize_rows_u8": (_int, [_vp, _u64, _u64, _qp, _vp, _vp, _vp, _int, _vp]),
     "ltq_row_sums_u8": (_int, [_vp, _u64, _u64, _vp, _int, _vp]),
+    "ltq_interleave_column_blocks": (_int, [_vp, _vp, _u64, _u64, _u64, _int, _vp]),
     "ltq_quantized_matmul": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp, _vp,
                                     _int, _vp]),
     "ltq_quantized_matmul_static": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp,
