@@ -307,6 +307,8 @@ def run_linear(args):
     # kernels per timed region: warm-up steps and the capture pass each launch the same list; replays re-run it
     launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
     ms_gemm = h.timed(gemm_only, args.steps, max(3, args.warmup), graph=not args.no_graph)
+    ms_quant = h.timed(lambda i: ltq.quantize_rows(xs[i % sets], qp=qps_x[i % sets], q=xq[i % sets], asum=asum[i % sets]),
+                       args.steps, 3, graph=not args.no_graph)
     for lh in layers:
         lh.check()
 
@@ -367,7 +369,10 @@ def run_linear(args):
            "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue",
            "timing": "CUDA events around one replay of a CUDA graph holding exactly `steps` steps"
            if not args.no_graph else "CUDA events around `steps` eager launches"}
+    quant_bytes = 5.0 * M * K + 4.0 * M  # fp32 in, uint8 out, one int32 row sum per row
     h.finish(base_line(h, args, tops, "TOPS", ms_step, "weak", cfg, gemm_only={"ms": ms_gemm, "tops": gemm_tops},
+                       quantize_only={"ms": ms_quant, "gbs": quant_bytes / (ms_quant * 1e-3) / 1e9,
+                                      "frac_of_hbm_peak": quant_bytes / (ms_quant * 1e-3) / 1e9 / pk["hbm_gbs"]},
                        roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches),
                        clocks=getattr(h, "clocks", None)))
 

@@ -128,11 +128,70 @@ cudaError_t launch_qparams_from_minmax(const float *minmax, ltq_qparams *qp, cud
 }
 
 // ---- Quantize / Dequantize, l-ten/utils.cpp:228-264 -------------------------------------------------------------
-__device__ __forceinline__ uint32_t quant_u8(float x, float scale, float zpf)
+// round(v), half away from zero, for v in [0, 255] without the conversion unit: adding 2^23 rounds to the nearest integer
+// with ties to even; the only difference from half-away is a tie that went DOWN (v = r + 0.5 with r even), which is put
+// right by one comparison.  The integer is then read from the low mantissa bits.
+__device__ __forceinline__ uint32_t round_u8(float v)
+{
+    float r = __fadd_rn(__fadd_rn(v, 8388608.f), -8388608.f);
+    if (__fsub_rn(v, r) == 0.5f) r = __fadd_rn(r, 1.f);
+    return __float_as_uint(__fadd_rn(r, 8388608.f)) & 0xFFu;
+}
+
+// The reference's arithmetic to the letter (l-ten/utils.cpp:249-251): IEEE division, add, clamp, round.
+__device__ __forceinline__ uint32_t quant_u8_exact(float x, float scale, float zpf)
 {
     float v = __fadd_rn(zpf, __fdiv_rn(x, scale));
     v = fmaxf(0.f, fminf(255.f, v));
-    return (uint32_t)(int)roundf(v);
+    return round_u8(v);
+}
+
+// Multiplier for the screening step below, or 0 when the scale is too extreme for the screening bound to hold.
+__device__ __forceinline__ float quant_screen_inv(float scale)
+{
+    return (scale > 1e-30f && scale < 1e30f) ? __fdiv_rn(1.f, scale) : 0.f;
+}
+
+// Same result as quant_u8_exact, usually without the division (these kernels are bound by instruction issue, not by
+// HBM, and an IEEE division is half of their instructions).  x * (1/scale) differs from x / scale by at most 2^-22
+// relative; inside the clamp range that is less than 1.3e-4 absolute on v, so whenever the screened v lies farther than
+// 4e-4 from every half-integer k + 0.5 both round to the same byte (clamping is monotone and its edges 0 and 255 are
+// themselves 0.5 away from the nearest rounding boundary).  Elements closer than that, a few in ten thousand, take the
+// exact path.
+__device__ __forceinline__ uint32_t quant_u8(float x, float scale, float zpf, float inv)
+{
+    if (inv == 0.f) return quant_u8_exact(x, scale, zpf);
+    float v = __fadd_rn(zpf, __fmul_rn(x, inv));
+    v = fmaxf(0.f, fminf(255.f, v));
+    const float big = __fadd_rn(v, 8388608.f);
+    const float r = __fadd_rn(big, -8388608.f);            // nearest integer, |v - r| <= 0.5
+    const float d = fabsf(__fsub_rn(v, r));
+    if (__fsub_rn(0.5f, d) < 4e-4f) return quant_u8_exact(x, scale, zpf);
+    return __float_as_uint(big) & 0xFFu;
+}
+
+// Four elements at once, packed little-endian into one word.  The screening value may come from a fused multiply-add
+// (it only has to be within 1.3e-4 of the reference's v, and an FMA is closer than separate roundings); the bytes are
+// taken from the low mantissa bytes of v + 2^23 with three byte permutes.  If any of the four lies within 4e-4 of a
+// rounding boundary, all four are redone with the reference's exact sequence.
+__device__ __forceinline__ uint32_t quant4_u8(float4 x, float scale, float zpf, float inv)
+{
+    if (inv != 0.f) {
+        const float v0 = fmaxf(0.f, fminf(255.f, fmaf(x.x, inv, zpf))), v1 = fmaxf(0.f, fminf(255.f, fmaf(x.y, inv, zpf)));
+        const float v2 = fmaxf(0.f, fminf(255.f, fmaf(x.z, inv, zpf))), v3 = fmaxf(0.f, fminf(255.f, fmaf(x.w, inv, zpf)));
+        const float b0 = __fadd_rn(v0, 8388608.f), b1 = __fadd_rn(v1, 8388608.f);
+        const float b2 = __fadd_rn(v2, 8388608.f), b3 = __fadd_rn(v3, 8388608.f);
+        const float d0 = __fsub_rn(v0, __fadd_rn(b0, -8388608.f)), d1 = __fsub_rn(v1, __fadd_rn(b1, -8388608.f));
+        const float d2 = __fsub_rn(v2, __fadd_rn(b2, -8388608.f)), d3 = __fsub_rn(v3, __fadd_rn(b3, -8388608.f));
+        const bool near = fabsf(d0) > 0.4996f || fabsf(d1) > 0.4996f || fabsf(d2) > 0.4996f || fabsf(d3) > 0.4996f;
+        if (!near) {
+            const uint32_t lo = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x0040);  // bytes b0[0], b1[0]
+            const uint32_t hi = __byte_perm(__float_as_uint(b2), __float_as_uint(b3), 0x0040);
+            return __byte_perm(lo, hi, 0x5410);
+        }
+    }
+    return quant_u8_exact(x.x, scale, zpf) | (quant_u8_exact(x.y, scale, zpf) << 8) |
+           (quant_u8_exact(x.z, scale, zpf) << 16) | (quant_u8_exact(x.w, scale, zpf) << 24);
 }
 
 __device__ __forceinline__ int32_t quant_i32(float x, float scale, float zpf)
@@ -154,13 +213,11 @@ __global__ void __launch_bounds__(256) quantize_u8_kernel(const float *__restric
     const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
     const bool aligned = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
     uint64_t nvec = aligned ? len / 4 : 0;
+    const float inv = quant_screen_inv(scale);
     for (uint64_t i = tid; i < nvec; i += nth) {
-        float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
-        uint32_t p = quant_u8(v.x, scale, zpf) | (quant_u8(v.y, scale, zpf) << 8) | (quant_u8(v.z, scale, zpf) << 16) |
-                     (quant_u8(v.w, scale, zpf) << 24);
-        reinterpret_cast<uint32_t *>(q)[i] = p;
+        reinterpret_cast<uint32_t *>(q)[i] = quant4_u8(__ldg(reinterpret_cast<const float4 *>(x) + i), scale, zpf, inv);
     }
-    for (uint64_t i = nvec * 4 + tid; i < len; i += nth) q[i] = (uint8_t)quant_u8(x[i], scale, zpf);
+    for (uint64_t i = nvec * 4 + tid; i < len; i += nth) q[i] = (uint8_t)quant_u8(x[i], scale, zpf, inv);
 }
 
 __global__ void __launch_bounds__(256) quantize_i32_kernel(const float *__restrict__ x, int32_t *__restrict__ q,
@@ -232,6 +289,7 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float *__restr
         scale = qp_dev->scale;
         zpf = (float)(int)qp_dev->zero_point;
     }
+    const float inv = quant_screen_inv(scale);
     constexpr int ROWS_PER_CTA = 256 / TPR;
     const int lane = threadIdx.x % TPR;
     const int sub = threadIdx.x / TPR;
@@ -242,25 +300,38 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float *__restr
         const float *xr = x + row * K;
         uint8_t *qr = q + row * K;
         const bool aligned = (((uintptr_t)xr & 15) == 0) && (((uintptr_t)qr & 3) == 0);
-        const uint64_t nvec = aligned ? K / 4 : 0;
-        int32_t s = 0;
-        for (uint64_t i = lane; i < nvec; i += TPR) {
-            float4 v = __ldg(reinterpret_cast<const float4 *>(xr) + i);
-            uint32_t a = quant_u8(v.x, scale, zpf), b = quant_u8(v.y, scale, zpf), c = quant_u8(v.z, scale, zpf),
-                     d = quant_u8(v.w, scale, zpf);
-            s += (int32_t)(a + b + c + d);
-            reinterpret_cast<uint32_t *>(qr)[i] = a | (b << 8) | (c << 16) | (d << 24);
+        const uint32_t nvec = aligned ? (uint32_t)(K / 4) : 0u;
+        uint32_t s = 0;
+        const float4 *xv = reinterpret_cast<const float4 *>(xr);
+        uint32_t *qv = reinterpret_cast<uint32_t *>(qr);
+        // four independent 16-byte loads per thread before any arithmetic: the kernel lives on bytes in flight
+        for (uint32_t i0 = lane; i0 < nvec; i0 += 4 * TPR) {
+            float4 v4[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const uint32_t i = i0 + u * TPR;
+                v4[u] = i < nvec ? __ldg(xv + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const uint32_t i = i0 + u * TPR;
+                if (i < nvec) {
+                    const uint32_t p = quant4_u8(v4[u], scale, zpf, inv);
+                    s = __dp4a(p, 0x01010101u, s);
+                    qv[i] = p;
+                }
+            }
         }
-        for (uint64_t i = nvec * 4 + lane; i < K; i += TPR) {
-            uint32_t a = quant_u8(xr[i], scale, zpf);
-            s += (int32_t)a;
+        for (uint64_t i = (uint64_t)nvec * 4 + lane; i < K; i += TPR) {
+            uint32_t a = quant_u8(xr[i], scale, zpf, inv);
+            s += a;
             qr[i] = (uint8_t)a;
         }
         for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
         if (TPR == 32) {
-            if (lane == 0) asum[row] = s;
+            if (lane == 0) asum[row] = (int32_t)s;
         } else {
-            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = s;
+            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = (int32_t)s;
             __syncthreads();
             if (threadIdx.x == 0) {
                 int32_t t = 0;
