@@ -167,6 +167,15 @@ int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asu
  * kernel ran out since the last check.  Synchronises `stream`. */
 int ltq_layer_check(ltq_layer *layer, void *stream);
 
+/* Same check for a device without a layer at hand (the stateless entry points share the device's status word). */
+int ltq_device_check(int device, void *stream);
+
+/* Failure-path self-test, no counterpart in the reference: launches one warp that waits on a barrier nothing will
+ * ever arrive on.  The wait gives up after limit_us (1 .. 1 000 000), leaves code 0x900 in the device status word and
+ * the kernel returns normally; the next ltq_device_check / ltq_layer_check then reports LTQ_ERR_DEVICE_TIMEOUT and
+ * clears it.  Nothing hangs or faults: this is how the bounded waits inside the GEMM kernels are exercised. */
+int ltq_selftest_bounded_wait(int device, uint32_t limit_us, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

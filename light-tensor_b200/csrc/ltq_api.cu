@@ -407,18 +407,37 @@ int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asu
     return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi, out_dev, flags, layer, st);
 }
 
-int ltq_layer_check(ltq_layer *layer, void *stream)
+int ltq_device_check(int device, void *stream)
 {
-    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
-    LTQ_ENTER_DEVICE(layer->device);
+    LTQ_ENTER_DEVICE(device);
+    DeviceState *dev;
+    int rc = device_state(device, &dev);
+    if (rc != LTQ_OK) return rc;
     uint32_t code = 0;
-    LTQ_CUDA_TRY(cudaMemcpyAsync(&code, layer->dev->status, sizeof code, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    LTQ_CUDA_TRY(cudaMemcpyAsync(&code, dev->status, sizeof code, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     LTQ_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
     if (code) {
-        LTQ_CUDA_TRY(cudaMemsetAsync(layer->dev->status, 0, sizeof code, (cudaStream_t)stream));
+        LTQ_CUDA_TRY(cudaMemsetAsync(dev->status, 0, sizeof code, (cudaStream_t)stream));
         set_error("a bounded device-side wait expired (code 0x%x: role %u, slot %u)", code, code >> 8, code & 0xFF);
         return LTQ_ERR_DEVICE_TIMEOUT;
     }
+    return LTQ_OK;
+}
+
+int ltq_layer_check(ltq_layer *layer, void *stream)
+{
+    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    return ltq_device_check(layer->device, stream);
+}
+
+int ltq_selftest_bounded_wait(int device, uint32_t limit_us, void *stream)
+{
+    LTQ_REQUIRE(limit_us >= 1 && limit_us <= 1000000, LTQ_ERR_INVALID_ARG, "limit must be between 1 us and 1 s");
+    LTQ_ENTER_DEVICE(device);
+    DeviceState *dev;
+    int rc = device_state(device, &dev);
+    if (rc != LTQ_OK) return rc;
+    LTQ_CUDA_TRY(launch_bounded_wait_probe(dev->status, (uint64_t)limit_us * 1000ull, (cudaStream_t)stream));
     return LTQ_OK;
 }
 

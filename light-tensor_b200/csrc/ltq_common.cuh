@@ -155,6 +155,9 @@ cudaError_t launch_scale_i32(int32_t *v, uint64_t n, int32_t factor, cudaStream_
 // dst[m][g*W + w] = src[g][m][w] over bytes: undoes the plane-per-rank layout an all-gather of column slices leaves.
 cudaError_t launch_interleave_blocks(const void *src, void *dst, uint64_t G, uint64_t M, uint64_t W, cudaStream_t stream);
 
+// One warp waits on a barrier nothing arrives on, for at most limit_ns, then records code 0x900 in *status.
+cudaError_t launch_bounded_wait_probe(uint32_t *status, uint64_t limit_ns, cudaStream_t stream);
+
 cudaError_t launch_min_max(const float *data, uint64_t len, float *minmax, cudaStream_t stream);
 cudaError_t launch_qparams_from_minmax(const float *minmax, ltq_qparams *qp, cudaStream_t stream);
 cudaError_t launch_quantize_u8(const float *x, uint8_t *q, uint64_t len, const ltq_qparams &qp, cudaStream_t stream);

@@ -4,8 +4,8 @@
 //
 //  * operands are swapped for the tensor core: the WEIGHT rows are the 128-row (M) operand of tcgen05.mma and the
 //    <= 16 activation rows are its 16-column (N) operand, D[weight row, token] accumulating in TMEM.  Such a narrow MMA
-//    is short, but back-to-back MMAs into one accumulator serialise on the pipeline's latency (~120 cycles each), so
-//    the K steps rotate over 4 independent 16-column accumulators that the epilogue adds up;
+//    still costs its issuing thread ~70 cycles, so four warps issue: warp k owns the k-th 32-byte K step of every line
+//    and its own 16-column accumulator (the epilogue adds the four up), which keeps a stage's hold time short;
 //  * one persistent CTA per SM owns a contiguous band of weight rows (N split evenly in units of 8 rows; a band is one
 //    MMA tile of up to 128 rows, of which only the band's rows are loaded - the tile's remaining rows compute on stale
 //    shared memory and are never stored);
@@ -31,7 +31,7 @@ namespace ltq {
 
 namespace {
 
-constexpr int THREADS = 192;               // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
+constexpr int THREADS = 288;               // warp 0 producer, warps 1,6,7,8 MMA issuers, warps 2..5 epilogue
 constexpr int LINE = 128;                  // bytes of K per line (one swizzle atom wide)
 constexpr int XROWS = 16;                  // activation rows as seen by the MMA (N = 16), TMEM columns per accumulator
 constexpr int TILE_M = 128;                // MMA M: weight rows per tile (upper bound)
@@ -138,12 +138,12 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; s++) {
             mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, NACC);  // one commit per MMA-issuing warp
         }
         mbar_init(xbar, 1);
         for (int s = 0; s < 2; s++) {
-            mbar_init(tfull0 + 8 * s, 1);
-            mbar_init(tempty0 + 8 * s, 4);  // one arrival per epilogue warp
+            mbar_init(tfull0 + 8 * s, NACC);  // one commit per MMA-issuing warp
+            mbar_init(tempty0 + 8 * s, 4);    // one arrival per epilogue warp
         }
         misc[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -166,9 +166,11 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         if (lane == 0) {
             while (p_t < t_end && produce(false)) {}
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+    } else if (warp == 1 || warp >= 6) {
+        // ---------------- MMA issuers (warps 1, 6, 7, 8): warp-uniform loops, one elected lane issues ----------------
+        // Issuer k handles K step k (bytes [32k, 32k + 32) of every 128-byte line) into accumulator k.
         constexpr uint32_t idesc = make_idesc_i8(TILE_M, XROWS);
+        const uint32_t kstep = warp == 1 ? 0u : (uint32_t)(warp - 5);
         uint32_t st = 0, ph = 0, as = 0, aph = 0;
         bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(xbar, 0, abort_flag, status, 0x600u));
         for (uint32_t t = t_begin; ok && t < t_end; t++) {
@@ -177,25 +179,20 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
             ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
             if (!ok) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + as * (NACC * XROWS);
+            const uint32_t d_tmem = tmem_base + as * (NACC * XROWS) + kstep * XROWS;
             for (uint32_t kc = 0; kc < chunks; kc++) {
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t l0 = kc * lines, nl = (klines - l0) < lines ? (klines - l0) : lines;
-                for (uint32_t l = 0; l < nl; l++) {
-                    const uint64_t a_desc = make_smem_desc(ring + st * stage_bytes + l * line_stride);
-                    const uint64_t b_desc = make_smem_desc(xs + (l0 + l) * (xrows * LINE));
-                    // one accumulator per K step of a line; the first line overwrites, later lines accumulate
-                    const uint32_t gl = l0 + l, d_line = d_tmem, acc = gl >= 1u;
-                    if (elect_one()) {
-#pragma unroll
-                        for (int k = 0; k < LINE / 32; k++)
-                            umma_i8(d_line + k * XROWS, a_desc + 2u * k, b_desc + 2u * k, idesc, acc);
-                    }
-                    __syncwarp();
+                const uint64_t a_desc = make_smem_desc(ring + st * stage_bytes) + 2u * kstep;
+                const uint64_t b_desc = make_smem_desc(xs + l0 * (xrows * LINE)) + 2u * kstep;
+                if (elect_one()) {
+                    for (uint32_t l = 0; l < nl; l++)  // the first line of a tile overwrites, later lines accumulate
+                        umma_i8(d_tmem, a_desc + (uint64_t)((l * line_stride) >> 4), b_desc + (uint64_t)((l * xrows * LINE) >> 4),
+                                idesc, (l0 + l) >= 1u);
+                    umma_commit(empty0 + 8 * st);
                 }
-                if (elect_one()) umma_commit(empty0 + 8 * st);
                 __syncwarp();
                 if (++st == stages) { st = 0; ph ^= 1; }
             }
@@ -227,16 +224,15 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 tc_fence_after();
                 uint32_t v[XROWS];
                 const uint32_t tacc = tmem_base + ((q * 32u) << 16) + as * (NACC * XROWS);
+                uint32_t w1[XROWS], w2[XROWS], w3[XROWS];
+                static_assert(NACC == 4, "the epilogue adds four accumulators");
                 tmem_ld16(tacc, v);
+                tmem_ld16(tacc + XROWS, w1);
+                tmem_ld16(tacc + 2 * XROWS, w2);
+                tmem_ld16(tacc + 3 * XROWS, w3);
                 tmem_ld_wait();
 #pragma unroll
-                for (int a = 1; a < NACC; a++) {
-                    uint32_t w[XROWS];
-                    tmem_ld16(tacc + a * XROWS, w);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int m = 0; m < XROWS; m++) v[m] += w[m];
-                }
+                for (int m = 0; m < XROWS; m++) v[m] += w1[m] + w2[m] + w3[m];
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * as);  // accumulator buffer may be overwritten

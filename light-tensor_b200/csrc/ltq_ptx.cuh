@@ -46,7 +46,7 @@ __device__ __forceinline__ uint64_t global_ns()
 // The wall clock (%globaltimer) takes a few hundred nanoseconds to read, far longer than a barrier poll, so it is
 // consulted only once per 4096 failed polls: a wait that is satisfied quickly never touches it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code)
+                                          uint32_t *status, uint32_t code, uint64_t limit_ns = WAIT_LIMIT_NS)
 {
     uint64_t t0 = 0;
     for (uint32_t spin = 1;; spin++) {
@@ -56,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             const uint64_t now = global_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > WAIT_LIMIT_NS) {
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0u, code);
                 return false;

@@ -52,6 +52,8 @@ _SIGNATURES = {
     "ltq_layer_set_qparams": (_int, [_vp, _qp, _qp, _qp]),
     "ltq_layer_forward": (_int, [_vp, _vp, _vp, _u64, _vp, _int, C.c_uint, _vp, _vp]),
     "ltq_layer_check": (_int, [_vp, _vp]),
+    "ltq_device_check": (_int, [_int, _vp]),
+    "ltq_selftest_bounded_wait": (_int, [_int, C.c_uint32, _vp]),
 }
 DECLARED_SYMBOLS = tuple(_SIGNATURES)
 
