@@ -56,6 +56,8 @@ typedef enum ltq_out_mode {
 #define LTQ_FLAG_SATURATE 2u /* U8 cast clamps to [0,255]. Default (flag clear) reproduces the reference build's cast:
                                 truncate toward zero, keep the low byte when out of range */
 /* Kernel selection override, for tests and profiling (default: by shape). */
+#define LTQ_FLAG_BIAS_PER_CHANNEL 4u /* ltq_conv2d_forward only: bias[c] per output channel instead of the reference's
+                                       indexing by output position (see ltq_conv2d_forward) */
 #define LTQ_FLAG_FORCE_SIMT 0x100u  /* generic dp4a tile kernel */
 #define LTQ_FLAG_FORCE_TC 0x200u    /* tcgen05 kernel (needs K % 16 == 0) */
 #define LTQ_FLAG_FORCE_TC_PAIR 0x800u   /* with the tcgen05 path: the 2-CTA (cta_group::2) 256 x 256 tile kernel */
@@ -166,6 +168,50 @@ int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asu
 /* Reads (and clears) the layer's device status word: LTQ_OK, or LTQ_ERR_DEVICE_TIMEOUT when a bounded wait inside a
  * kernel ran out since the last check.  Synchronises `stream`. */
 int ltq_layer_check(ltq_layer *layer, void *stream);
+
+/* ---- quantized convolution: Conv2d_q (l-ten/layers.h:453-524, l-ten/conv2d.cpp:238-379) -------------------------
+ * The reference runs this layer on the CPU only ("Conv2d_q only supports the CPU device type", conv2d.cpp:371); here
+ * it is an im2col pass over the whole batch followed by one GEMM per image on the kernels of the linear path. */
+
+typedef struct ltq_conv2d ltq_conv2d;
+
+/* Conv2d_q's constructor + init (l-ten/layers.h:456-472, conv2d.cpp:238-264).  The handle owns derived state only:
+ * weight row sums, a zero-padded weight copy when C*kh*kw is not a multiple of 16, the patch buffer and patch sums
+ * (the reference's col_buffer_ptr_ and workspace_, grown on demand the same way). */
+int ltq_conv2d_create(ltq_conv2d **conv, int device, uint64_t channels_in, uint64_t channels_out, uint64_t kernel_h,
+                      uint64_t kernel_w, uint64_t pad_h, uint64_t pad_w, uint64_t stride_h, uint64_t stride_w);
+int ltq_conv2d_destroy(ltq_conv2d *conv);
+
+/* Bind device weights uint8 [channels_out, channels_in * kernel_h * kernel_w] (the {Cout, Cin, kh*kw} tensor of
+ * conv2d.cpp:247) and optional int32 bias [channels_out].  Synchronises `stream`. */
+int ltq_conv2d_set_weights(ltq_conv2d *conv, const uint8_t *w_dev, const int32_t *bias_dev, void *stream);
+
+/* set_qparams_in / set_qparams_out / set_qparams_params, l-ten/layers.h:505-507. */
+int ltq_conv2d_set_qparams(ltq_conv2d *conv, const ltq_qparams *qp_in, const ltq_qparams *qp_wt,
+                           const ltq_qparams *qp_out);
+
+/* height_out = (height_in + 2*pad_h - kernel_h) / stride_h + 1 and likewise for the width (conv2d.cpp:313-314). */
+int ltq_conv2d_output_size(const ltq_conv2d *conv, uint64_t height_in, uint64_t width_in, uint64_t *height_out,
+                           uint64_t *width_out);
+
+/* Conv2d_q::forward (conv2d.cpp:266-379): x_dev uint8 NCHW [batches, channels_in, height_in, width_in] ->
+ * out_dev [batches, channels_out, height_out, width_out], uint8 (LTQ_OUT_U8, what the reference returns), float or
+ * int32 by out_mode.  Arithmetic per image is quantized_matmul(false, false, M = channels_out, N = Ho*Wo,
+ * K = Cin*kh*kw, weights, im2col(image)) with qparams {weights, input, output}; padding taps are the byte 0
+ * (l-ten/im_col.h:27-28), not the input zero point.
+ * Bias: the reference adds bias[j] with j the output POSITION (math_fns.cpp:1469-1472) although the tensor holds
+ * channels_out values; that is reproduced as long as Ho*Wo <= channels_out and refused (LTQ_ERR_UNSUPPORTED) beyond,
+ * where the reference reads past the tensor.  LTQ_FLAG_BIAS_PER_CHANNEL adds bias[c] per output channel instead.
+ * LTQ_FLAG_RELU / LTQ_FLAG_SATURATE / LTQ_FLAG_FORCE_* act as in ltq_layer_forward. */
+int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches, uint64_t height_in, uint64_t width_in,
+                       int out_mode, unsigned flags, void *out_dev, void *stream);
+
+/* The patch gather on its own: im2col_cpu (l-ten/im_col.h:5-33) for `batches` images in one launch, written
+ * TRANSPOSED and padded: col_t[b][ho*Wo + wo][k], k = (c*kernel_h + i)*kernel_w + j, each row row_pitch bytes
+ * (= C*kh*kw rounded up to a multiple of 16) with a zero tail.  col_t_dev must be 16-byte aligned. */
+int ltq_im2col_t_u8(const uint8_t *im_dev, uint64_t batches, uint64_t channels, uint64_t height, uint64_t width,
+                    uint64_t kernel_h, uint64_t kernel_w, uint64_t pad_h, uint64_t pad_w, uint64_t stride_h,
+                    uint64_t stride_w, uint8_t *col_t_dev, uint64_t row_pitch, int device, void *stream);
 
 /* Same check for a device without a layer at hand (the stateless entry points share the device's status word). */
 int ltq_device_check(int device, void *stream);

@@ -66,6 +66,7 @@ Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *
     e.bsum = bsum;
     e.asum = asum;
     e.bias = bias;
+    e.row_bias = nullptr;
     e.qpA_dev = nullptr;
     e.sA = qa.scale;
     e.sB = qb.scale;
@@ -124,6 +125,26 @@ struct ltq_layer {
     GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
     DeviceState *dev = nullptr;
 };
+
+// Grow-only device buffer, same policy as the reference's col buffer and workspace.
+template <typename T>
+static int grow(T **buf, uint64_t *cap, uint64_t need, cudaStream_t st, const char *what)
+{
+    if (need <= *cap) return LTQ_OK;
+    T *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, need * sizeof(T));
+    if (e != cudaSuccess) {
+        set_error("cudaMalloc of %llu bytes for %s failed: %s", (unsigned long long)(need * sizeof(T)), what, cudaGetErrorString(e));
+        return LTQ_ERR_NO_MEMORY;
+    }
+    if (*buf) {
+        LTQ_CUDA_TRY(cudaStreamSynchronize(st));
+        cudaFree(*buf);
+    }
+    *buf = p;
+    *cap = need;
+    return LTQ_OK;
+}
 
 extern "C" {
 
@@ -405,6 +426,223 @@ int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asu
                                  out_mode, flags);
     epi.qpA_dev = qp_in_dev;
     return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi, out_dev, flags, layer, st);
+}
+
+// ---- quantized convolution (Conv2d_q) ----------------------------------------------------------------------------------
+struct ltq_conv2d {
+    int device = 0;
+    uint64_t Cin = 0, Cout = 0, kh = 0, kw = 0, ph = 0, pw = 0, sh = 1, sw = 1;
+    uint64_t K = 0, Kp = 0;        // patch length C*kh*kw and its 16-byte padded row pitch
+    const uint8_t *w = nullptr;    // weights as the GEMM reads them: the caller's buffer, or w_pad when K % 16 != 0
+    uint8_t *w_pad = nullptr;      // owned zero-padded copy [Cout, Kp]
+    const int32_t *bias = nullptr;
+    int32_t *wsum = nullptr;       // [Cout] sums over K of the weights
+    uint8_t *col = nullptr;        // transposed patch buffer; grows with the input like Conv2d_q::col_buffer_ptr_
+    uint64_t col_cap = 0;          // (l-ten/conv2d.cpp:326-338), but holds several images per pass
+    int32_t *colsum = nullptr;     // per-patch sums, the part of Conv2d_q::workspace_ that depends on the input
+    uint64_t colsum_cap = 0;
+    ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
+    DeviceState *dev = nullptr;
+};
+
+// Patch-buffer budget of one pass over a chunk of the batch.
+static constexpr uint64_t CONV_COL_BYTES = 256ull << 20;
+
+int ltq_conv2d_create(ltq_conv2d **conv, int device, uint64_t channels_in, uint64_t channels_out, uint64_t kernel_h,
+                      uint64_t kernel_w, uint64_t pad_h, uint64_t pad_w, uint64_t stride_h, uint64_t stride_w)
+{
+    LTQ_REQUIRE(conv, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    *conv = nullptr;
+    LTQ_REQUIRE(channels_in >= 1 && channels_out >= 1 && kernel_h >= 1 && kernel_w >= 1 && stride_h >= 1 && stride_w >= 1,
+                LTQ_ERR_INVALID_ARG, "channel counts, kernel size and strides must be >= 1");
+    const uint64_t lim = 1ull << 20;
+    LTQ_REQUIRE(channels_in < lim && channels_out < (1ull << 31) && kernel_h < lim && kernel_w < lim && pad_h < lim &&
+                    pad_w < lim && stride_h < lim && stride_w < lim && channels_in * kernel_h * kernel_w < (1ull << 31),
+                LTQ_ERR_TOO_LARGE, "convolution geometry out of range");
+    LTQ_ENTER_DEVICE(device);
+    DeviceState *dev;
+    int rc = device_state(device, &dev);
+    if (rc != LTQ_OK) return rc;
+    ltq_conv2d *c = new (std::nothrow) ltq_conv2d;
+    LTQ_REQUIRE(c, LTQ_ERR_NO_MEMORY, "out of host memory");
+    c->device = device;
+    c->Cin = channels_in;
+    c->Cout = channels_out;
+    c->kh = kernel_h;
+    c->kw = kernel_w;
+    c->ph = pad_h;
+    c->pw = pad_w;
+    c->sh = stride_h;
+    c->sw = stride_w;
+    c->K = channels_in * kernel_h * kernel_w;
+    c->Kp = (c->K + 15) / 16 * 16;
+    c->dev = dev;
+    cudaError_t e = cudaMalloc(&c->wsum, channels_out * sizeof(int32_t));
+    if (e == cudaSuccess && c->Kp != c->K) e = cudaMalloc(&c->w_pad, channels_out * c->Kp);
+    if (e != cudaSuccess) {
+        cudaFree(c->wsum);
+        delete c;
+        set_error("cudaMalloc of the convolution's weight buffers failed: %s", cudaGetErrorString(e));
+        return LTQ_ERR_NO_MEMORY;
+    }
+    *conv = c;
+    return LTQ_OK;
+}
+
+int ltq_conv2d_destroy(ltq_conv2d *conv)
+{
+    if (!conv) return LTQ_OK;
+    LTQ_ENTER_DEVICE(conv->device);
+    cudaFree(conv->wsum);
+    cudaFree(conv->w_pad);
+    cudaFree(conv->col);
+    cudaFree(conv->colsum);
+    delete conv;
+    return LTQ_OK;
+}
+
+int ltq_conv2d_set_weights(ltq_conv2d *conv, const uint8_t *w_dev, const int32_t *bias_dev, void *stream)
+{
+    LTQ_REQUIRE(conv && w_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_ENTER_DEVICE(conv->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    conv->bias = bias_dev;
+    if (conv->w_pad) {
+        LTQ_CUDA_TRY(cudaMemsetAsync(conv->w_pad, 0, conv->Cout * conv->Kp, st));
+        LTQ_CUDA_TRY(cudaMemcpy2DAsync(conv->w_pad, conv->Kp, w_dev, conv->K, conv->K, conv->Cout, cudaMemcpyDeviceToDevice, st));
+        conv->w = conv->w_pad;
+    } else {
+        conv->w = w_dev;
+    }
+    LTQ_CUDA_TRY(launch_row_sums(conv->w, conv->Cout, conv->Kp, conv->wsum, st));
+    LTQ_CUDA_TRY(cudaStreamSynchronize(st));
+    return LTQ_OK;
+}
+
+int ltq_conv2d_set_qparams(ltq_conv2d *conv, const ltq_qparams *qp_in, const ltq_qparams *qp_wt, const ltq_qparams *qp_out)
+{
+    LTQ_REQUIRE(conv, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    if (qp_in) conv->qp_in = *qp_in;
+    if (qp_wt) conv->qp_wt = *qp_wt;
+    if (qp_out) conv->qp_out = *qp_out;
+    return LTQ_OK;
+}
+
+int ltq_conv2d_output_size(const ltq_conv2d *conv, uint64_t height_in, uint64_t width_in, uint64_t *height_out,
+                           uint64_t *width_out)
+{
+    LTQ_REQUIRE(conv && height_out && width_out, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE(height_in < (1ull << 31) && width_in < (1ull << 31), LTQ_ERR_TOO_LARGE, "image size must be below 2^31");
+    LTQ_REQUIRE(height_in + 2 * conv->ph >= conv->kh && width_in + 2 * conv->pw >= conv->kw, LTQ_ERR_INVALID_ARG,
+                "padded image (%llu x %llu) smaller than the kernel (%llu x %llu)",
+                (unsigned long long)(height_in + 2 * conv->ph), (unsigned long long)(width_in + 2 * conv->pw),
+                (unsigned long long)conv->kh, (unsigned long long)conv->kw);
+    *height_out = (height_in + 2 * conv->ph - conv->kh) / conv->sh + 1;  // l-ten/conv2d.cpp:313-314
+    *width_out = (width_in + 2 * conv->pw - conv->kw) / conv->sw + 1;
+    return LTQ_OK;
+}
+
+int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches, uint64_t height_in, uint64_t width_in,
+                       int out_mode, unsigned flags, void *out_dev, void *stream)
+{
+    LTQ_REQUIRE(conv && (batches == 0 || (x_dev && out_dev)), LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE(conv->w, LTQ_ERR_INVALID_ARG, "ltq_conv2d_set_weights has not been called");
+    LTQ_REQUIRE(out_mode == LTQ_OUT_U8 || out_mode == LTQ_OUT_F32 || out_mode == LTQ_OUT_I32, LTQ_ERR_INVALID_ARG,
+                "unknown out_mode %d", out_mode);
+    uint64_t Ho, Wo;
+    int rc = ltq_conv2d_output_size(conv, height_in, width_in, &Ho, &Wo);
+    if (rc != LTQ_OK) return rc;
+    LTQ_REQUIRE(Ho * Wo < (1ull << 31) && batches < (1ull << 31), LTQ_ERR_TOO_LARGE, "output plane or batch too large");
+    const uint64_t N = Ho * Wo, M = conv->Cout, K = conv->K, Kp = conv->Kp;
+    const bool per_channel = (flags & LTQ_FLAG_BIAS_PER_CHANNEL) != 0;
+    // The reference adds bias[j] with j the OUTPUT POSITION (its GEMM's column index, l-ten/math_fns.cpp:1469-1472) out of
+    // a tensor that holds channels_out values, which is only defined while Ho*Wo <= channels_out.
+    LTQ_REQUIRE(!conv->bias || per_channel || N <= M, LTQ_ERR_UNSUPPORTED,
+                "the reference indexes the bias by output position and would read %llu values from a %llu-element tensor; "
+                "pass LTQ_FLAG_BIAS_PER_CHANNEL for one bias per output channel",
+                (unsigned long long)N, (unsigned long long)M);
+    const uint64_t bc = K * (uint64_t)conv->qp_wt.zero_point * (uint64_t)conv->qp_in.zero_point;
+    LTQ_REQUIRE(bc <= 0x7FFFFFFFull, LTQ_ERR_UNSUPPORTED, "K*zA*zB = %llu does not fit an int", (unsigned long long)bc);
+    if (batches == 0 || N == 0) return LTQ_OK;
+    LTQ_ENTER_DEVICE(conv->device);
+    cudaStream_t st = (cudaStream_t)stream;
+
+    uint64_t chunk = CONV_COL_BYTES / (N * Kp);
+    chunk = chunk < 1 ? 1 : (chunk > batches ? batches : chunk);
+    rc = grow(&conv->col, &conv->col_cap, chunk * N * Kp, st, "the patch buffer");
+    if (rc != LTQ_OK) return rc;
+    rc = grow(&conv->colsum, &conv->colsum_cap, chunk * N, st, "the patch sums");
+    if (rc != LTQ_OK) return rc;
+
+    ConvGeom g;
+    g.C = (uint32_t)conv->Cin;
+    g.H = (uint32_t)height_in;
+    g.W = (uint32_t)width_in;
+    g.kh = (uint32_t)conv->kh;
+    g.kw = (uint32_t)conv->kw;
+    g.ph = (uint32_t)conv->ph;
+    g.pw = (uint32_t)conv->pw;
+    g.sh = (uint32_t)conv->sh;
+    g.sw = (uint32_t)conv->sw;
+    g.Ho = (uint32_t)Ho;
+    g.Wo = (uint32_t)Wo;
+    g.K = (uint32_t)K;
+    g.Kp = (uint32_t)Kp;
+    const uint64_t in_stride = conv->Cin * height_in * width_in;
+    const uint64_t esize = out_mode == LTQ_OUT_U8 ? 1 : 4, out_stride = M * N * esize;
+    for (uint64_t b0 = 0; b0 < batches; b0 += chunk) {
+        const uint64_t nb = batches - b0 < chunk ? batches - b0 : chunk;
+        LTQ_CUDA_TRY(launch_im2col_t(x_dev + b0 * in_stride, nb, g, conv->col, st));
+        LTQ_CUDA_TRY(launch_row_sums(conv->col, nb * N, Kp, conv->colsum, st));
+        for (uint64_t i = 0; i < nb; i++) {
+            // out[co, n] = weights[co, :] . patch[n, :]: the weights are the row operand (qparams[0] in the reference's
+            // call, l-ten/conv2d.cpp:348-350), the patches the column operand.
+            Epilogue epi = make_epilogue(conv->colsum + i * N, conv->wsum, per_channel ? nullptr : conv->bias, conv->qp_wt,
+                                         conv->qp_in, conv->qp_out, K, out_mode, flags);
+            epi.row_bias = per_channel ? conv->bias : nullptr;
+            rc = run_fc_gemm(conv->dev, M, N, Kp, conv->w, conv->col + i * N * Kp, epi,
+                             static_cast<uint8_t *>(out_dev) + (b0 + i) * out_stride, flags, nullptr, st);
+            if (rc != LTQ_OK) return rc;
+        }
+    }
+    return LTQ_OK;
+}
+
+int ltq_im2col_t_u8(const uint8_t *im_dev, uint64_t batches, uint64_t channels, uint64_t height, uint64_t width,
+                    uint64_t kernel_h, uint64_t kernel_w, uint64_t pad_h, uint64_t pad_w, uint64_t stride_h,
+                    uint64_t stride_w, uint8_t *col_t_dev, uint64_t row_pitch, int device, void *stream)
+{
+    LTQ_REQUIRE(im_dev && col_t_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE(kernel_h >= 1 && kernel_w >= 1 && stride_h >= 1 && stride_w >= 1 && channels >= 1, LTQ_ERR_INVALID_ARG,
+                "channel count, kernel size and strides must be >= 1");
+    const uint64_t lim = 1ull << 20;
+    LTQ_REQUIRE(channels < lim && kernel_h < lim && kernel_w < lim && pad_h < lim && pad_w < lim && stride_h < lim &&
+                    stride_w < lim && height < (1ull << 31) && width < (1ull << 31) &&
+                    channels * kernel_h * kernel_w < (1ull << 31),
+                LTQ_ERR_TOO_LARGE, "convolution geometry out of range");
+    LTQ_REQUIRE(height + 2 * pad_h >= kernel_h && width + 2 * pad_w >= kernel_w, LTQ_ERR_INVALID_ARG,
+                "padded image smaller than the kernel");
+    const uint64_t K = channels * kernel_h * kernel_w;
+    LTQ_REQUIRE(row_pitch % 16 == 0 && row_pitch >= K && row_pitch < K + 16 && (((uintptr_t)col_t_dev & 15) == 0),
+                LTQ_ERR_INVALID_ARG, "row_pitch must be C*kh*kw rounded up to a multiple of 16 and the buffer 16-byte aligned");
+    LTQ_ENTER_DEVICE(device);
+    ConvGeom g;
+    g.C = (uint32_t)channels;
+    g.H = (uint32_t)height;
+    g.W = (uint32_t)width;
+    g.kh = (uint32_t)kernel_h;
+    g.kw = (uint32_t)kernel_w;
+    g.ph = (uint32_t)pad_h;
+    g.pw = (uint32_t)pad_w;
+    g.sh = (uint32_t)stride_h;
+    g.sw = (uint32_t)stride_w;
+    g.Ho = (uint32_t)((height + 2 * pad_h - kernel_h) / stride_h + 1);
+    g.Wo = (uint32_t)((width + 2 * pad_w - kernel_w) / stride_w + 1);
+    g.K = (uint32_t)K;
+    g.Kp = (uint32_t)row_pitch;
+    LTQ_REQUIRE((uint64_t)g.Ho * g.Wo < (1ull << 31), LTQ_ERR_TOO_LARGE, "output plane too large");
+    LTQ_CUDA_TRY(launch_im2col_t(im_dev, batches, g, col_t_dev, (cudaStream_t)stream));
+    return LTQ_OK;
 }
 
 int ltq_device_check(int device, void *stream)

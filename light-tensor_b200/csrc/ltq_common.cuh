@@ -64,7 +64,8 @@ struct DeviceGuard {
 struct Epilogue {
     const int32_t *bsum;          // [N] raw sums over K of the B operand (weights for the FC layer)
     const int32_t *asum;          // [M] raw sums over K of the A operand (activations)
-    const int32_t *bias;          // [N] or nullptr
+    const int32_t *bias;          // [N] or nullptr: added per output column (the reference's `bias[j]`)
+    const int32_t *row_bias;      // [M] or nullptr: added per output row (Conv2d_q: one value per output channel)
     const ltq_qparams *qpA_dev;   // optional device-resident override of (sA, zA)
     float sA, sB, sC;
     int32_t zA, zB, zC;
@@ -97,10 +98,12 @@ __device__ __forceinline__ EpilogueConsts epilogue_consts(const Epilogue &e)
     return c;
 }
 
-// Row part of the correction: -zB*asum[i] + K*zA*zB.
+// Row part of the correction: -zB*asum[i] + K*zA*zB (+ row_bias[i]).
 __device__ __forceinline__ uint32_t epilogue_row_term(const Epilogue &e, const EpilogueConsts &c, uint64_t i)
 {
-    return c.neg_zB * (uint32_t)e.asum[i] + c.bc;
+    uint32_t t = c.neg_zB * (uint32_t)e.asum[i] + c.bc;
+    if (e.row_bias) t += (uint32_t)e.row_bias[i];
+    return t;
 }
 // Column part: -zA*bsum[j] (+ bias[j]).
 __device__ __forceinline__ uint32_t epilogue_col_term(const Epilogue &e, const EpilogueConsts &c, uint64_t j)
@@ -157,6 +160,13 @@ cudaError_t launch_interleave_blocks(const void *src, void *dst, uint64_t G, uin
 
 // One warp waits on a barrier nothing arrives on, for at most limit_ns, then records code 0x900 in *status.
 cudaError_t launch_bounded_wait_probe(uint32_t *status, uint64_t limit_ns, cudaStream_t stream);
+
+// Patch gather for Conv2d_q over `batches` NCHW images, K-contiguous and zero-padded to Kp (a multiple of 16) bytes per
+// row: col_t[b][ho*Wo + wo][k], k = (c*kh + i)*kw + j.  Out-of-image taps and the padding are the byte 0.
+struct ConvGeom {
+    uint32_t C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo, K, Kp;
+};
+cudaError_t launch_im2col_t(const uint8_t *im, uint64_t batches, const ConvGeom &g, uint8_t *col_t, cudaStream_t stream);
 
 cudaError_t launch_min_max(const float *data, uint64_t len, float *minmax, cudaStream_t stream);
 cudaError_t launch_qparams_from_minmax(const float *minmax, ltq_qparams *qp, cudaStream_t stream);

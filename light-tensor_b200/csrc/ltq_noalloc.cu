@@ -99,6 +99,7 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
     epi.bsum = bsum;
     epi.asum = asum;
     epi.bias = bias_dev;
+    epi.row_bias = nullptr;
     epi.qpA_dev = nullptr;
     epi.sA = qparams[0].scale;
     epi.sB = qparams[1].scale;

@@ -261,6 +261,121 @@ Tensor FullyConnected_q::forward(Tensor &input)
     return result;
 }
 
+// ---- Conv2d_q ----------------------------------------------------------------------------------------------------------
+Conv2d_q::Conv2d_q(const int channels_in, const int channels_out, bool use_bias, const int kernel_h, const int kernel_w,
+                   const int pad_h, const int pad_w, const int stride_h, const int stride_w)
+    : channels_in_((uint64_t)channels_in), channels_out_((uint64_t)channels_out), kernel_h_((uint64_t)kernel_h),
+      kernel_w_((uint64_t)kernel_w), pad_h_((uint64_t)pad_h), pad_w_((uint64_t)pad_w), stride_h_((uint64_t)stride_h),
+      stride_w_((uint64_t)stride_w), use_bias_(use_bias)
+{
+}
+
+Conv2d_q::Conv2d_q(const Conv2d_q &o) : Module(o) { *this = o; }
+
+Conv2d_q &Conv2d_q::operator=(const Conv2d_q &o)
+{
+    if (this == &o) return *this;
+    if (o.weight_ptr_ || o.handle_) LTEN_ERR("Conv2d_q can only be copied before init()");
+    channels_in_ = o.channels_in_;
+    channels_out_ = o.channels_out_;
+    kernel_h_ = o.kernel_h_;
+    kernel_w_ = o.kernel_w_;
+    pad_h_ = o.pad_h_;
+    pad_w_ = o.pad_w_;
+    stride_h_ = o.stride_h_;
+    stride_w_ = o.stride_w_;
+    use_bias_ = o.use_bias_;
+    qparams_in_ = o.qparams_in_;
+    qparams_out_ = o.qparams_out_;
+    qparams_wt_ = o.qparams_wt_;
+    out_mode_ = o.out_mode_;
+    flags_ = o.flags_;
+    is_training_ = o.is_training_;
+    return *this;
+}
+
+Conv2d_q::~Conv2d_q()
+{
+    ltq_conv2d_destroy(handle_);
+    delete weight_ptr_;
+    delete bias_ptr_;
+}
+
+// l-ten/conv2d.cpp:238-264: uint8 weights {Cout, Cin, kh*kw}, int32 bias {1, Cout, 1, 1}, on the CPU, no initialisation.
+bool Conv2d_q::init()
+{
+    TensorOps options;
+    options.data_type = UINT8;
+    weight_ptr_ = new Tensor;
+    *weight_ptr_ = AllocateTensor({channels_out_, channels_in_, kernel_h_ * kernel_w_}, &options);
+    if (use_bias_) {
+        options.data_type = INT32;
+        bias_ptr_ = new Tensor;
+        *bias_ptr_ = AllocateTensor({1, channels_out_, 1, 1}, &options);
+    }
+    return true;
+}
+
+std::vector<Tensor *> Conv2d_q::get_all_weights()
+{
+    std::vector<Tensor *> weights;
+    weights.push_back(weight_ptr_);
+    if (use_bias_) weights.push_back(bias_ptr_);
+    return weights;
+}
+
+void Conv2d_q::set_qparams_params(QuantizationParams *qparams, int count)
+{
+    if (qparams && count) qparams_wt_ = qparams[0];  // l-ten/conv2d.cpp:400-406
+}
+
+void Conv2d_q::set_output(ltq_out_mode mode, bool relu, bool saturate, bool bias_per_channel)
+{
+    out_mode_ = mode;
+    flags_ = (relu ? LTQ_FLAG_RELU : 0u) | (saturate ? LTQ_FLAG_SATURATE : 0u) |
+             (bias_per_channel ? LTQ_FLAG_BIAS_PER_CHANNEL : 0u);
+}
+
+void Conv2d_q::to(device target_device, int target_device_index)
+{
+    if (!weight_ptr_) LTEN_ERR("init() has not been called");
+    *weight_ptr_ = weight_ptr_->to(target_device, target_device_index);
+    if (bias_ptr_) *bias_ptr_ = bias_ptr_->to(target_device, target_device_index);
+    ltq_conv2d_destroy(handle_);
+    handle_ = nullptr;
+    if (target_device == GPU) {
+        LTQ_CALL(ltq_conv2d_create(&handle_, target_device_index, channels_in_, channels_out_, kernel_h_, kernel_w_, pad_h_,
+                                   pad_w_, stride_h_, stride_w_));
+        LTQ_CALL(ltq_conv2d_set_weights(handle_, static_cast<const uint8_t *>(weight_ptr_->get_data_ptr()),
+                                        bias_ptr_ ? static_cast<const int32_t *>(bias_ptr_->get_data_ptr()) : nullptr,
+                                        nullptr));
+    }
+}
+
+Tensor Conv2d_q::forward(Tensor &input)
+{
+    // the reference's checks, messages and order: l-ten/conv2d.cpp:285-301
+    if (input.get_data_type() != UINT8) LTEN_ERR("Conv2d_q is only supported for UINT8 tensors");
+    if (input.get_device() != weight_ptr_->get_device() || input.get_device_index() != weight_ptr_->get_device_index() ||
+        input.get_data_type() != weight_ptr_->get_data_type())
+        LTEN_ERR("Input tensor device type or data type are not the same as this layer's parameters");
+    if (input.get_ndims() != 4) LTEN_ERR("Conv2d_q requires tensors with exactly 4 dimensions (NCHW)");
+    if (input.get_device() != GPU) LTEN_ERR("Conv2d_q: this build computes on GPU tensors only; call to(GPU, index) first");
+    const uint64_t *in = input.get_sizes();
+    uint64_t ho = 0, wo = 0;
+    LTQ_CALL(ltq_conv2d_output_size(handle_, in[2], in[3], &ho, &wo));
+
+    TensorOps options;
+    options.data_type = out_mode_ == LTQ_OUT_U8 ? UINT8 : (out_mode_ == LTQ_OUT_F32 ? FLOAT32 : INT32);
+    options.device_type = GPU;
+    options.device_index = input.get_device_index();
+    Tensor result = AllocateTensor({in[0], channels_out_, ho, wo}, &options);
+    LTQ_CALL(ltq_conv2d_set_qparams(handle_, &qparams_in_, &qparams_wt_, &qparams_out_));
+    LTQ_CALL(ltq_conv2d_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), in[0], in[2], in[3], out_mode_,
+                                flags_, result.get_data_ptr(), nullptr));
+    return result;
+}
+
 }  // namespace lten
 
 // ---- free functions ----------------------------------------------------------------------------------------------------

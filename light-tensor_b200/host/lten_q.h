@@ -2,7 +2,7 @@
 // that this path touches, driving libltq (include/ltq.h) for everything that computes.
 //
 //   lten::Tensor / TensorOps / AllocateTensor / TensorFromBuffer      l-ten/tensor.h:33-81,1478-1482, tensorimpl.h:46-63
-//   lten::Module, lten::FullyConnected_q                              l-ten/layers.h:14-31,69-106
+//   lten::Module, lten::FullyConnected_q, lten::Conv2d_q              l-ten/layers.h:14-31,69-106,453-524
 //   QuantizationParams                                                l-ten/math_fns.h:12-16
 //   GetMinMax / ComputeQuantizationParams / Quantize / Dequantize     l-ten/utils.h:23-27
 //
@@ -124,6 +124,52 @@ private:
     bool use_bias_;
     QuantizationParams qparams_in_{1.f, 0}, qparams_out_{1.f, 0}, qparams_wt_{1.f, 0};
     ltq_layer *handle_ = nullptr;  // created by to(GPU), never by the constructor
+    ltq_out_mode out_mode_ = LTQ_OUT_U8;
+    unsigned flags_ = 0;
+};
+
+// Quantized 2-D convolution, l-ten/layers.h:453-524 and l-ten/conv2d.cpp:238-406.  The reference computes it on the CPU
+// only (its to() throws "Only CPU device supported"); here to(GPU, idx) builds the device state and forward() takes an
+// NCHW uint8 GPU tensor.
+class Conv2d_q : public Module {
+public:
+    Conv2d_q(const int channels_in, const int channels_out, bool use_bias, const int kernel_h, const int kernel_w,
+             const int pad_h = 0, const int pad_w = 0, const int stride_h = 1, const int stride_w = 1);
+    Conv2d_q(const Conv2d_q &other);             // copyable before init(), as register_module needs
+    Conv2d_q &operator=(const Conv2d_q &other);
+    ~Conv2d_q();
+
+    uint64_t get_channels_out() { return channels_out_; }
+    uint64_t get_channels_in() { return channels_in_; }
+    uint64_t get_kernel_h() { return kernel_h_; }
+    uint64_t get_kernel_w() { return kernel_w_; }
+    uint64_t get_pad_h() { return pad_h_; }
+    uint64_t get_pad_w() { return pad_w_; }
+    uint64_t get_stride_h() { return stride_h_; }
+    uint64_t get_stride_w() { return stride_w_; }
+
+    bool init();
+    Tensor forward(Tensor &input);
+    std::vector<Tensor *> get_all_weights();
+    Tensor *get_weights() { return weight_ptr_; }
+    Tensor *get_bias() { return bias_ptr_; }
+    void clear_gradients() {}
+    void to(device target_device, int target_device_index = 0);
+
+    void set_qparams_in(QuantizationParams qparams_in) { qparams_in_ = qparams_in; }
+    void set_qparams_out(QuantizationParams qparams_out) { qparams_out_ = qparams_out; }
+    void set_qparams_params(QuantizationParams *qparams, int count);
+
+    // Additive.  bias_per_channel adds bias[c] per output channel; the default applies the bias the way the reference's
+    // GEMM does, per output position, which it only defines while Ho*Wo <= channels_out.
+    void set_output(ltq_out_mode mode, bool relu = false, bool saturate = false, bool bias_per_channel = false);
+
+private:
+    uint64_t channels_in_, channels_out_, kernel_h_, kernel_w_, pad_h_, pad_w_, stride_h_, stride_w_;
+    bool use_bias_;
+    Tensor *weight_ptr_ = nullptr, *bias_ptr_ = nullptr;
+    QuantizationParams qparams_in_{1.f, 0}, qparams_out_{1.f, 0}, qparams_wt_{1.f, 0};
+    ltq_conv2d *handle_ = nullptr;
     ltq_out_mode out_mode_ = LTQ_OUT_U8;
     unsigned flags_ = 0;
 };

@@ -76,6 +76,9 @@ class _Port:
         L.oracle_quantized_matmul.argtypes = [C.c_int, C.c_int, u64, u64, u64, C.c_uint8, vp, vp, C.c_uint8, vp,
                                               C.POINTER(QParams), vp, vp]
         L.oracle_quantized_matmul.restype = C.c_int
+        L.oracle_im2col.argtypes = [vp] + [u64] * 9 + [vp]
+        L.oracle_conv2d_q.argtypes = [vp, u64, u64, u64, u64, vp, vp, C.c_int] + [u64] * 7 + [C.POINTER(QParams)] * 3 + [vp]
+        L.oracle_conv2d_q.restype = C.c_int
 
     def get_min_max(self, x):
         x = _c(x, np.float32)
@@ -155,6 +158,31 @@ class _Port:
         return Cm, ws
 
 
+    def im2col(self, im, kh, kw, ph=0, pw=0, sh=1, sw=1):
+        """im u8 [C,H,W] -> col u8 [C*kh*kw, Ho*Wo] (the reference's layout)."""
+        im = _c(im, np.uint8)
+        Cn, H, W = im.shape
+        ho, wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        col = np.empty((Cn * kh * kw, ho * wo), np.uint8)
+        self.lib.oracle_im2col(im.ctypes.data, Cn, H, W, kh, kw, ph, pw, sh, sw, col.ctypes.data)
+        return col
+
+    def conv2d_q(self, x, w, cout, kh, kw, qp_in, qp_wt, qp_out, bias=None, ph=0, pw=0, sh=1, sw=1,
+                 bias_per_channel=False):
+        """x u8 [B,Cin,H,W], w u8 [Cout, Cin*kh*kw] -> out u8 [B,Cout,Ho,Wo]."""
+        x, w = _c(x, np.uint8), _c(w, np.uint8)
+        B, Cin, H, W = x.shape
+        ho, wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        out = np.empty((B, cout, ho, wo), np.uint8)
+        b = None if bias is None else _c(bias, np.int32)
+        rc = self.lib.oracle_conv2d_q(x.ctypes.data, B, Cin, H, W, w.ctypes.data, None if b is None else b.ctypes.data,
+                                      int(bias_per_channel), cout, kh, kw, ph, pw, sh, sw, C.byref(qp_in),
+                                      C.byref(qp_wt), C.byref(qp_out), out.ctypes.data)
+        if rc != 0:
+            raise MemoryError("oracle_conv2d_q")
+        return out
+
+
 class _Ref:
     """The unmodified reference (``kind: "reference"``)."""
 
@@ -173,6 +201,10 @@ class _Ref:
         L.ref_fc_q_forward.argtypes = [u64, u64, u64, vp, vp, vp, C.POINTER(QParams), C.POINTER(QParams),
                                        C.POINTER(QParams), vp, C.c_int]
         L.ref_fc_q_forward.restype = C.c_double
+        if hasattr(L, "ref_conv2d_q_forward"):
+            L.ref_im2col.argtypes = [vp] + [u64] * 9 + [vp]
+            L.ref_conv2d_q_forward.argtypes = [u64] * 5 + [C.c_int] * 6 + [vp, vp, vp] + [C.POINTER(QParams)] * 3 + [vp]
+            L.ref_conv2d_q_forward.restype = C.c_int
 
     def get_min_max(self, x):
         x = _c(x, np.float32)
@@ -225,6 +257,31 @@ class _Ref:
         if secs < 0:
             raise RuntimeError("reference raised")
         return out, secs
+
+
+    def im2col(self, im, kh, kw, ph=0, pw=0, sh=1, sw=1):
+        im = _c(im, np.uint8)
+        Cn, H, W = im.shape
+        ho, wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        col = np.empty((Cn * kh * kw, ho * wo), np.uint8)
+        self.lib.ref_im2col(im.ctypes.data, Cn, H, W, kh, kw, ph, pw, sh, sw, col.ctypes.data)
+        return col
+
+    def conv2d_q(self, x, w, cout, kh, kw, qp_in, qp_wt, qp_out, bias=None, ph=0, pw=0, sh=1, sw=1):
+        """Conv2d_q::forward; only call with a bias while Ho*Wo <= cout (beyond that the reference reads out of bounds)."""
+        x, w = _c(x, np.uint8), _c(w, np.uint8)
+        B, Cin, H, W = x.shape
+        ho, wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        if bias is not None and ho * wo > cout:
+            raise ValueError("the reference would read past its bias tensor")
+        out = np.empty((B, cout, ho, wo), np.uint8)
+        b = None if bias is None else _c(bias, np.int32)
+        rc = self.lib.ref_conv2d_q_forward(B, Cin, H, W, cout, kh, kw, ph, pw, sh, sw, x.ctypes.data, w.ctypes.data,
+                                           None if b is None else b.ctypes.data, C.byref(qp_in), C.byref(qp_wt),
+                                           C.byref(qp_out), out.ctypes.data)
+        if rc != 0:
+            raise RuntimeError("reference raised")
+        return out
 
 
 def _load():

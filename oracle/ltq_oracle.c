@@ -15,6 +15,7 @@
 #include <stddef.h>
 #include <math.h>
 #include <limits.h>
+#include <stdlib.h>
 
 typedef struct {
     float scale;
@@ -215,9 +216,9 @@ void oracle_epilogue_f32(const int32_t *acc, uint64_t len, float sA, float sB, i
  * workspace receives the reference's pre-multiplied vectors
  * [ -zA*bsum (N) | -zB*asum (M) ] (l-ten/math_fns.cpp:1325-1326).
  * Returns -1 for alpha != 1 or beta != 0 (reference: LTEN_ERR, :1331-1334). */
-int oracle_quantized_matmul(int tA, int tB, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
-                            const uint8_t *A, const uint8_t *B, uint8_t beta, uint8_t *C,
-                            const oracle_qparams *qp, const int32_t *bias, int32_t *workspace)
+static int qmm_core(int tA, int tB, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha, const uint8_t *A,
+                    const uint8_t *B, uint8_t beta, uint8_t *C, const oracle_qparams *qp, const int32_t *bias,
+                    const int32_t *row_bias, int32_t *workspace)
 {
     if (alpha != 1 || beta != 0) return -1;
     int32_t *row = workspace, *col = workspace + N;
@@ -233,10 +234,72 @@ int oracle_quantized_matmul(int tA, int tB, uint64_t M, uint64_t N, uint64_t K, 
                 e += (uint32_t)(a_at(A, tA, M, K, i, k) * b_at(B, tB, N, K, j, k));
             e += (uint32_t)row[j] + (uint32_t)col[i] + bc;
             if (bias) e += (uint32_t)bias[j];
+            if (row_bias) e += (uint32_t)row_bias[i];
             volatile float m = rm * (float)(int32_t)e;
             float t = m + (float)(int)qp[2].zero_point;
             C[i * N + j] = cast_u8(t, 0);
         }
     }
+    return 0;
+}
+
+int oracle_quantized_matmul(int tA, int tB, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                            const uint8_t *A, const uint8_t *B, uint8_t beta, uint8_t *C,
+                            const oracle_qparams *qp, const int32_t *bias, int32_t *workspace)
+{
+    return qmm_core(tA, tB, M, N, K, alpha, A, B, beta, C, qp, bias, NULL, workspace);
+}
+
+/* Patch gather, l-ten/im_col.h:5-33: col is [C*kh*kw, Ho*Wo]; row c = (channel, kernel row, kernel column), taps outside
+ * the image are 0.  The reference computes the tap position in uint64_t, so a "negative" position wraps to a huge
+ * value and fails the `< height` test; signed arithmetic with an explicit >= 0 test says the same. */
+void oracle_im2col(const uint8_t *im, uint64_t channels, uint64_t height, uint64_t width, uint64_t kernel_h,
+                   uint64_t kernel_w, uint64_t pad_h, uint64_t pad_w, uint64_t stride_h, uint64_t stride_w, uint8_t *col)
+{
+    const uint64_t hc = (height + 2 * pad_h - kernel_h) / stride_h + 1;
+    const uint64_t wc = (width + 2 * pad_w - kernel_w) / stride_w + 1;
+    const uint64_t rows = channels * kernel_h * kernel_w;
+    for (uint64_t c = 0; c < rows; c++) {
+        const uint64_t wo = c % kernel_w, ho = (c / kernel_w) % kernel_h, ci = c / kernel_h / kernel_w;
+        for (uint64_t h = 0; h < hc; h++)
+            for (uint64_t w = 0; w < wc; w++) {
+                const int64_t y = (int64_t)(h * stride_h + ho) - (int64_t)pad_h;
+                const int64_t x = (int64_t)(w * stride_w + wo) - (int64_t)pad_w;
+                uint8_t v = 0;
+                if (y >= 0 && y < (int64_t)height && x >= 0 && x < (int64_t)width) v = im[(ci * height + y) * width + x];
+                col[(c * hc + h) * wc + w] = v;
+            }
+    }
+}
+
+/* Conv2d_q::forward, l-ten/conv2d.cpp:266-379: per image, im2col then quantized_matmul(false, false, M = Cout,
+ * N = Ho*Wo, K = Cin*kh*kw, weights, col) with qparams {weights, input, output} (:348-350).  `bias` is handed to
+ * quantized_matmul as the reference does (added per output POSITION j, so only defined while Ho*Wo <= Cout);
+ * bias_per_channel != 0 adds bias[channel] instead, which is what the shipped library offers as an option and has no
+ * counterpart in the reference.  Returns -1 if memory runs out. */
+int oracle_conv2d_q(const uint8_t *x, uint64_t batches, uint64_t cin, uint64_t height, uint64_t width, const uint8_t *w,
+                    const int32_t *bias, int bias_per_channel, uint64_t cout, uint64_t kernel_h, uint64_t kernel_w,
+                    uint64_t pad_h, uint64_t pad_w, uint64_t stride_h, uint64_t stride_w, const oracle_qparams *qp_in,
+                    const oracle_qparams *qp_wt, const oracle_qparams *qp_out, uint8_t *out)
+{
+    const uint64_t ho = (height + 2 * pad_h - kernel_h) / stride_h + 1;
+    const uint64_t wo = (width + 2 * pad_w - kernel_w) / stride_w + 1;
+    const uint64_t M = cout, N = ho * wo, K = cin * kernel_h * kernel_w;
+    uint8_t *col = (uint8_t *)malloc(K * N ? K * N : 1);
+    int32_t *ws = (int32_t *)malloc((M + N) * sizeof(int32_t));
+    if (!col || !ws) {
+        free(col);
+        free(ws);
+        return -1;
+    }
+    const oracle_qparams qp[3] = {*qp_wt, *qp_in, *qp_out};
+    for (uint64_t b = 0; b < batches; b++) {
+        oracle_im2col(x + b * cin * height * width, cin, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h,
+                      stride_w, col);
+        qmm_core(0, 0, M, N, K, 1, w, col, 0, out + b * M * N, qp, bias_per_channel ? NULL : bias,
+                 bias_per_channel ? bias : NULL, ws);
+    }
+    free(col);
+    free(ws);
     return 0;
 }

@@ -8,6 +8,7 @@
 #include <chrono>
 #include "lten.h"   // l-ten/lten.h (reference public umbrella header)
 #include "utils.h"  // l-ten/utils.h:23-27
+#include "im_col.h" // l-ten/im_col.h:5-33
 
 extern "C" {
 
@@ -100,6 +101,44 @@ double ref_fc_q_forward(uint64_t M, uint64_t N, uint64_t K, const uint8_t* x, co
         return best;
     } catch (...) {
         return -1.0;
+    }
+}
+
+// The patch gather on its own, l-ten/im_col.h:5-33.
+void ref_im2col(const uint8_t* im, uint64_t channels, uint64_t height, uint64_t width, uint64_t kernel_h, uint64_t kernel_w,
+                uint64_t pad_h, uint64_t pad_w, uint64_t stride_h, uint64_t stride_w, uint8_t* col)
+{
+    im2col_cpu<uint8_t>(im, channels, height, width, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, col);
+}
+
+// Conv2d_q through the reference's public API (l-ten/layers.h:453-524), set up the way tests/nn_tests.cpp:625 and
+// :829-840 do: weights through get_all_weights(), qparams through the three setters, forward on an NCHW uint8 tensor.
+// Returns 0, or -1 on an exception.
+int ref_conv2d_q_forward(uint64_t batches, uint64_t cin, uint64_t height, uint64_t width, uint64_t cout, int kernel_h,
+                         int kernel_w, int pad_h, int pad_w, int stride_h, int stride_w, const uint8_t* x, const uint8_t* w,
+                         const int* bias, const ref_qparams* qp_in, const ref_qparams* qp_wt, const ref_qparams* qp_out,
+                         uint8_t* out)
+{
+    try {
+        lten::Conv2d_q conv((int)cin, (int)cout, bias != nullptr, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w);
+        conv.init();
+        conv.train(false);
+        auto wts = conv.get_all_weights();
+        memcpy(wts[0]->get_data_ptr(), w, cout * cin * kernel_h * kernel_w);
+        if (bias) memcpy(wts[1]->get_data_ptr(), bias, cout * sizeof(int));
+        QuantizationParams qw = to_qp(*qp_wt);
+        conv.set_qparams_in(to_qp(*qp_in));
+        conv.set_qparams_out(to_qp(*qp_out));
+        conv.set_qparams_params(&qw, 1);
+        lten::TensorOps opts;
+        opts.data_type = lten::UINT8;
+        lten::Tensor input = lten::AllocateTensor({ batches, cin, height, width }, &opts);
+        memcpy(input.get_data_ptr(), x, batches * cin * height * width);
+        lten::Tensor result = conv.forward(input);
+        memcpy(out, result.get_data_ptr(), result.get_numels());
+        return 0;
+    } catch (...) {
+        return -1;
     }
 }
 

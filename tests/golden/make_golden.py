@@ -171,7 +171,45 @@ def linear_1024():
     print("linear_1024.npz:", len(outs), "output settings")
 
 
+CONV_CASES = [
+    # batches, Cin, H, W, Cout, kh, kw, ph, pw, sh, sw, bias
+    (4, 1, 28, 28, 10, 5, 5, 0, 0, 1, 1, 0),     # the reference's quantized conv test net (tests/nn_tests.cpp:620-627)
+    (2, 3, 17, 13, 8, 3, 3, 1, 1, 1, 1, 0),      # padding, K = 27
+    (2, 16, 12, 12, 24, 3, 3, 1, 1, 2, 2, 0),    # stride 2, K = 144 (multiple of 16)
+    (1, 64, 14, 14, 32, 3, 3, 1, 1, 1, 1, 0),    # K = 576
+    (3, 5, 9, 11, 7, 2, 4, 0, 2, 1, 3, 0),       # rectangular kernel, pad and stride differ per axis
+    (2, 32, 6, 6, 16, 1, 1, 0, 0, 1, 1, 0),      # 1 x 1 kernel
+    (2, 4, 8, 8, 32, 5, 5, 0, 0, 1, 1, 1),       # bias: Ho*Wo = 16 <= Cout = 32, the only range where the reference's
+    (1, 8, 5, 5, 48, 3, 3, 1, 1, 2, 2, 1),       # per-position bias indexing stays inside its tensor (9 <= 48)
+    (2, 2, 7, 7, 3, 7, 7, 3, 3, 1, 1, 0),        # kernel as large as the image, heavy padding
+]
+
+
+def conv2d():
+    """Conv2d_q::forward (l-ten/conv2d.cpp:266-379) and im2col_cpu (l-ten/im_col.h:5-33) on seeded inputs."""
+    rng = np.random.default_rng(300)
+    qsets = [((0.02, 128), (0.005, 127), (0.05, 3)), ((0.1, 7), (0.03, 250), (0.9, 100)), ((0.05, 0), (0.01, 131), (0.02, 64))]
+    out = {"cases": np.array(CONV_CASES, np.int64)}
+    for ci, (B, Cin, H, W, Cout, kh, kw, ph, pw, sh, sw, use_bias) in enumerate(CONV_CASES):
+        x = rng.integers(0, 256, (B, Cin, H, W), dtype=np.uint8)
+        w = rng.integers(0, 256, (Cout, Cin * kh * kw), dtype=np.uint8)
+        bias = rng.integers(-20000, 20000, Cout, dtype=np.int32) if use_bias else None
+        q_in, q_wt, q_out = [oracle.qp(*q) for q in qsets[ci % len(qsets)]]
+        y = ref.conv2d_q(x, w, Cout, kh, kw, q_in, q_wt, q_out, bias=bias, ph=ph, pw=pw, sh=sh, sw=sw)
+        key = f"v{ci}"
+        out[key + ".qp"] = np.array([[q.scale, q.zero_point] for q in (q_in, q_wt, q_out)], np.float64)
+        out[key + ".x"] = x
+        out[key + ".w"] = w
+        if use_bias:
+            out[key + ".bias"] = bias
+        out[key + ".y"] = y
+        out[key + ".col0"] = ref.im2col(x[0], kh, kw, ph, pw, sh, sw)
+    np.savez_compressed(os.path.join(HERE, "conv2d.npz"), **out)
+    print("conv2d.npz:", len(CONV_CASES), "cases")
+
+
 if __name__ == "__main__":
+    conv2d()
     helpers()
     qmm_small()
     fc_mlp()

@@ -1,0 +1,140 @@
+"""GPU: Conv2d_q through the C ABI -- against the fixtures generated from the reference build, against the CPU oracle
+on other shapes, and through size-independent properties where the oracle would take too long."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import iter_conv_cases, ltq_qp, qp_of
+
+pytestmark = pytest.mark.gpu
+
+
+def _conv(cuda, ltq, c, qps, flags=0, out_mode=0, bias=None):
+    h = ltq.ConvHandle(0, c["Cin"], c["Cout"], c["kh"], c["kw"], c["ph"], c["pw"], c["sh"], c["sw"])
+    w = cuda.from_numpy(np.ascontiguousarray(c["w"])).cuda()
+    b = None if bias is None else cuda.from_numpy(bias).cuda()
+    h.set_weights(w, b)
+    h.set_qparams(*qps)
+    y = h.forward(cuda.from_numpy(np.ascontiguousarray(c["x"])).cuda(), out_mode, flags)
+    cuda.cuda.synchronize()
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("force", ["auto", "simt"])
+def test_conv_matches_golden(cuda, golden, force):
+    import ltq
+    g = golden("conv2d.npz")
+    flags = ltq.FLAG_FORCE_SIMT if force == "simt" else 0
+    for c in iter_conv_cases(g):
+        y = _conv(cuda, ltq, c, [ltq_qp(r) for r in c["qp"]], flags=flags, bias=c["bias"])
+        np.testing.assert_array_equal(y, c["y"], err_msg=c["key"])
+    assert ltq.lib().ltq_device_check(0, None) == 0
+
+
+def test_im2col_t_is_the_transposed_padded_reference_buffer(cuda, golden):
+    import ltq
+    g = golden("conv2d.npz")
+    for c in iter_conv_cases(g):
+        K, N = c["col0"].shape
+        Kp = (K + 15) // 16 * 16
+        x = cuda.from_numpy(np.ascontiguousarray(c["x"])).cuda()
+        col = cuda.full((c["B"], N, Kp), 0xEE, dtype=cuda.uint8, device="cuda")
+        ltq._binding.check(ltq.lib().ltq_im2col_t_u8(x.data_ptr(), c["B"], c["Cin"], c["H"], c["W"], c["kh"], c["kw"],
+                                                     c["ph"], c["pw"], c["sh"], c["sw"], col.data_ptr(), Kp, 0, None))
+        cuda.cuda.synchronize()
+        col = col.cpu().numpy()
+        np.testing.assert_array_equal(col[0, :, :K], c["col0"].T, err_msg=c["key"])
+        assert not col[:, :, K:].any(), "padding bytes must be zero"
+
+
+@pytest.mark.parametrize("shape", [
+    # B, Cin, H, W, Cout, kh, kw, ph, pw, sh, sw
+    (2, 32, 20, 20, 160, 3, 3, 1, 1, 1, 1),      # 160 x 400 x 288: tensor-core path, two row tiles
+    (3, 8, 33, 31, 12, 4, 4, 0, 0, 1, 1),        # M = 12, K = 128: eligible for the skinny kernel
+    (1, 3, 40, 40, 64, 7, 7, 3, 3, 2, 2),        # K = 147 -> padded to 160
+    (5, 1, 28, 28, 10, 5, 5, 2, 2, 1, 1),
+])
+def test_conv_matches_oracle(cuda, oracle, shape):
+    import ltq
+    B, Cin, H, W, Cout, kh, kw, ph, pw, sh, sw = shape
+    rng = np.random.default_rng(sum(shape))
+    c = dict(Cin=Cin, Cout=Cout, kh=kh, kw=kw, ph=ph, pw=pw, sh=sh, sw=sw,
+             x=rng.integers(0, 256, (B, Cin, H, W), dtype=np.uint8),
+             w=rng.integers(0, 256, (Cout, Cin * kh * kw), dtype=np.uint8))
+    rows = [(0.02, 128), (0.005, 127), (0.6, 3)]
+    want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], ph=ph, pw=pw, sh=sh,
+                                sw=sw)
+    got = _conv(cuda, ltq, c, [ltq_qp(r) for r in rows])
+    np.testing.assert_array_equal(got, want)
+    # one bias per output channel (the library's option; the oracle restates the same arithmetic)
+    bias = rng.integers(-30000, 30000, Cout, dtype=np.int32)
+    want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], bias=bias, ph=ph,
+                                pw=pw, sh=sh, sw=sw, bias_per_channel=True)
+    got = _conv(cuda, ltq, c, [ltq_qp(r) for r in rows], flags=ltq.FLAG_BIAS_PER_CHANNEL, bias=bias)
+    np.testing.assert_array_equal(got, want)
+
+
+def test_reference_bias_indexing_is_refused_beyond_its_tensor(cuda):
+    import ltq
+    h = ltq.ConvHandle(0, 2, 4, 3, 3)
+    w = cuda.zeros((4, 18), dtype=cuda.uint8, device="cuda")
+    b = cuda.zeros(4, dtype=cuda.int32, device="cuda")
+    h.set_weights(w, b)
+    x = cuda.zeros((1, 2, 8, 8), dtype=cuda.uint8, device="cuda")       # 36 output positions > 4 channels
+    with pytest.raises(ltq.LtqError, match="output position"):
+        h.forward(x)
+    assert h.forward(x, flags=ltq.FLAG_BIAS_PER_CHANNEL).shape == (1, 4, 6, 6)
+
+
+def test_geometry_errors(cuda):
+    import ltq
+    h = ltq.ConvHandle(0, 1, 1, 5, 5)
+    with pytest.raises(ltq.LtqError, match="smaller than the kernel"):
+        h.output_size(4, 10)
+    hp = C.c_void_p()
+    assert ltq.lib().ltq_conv2d_create(C.byref(hp), 0, 1, 1, 3, 3, 0, 0, 0, 1) == -1   # stride 0
+    h.set_weights(cuda.zeros((1, 25), dtype=cuda.uint8, device="cuda"))
+    assert h.forward(cuda.zeros((0, 1, 8, 8), dtype=cuda.uint8, device="cuda")).shape == (0, 1, 4, 4)
+
+
+def test_float_and_int32_outputs_and_relu(cuda, oracle):
+    """out_mode / ReLU act on the convolution exactly as on the linear layer: int32 is the corrected accumulator,
+    float = (s_wt*s_in)*acc, ReLU clamps the accumulator first."""
+    import ltq
+    rng = np.random.default_rng(12)
+    c = dict(Cin=4, Cout=9, kh=3, kw=3, ph=1, pw=1, sh=1, sw=1, x=rng.integers(0, 256, (2, 4, 10, 10), dtype=np.uint8),
+             w=rng.integers(0, 256, (9, 36), dtype=np.uint8))
+    rows = [(0.02, 128), (0.005, 127), (1.0, 0)]
+    qps = [ltq_qp(r) for r in rows]
+    acc = _conv(cuda, ltq, c, qps, out_mode=ltq.OUT_I32)
+    want = np.empty_like(acc)
+    for b in range(2):
+        col = oracle.port.im2col(c["x"][b], 3, 3, 1, 1, 1, 1)
+        want[b] = oracle.port.acc_i32(c["w"], col, 9, 100, 36, 127, 128, tA=False, tB=False).reshape(9, 10, 10)
+    np.testing.assert_array_equal(acc, want)
+    f = _conv(cuda, ltq, c, qps, out_mode=ltq.OUT_F32, flags=ltq.FLAG_RELU)
+    sab = np.float32(0.005) * np.float32(0.02)
+    np.testing.assert_array_equal(f, sab * np.maximum(want, 0).astype(np.float32))
+
+
+def test_large_batch_is_processed_in_chunks_and_equals_per_image_calls(cuda):
+    """Property at a size the CPU oracle cannot reach: a batch whose patch buffer exceeds one pass (256 MiB) gives, image
+    by image, what single-image calls give (different chunking, different buffer offsets, same arithmetic)."""
+    import ltq
+    g = cuda.Generator(device="cuda").manual_seed(3)
+    B, Cin, H, W, Cout = 180, 64, 56, 56, 64           # patch rows: 3136 x 576 B = 1.8 MB per image -> 148 images per pass
+    x = cuda.randint(0, 256, (B, Cin, H, W), dtype=cuda.uint8, device="cuda", generator=g)
+    w = cuda.randint(0, 256, (Cout, Cin * 9), dtype=cuda.uint8, device="cuda", generator=g)
+    h = ltq.ConvHandle(0, Cin, Cout, 3, 3, 1, 1, 1, 1)
+    h.set_weights(w)
+    h.set_qparams(ltq.QParams(0.02, 128), ltq.QParams(0.005, 127), ltq.QParams(0.1, 5))
+    y = h.forward(x)
+    assert tuple(y.shape) == (B, Cout, H, W)
+    for b in (0, 1, 147, 148, 179):
+        yb = h.forward(x[b:b + 1].contiguous())
+        assert cuda.equal(yb[0], y[b]), f"image {b}"
+    # and the simplest cross-kernel check: the generic kernel on one image agrees with the tensor-core result
+    y0 = h.forward(x[179:180].contiguous(), flags=ltq.FLAG_FORCE_SIMT)
+    assert cuda.equal(y0[0], y[179])
+    assert ltq.lib().ltq_device_check(0, None) == 0
