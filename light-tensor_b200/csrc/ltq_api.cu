@@ -253,7 +253,9 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
     if (rc != LTQ_OK) return rc;
     switch (path) {
         case PATH_SKINNY:
-            LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->status, dev->sms, stream, layer ? &layer->map_w_gemv : nullptr));
+            // a layer's weights are fixed between ltq_layer_set_weights calls (which synchronise), so they may be streamed early
+            LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->status, dev->sms, stream, layer ? &layer->map_w_gemv : nullptr,
+                                     layer != nullptr));
             break;
         case PATH_TC: {
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&

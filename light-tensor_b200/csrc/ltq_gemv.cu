@@ -12,11 +12,20 @@
 //  * the producer thread issues TMA tensor copies (cp.async.bulk.tensor.3d, no multicast) into a shared-memory ring.
 //    The matrices are described to TMA as {128-byte line, row, line index along K}: a box of R rows x L lines lands as
 //    L consecutive K-major tiles [R rows][128 B] under the 128-byte swizzle, exactly the layout the MMA's shared-memory
-//    descriptors read, while each row contributes L x 128 contiguous bytes of DRAM per box.  The activation block is
-//    fetched the same way, once (rows beyond M are zero-filled by TMA);
+//    descriptors read, while each row contributes L x 128 contiguous bytes of DRAM per box.  Every ring stage holds a
+//    weight box and the matching box of the activation block (rows beyond M are zero-filled by TMA; the activations
+//    come out of L2, every CTA reads the same ones).  Nothing but the ring lives in shared memory, which keeps a CTA
+//    under half an SM: the CTA of the NEXT launch moves in beside it (see below);
 //  * four epilogue warps read the accumulators with tcgen05.ld (thread = weight row, register = token), apply the fused
 //    epilogue (l-ten/math_fns.cpp:1469-1474) and store; for every token the 32 lanes of a warp write 32 consecutive
 //    outputs.  Accumulators are double buffered in TMEM.
+//
+//  * with `early_weights` the kernel is launched as a programmatic dependent of the kernel before it in the stream.
+//    Every CTA releases its dependents at once, so the next launch's CTAs become resident on the same SMs while this
+//    one is still streaming, and fill their rings with WEIGHTS straight away (the caller guarantees that nothing in
+//    flight writes them).  Everything that can depend on the previous kernel - the activation boxes, the activation
+//    row sums, every store - comes after griddepcontrol.wait.  In a chain of such launches the start-up (barrier
+//    set-up, first DRAM round trip) and the tail (last MMAs, epilogue) of neighbouring launches overlap.
 //
 // Every mbarrier wait is bounded (2 s by %globaltimer); on expiry a code is left in the device status word.
 #include <cuda.h>
@@ -36,7 +45,7 @@ constexpr int LINE = 128;                  // bytes of K per line (one swizzle a
 constexpr int XROWS = 16;                  // activation rows as seen by the MMA (N = 16), TMEM columns per accumulator
 constexpr int TILE_M = 128;                // MMA M: weight rows per tile (upper bound)
 constexpr int MAX_STAGES = 16;
-constexpr int SMEM_LIMIT = 220 * 1024;
+constexpr int SMEM_LIMIT = 112 * 1024;     // two CTAs (this launch's and the next one's) share an SM
 constexpr int OVERREAD = TILE_M * LINE;    // an MMA reads 128 rows from a tile's start whatever the band holds
 constexpr int NACC = 4;                    // independent partial accumulators per tile (summed in the epilogue)
 constexpr uint32_t TMEM_COLS = 2 * NACC * XROWS;  // two buffers of NACC accumulators of 16 columns = 128
@@ -46,7 +55,8 @@ struct Plan {
     uint32_t oct_lo, oct_hi;               // a tile holds oct_lo or oct_hi groups of 8 rows (oct_hi <= 16)
     uint32_t lines;                        // lines per stage (per TMA box)
     uint32_t stages;
-    uint32_t stage_bytes;                  // lines * oct_hi * 8 * 128
+    uint32_t w_stage, x_stage;             // bytes per stage: lines * oct_hi * 8 * 128 and lines * (8 or 16) * 128
+    uint32_t slack;                        // bytes kept free behind the activation boxes for the MMA's over-reads
     size_t smem;
     bool ok;
 };
@@ -62,24 +72,31 @@ Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms)
     p.oct_hi = (uint32_t)((octs + p.tiles - 1) / p.tiles);
     const uint32_t klines = (uint32_t)(K / LINE);
     const uint32_t line_bytes = p.oct_hi * 8 * LINE;
-    uint32_t L = (20u * 1024u) / line_bytes;
+    uint32_t L = (20u * 1024u) / line_bytes;  // boxes of ~20 KB: smaller tensor copies pay a fixed per-copy cost
     L = L < 1 ? 1 : (L > 4 ? 4 : L);
     if (L > klines) L = klines;
     p.lines = L;
-    p.stage_bytes = L * line_bytes;
-    // The MMA's over-read past the last tile may run into the activation block that follows the ring; only when that
-    // block is smaller than the over-read is extra slack needed.
-    // Activation block: 8 rows per line when M <= 8 (the MMA still reads 16 rows per line tile; rows 8..15 are then the
-    // next line's rows, whose products land in TMEM columns that are never stored), plus 1 KB so that this over-read of
-    // the last line stays inside the block.
-    const size_t xbytes = (size_t)(M > 8 ? 16 : 8) * K + 1024;
-    const size_t slack = xbytes >= (size_t)OVERREAD ? 0 : (size_t)OVERREAD - xbytes;
-    const size_t fixed = 1024 + xbytes + slack + 512;
-    p.ok = fixed + 2 * (size_t)p.stage_bytes <= (size_t)SMEM_LIMIT && p.oct_hi <= 16 && p.oct_lo >= 1;
+    p.w_stage = L * line_bytes;
+    // Activation boxes hold 8 rows per line when M <= 8 (the MMA still reads 16 rows per line tile; rows 8..15 are then
+    // the next line's rows, whose products land in TMEM columns that are never stored).
+    p.x_stage = L * (uint32_t)(M > 8 ? 16 : 8) * LINE;
+    p.ok = p.oct_hi <= 16 && p.oct_lo >= 1;
     if (!p.ok) return p;
-    uint32_t s = (uint32_t)(((size_t)SMEM_LIMIT - fixed) / p.stage_bytes);
-    p.stages = s > MAX_STAGES ? MAX_STAGES : s;
-    p.smem = fixed + (size_t)p.stages * p.stage_bytes;
+    // Layout: [W boxes of all stages][x boxes of all stages][slack][barriers].  The MMA reads 128 rows from the start of
+    // every weight line tile, so up to OVERREAD bytes behind the last weight box are read (never used), and 1 KB behind
+    // the last activation box when those hold 8 rows.
+    for (uint32_t st = MAX_STAGES; st >= 2; st--) {
+        const size_t after = (size_t)st * p.x_stage;
+        const size_t slack = (after >= (size_t)OVERREAD ? 0 : (size_t)OVERREAD - after) + 1024;
+        const size_t total = 1024 + (size_t)st * (p.w_stage + p.x_stage) + slack + 512;
+        if (total <= (size_t)SMEM_LIMIT) {
+            p.stages = st;
+            p.slack = (uint32_t)slack;
+            p.smem = total;
+            return p;
+        }
+    }
+    p.ok = false;
     return p;
 }
 
@@ -87,60 +104,63 @@ Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms)
 
 // OUT: 0 = uint8, 1 = float, 2 = int32 (ltq_out_mode).
 template <int OUT>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w_lo,
             const __grid_constant__ CUtensorMap map_w_hi, uint32_t M, uint32_t N, uint32_t K, uint32_t tiles_per_cta,
-            uint32_t tiles, uint32_t oct_lo, uint32_t lines, uint32_t stages, uint32_t stage_bytes, Epilogue epi,
-            void *__restrict__ out, uint32_t *status)
+            uint32_t tiles, uint32_t oct_lo, uint32_t lines, uint32_t stages, uint32_t w_stage, uint32_t x_stage,
+            uint32_t slack, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
+    // By every thread, first thing: the CTA counts as released once all of them have said so, and the next launch's CTAs
+    // should move in (and start fetching their weights) as early as they can.
+    griddep_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw0 = smem_u32(smem_raw);
     const uint32_t ring = (raw0 + 1023u) & ~1023u;                       // [stages][lines][rows][128 B]
-    const uint32_t xs = ring + stages * stage_bytes;                     // [K/128][8 or 16][128 B], then slack if small
-    const uint32_t xrows = M > 8 ? 16u : 8u;                             // rows per line tile of the activation block
-    const uint32_t xbytes = xrows * K + 1024u, slack = xbytes >= (uint32_t)OVERREAD ? 0u : (uint32_t)OVERREAD - xbytes;
-    uint8_t *after = smem_raw + (xs - raw0) + xbytes + slack;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(after);                // full[S] empty[S] xbar tfull[2] tempty[2]
-    uint32_t *misc = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 5);  // [0] tmem base, [1] abort flag
+    const uint32_t xs = ring + stages * w_stage;                         // [stages][lines][8 or 16][128 B]
+    const uint32_t xrows = M > 8 ? 16u : 8u;                             // rows per line tile of an activation box
+    uint8_t *after = smem_raw + (xs - raw0) + stages * x_stage + slack;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after);                // full[S] empty[S] tfull[2] tempty[2]
+    uint32_t *misc = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 4);  // [0] tmem base, [1] abort flag
     volatile uint32_t *abort_flag = misc + 1;
 
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES, xbar = empty0 + 8 * MAX_STAGES;
-    const uint32_t tfull0 = xbar + 8, tempty0 = tfull0 + 16;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES;
+    const uint32_t tfull0 = empty0 + 8 * MAX_STAGES, tempty0 = tfull0 + 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t octs = (N + 7) / 8;
     const uint32_t klines = K / LINE, chunks = (klines + lines - 1) / lines;
     const uint32_t t_begin = blockIdx.x * tiles_per_cta, t_end = t_begin + tiles_per_cta;
+    const uint32_t x_bytes = lines * xrows * LINE;
 
-    // Producer state lives in thread 0: (tile, K chunk) of the next box, ring slot and its phase.
-    uint32_t p_t = t_begin, p_kc = 0, p_st = 0, p_ph = 0;
-    bool p_x_sent = false;
-    // Issues the next weight box (and, behind the very first one, the activation block).  `fresh`: the ring slot has
-    // never been used, so there is nothing to wait for.
-    auto produce = [&](bool fresh) -> bool {
-        const uint32_t o0 = (uint32_t)(((uint64_t)p_t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(p_t + 1) * octs) / tiles);
-        const uint32_t rows = (o1 - o0) * 8;
-        const CUtensorMap *mw = (o1 - o0) == oct_lo ? &map_w_lo : &map_w_hi;
-        if (!fresh && !mbar_wait(empty0 + 8 * p_st, p_ph ^ 1, abort_flag, status, 0x500u | p_st)) return false;
-        // a box always transfers its full size: lines or rows outside the matrix arrive as zeros
-        mbar_expect_tx(full0 + 8 * p_st, lines * rows * LINE);
-        tma_load_3d(ring + p_st * stage_bytes, mw, full0 + 8 * p_st, 0, (int32_t)(o0 * 8), (int32_t)(p_kc * lines));
-        if (!p_x_sent) {
-            // the activation block rides behind the first weight box: [K/128 lines][8 or 16 rows][128 B]
-            mbar_expect_tx(xbar, xrows * K);
-            tma_load_3d(xs, &map_x, xbar, 0, 0, 0);
-            p_x_sent = true;
-        }
-        if (++p_st == stages) { p_st = 0; p_ph ^= 1; }
-        if (++p_kc == chunks) { p_kc = 0; p_t++; }
-        return true;
+    // Producer state lives in thread 0.  A cursor names the next box: (tile, K chunk) and the ring slot with its phase.
+    struct Cursor {
+        uint32_t t, kc, st, ph;
     };
+    auto advance = [&](Cursor &c) {
+        if (++c.st == stages) { c.st = 0; c.ph ^= 1; }
+        if (++c.kc == chunks) { c.kc = 0; c.t++; }
+    };
+    // Weight box of cursor c.  A box always transfers its full size: lines or rows outside the matrix arrive as zeros.
+    // `with_x`: the activation box goes out with it and the pair makes the stage's one arrival; otherwise only the byte
+    // count is announced and the arrival comes later with the activation box.
+    auto issue_w = [&](const Cursor &c, bool with_x) {
+        const uint32_t o0 = (uint32_t)(((uint64_t)c.t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(c.t + 1) * octs) / tiles);
+        const uint32_t w_bytes = lines * (o1 - o0) * 8 * LINE;
+        const CUtensorMap *mw = (o1 - o0) == oct_lo ? &map_w_lo : &map_w_hi;
+        if (with_x) mbar_expect_tx(full0 + 8 * c.st, w_bytes + x_bytes);
+        else mbar_expect_tx_only(full0 + 8 * c.st, w_bytes);
+        tma_load_3d(ring + c.st * w_stage, mw, full0 + 8 * c.st, 0, (int32_t)(o0 * 8), (int32_t)(c.kc * lines));
+    };
+    auto issue_x = [&](const Cursor &c, bool arrive) {
+        if (arrive) mbar_expect_tx(full0 + 8 * c.st, x_bytes);
+        tma_load_3d(xs + c.st * x_stage, &map_x, full0 + 8 * c.st, 0, 0, (int32_t)(c.kc * lines));
+    };
+    Cursor cur{t_begin, 0, 0, 0};
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, NACC);  // one commit per MMA-issuing warp
         }
-        mbar_init(xbar, 1);
         for (int s = 0; s < 2; s++) {
             mbar_init(tfull0 + 8 * s, NACC);  // one commit per MMA-issuing warp
             mbar_init(tempty0 + 8 * s, 4);    // one arrival per epilogue warp
@@ -148,9 +168,20 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         misc[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // Fill the ring before anything else happens in the CTA: the first bytes from HBM are ~1.5 us away and every
-        // set-up step below (TMEM allocation, the CTA-wide barrier) would otherwise add to that.
-        for (uint32_t i = 0; i < stages && p_t < t_end; i++) produce(true);
+        // Fill the ring with weights before anything else happens in the CTA: the first bytes from HBM are more than a
+        // microsecond away.  Weights do not depend on the previous kernel, so this runs ahead of the grid dependency.
+        Cursor w = cur;
+        uint32_t primed = 0;
+        for (; primed < stages && w.t < t_end; primed++) {
+            issue_w(w, false);
+            advance(w);
+        }
+        // The activations may have been written by the previous kernel.
+        griddep_wait();
+        for (uint32_t i = 0; i < primed; i++) {
+            issue_x(cur, true);
+            advance(cur);
+        }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(misc), TMEM_COLS);
@@ -164,15 +195,21 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     if (warp == 0) {
         // ---------------- TMA producer (continues where the pre-fill stopped) ----------------
         if (lane == 0) {
-            while (p_t < t_end && produce(false)) {}
+            while (cur.t < t_end) {
+                if (!mbar_wait(empty0 + 8 * cur.st, cur.ph ^ 1, abort_flag, status, 0x500u | cur.st)) break;
+                issue_w(cur, true);
+                issue_x(cur, false);
+                advance(cur);
+            }
         }
+        __syncwarp();  // the warp arrives at the CTA-wide barriers below as a whole
     } else if (warp == 1 || warp >= 6) {
         // ---------------- MMA issuers (warps 1, 6, 7, 8): warp-uniform loops, one elected lane issues ----------------
         // Issuer k handles K step k (bytes [32k, 32k + 32) of every 128-byte line) into accumulator k.
         constexpr uint32_t idesc = make_idesc_i8(TILE_M, XROWS);
         const uint32_t kstep = warp == 1 ? 0u : (uint32_t)(warp - 5);
         uint32_t st = 0, ph = 0, as = 0, aph = 0;
-        bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(xbar, 0, abort_flag, status, 0x600u));
+        bool ok = true;
         for (uint32_t t = t_begin; ok && t < t_end; t++) {
             const uint32_t o0 = (uint32_t)(((uint64_t)t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(t + 1) * octs) / tiles);
             const uint32_t line_stride = (o1 - o0) * 8 * LINE;  // bytes between the K-major tiles of one box
@@ -185,8 +222,8 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t l0 = kc * lines, nl = (klines - l0) < lines ? (klines - l0) : lines;
-                const uint64_t a_desc = make_smem_desc(ring + st * stage_bytes) + 2u * kstep;
-                const uint64_t b_desc = make_smem_desc(xs + l0 * (xrows * LINE)) + 2u * kstep;
+                const uint64_t a_desc = make_smem_desc(ring + st * w_stage) + 2u * kstep;
+                const uint64_t b_desc = make_smem_desc(xs + st * x_stage) + 2u * kstep;
                 if (elect_one()) {
                     for (uint32_t l = 0; l < nl; l++)  // the first line of a tile overwrites, later lines accumulate
                         umma_i8(d_tmem, a_desc + (uint64_t)((l * line_stride) >> 4), b_desc + (uint64_t)((l * xrows * LINE) >> 4),
@@ -204,6 +241,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     } else {
         // ---------------- epilogue (warps 2..5): thread = weight row, register = token ----------------
         const uint32_t q = (uint32_t)warp & 3u;
+        griddep_wait();  // the activation row sums (and device-side qparams) come from the previous kernel
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
@@ -275,7 +313,8 @@ namespace {
 
 template <int OUT>
 cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOperandMap &hi, const Plan &p, uint64_t M,
-                     uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, cudaStream_t stream)
+                     uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, cudaStream_t stream,
+                     bool early_weights)
 {
     // The opt-in shared-memory size is set once per device: the kernel runs for a few microseconds and a runtime
     // attribute call per launch would cost as much as the launch.
@@ -285,35 +324,45 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_done[dev]) {
-        e = cudaFuncSetAttribute(gemv_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT + 2048);
+        e = cudaFuncSetAttribute(gemv_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    gemv_kernel<OUT><<<p.grid, THREADS, p.smem, stream>>>(
-        *reinterpret_cast<const CUtensorMap *>(mx.opaque), *reinterpret_cast<const CUtensorMap *>(lo.opaque),
-        *reinterpret_cast<const CUtensorMap *>(hi.opaque), (uint32_t)M, (uint32_t)N, (uint32_t)K, p.tiles_per_cta, p.tiles,
-        p.oct_lo, p.lines, p.stages, p.stage_bytes, epi, out, status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = early_weights ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, gemv_kernel<OUT>, *reinterpret_cast<const CUtensorMap *>(mx.opaque),
+                           *reinterpret_cast<const CUtensorMap *>(lo.opaque), *reinterpret_cast<const CUtensorMap *>(hi.opaque),
+                           (uint32_t)M, (uint32_t)N, (uint32_t)K, p.tiles_per_cta, p.tiles, p.oct_lo, p.lines, p.stages,
+                           p.w_stage, p.x_stage, p.slack, epi, out, status);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 }  // namespace
 
 bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W)
 {
-    return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 128 && K % 128 == 0 && K <= 8192 &&
+    return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 128 && K % 128 == 0 && K < (1ull << 31) &&
            (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148).ok;
 }
 
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache)
+                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache, bool early_weights)
 {
     const Plan p = make_plan(M, N, K, sms);
     if (!p.ok) return cudaErrorInvalidConfiguration;
     TcOperandMap mx;
     GemvWeightMaps local;
-    // activations: one box holds the whole block, [K/128 lines][8 or 16 rows][128 B]; rows >= M are out of bounds -> zeros
-    if (tc_make_map_lines(&mx, x, M, K, M > 8 ? 16 : 8, (int)(K / LINE)) != 0) return cudaErrorInvalidValue;
+    // activations: a box is [lines][8 or 16 rows][128 B]; rows >= M are out of bounds -> zeros
+    if (tc_make_map_lines(&mx, x, M, K, M > 8 ? 16 : 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
     GemvWeightMaps *wm = cache ? cache : &local;
     if (!wm->lo.matches(W, N, K, (int)p.oct_lo * 8, (int)p.lines)) {
         if (tc_make_map_lines(&wm->lo, W, N, K, (int)p.oct_lo * 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
@@ -322,9 +371,9 @@ cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t
         if (tc_make_map_lines(&wm->hi, W, N, K, (int)p.oct_hi * 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
     }
     switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_t<0>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream);
-        case LTQ_OUT_F32: return launch_t<1>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream);
-        default: return launch_t<2>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream);
+        case LTQ_OUT_U8: return launch_t<0>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights);
+        case LTQ_OUT_F32: return launch_t<1>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights);
+        default: return launch_t<2>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights);
     }
 }
 

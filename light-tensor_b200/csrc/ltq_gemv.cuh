@@ -17,7 +17,11 @@ struct GemvWeightMaps {
 
 // `status`: device word that receives a code if a bounded wait inside the kernel expires.
 // `cache`: optional storage for the weight tensor maps, reused across calls while W, N, K stay the same.
+// `early_weights`: the caller guarantees that no work still in flight on `stream` writes W; the kernel is then launched
+// as a programmatic dependent of its predecessor and streams weights before that predecessor has finished (x, the
+// epilogue's vectors and `out` are only touched after it has).
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache);
+                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache,
+                        bool early_weights);
 
 }  // namespace ltq

@@ -112,7 +112,7 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
     epi.flags = 0;
 
     if (!tA && tB && K > 0 && gemv_shape_ok(M, N, K, A_dev, B_dev)) {
-        LTQ_CUDA_TRY(launch_gemv(A_dev, B_dev, M, N, K, epi, C_dev, sd->status, sd->sms, st, nullptr));
+        LTQ_CUDA_TRY(launch_gemv(A_dev, B_dev, M, N, K, epi, C_dev, sd->status, sd->sms, st, nullptr, false));
     } else if (!tA && tB && K > 0 && tc_shape_ok(M, N, K, A_dev, B_dev)) {
         const int bn = tc_pick_bn(M, N, sd->sms);
         TcOperandMap map_a, map_b;  // encoded on the host into these stack objects; no device memory involved

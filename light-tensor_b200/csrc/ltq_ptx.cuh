@@ -17,6 +17,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// Announces bytes without arriving: the phase cannot complete before a later arrival, whatever lands meanwhile.
+__device__ __forceinline__ void mbar_expect_tx_only(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -81,6 +86,13 @@ __device__ __forceinline__ bool elect_one()
         : "=r"(pred));
     return pred != 0;
 }
+
+// Programmatic dependent launch.  griddep_wait: returns once every kernel this grid programmatically depends on has
+// completed and its writes are visible (at once when the grid was launched without such a dependency).
+// griddep_launch_dependents: this CTA no longer holds back the launch of the next kernel in the stream; that kernel
+// starts when every CTA of this grid has said so or exited.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion counted in bytes on `bar`.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)

@@ -184,3 +184,43 @@ def test_skinny_sweep_full_vs_oracle(cuda, oracle, M):
     rel = np.abs(out - want) / np.maximum(np.abs(want), 1e-30)
     assert rel.max() <= 1e-5
     np.testing.assert_array_equal(out.view(np.uint32), want.view(np.uint32))
+
+
+def test_back_to_back_skinny_launches_respect_their_inputs(cuda, oracle):
+    """The skinny kernel starts streaming weights before the kernel in front of it has finished.  Everything else it
+    reads must wait: here each call's activations and row sums are written by the kernel launched just before it (the
+    same buffers every time), and a second layer consumes the first layer's output directly."""
+    import ltq
+    rng = np.random.default_rng(21)
+    K, N1, N2, M, reps = 1024, 2048, 512, 4, 12
+    w1 = rng.integers(0, 256, (N1, K), dtype=np.uint8)
+    w2 = rng.integers(0, 256, (N2, N1), dtype=np.uint8)
+    b1 = rng.integers(-5000, 5000, N1, dtype=np.int32)
+    rows = [(0.02, 128), (0.005, 127), (3.0, 7), (0.004, 120), (40.0, 100)]   # in, w1, mid, w2, out
+    q_in, q_w1, q_mid, q_w2, q_out = [ltq_qp(r) for r in rows]
+    l1 = ltq.LayerHandle(0, K, N1)
+    l1.set_weights(cuda.from_numpy(w1).cuda(), cuda.from_numpy(b1).cuda())
+    l1.set_qparams(q_in, q_w1, q_mid)
+    l2 = ltq.LayerHandle(0, N1, N2)
+    l2.set_weights(cuda.from_numpy(w2).cuda())
+    l2.set_qparams(q_mid, q_w2, q_out)
+    xs = [rng.normal(0, 0.8, (M, K)).astype(np.float32) for _ in range(reps)]
+    xs_dev = [cuda.from_numpy(x).cuda() for x in xs]
+    xq = cuda.empty((M, K), dtype=cuda.uint8, device="cuda")
+    asum = cuda.empty(M, dtype=cuda.int32, device="cuda")
+    mids = [cuda.empty((M, N1), dtype=cuda.uint8, device="cuda") for _ in range(reps)]
+    outs = [cuda.empty((M, N2), dtype=cuda.uint8, device="cuda") for _ in range(reps)]
+    cuda.cuda.synchronize()
+    for i in range(reps):   # no synchronisation inside the loop: 3 dependent kernels per iteration, back to back
+        ltq.quantize_rows(xs_dev[i], qp=q_in, q=xq, asum=asum)
+        l1.forward(xq, ltq.OUT_U8, ltq.FLAG_FORCE_SKINNY, asum=asum, out=mids[i])
+        l2.forward(mids[i], ltq.OUT_U8, ltq.FLAG_FORCE_SKINNY, out=outs[i])
+    cuda.cuda.synchronize()
+    o_in, o_w1, o_mid, o_w2, o_out = [qp_of(oracle, r) for r in rows]
+    for i in range(reps):
+        xq_ref = oracle.port.quantize_u8(xs[i], o_in)
+        mid_ref, _ = oracle.port.quantized_matmul(xq_ref, w1, M, N1, K, [o_in, o_w1, o_mid], bias=b1)
+        out_ref, _ = oracle.port.quantized_matmul(mid_ref, w2, M, N2, N1, [o_mid, o_w2, o_out])
+        np.testing.assert_array_equal(mids[i].cpu().numpy(), mid_ref, err_msg=f"layer 1, iteration {i}")
+        np.testing.assert_array_equal(outs[i].cpu().numpy(), out_ref, err_msg=f"layer 2, iteration {i}")
+    l1.check()
