@@ -62,7 +62,7 @@ typedef enum ltq_out_mode {
 #define LTQ_FLAG_FORCE_TC 0x200u    /* tcgen05 kernel (needs K % 16 == 0) */
 #define LTQ_FLAG_FORCE_TC_PAIR 0x800u   /* with the tcgen05 path: the 2-CTA (cta_group::2) 256 x 256 tile kernel */
 #define LTQ_FLAG_FORCE_TC_SINGLE 0x1000u/* with the tcgen05 path: the single-CTA kernel */
-#define LTQ_FLAG_FORCE_SKINNY 0x400u/* weight-streaming kernel (needs M <= 16, K % 128 == 0, K <= 8192) */
+#define LTQ_FLAG_FORCE_SKINNY 0x400u/* weight-streaming kernel (needs M <= 16, K % 128 == 0) */
 
 int ltq_version(void);
 const char *ltq_last_error(void);
@@ -160,7 +160,7 @@ int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_
  *   qp_in_dev optional DEVICE qparams overriding the layer's input qparams (dynamic activation quantisation
  *             without a host round trip); NULL = use the value set by ltq_layer_set_qparams
  *   out_dev   uint8 / float / int32 [M,N] by out_mode
- * Kernel choice: M <= 16 with K % 128 == 0 and K <= 8192 -> weight-streaming kernel; otherwise the tcgen05 kernel
+ * Kernel choice: M <= 16 with K % 128 == 0 -> weight-streaming kernel; otherwise the tcgen05 kernel
  * when K % 16 == 0; else the generic kernel. */
 int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
                       const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream);

@@ -93,7 +93,7 @@ int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B
                     (unsigned long long)M, (unsigned long long)N, (unsigned long long)K);
         *path = PATH_TC;
     } else if (flags & LTQ_FLAG_FORCE_SKINNY) {
-        LTQ_REQUIRE(sk_ok, LTQ_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, K %% 128 == 0, K <= 8192 and 16-byte aligned operands (M=%llu K=%llu)",
+        LTQ_REQUIRE(sk_ok, LTQ_ERR_UNSUPPORTED, "skinny kernel needs M <= 16, K %% 128 == 0 and 16-byte aligned operands (M=%llu K=%llu)",
                     (unsigned long long)M, (unsigned long long)K);
         *path = PATH_SKINNY;
     } else if (sk_ok) {

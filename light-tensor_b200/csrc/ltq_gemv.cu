@@ -49,6 +49,7 @@ constexpr int SMEM_LIMIT = 112 * 1024;     // two CTAs (this launch's and the ne
 constexpr int OVERREAD = TILE_M * LINE;    // an MMA reads 128 rows from a tile's start whatever the band holds
 constexpr int NACC = 4;                    // independent partial accumulators per tile (summed in the epilogue)
 constexpr uint32_t TMEM_COLS = 2 * NACC * XROWS;  // two buffers of NACC accumulators of 16 columns = 128
+constexpr uint32_t PREFETCH_AHEAD = 16;    // boxes requested into L2 beyond the ring (~320 KB per CTA, ~47 MB per GPU)
 
 struct Plan {
     uint32_t grid, tiles_per_cta, tiles;   // tiles = grid * tiles_per_cta
@@ -131,30 +132,41 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     const uint32_t t_begin = blockIdx.x * tiles_per_cta, t_end = t_begin + tiles_per_cta;
     const uint32_t x_bytes = lines * xrows * LINE;
 
-    // Producer state lives in thread 0.  A cursor names the next box: (tile, K chunk) and the ring slot with its phase.
+    const uint64_t w_policy = l2_policy_evict_first();  // weights are read once per launch
+    // Producer state lives in thread 0.  A cursor names a box: (tile, K chunk), the tile's first row, row count and
+    // tensor map, and the ring slot with its phase.
     struct Cursor {
-        uint32_t t, kc, st, ph;
+        uint32_t t, kc, st, ph, row0, rows;
+        const CUtensorMap *map;
+    };
+    auto enter_tile = [&](Cursor &c) {
+        const uint32_t o0 = (uint32_t)(((uint64_t)c.t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(c.t + 1) * octs) / tiles);
+        c.row0 = o0 * 8;
+        c.rows = (o1 - o0) * 8;
+        c.map = (o1 - o0) == oct_lo ? &map_w_lo : &map_w_hi;
     };
     auto advance = [&](Cursor &c) {
         if (++c.st == stages) { c.st = 0; c.ph ^= 1; }
-        if (++c.kc == chunks) { c.kc = 0; c.t++; }
+        if (++c.kc == chunks) {
+            c.kc = 0;
+            if (++c.t < t_end) enter_tile(c);
+        }
     };
     // Weight box of cursor c.  A box always transfers its full size: lines or rows outside the matrix arrive as zeros.
     // `with_x`: the activation box goes out with it and the pair makes the stage's one arrival; otherwise only the byte
     // count is announced and the arrival comes later with the activation box.
     auto issue_w = [&](const Cursor &c, bool with_x) {
-        const uint32_t o0 = (uint32_t)(((uint64_t)c.t * octs) / tiles), o1 = (uint32_t)(((uint64_t)(c.t + 1) * octs) / tiles);
-        const uint32_t w_bytes = lines * (o1 - o0) * 8 * LINE;
-        const CUtensorMap *mw = (o1 - o0) == oct_lo ? &map_w_lo : &map_w_hi;
+        const uint32_t w_bytes = lines * c.rows * LINE;
         if (with_x) mbar_expect_tx(full0 + 8 * c.st, w_bytes + x_bytes);
         else mbar_expect_tx_only(full0 + 8 * c.st, w_bytes);
-        tma_load_3d(ring + c.st * w_stage, mw, full0 + 8 * c.st, 0, (int32_t)(o0 * 8), (int32_t)(c.kc * lines));
+        tma_load_3d_hint(ring + c.st * w_stage, c.map, full0 + 8 * c.st, 0, (int32_t)c.row0, (int32_t)(c.kc * lines), w_policy);
     };
     auto issue_x = [&](const Cursor &c, bool arrive) {
         if (arrive) mbar_expect_tx(full0 + 8 * c.st, x_bytes);
         tma_load_3d(xs + c.st * x_stage, &map_x, full0 + 8 * c.st, 0, 0, (int32_t)(c.kc * lines));
     };
-    Cursor cur{t_begin, 0, 0, 0};
+    Cursor cur{t_begin, 0, 0, 0, 0, 0, nullptr};  // next box to load into the ring
+    Cursor pf = cur;                              // next box to ask into L2; runs up to PREFETCH_AHEAD boxes in front
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; s++) {
@@ -170,11 +182,20 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // Fill the ring with weights before anything else happens in the CTA: the first bytes from HBM are more than a
         // microsecond away.  Weights do not depend on the previous kernel, so this runs ahead of the grid dependency.
-        Cursor w = cur;
+        enter_tile(cur);
+        pf = cur;
         uint32_t primed = 0;
-        for (; primed < stages && w.t < t_end; primed++) {
-            issue_w(w, false);
-            advance(w);
+        for (; primed < stages && pf.t < t_end; primed++) {
+            issue_w(pf, false);
+            advance(pf);
+        }
+        // The ring is all this CTA can hold while it waits for its turn, a fraction of its weights.  The boxes behind it
+        // are requested into L2, so that HBM keeps streaming through the hand-over between two launches (the wait for
+        // the previous kernel, the first activation fetch, the previous kernel's last MMAs and epilogue) and the ring
+        // later refills from L2.
+        for (uint32_t i = 0; i < PREFETCH_AHEAD && pf.t < t_end; i++) {
+            tma_prefetch_3d(pf.map, 0, (int32_t)pf.row0, (int32_t)(pf.kc * lines));
+            advance(pf);
         }
         // The activations may have been written by the previous kernel.
         griddep_wait();
@@ -200,6 +221,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 issue_w(cur, true);
                 issue_x(cur, false);
                 advance(cur);
+                if (pf.t < t_end) {
+                    tma_prefetch_3d(pf.map, 0, (int32_t)pf.row0, (int32_t)(pf.kc * lines));
+                    advance(pf);
+                }
             }
         }
         __syncwarp();  // the warp arrives at the CTA-wide barriers below as a whole

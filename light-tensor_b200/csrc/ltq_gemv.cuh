@@ -5,8 +5,8 @@
 
 namespace ltq {
 
-// True when the kernel can take the problem: 1 <= M <= 16, K a multiple of 128 and at most 8192 (the activation block and
-// a ring of weight stages must fit in shared memory), 16-byte aligned bases.
+// True when the kernel can take the problem: 1 <= M <= 16, K a multiple of 128, 16-byte aligned bases, and a band of at
+// most 128 weight rows per tile with at least two ring stages in shared memory.
 bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W);
 // x uint8 [M,K], W uint8 [N,K], both K-contiguous.
 // Weight tensor maps of the kernel (two box heights, because the row bands of the CTAs differ by at most one group of
