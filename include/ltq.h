@@ -58,6 +58,7 @@ typedef enum ltq_out_mode {
 /* Kernel selection override, for tests and profiling (default: by shape). */
 #define LTQ_FLAG_BIAS_PER_CHANNEL 4u /* ltq_conv2d_forward only: bias[c] per output channel instead of the reference's
                                        indexing by output position (see ltq_conv2d_forward) */
+#define LTQ_MAX_DESTS 8  /* destinations of one ltq_layer_forward_scatter call (this GPU's buffer + 7 peers) */
 #define LTQ_FLAG_FORCE_SIMT 0x100u  /* generic dp4a tile kernel */
 #define LTQ_FLAG_FORCE_TC 0x200u    /* tcgen05 kernel (needs K % 16 == 0) */
 #define LTQ_FLAG_FORCE_TC_PAIR 0x800u   /* with the tcgen05 path: the 2-CTA (cta_group::2) 256 x 256 tile kernel */
@@ -164,6 +165,29 @@ int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_
  * when K % 16 == 0; else the generic kernel. */
 int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
                       const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream);
+
+/* ltq_layer_forward with the result written into several buffers at once, each holding rows of ld_out elements, at
+ * column col_offset: element (i, j) of this layer's output goes to dests[d][i * ld_out + col_offset + j] for every d.
+ * No counterpart in the reference (which runs on one device).  This is the exchange step of a COLUMN-SHARDED layer
+ * done by the GEMM epilogue itself: each rank owns out_features / world columns, dests[0] is its own [M, ld_out]
+ * buffer and dests[1 .. n_dests-1] are the other ranks' buffers mapped into this process (ltq_peer_open), so the
+ * stores travel over NVLink while the tiles are still being computed and no all-gather or relayout pass follows.
+ * n_dests <= LTQ_MAX_DESTS.  The call only orders its own stores: before any rank READS its buffer, every rank's
+ * call must have completed (a stream-ordered collective of any size, or a host barrier after a stream sync), and a
+ * buffer must not be rewritten while another rank may still read it (alternate two buffers).
+ * 16-byte stores are used when ld_out * element size, col_offset * element size and all bases are multiples of 16. */
+int ltq_layer_forward_scatter(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
+                              const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *const *dests, int n_dests,
+                              uint64_t ld_out, uint64_t col_offset, void *stream);
+
+/* Device buffers that other processes on the same node can map (CUDA IPC: cudaMalloc + cudaIpcGetMemHandle on the
+ * owner, cudaIpcOpenMemHandle with lazy peer access on the others).  handle64 is 64 opaque bytes to be carried to the
+ * other process by any means (torch.distributed's object collectives in this repository).  No counterpart in the
+ * reference. */
+int ltq_peer_alloc(void **dev_ptr, uint64_t bytes, int device, unsigned char *handle64);
+int ltq_peer_free(void *dev_ptr, int device);
+int ltq_peer_open(const unsigned char *handle64, int device, void **peer_ptr);
+int ltq_peer_close(void *peer_ptr, int device);
 
 /* Reads (and clears) the layer's device status word: LTQ_OK, or LTQ_ERR_DEVICE_TIMEOUT when a bounded wait inside a
  * kernel ran out since the last check.  Synchronises `stream`. */

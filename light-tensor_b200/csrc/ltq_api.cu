@@ -67,6 +67,9 @@ Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *
     e.asum = asum;
     e.bias = bias;
     e.row_bias = nullptr;
+    e.ldc = 0;
+    e.n_more = 0;
+    for (auto &m : e.more_out) m = nullptr;
     e.qpA_dev = nullptr;
     e.sA = qa.scale;
     e.sB = qb.scale;
@@ -394,40 +397,108 @@ int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_
     return LTQ_OK;
 }
 
-int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
-                      const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream)
+// Shared by ltq_layer_forward (one dense destination) and ltq_layer_forward_scatter.
+static int layer_forward_impl(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
+                              const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *const *dests, int n_dests,
+                              uint64_t ld_out, uint64_t col_offset, void *stream)
 {
-    LTQ_REQUIRE(layer && x_dev && out_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE(layer && x_dev && dests && n_dests >= 1 && n_dests <= LTQ_MAX_DESTS, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    for (int d = 0; d < n_dests; d++) LTQ_REQUIRE(dests[d], LTQ_ERR_INVALID_ARG, "Invalid argument");
     LTQ_REQUIRE(layer->w, LTQ_ERR_INVALID_ARG, "ltq_layer_set_weights has not been called");
     LTQ_REQUIRE(out_mode == LTQ_OUT_U8 || out_mode == LTQ_OUT_F32 || out_mode == LTQ_OUT_I32, LTQ_ERR_INVALID_ARG,
                 "unknown out_mode %d", out_mode);
     LTQ_REQUIRE(M < (1ull << 31), LTQ_ERR_TOO_LARGE, "M must be below 2^31");
+    LTQ_REQUIRE(ld_out == 0 || (ld_out >= layer->N && col_offset <= ld_out - layer->N), LTQ_ERR_INVALID_ARG,
+                "the layer's %llu columns do not fit at column %llu of a row of %llu", (unsigned long long)layer->N,
+                (unsigned long long)col_offset, (unsigned long long)ld_out);
     if (M == 0) return LTQ_OK;
     LTQ_ENTER_DEVICE(layer->device);
     cudaStream_t st = (cudaStream_t)stream;
     if (!asum_dev) {
-        if (M > layer->asum_cap) {
-            // Same policy as the reference's workspace: reallocate only when the batch grows.
-            int32_t *p = nullptr;
-            cudaError_t e = cudaMalloc(&p, M * sizeof(int32_t));
-            if (e != cudaSuccess) {
-                set_error("cudaMalloc of %llu activation sums failed: %s", (unsigned long long)M, cudaGetErrorString(e));
-                return LTQ_ERR_NO_MEMORY;
-            }
-            if (layer->asum_ws) {
-                LTQ_CUDA_TRY(cudaStreamSynchronize(st));
-                cudaFree(layer->asum_ws);
-            }
-            layer->asum_ws = p;
-            layer->asum_cap = M;
-        }
+        // Same policy as the reference's workspace (l-ten/fully_connected.cpp:366-371): reallocate only when the batch grows.
+        int rc = grow(&layer->asum_ws, &layer->asum_cap, M, st, "the activation sums");
+        if (rc != LTQ_OK) return rc;
         LTQ_CUDA_TRY(launch_row_sums(x_dev, M, layer->K, layer->asum_ws, st));
         asum_dev = layer->asum_ws;
     }
     Epilogue epi = make_epilogue(layer->wsum, asum_dev, layer->bias, layer->qp_in, layer->qp_wt, layer->qp_out, layer->K,
                                  out_mode, flags);
     epi.qpA_dev = qp_in_dev;
-    return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi, out_dev, flags, layer, st);
+    const uint64_t esize = out_mode == LTQ_OUT_U8 ? 1 : 4;
+    epi.ldc = ld_out;
+    epi.n_more = n_dests - 1;
+    for (int d = 1; d < n_dests; d++) epi.more_out[d - 1] = static_cast<uint8_t *>(dests[d]) + col_offset * esize;
+    return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi,
+                       static_cast<uint8_t *>(dests[0]) + col_offset * esize, flags, layer, st);
+}
+
+int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
+                      const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream)
+{
+    LTQ_REQUIRE(out_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    void *dests[1] = {out_dev};
+    return layer_forward_impl(layer, x_dev, asum_dev, M, qp_in_dev, out_mode, flags, dests, 1, 0, 0, stream);
+}
+
+int ltq_layer_forward_scatter(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
+                              const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *const *dests, int n_dests,
+                              uint64_t ld_out, uint64_t col_offset, void *stream)
+{
+    LTQ_REQUIRE(ld_out >= 1, LTQ_ERR_INVALID_ARG, "ld_out must be the row length of the destination buffers");
+    return layer_forward_impl(layer, x_dev, asum_dev, M, qp_in_dev, out_mode, flags, dests, n_dests, ld_out, col_offset,
+                              stream);
+}
+
+// ---- buffers that other processes on this node can map (CUDA IPC) -----------------------------------------------------
+int ltq_peer_alloc(void **dev_ptr, uint64_t bytes, int device, unsigned char *handle64)
+{
+    LTQ_REQUIRE(dev_ptr && handle64 && bytes >= 1, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    *dev_ptr = nullptr;
+    LTQ_ENTER_DEVICE(device);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+        set_error("cudaMalloc of %llu bytes failed: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+        return LTQ_ERR_NO_MEMORY;
+    }
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        set_error("cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+        return LTQ_ERR_CUDA;
+    }
+    memcpy(handle64, &h, sizeof h);
+    *dev_ptr = p;
+    return LTQ_OK;
+}
+
+int ltq_peer_free(void *dev_ptr, int device)
+{
+    if (!dev_ptr) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(cudaFree(dev_ptr));
+    return LTQ_OK;
+}
+
+int ltq_peer_open(const unsigned char *handle64, int device, void **peer_ptr)
+{
+    LTQ_REQUIRE(handle64 && peer_ptr, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    *peer_ptr = nullptr;
+    LTQ_ENTER_DEVICE(device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof h);
+    LTQ_CUDA_TRY(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return LTQ_OK;
+}
+
+int ltq_peer_close(void *peer_ptr, int device)
+{
+    if (!peer_ptr) return LTQ_OK;
+    LTQ_ENTER_DEVICE(device);
+    LTQ_CUDA_TRY(cudaIpcCloseMemHandle(peer_ptr));
+    return LTQ_OK;
 }
 
 // ---- quantized convolution (Conv2d_q) ----------------------------------------------------------------------------------

@@ -72,7 +72,22 @@ struct Epilogue {
     uint32_t K;
     int out_mode;                 // ltq_out_mode
     unsigned flags;               // LTQ_FLAG_RELU | LTQ_FLAG_SATURATE
+    // Where results go.  Element (i, j) is written at index i*ldc + j of the kernel's `out` argument and of every
+    // further destination (buffers of the same layout, e.g. the peer GPUs' copies of a column-sharded output: the
+    // epilogue then IS the all-gather).  ldc = 0 means a dense [M, N] output.
+    uint64_t ldc;
+    void *more_out[LTQ_MAX_DESTS - 1];
+    int n_more;
 };
+
+__device__ __forceinline__ uint64_t epilogue_pitch(const Epilogue &e, uint64_t N) { return e.ldc ? e.ldc : N; }
+// 16-byte stores need every row start aligned in every destination: pitch and bases multiples of 16 bytes.
+__device__ __forceinline__ bool epilogue_vec_ok(const Epilogue &e, const void *out, uint64_t N, uint32_t esize)
+{
+    bool ok = ((epilogue_pitch(e, N) * esize) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+    for (int d = 0; d < e.n_more; d++) ok = ok && (((uintptr_t)e.more_out[d] & 15) == 0);
+    return ok;
+}
 
 // Per-launch constants derived once per thread.
 struct EpilogueConsts {
@@ -141,6 +156,69 @@ __device__ __forceinline__ uint8_t epilogue_u8(int32_t acc, const EpilogueConsts
 __device__ __forceinline__ float epilogue_f32(int32_t acc, const EpilogueConsts &c)
 {
     return __fmul_rn(c.sAB, __int2float_rn(acc));
+}
+
+// One chunk of W (32 or 16) accumulator columns of one output row: correction terms, conversion, then the same stores
+// into every destination at element offset `off` (16-byte stores when vec_ok and the chunk is complete).
+template <int OUT, int W>
+__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
+                                               const EpilogueConsts &c, bool relu, bool sat, const Epilogue &e, void *out,
+                                               uint64_t off, bool vec_ok, int valid)
+{
+    // column terms: 16-byte shared loads (the chunk starts at a multiple of 16 columns)
+    uint32_t col[W];
+#pragma unroll
+    for (int g = 0; g < W / 4; g++) {
+        const uint4 t4 = reinterpret_cast<const uint4 *>(col_smem)[g];
+        col[4 * g] = t4.x;
+        col[4 * g + 1] = t4.y;
+        col[4 * g + 2] = t4.z;
+        col[4 * g + 3] = t4.w;
+    }
+    if (OUT == 0) {
+        uint32_t p[W / 4];
+#pragma unroll
+        for (int g = 0; g < W / 4; g++) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                const int j = g * 4 + b;
+                const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
+                w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
+            }
+            p[g] = w;
+        }
+        for (int d = -1; d < e.n_more; d++) {
+            uint8_t *dst = static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + off;
+            if (vec_ok && valid == W) {
+                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                for (int g = 0; g < W / 16; g++) d4[g] = make_uint4(p[4 * g], p[4 * g + 1], p[4 * g + 2], p[4 * g + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < W; j++)
+                    if (j < valid) dst[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < W; j++) {
+            const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
+            v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
+        }
+        for (int d = -1; d < e.n_more; d++) {
+            uint32_t *dst = static_cast<uint32_t *>(d < 0 ? out : e.more_out[d]) + off;
+            if (vec_ok && valid == W) {
+                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                for (int g = 0; g < W / 4; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < W; j++)
+                    if (j < valid) dst[j] = v[j];
+            }
+        }
+    }
 }
 
 // ---- kernel launchers implemented in the other translation units --------------------------------------------------

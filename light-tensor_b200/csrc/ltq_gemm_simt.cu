@@ -80,13 +80,16 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, ui
             const uint64_t col = n0 + tx + 16 * j;
             if (col >= N) continue;
             const int32_t v = epilogue_acc((uint32_t)acc[i][j], rt, epilogue_col_term(epi, c, col), relu);
-            const uint64_t o = row * N + col;
-            if (epi.out_mode == LTQ_OUT_U8)
-                static_cast<uint8_t *>(out)[o] = epilogue_u8(v, c, sat);
-            else if (epi.out_mode == LTQ_OUT_F32)
-                static_cast<float *>(out)[o] = epilogue_f32(v, c);
-            else
-                static_cast<int32_t *>(out)[o] = v;
+            const uint64_t o = row * epilogue_pitch(epi, N) + col;
+            for (int d = -1; d < epi.n_more; d++) {
+                void *dst = d < 0 ? out : epi.more_out[d];
+                if (epi.out_mode == LTQ_OUT_U8)
+                    static_cast<uint8_t *>(dst)[o] = epilogue_u8(v, c, sat);
+                else if (epi.out_mode == LTQ_OUT_F32)
+                    static_cast<float *>(dst)[o] = epilogue_f32(v, c);
+                else
+                    static_cast<int32_t *>(dst)[o] = v;
+            }
         }
     }
 }

@@ -109,6 +109,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
+        __syncwarp();  // the warp arrives at the CTA-wide barriers below as a whole
     } else if (warp == 1) {
         // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
         constexpr uint32_t idesc = make_idesc_i8(BM, BN);
@@ -147,9 +148,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
-        OutT *o = static_cast<OutT *>(out);
-        // 16-byte stores need every row start aligned: row pitch and base both multiples of 16 bytes.
-        const bool vec_ok = (((uint64_t)N * sizeof(OutT)) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+        const uint64_t ldc = epilogue_pitch(epi, N);
+        const bool vec_ok = epilogue_vec_ok(epi, out, N, sizeof(OutT));
         uint32_t as = 0, aph = 0;
         bool ok = true;
         for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -174,47 +174,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_ld32(taddr + ch * 32, v);
                     tmem_ld_wait();
                     const uint32_t c0 = n0 + ch * 32;
-                    if (row < M && c0 < N) {
-                        OutT *dst = o + (uint64_t)row * N + c0;
-                        const int valid = (N - c0) < 32u ? (int)(N - c0) : 32;
-                        if (OUT == 0) {
-                            uint32_t p[8];
-#pragma unroll
-                            for (int g = 0; g < 8; g++) {
-                                uint32_t w = 0;
-#pragma unroll
-                                for (int b = 0; b < 4; b++) {
-                                    const int j = g * 4 + b;
-                                    const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
-                                    w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
-                                }
-                                p[g] = w;
-                            }
-                            if (vec_ok && valid == 32) {
-                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-                                d4[0] = make_uint4(p[0], p[1], p[2], p[3]);
-                                d4[1] = make_uint4(p[4], p[5], p[6], p[7]);
-                            } else {
-                                for (int j = 0; j < valid; j++)
-                                    reinterpret_cast<uint8_t *>(dst)[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                const int32_t a = epilogue_acc(v[j], rt, col[ch * 32 + j], relu);
-                                v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
-                            }
-                            if (vec_ok && valid == 32) {
-                                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-                                for (int g = 0; g < 8; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (j < valid) reinterpret_cast<uint32_t *>(dst)[j] = v[j];
-                            }
-                        }
-                    }
+                    if (row < M && c0 < N)
+                        epilogue_chunk<OUT, 32>(v, rt, col + ch * 32, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
+                                                (N - c0) < 32u ? (int)(N - c0) : 32);
                 }
                 // all of this warp's reads of the accumulator are done -> hand the buffer back to the MMA warp
                 tc_fence_before();
@@ -265,62 +227,6 @@ struct PCfg {
     static_assert(B_BYTES % 1024 == 0, "swizzled tiles must stay 1024-byte aligned");
     static_assert(PBN % 16 == 0 && PBN >= 144 && PBN <= 256, "tile width");
 };
-
-// One chunk of W (32 or 16) accumulator columns of one row: correction terms, conversion, store.
-template <int OUT, int W>
-__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
-                                               const EpilogueConsts &c, bool relu, bool sat, void *dst_v, bool vec_ok,
-                                               int valid)
-{
-    // column terms: 16-byte shared loads (the chunk starts at a multiple of 16 columns)
-    uint32_t col[W];
-#pragma unroll
-    for (int g = 0; g < W / 4; g++) {
-        const uint4 t4 = reinterpret_cast<const uint4 *>(col_smem)[g];
-        col[4 * g] = t4.x;
-        col[4 * g + 1] = t4.y;
-        col[4 * g + 2] = t4.z;
-        col[4 * g + 3] = t4.w;
-    }
-    if (OUT == 0) {
-        uint32_t p[W / 4];
-#pragma unroll
-        for (int g = 0; g < W / 4; g++) {
-            uint32_t w = 0;
-#pragma unroll
-            for (int b = 0; b < 4; b++) {
-                const int j = g * 4 + b;
-                const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
-                w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
-            }
-            p[g] = w;
-        }
-        if (vec_ok && valid == W) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst_v);
-#pragma unroll
-            for (int g = 0; g < W / 16; g++) d4[g] = make_uint4(p[4 * g], p[4 * g + 1], p[4 * g + 2], p[4 * g + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < W; j++)
-                if (j < valid) reinterpret_cast<uint8_t *>(dst_v)[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < W; j++) {
-            const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
-            v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
-        }
-        if (vec_ok && valid == W) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst_v);
-#pragma unroll
-            for (int g = 0; g < W / 4; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < W; j++)
-                if (j < valid) reinterpret_cast<uint32_t *>(dst_v)[j] = v[j];
-        }
-    }
-}
 
 }  // namespace
 
@@ -394,6 +300,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
         }
+        __syncwarp();  // the warp arrives at the CTA-wide barriers below as a whole
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only): warp-uniform loop, one elected lane issues ----------------
         if (rank == 0) {
@@ -435,8 +342,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
-        OutT *o = static_cast<OutT *>(out);
-        const bool vec_ok = (((uint64_t)N * sizeof(OutT)) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+        const uint64_t ldc = epilogue_pitch(epi, N);
+        const bool vec_ok = epilogue_vec_ok(epi, out, N, sizeof(OutT));
         constexpr int COL0 = 128;                          // column split between the two warps of a quarter
         uint32_t as = 0, aph = 0;
         bool ok = true;
@@ -463,7 +370,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_wait();
                     const uint32_t c0 = n0 + cc;
                     if (row < M && c0 < N)
-                        epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, o + (uint64_t)row * N + c0, vec_ok,
+                        epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
                                                 (N - c0) < 32u ? (int)(N - c0) : 32);
                 }
                 if ((ce - cb) % 32 != 0) {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
@@ -473,7 +380,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_wait();
                     const uint32_t c0 = n0 + cc;
                     if (row < M && c0 < N)
-                        epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, o + (uint64_t)row * N + c0, vec_ok,
+                        epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
                                                 (N - c0) < 16u ? (int)(N - c0) : 16);
                 }
                 // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)

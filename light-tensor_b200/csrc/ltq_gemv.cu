@@ -271,6 +271,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
         OutT *o = static_cast<OutT *>(out);
+        const uint64_t ldc = epilogue_pitch(epi, N);
         uint32_t rt[XROWS];  // per-token part of the correction; identical for every weight row
 #pragma unroll
         for (int m = 0; m < XROWS; m++) rt[m] = (uint32_t)m < M ? epilogue_row_term(epi, c, (uint32_t)m) : 0u;
@@ -308,7 +309,8 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                             if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
                             else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
                             else r = (OutT)a;
-                            o[(size_t)m * N + n] = r;
+                            for (int d = -1; d < epi.n_more; d++)
+                                (d < 0 ? o : static_cast<OutT *>(epi.more_out[d]))[(size_t)m * ldc + n] = r;
                         }
                     }
                 }

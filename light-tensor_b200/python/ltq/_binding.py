@@ -21,6 +21,7 @@ class QParams(C.Structure):
 
 
 OUT_U8, OUT_F32, OUT_I32 = 0, 1, 2
+MAX_DESTS = 8
 FLAG_RELU, FLAG_SATURATE, FLAG_BIAS_PER_CHANNEL = 1, 2, 4
 FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FORCE_SKINNY = 0x100, 0x200, 0x400
 FLAG_FORCE_TC_PAIR, FLAG_FORCE_TC_SINGLE = 0x800, 0x1000
@@ -52,6 +53,11 @@ _SIGNATURES = {
     "ltq_layer_set_qparams": (_int, [_vp, _qp, _qp, _qp]),
     "ltq_layer_forward": (_int, [_vp, _vp, _vp, _u64, _vp, _int, C.c_uint, _vp, _vp]),
     "ltq_layer_check": (_int, [_vp, _vp]),
+    "ltq_layer_forward_scatter": (_int, [_vp, _vp, _vp, _u64, _vp, _int, C.c_uint, C.POINTER(_vp), _int, _u64, _u64, _vp]),
+    "ltq_peer_alloc": (_int, [C.POINTER(_vp), _u64, _int, C.c_char_p]),
+    "ltq_peer_free": (_int, [_vp, _int]),
+    "ltq_peer_open": (_int, [C.c_char_p, _int, C.POINTER(_vp)]),
+    "ltq_peer_close": (_int, [_vp, _int]),
     "ltq_conv2d_create": (_int, [C.POINTER(_vp), _int] + [_u64] * 8),
     "ltq_conv2d_destroy": (_int, [_vp]),
     "ltq_conv2d_set_weights": (_int, [_vp, _vp, _vp, _vp]),

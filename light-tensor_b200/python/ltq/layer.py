@@ -56,6 +56,16 @@ class LayerHandle:
                                       out.data_ptr(), self._stream()))
         return out
 
+    def forward_scatter(self, x, dest_ptrs, ld_out, col_offset, out_mode=OUT_U8, flags=0, asum=None, qp_in_dev=None):
+        """Like forward, but element (i, j) goes to ``dest_ptrs[d] + (i * ld_out + col_offset + j) * itemsize`` for
+        every d.  dest_ptrs are raw device addresses (this GPU's buffer first, then peers' mapped buffers)."""
+        assert x.is_cuda and x.dtype == torch.uint8 and x.is_contiguous()
+        M = x.numel() // self.K
+        arr = (C.c_void_p * len(dest_ptrs))(*dest_ptrs)
+        check(lib().ltq_layer_forward_scatter(self._h, x.data_ptr(), None if asum is None else asum.data_ptr(), M,
+                                              None if qp_in_dev is None else qp_in_dev.data_ptr(), out_mode, flags, arr,
+                                              len(dest_ptrs), ld_out, col_offset, self._stream()))
+
     def check(self):
         check(lib().ltq_layer_check(self._h, self._stream()))
 

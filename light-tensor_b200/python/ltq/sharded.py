@@ -69,6 +69,51 @@ class CudaBackend:
         return out
 
 
+class PeerBuffer:
+    """One device buffer per rank, each mapped into every other rank of the group (CUDA IPC through libltq).
+    ``ptrs[r]`` is the address under which THIS process reaches rank r's buffer; ``local`` is a uint8 torch view of
+    this rank's own buffer.  Collective: every rank of the group must construct it at the same point."""
+
+    def __init__(self, nbytes, device_index, group=None):
+        self.device_index, self.nbytes = device_index, int(nbytes)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        own = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        check(lib().ltq_peer_alloc(C.byref(own), self.nbytes, device_index, handle))
+        self._own = own
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs, self._opened = [], []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(own.value)
+                continue
+            p = C.c_void_p()
+            check(lib().ltq_peer_open(h, device_index, C.byref(p)))
+            self._opened.append(p)
+            self.ptrs.append(p.value)
+        self.local = _wrap_device_memory(own.value, self.nbytes, device_index, self)
+
+    def close(self):
+        for p in self._opened:
+            lib().ltq_peer_close(p, self.device_index)
+        self._opened = []
+        if self._own:
+            lib().ltq_peer_free(self._own, self.device_index)
+            self._own = None
+
+
+def _wrap_device_memory(ptr, nbytes, device_index, owner):
+    """uint8 CUDA tensor over memory this module allocated itself (no copy; `owner` is kept alive by the tensor)."""
+    class _Iface:
+        pass
+    holder = _Iface()
+    holder.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                       "strides": None}
+    holder._owner = owner
+    return torch.as_tensor(holder, device=torch.device("cuda", device_index))
+
+
 class RowShardedLinear:
     """Weights replicated, activation rows split.  ``forward`` takes THIS rank's rows and returns this rank's rows of
     the output; nothing is exchanged."""
@@ -90,7 +135,11 @@ class ColShardedLinear:
     """Weight rows (output features) split in blocks of a multiple of 16 columns, activations replicated.
     ``forward`` returns the full ``[M, N]`` output on every rank."""
 
-    def __init__(self, w_q_full_or_local, bias_q, N_total, qp_in, qp_wt, qp_out, backend=None, group=None, is_local=False):
+    def __init__(self, w_q_full_or_local, bias_q, N_total, qp_in, qp_wt, qp_out, backend=None, group=None, is_local=False,
+                 fused=False, max_rows=0, out_mode=OUT_U8):
+        """``fused=True``: no all-gather; the GEMM epilogue stores this rank's columns straight into every rank's
+        ``[max_rows, N]`` output buffer over NVLink (peer-mapped memory, two buffers used alternately), followed by one
+        tiny stream-ordered collective as the barrier.  Needs the CUDA backend and ``max_rows``/``out_mode`` up front."""
         self.backend = backend or CudaBackend()
         self.group = group
         self.world = dist.get_world_size(group)
@@ -106,11 +155,23 @@ class ColShardedLinear:
             b_loc = None if bias_q is None else bias_q[self.n0:self.n1].contiguous()
         self._keep = (w_loc, b_loc)
         self.layer = self.backend.make_layer(w_loc, b_loc, qp_in, qp_wt, qp_out)
+        self.fused = bool(fused) and self.world > 1
+        if self.fused:
+            if max_rows < 1:
+                raise ValueError("fused column sharding needs max_rows")
+            self.max_rows, self.out_mode = int(max_rows), out_mode
+            self._esize = torch.empty(0, dtype=_OUT_DTYPE[out_mode]).element_size()
+            dev = w_loc.device.index
+            self._bufs = [PeerBuffer(self.max_rows * self.N * self._esize, dev, group) for _ in range(2)]
+            self._turn = 0
+            self._flag = torch.zeros(1, dtype=torch.int32, device=w_loc.device)
 
     def forward(self, x_q, out_mode=OUT_U8, flags=0, out=None, gathered=None, local=None):
         M = x_q.shape[0]
         nloc = self.n1 - self.n0
         dt = _OUT_DTYPE[out_mode]
+        if self.fused:
+            return self._forward_fused(x_q, M, out_mode, flags)
         if local is None:
             local = torch.empty((M, nloc), dtype=dt, device=x_q.device)
         self.backend.forward(self.layer, x_q, out_mode, flags, out=local)
@@ -122,3 +183,24 @@ class ColShardedLinear:
         if out is None:
             out = torch.empty((M, self.N), dtype=dt, device=x_q.device)
         return self.backend.interleave(gathered, out)
+
+    def _forward_fused(self, x_q, M, out_mode, flags):
+        """Returns a view of this rank's current output buffer, valid until the forward after next."""
+        if out_mode != self.out_mode or M > self.max_rows:
+            raise ValueError("fused column sharding was set up for another out_mode or fewer rows")
+        buf = self._bufs[self._turn]
+        self._turn ^= 1
+        # this rank's pointer first (the kernel's primary destination), then the peers'
+        ptrs = [buf.ptrs[self.rank]] + [p for r, p in enumerate(buf.ptrs) if r != self.rank]
+        self.layer.forward_scatter(x_q, ptrs, self.N, self.n0, out_mode, flags)
+        self._barrier(x_q.device)
+        return buf.local[:M * self.N * self._esize].view(_OUT_DTYPE[out_mode]).view(M, self.N)
+
+    def _barrier(self, device):
+        """Every rank's stores have landed before anyone reads.  NCCL: a 4-byte all-reduce on the compute stream (device
+        ordered, no host sync).  Other backends (tests with gloo): drain the stream, then a host barrier."""
+        if dist.get_backend(self.group) == "nccl":
+            dist.all_reduce(self._flag, group=self.group)
+        else:
+            torch.cuda.current_stream(device).synchronize()
+            dist.barrier(group=self.group)
