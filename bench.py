@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the uint8 quantized fully-connected forward path (libltq, sm_100a).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_block|mlp_mnist] [--shard rows|cols]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_block|mlp_mnist] [--shard rows|cols|cols_fused]
     python bench.py --impl reference ...      # the reference's own CPU code on the host cores
 
 One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch: activation quantise
@@ -406,8 +406,10 @@ def run_mlp_block(args):
         l2 = sharded.RowShardedLinear(w2q, None, qh, qw2, ltq.QParams(1.0, 0))
     else:
         M = Mt
-        l1 = sharded.ColShardedLinear(w1q, None, N1, qx, qw1, qh)
-        l2 = sharded.ColShardedLinear(w2q, None, N2, qh, qw2, ltq.QParams(1.0, 0))
+        fused = args.shard == "cols_fused"
+        l1 = sharded.ColShardedLinear(w1q, None, N1, qx, qw1, qh, fused=fused, max_rows=M, out_mode=ltq.OUT_U8)
+        l2 = sharded.ColShardedLinear(w2q, None, N2, qh, qw2, ltq.QParams(1.0, 0), fused=fused, max_rows=M,
+                                      out_mode=ltq.OUT_F32)
         del w1q, w2q
     gx = torch.Generator(device=dev).manual_seed(1000 + (rank if args.shard == "rows" else 0))
     x = torch.randn((M, K1), generator=gx, device=dev)
@@ -421,6 +423,11 @@ def run_mlp_block(args):
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
             l1.layer.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=hq)
             l2.layer.forward(hq, ltq.OUT_F32, 0, out=y)
+    elif args.shard == "cols_fused":
+        def step(i):
+            ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
+            hh = l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU)      # epilogue stores into every rank's buffer
+            l2.forward(hh, ltq.OUT_F32, 0)
     else:
         n1l, n2l = N1 // world, N2 // world
         loc1 = torch.empty((M, n1l), dtype=torch.uint8, device=dev)
@@ -446,7 +453,10 @@ def run_mlp_block(args):
                        "activations via fused requant, fp32 output",
            "sharding": {"rows": "activation rows split over the ranks, weights replicated, no collective",
                         "cols": "weight columns split over the ranks, all-gather of output slices (NCCL) + relayout "
-                                "after each layer"}[args.shard],
+                                "after each layer",
+                        "cols_fused": "weight columns split over the ranks, the GEMM epilogue stores each rank's columns "
+                                      "into every rank's output buffer over NVLink (peer stores), one 4-byte all-reduce "
+                                      "per layer as the barrier"}[args.shard],
            "M_per_gpu": M, "l2": "operands far larger than L2 (x, hidden and output are each >= 0.25 GB per rank)",
            "step": "quantize_rows + layer 1 (uint8, ReLU) + layer 2 (fp32)",
            "timing": "CUDA graph replay" if use_graph else "eager launches (NCCL inside the step)"}
@@ -513,7 +523,7 @@ def main():
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
     ap.add_argument("--m-total", type=int, default=65536, help="tokens of the mlp_block workload (all ranks together)")
     ap.add_argument("--d-model", type=int, default=8192, help="width of the mlp_block workload (hidden = 4x)")
-    ap.add_argument("--shard", default="rows", choices=["rows", "cols"], help="mlp_block partitioning")
+    ap.add_argument("--shard", default="rows", choices=["rows", "cols", "cols_fused"], help="mlp_block partitioning")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
