@@ -196,7 +196,7 @@ class Harness:
             self.dist.barrier()
             self.torch.cuda.synchronize()
 
-    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False):
+    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False, join=None):
         """ms per step over EXACTLY `steps` steps, CUDA events on the launching stream, max over ranks.  The steps are
         captured once into a CUDA graph (the kernels run for tens of microseconds; launching them one by one from
         Python would time the interpreter) and the graph is replayed once untimed before the timed replay.  With
@@ -224,6 +224,8 @@ class Harness:
             e0.record()
             for i in range(steps):
                 fn(warmup + i)
+            if join is not None:
+                join()  # the timing stream waits for work the steps put on other streams
             e1.record()
         self.sync_all()
         ms = e0.elapsed_time(e1)
@@ -325,17 +327,42 @@ def run_linear(args):
         fc.weight_ptr_ = layers[0]._keep[0].view(1, 1, N, K)  # device weights already quantized above
         fc._handle = layers[0]
         fc.set_output(out_mode)
+        # Three streams (upload, compute, download) over two buffer sets: the upload of step i+1 and the download of
+        # step i-1 run while step i computes, so a step costs what the slower PCIe direction costs.
         host_x = [torch.randn((M, K)).pin_memory() for _ in range(2)]
-        host_out = torch.empty((M, N), dtype=out_dtype).pin_memory()
-        dev_x = torch.empty((M, K), device=dev)
+        host_out = [torch.empty((M, N), dtype=out_dtype).pin_memory() for _ in range(2)]
+        dev_x = [torch.empty((M, K), device=dev) for _ in range(2)]
+        dev_q = [torch.empty((M, K), dtype=torch.uint8, device=dev) for _ in range(2)]
+        dev_s = [torch.empty(M, dtype=torch.int32, device=dev) for _ in range(2)]
+        s_up, s_run, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_up = [torch.cuda.Event() for _ in range(2)]      # upload of set b finished
+        ev_run = [torch.cuda.Event() for _ in range(2)]     # compute on set b finished (dev_x[b] free, y[b] ready)
+        ev_down = [torch.cuda.Event() for _ in range(2)]    # download of set b finished
+        y_keep = [None, None]
 
         def e2e_step(i):
-            dev_x.copy_(host_x[i % 2], non_blocking=True)
-            q, s = ltq.quantize_rows(dev_x, qp=qps_x[0], q=xq[0], asum=asum[0])
-            y = fc.forward(q.view(1, M, K), asum=s)
-            host_out.copy_(y.view(M, N), non_blocking=True)
+            b = i % 2
+            with torch.cuda.stream(s_up):
+                s_up.wait_event(ev_run[b])                  # quantize of the step two back has read dev_x[b]
+                dev_x[b].copy_(host_x[b], non_blocking=True)
+                ev_up[b].record(s_up)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_up[b])
+                s_run.wait_event(ev_down[b])                # the download two steps back has read y_keep[b]
+                q, sm = ltq.quantize_rows(dev_x[b], qp=qps_x[0], q=dev_q[b], asum=dev_s[b])
+                y_keep[b] = fc.forward(q.view(1, M, K), asum=sm)
+                ev_run[b].record(s_run)
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(ev_run[b])
+                y_keep[b].record_stream(s_down)
+                host_out[b].copy_(y_keep[b].view(M, N), non_blocking=True)
+                ev_down[b].record(s_down)
 
-        ms_e2e = h.timed(e2e_step, max(3, args.steps // 2), 3, graph=False)
+        def e2e_join():
+            for st in (s_up, s_run, s_down):
+                torch.cuda.current_stream().wait_stream(st)
+
+        ms_e2e = h.timed(e2e_step, max(4, args.steps // 2), 4, graph=False, join=e2e_join)
         fc._handle = None
         e2e = {"value": ops / (ms_e2e * 1e-3) / 1e12 * world, "unit": "TOPS", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * esize}
