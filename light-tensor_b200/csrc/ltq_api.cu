@@ -69,6 +69,7 @@ Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *
     e.row_bias = nullptr;
     e.ldc = 0;
     e.n_more = 0;
+    e.staged = 0;
     for (auto &m : e.more_out) m = nullptr;
     e.qpA_dev = nullptr;
     e.sA = qa.scale;
@@ -264,7 +265,7 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
                               ((flags & LTQ_FLAG_FORCE_TC_PAIR) || tc_pair_preferred(M, N, dev->sms));
             // single CTA: B boxes of bn rows (bn = 64, 128, 256); pair: boxes of pbn / 2 rows (96 .. 128)
-            const int pbn = pair ? tc_pair_pick_bn(M, N, dev->sms) : 0;
+            const int pbn = pair ? tc_pair_pick_bn(M, N, dev->sms, epi.n_more > 0) : 0;
             const int bn = pair ? pbn / 2 : tc_pick_bn(M, N, dev->sms);
             TcOperandMap map_a, tmp_b;
             int er = tc_make_map(&map_a, A, M, K, 128);

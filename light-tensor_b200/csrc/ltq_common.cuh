@@ -78,6 +78,7 @@ struct Epilogue {
     uint64_t ldc;
     void *more_out[LTQ_MAX_DESTS - 1];
     int n_more;
+    int staged;                   // set by a launcher that gave its kernel a PeerStage area (see below)
 };
 
 __device__ __forceinline__ uint64_t epilogue_pitch(const Epilogue &e, uint64_t N) { return e.ldc ? e.ldc : N; }
@@ -158,12 +159,11 @@ __device__ __forceinline__ float epilogue_f32(int32_t acc, const EpilogueConsts 
     return __fmul_rn(c.sAB, __int2float_rn(acc));
 }
 
-// One chunk of W (32 or 16) accumulator columns of one output row: correction terms, conversion, then the same stores
-// into every destination at element offset `off` (16-byte stores when vec_ok and the chunk is complete).
+// One chunk of W (32 or 16) accumulator columns of one output row -> output words: W/4 words of packed uint8 (OUT == 0)
+// or W words of float / int32 bits.  `res` has room for W words either way.
 template <int OUT, int W>
-__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
-                                               const EpilogueConsts &c, bool relu, bool sat, const Epilogue &e, void *out,
-                                               uint64_t off, bool vec_ok, int valid)
+__device__ __forceinline__ void epilogue_convert(const uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
+                                                 const EpilogueConsts &c, bool relu, bool sat, uint32_t (&res)[W])
 {
     // column terms: 16-byte shared loads (the chunk starts at a multiple of 16 columns)
     uint32_t col[W];
@@ -176,7 +176,6 @@ __device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, co
         col[4 * g + 3] = t4.w;
     }
     if (OUT == 0) {
-        uint32_t p[W / 4];
 #pragma unroll
         for (int g = 0; g < W / 4; g++) {
             uint32_t w = 0;
@@ -186,40 +185,101 @@ __device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, co
                 const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
                 w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
             }
-            p[g] = w;
-        }
-        for (int d = -1; d < e.n_more; d++) {
-            uint8_t *dst = static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + off;
-            if (vec_ok && valid == W) {
-                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-                for (int g = 0; g < W / 16; g++) d4[g] = make_uint4(p[4 * g], p[4 * g + 1], p[4 * g + 2], p[4 * g + 3]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < W; j++)
-                    if (j < valid) dst[j] = (uint8_t)(p[j >> 2] >> (8 * (j & 3)));
-            }
+            res[g] = w;
         }
     } else {
 #pragma unroll
         for (int j = 0; j < W; j++) {
             const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
-            v[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
+            res[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
         }
+    }
+}
+
+// The same chunk stored into every destination at element offset `off` (16-byte stores when vec_ok and the chunk is
+// complete, element by element otherwise).
+template <int OUT, int W>
+__device__ __forceinline__ void epilogue_store(const uint32_t (&res)[W], const Epilogue &e, void *out, uint64_t off,
+                                               bool vec_ok, int valid)
+{
+    if (OUT == 0) {
+        for (int d = -1; d < e.n_more; d++) {
+            uint8_t *dst = static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + off;
+            if (vec_ok && valid == W) {
+                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                for (int g = 0; g < W / 16; g++) d4[g] = make_uint4(res[4 * g], res[4 * g + 1], res[4 * g + 2], res[4 * g + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < W; j++)
+                    if (j < valid) dst[j] = (uint8_t)(res[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    } else {
         for (int d = -1; d < e.n_more; d++) {
             uint32_t *dst = static_cast<uint32_t *>(d < 0 ? out : e.more_out[d]) + off;
             if (vec_ok && valid == W) {
                 uint4 *d4 = reinterpret_cast<uint4 *>(dst);
 #pragma unroll
-                for (int g = 0; g < W / 4; g++) d4[g] = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                for (int g = 0; g < W / 4; g++) d4[g] = make_uint4(res[4 * g], res[4 * g + 1], res[4 * g + 2], res[4 * g + 3]);
             } else {
 #pragma unroll
                 for (int j = 0; j < W; j++)
-                    if (j < valid) dst[j] = v[j];
+                    if (j < valid) dst[j] = res[j];
             }
         }
     }
 }
+
+template <int OUT, int W>
+__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
+                                               const EpilogueConsts &c, bool relu, bool sat, const Epilogue &e, void *out,
+                                               uint64_t off, bool vec_ok, int valid)
+{
+    uint32_t res[W];
+    epilogue_convert<OUT, W>(v, rt, col_smem, c, relu, sat, res);
+    epilogue_store<OUT, W>(res, e, out, off, vec_ok, valid);
+}
+
+// Row-coalescing stage for stores that leave the GPU.  In the accumulator layout a thread owns one output row, so a
+// direct store instruction writes 32 separate 16-byte pieces, one per row: harmless in local HBM (L2 merges them), but
+// over NVLink every piece travels as its own small packet.  A warp therefore parks a block of 32 rows x 128 bytes in
+// shared memory (16-byte units XOR-swizzled by row, conflict-free both ways) and writes it back out with each
+// instruction covering 4 rows x 128 contiguous bytes.
+struct PeerStage {
+    static constexpr int BYTES_PER_WARP = 32 * 128;
+
+    // This lane's row: `nunits` 16-byte units starting at unit `u0` of the row's 128 bytes.
+    template <int NW>
+    static __device__ __forceinline__ void put(uint8_t *stage, int lane, int u0, const uint32_t (&res)[NW], int nunits)
+    {
+#pragma unroll
+        for (int g = 0; g < NW / 4; g++)
+            if (g < nunits)
+                *reinterpret_cast<uint4 *>(stage + lane * 128 + (((u0 + g) ^ (lane & 7)) << 4)) =
+                    make_uint4(res[4 * g], res[4 * g + 1], res[4 * g + 2], res[4 * g + 3]);
+    }
+
+    // Writes units [0, units) of all 32 rows to every destination; `off_bytes` is the byte offset of (first row, first
+    // unit) and `pitch_bytes` the destinations' row pitch.  Called by the whole warp.
+    static __device__ __forceinline__ void flush(const uint8_t *stage, int lane, int units, const Epilogue &e, void *out,
+                                                 uint64_t off_bytes, uint64_t pitch_bytes)
+    {
+        __syncwarp();
+        const int u = lane & 7;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int r = it * 4 + (lane >> 3);
+            if (u < units) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(stage + r * 128 + ((u ^ (r & 7)) << 4));
+                const uint64_t o = off_bytes + (uint64_t)r * pitch_bytes + (uint64_t)u * 16;
+                for (int d = -1; d < e.n_more; d++)
+                    *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + o) = val;
+            }
+        }
+        __syncwarp();
+    }
+};
 
 // ---- kernel launchers implemented in the other translation units --------------------------------------------------
 // Generic dp4a tile kernel: any M, N, K and any transpose combination.

@@ -244,6 +244,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * PBN * 4);     // full[S] empty[S] tfull[2] tempty[2]
     uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * P_STAGES + 4);  // [0] tmem base, [1] abort flag
     volatile uint32_t *abort_flag = s_misc + 1;
+    uint8_t *s_stage = after + 2 * PBN * 4 + 256;     // [8 warps][32 rows][128 B], only allocated when epi.staged
 
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * P_STAGES;
     const uint32_t tfull0 = empty0 + 8 * P_STAGES, tempty0 = tfull0 + 16;
@@ -344,6 +345,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
         const uint64_t ldc = epilogue_pitch(epi, N);
         const bool vec_ok = epilogue_vec_ok(epi, out, N, sizeof(OutT));
+        const bool staged = epi.staged && vec_ok;
         constexpr int COL0 = 128;                          // column split between the two warps of a quarter
         uint32_t as = 0, aph = 0;
         bool ok = true;
@@ -363,25 +365,46 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * 256;
                 const int cb = h ? COL0 : 0, ce = h ? PBN : COL0;
+                // Blocks of 128 output bytes per row go through the row-coalescing stage when results leave the GPU and
+                // the warp's 32 rows and the block's columns are all inside the matrix; everything else is stored directly.
+                constexpr int ESZ = (int)sizeof(OutT), BLOCK_COLS = 128 / ESZ;   // 128 columns of uint8, 32 of 4 bytes
+                const bool rows_full = m0 + q * 32 + 32 <= M;
+                uint8_t *stage = s_stage + (warp - 2) * PeerStage::BYTES_PER_WARP;
 #pragma unroll 1
-                for (int cc = cb; cc + 32 <= ce; cc += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + cc, v);
-                    tmem_ld_wait();
+                for (int cc = cb; cc < ce; cc += 32) {
                     const uint32_t c0 = n0 + cc;
-                    if (row < M && c0 < N)
-                        epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
-                                                (N - c0) < 32u ? (int)(N - c0) : 32);
-                }
-                if ((ce - cb) % 32 != 0) {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
-                    const int cc = ce - 16;
-                    uint32_t v[16];
-                    tmem_ld16(taddr + cc, v);
-                    tmem_ld_wait();
-                    const uint32_t c0 = n0 + cc;
-                    if (row < M && c0 < N)
-                        epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
-                                                (N - c0) < 16u ? (int)(N - c0) : 16);
+                    const int bc0 = cb + ((cc - cb) / BLOCK_COLS) * BLOCK_COLS;          // first column of cc's block
+                    const int bcols = (ce - bc0) < BLOCK_COLS ? (ce - bc0) : BLOCK_COLS;  // its width
+                    const bool via_stage = staged && rows_full && n0 + bc0 + bcols <= N;
+                    if (cc + 32 <= ce) {
+                        uint32_t v[32];
+                        tmem_ld32(taddr + cc, v);
+                        tmem_ld_wait();
+                        if (via_stage) {
+                            uint32_t res[32];
+                            epilogue_convert<OUT, 32>(v, rt, col + cc, c, relu, sat, res);
+                            PeerStage::put<32>(stage, lane, (cc - bc0) * ESZ / 16, res, 32 * ESZ / 16);
+                        } else if (row < M && c0 < N) {
+                            epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
+                                                    (N - c0) < 32u ? (int)(N - c0) : 32);
+                        }
+                    } else {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
+                        uint32_t v[16];
+                        tmem_ld16(taddr + cc, v);
+                        tmem_ld_wait();
+                        if (via_stage) {
+                            uint32_t res[16];
+                            epilogue_convert<OUT, 16>(v, rt, col + cc, c, relu, sat, res);
+                            PeerStage::put<16>(stage, lane, (cc - bc0) * ESZ / 16, res, 16 * ESZ / 16);
+                        } else if (row < M && c0 < N) {
+                            epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
+                                                    (N - c0) < 16u ? (int)(N - c0) : 16);
+                        }
+                    }
+                    const int next = cc + 32 < ce ? cc + 32 : ce;
+                    if (via_stage && (next == ce || (next - cb) % BLOCK_COLS == 0))   // the block is complete
+                        PeerStage::flush(stage, lane, bcols * ESZ / 16, epi, out,
+                                         ((uint64_t)(m0 + q * 32) * ldc + n0 + bc0) * ESZ, ldc * ESZ);
                 }
                 // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)
                 tc_fence_before();
@@ -476,16 +499,22 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
+    // With further destinations (peer GPUs) the epilogue warps get a row-coalescing stage, where it fits beside the ring.
+    constexpr int STAGE_BYTES = 8 * PeerStage::BYTES_PER_WARP;
+    constexpr bool STAGE_FITS = C::SMEM_BYTES + STAGE_BYTES <= 227 * 1024;
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<PBN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             C::SMEM_BYTES);
+                                             C::SMEM_BYTES + (STAGE_FITS ? STAGE_BYTES : 0));
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
     const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
     const uint64_t pairs = tiles < (uint64_t)(sms / 2) ? tiles : (uint64_t)(sms / 2);
-    gemm_tc_pair_kernel<PBN, OUT><<<(unsigned)(2 * pairs), P_THREADS, C::SMEM_BYTES, stream>>>(
-        ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi, out, status);
+    Epilogue epi_l = epi;
+    epi_l.staged = (epi.n_more > 0 && STAGE_FITS) ? 1 : 0;
+    const size_t smem = C::SMEM_BYTES + (epi_l.staged ? STAGE_BYTES : 0);
+    gemm_tc_pair_kernel<PBN, OUT><<<(unsigned)(2 * pairs), P_THREADS, smem, stream>>>(
+        ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi_l, out, status);
     count_launch();
     return cudaGetLastError();
 }
@@ -510,14 +539,15 @@ bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
     return tiles * 4 >= (uint64_t)(sms / 2) * 3;
 }
 
-int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms)
+int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores)
 {
     // Time ~ (waves of tiles over the CTA pairs) x (tile width).  Wider tiles reuse operands better, so a narrower one
     // must win by a clear margin (3 %).
     const uint64_t tm = (M + 2 * BM - 1) / (2 * BM), pairs = (uint64_t)(sms / 2);
-    int best = 256;
+    int best = peer_stores ? 240 : 256;
     double best_cost = 1e30;
     for (int bn : {256, 240, 224, 192}) {
+        if (peer_stores && bn == 256) continue;  // no room for the row-coalescing stage beside a 6 x 32 KB ring
         const uint64_t tiles = tm * ((N + bn - 1) / bn);
         const double cost = (double)((tiles + pairs - 1) / pairs) * bn;
         if (cost < best_cost * 0.97) {

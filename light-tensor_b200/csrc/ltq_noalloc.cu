@@ -102,6 +102,7 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
     epi.row_bias = nullptr;
     epi.ldc = 0;
     epi.n_more = 0;
+    epi.staged = 0;
     for (auto &m : epi.more_out) m = nullptr;
     epi.qpA_dev = nullptr;
     epi.sA = qparams[0].scale;

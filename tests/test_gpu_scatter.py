@@ -21,6 +21,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 @pytest.mark.parametrize("path,shape", [
     ("simt", (33, 48, 100)), ("tc", (200, 272, 256)), ("tcpair", (300, 512, 128)), ("skinny", (5, 160, 256)),
     ("auto", (64, 96, 784)),
+    # pair kernel with several tile widths: with more than one destination the stores go through the row-coalescing
+    # stage in shared memory (full 32-row groups) or directly (the ragged last row tile)
+    ("tcpair", (2000, 2160, 64)), ("tcpair", (2048, 2016, 64)), ("tcpair", (1100, 2304, 64)),
 ])
 @pytest.mark.parametrize("mode", ["u8", "f32"])
 def test_scatter_writes_every_destination_at_the_offset(cuda, oracle, path, shape, mode):
