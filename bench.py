@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the uint8 quantized fully-connected forward path (libltq, sm_100a).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_block|mlp_mnist] [--shard rows|cols|cols_fused]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_block|mlp_mnist|conv] [--shard rows|cols|cols_fused]
     python bench.py --impl reference ...      # the reference's own CPU code on the host cores
 
 One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch: activation quantise
@@ -540,13 +540,52 @@ def run_mlp_mnist(args):
                        clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))
 
 
+def run_conv(args):
+    """Conv2d_q on a ResNet-like layer: batch 32, 64 -> 64 channels, 56 x 56, 3 x 3, pad 1 (not one of the configs the
+    metric is quoted on; it gives the convolution path a measured number).  A step = one Conv2d_q::forward on uint8
+    NCHW input: transposed im2col of the batch + patch sums + one quantized GEMM per image."""
+    import ltq
+    h = Harness(args)
+    torch, dev, world = h.torch, h.dev, h.world
+    B, Cin, H, W, Cout, k = 32, 64, 56, 56, 64, 3
+    sets = 4                                          # 4 x (6.4 MB input + 58 MB patches + 6.4 MB output)
+    g = torch.Generator(device=dev).manual_seed(4321 + h.rank)
+    xs = [torch.randint(0, 256, (B, Cin, H, W), dtype=torch.uint8, device=dev, generator=g) for _ in range(sets)]
+    convs, outs = [], []
+    for i in range(sets):
+        wq = torch.randint(0, 256, (Cout, Cin * k * k), dtype=torch.uint8, device=dev, generator=g)
+        c = ltq.ConvHandle(h.local, Cin, Cout, k, k, 1, 1, 1, 1)
+        c.set_weights(wq)
+        c.set_qparams(ltq.QParams(0.02, 128), ltq.QParams(0.005, 127), ltq.QParams(0.6, 5))
+        convs.append(c)
+        outs.append(torch.empty((B, Cout, H, W), dtype=torch.uint8, device=dev))
+
+    def step(i):
+        convs[i % sets].forward(xs[i % sets], ltq.OUT_U8, ltq.FLAG_RELU, out=outs[i % sets])
+
+    for i in range(sets):      # every handle allocates its patch buffer on first use, which must not happen in a capture
+        step(i)
+    launches0 = ltq.kernel_launches()
+    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
+    ops = 2.0 * B * H * W * Cout * Cin * k * k
+    cfg = {"workload": f"conv2d_q: batch {B}, {Cin}->{Cout} channels, {H}x{W}, {k}x{k} kernel, pad 1, uint8 NCHW in/out, "
+                       "fused ReLU", "sharding": "independent replicas, one batch stream per GPU",
+           "l2": f"rotating {sets} distinct input / patch-buffer / output sets",
+           "step": "im2col of the batch + patch sums + one quantized GEMM per image",
+           "timing": "CUDA graph replay" if not args.no_graph else "eager launches"}
+    h.finish(base_line(h, args, ops / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
+                       samples_per_s=B * world / (ms_step * 1e-3), gpu_launches=int(launches),
+                       clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ltq", choices=["ltq", "reference"])
-    ap.add_argument("--workload", default="square_4096", choices=["square_4096", "skinny", "mlp_block", "mlp_mnist"])
+    ap.add_argument("--workload", default="square_4096", choices=["square_4096", "skinny", "mlp_block", "mlp_mnist", "conv"])
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
     ap.add_argument("--m-total", type=int, default=65536, help="tokens of the mlp_block workload (all ranks together)")
     ap.add_argument("--d-model", type=int, default=8192, help="width of the mlp_block workload (hidden = 4x)")
@@ -562,6 +601,8 @@ def main():
         run_mlp_block(args)
     elif args.workload == "mlp_mnist":
         run_mlp_mnist(args)
+    elif args.workload == "conv":
+        run_conv(args)
     else:
         run_linear(args)
 

@@ -70,6 +70,8 @@ Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *
     e.ldc = 0;
     e.n_more = 0;
     e.staged = 0;
+    e.col_block = 0;
+    e.col_block_stride = 0;
     for (auto &m : e.more_out) m = nullptr;
     e.qpA_dev = nullptr;
     e.sA = qa.scale;
@@ -265,7 +267,7 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
                               ((flags & LTQ_FLAG_FORCE_TC_PAIR) || tc_pair_preferred(M, N, dev->sms));
             // single CTA: B boxes of bn rows (bn = 64, 128, 256); pair: boxes of pbn / 2 rows (96 .. 128)
-            const int pbn = pair ? tc_pair_pick_bn(M, N, dev->sms, epi.n_more > 0) : 0;
+            const int pbn = pair ? tc_pair_pick_bn(M, N, dev->sms, epi.n_more > 0, epi.col_block != 0) : 0;
             const int bn = pair ? pbn / 2 : tc_pick_bn(M, N, dev->sms);
             TcOperandMap map_a, tmp_b;
             int er = tc_make_map(&map_a, A, M, K, 128);
@@ -668,13 +670,23 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
         const uint64_t nb = batches - b0 < chunk ? batches - b0 : chunk;
         LTQ_CUDA_TRY(launch_im2col_t(x_dev + b0 * in_stride, nb, g, conv->col, st));
         LTQ_CUDA_TRY(launch_row_sums(conv->col, nb * N, Kp, conv->colsum, st));
-        for (uint64_t i = 0; i < nb; i++) {
-            // out[co, n] = weights[co, :] . patch[n, :]: the weights are the row operand (qparams[0] in the reference's
-            // call, l-ten/conv2d.cpp:348-350), the patches the column operand.
+        // out[co, n] = weights[co, :] . patch[n, :]: the weights are the row operand (qparams[0] in the reference's call,
+        // l-ten/conv2d.cpp:348-350), the patches the column operand.  When an image's Ho*Wo positions are a multiple of
+        // 32 the patches of the whole chunk are ONE GEMM with N = nb*Ho*Wo whose epilogue writes column block b (image b)
+        // at out[b]; otherwise one GEMM per image.
+        // (the reference's per-position bias indexes by the position inside ONE image, so it keeps the per-image form)
+        const bool batched = (N % 32 == 0) && nb > 1 && nb * N < (1ull << 31) && (per_channel || !conv->bias);
+        const uint64_t groups = batched ? 1 : nb, per = batched ? nb : 1;
+        for (uint64_t i = 0; i < groups; i++) {
             Epilogue epi = make_epilogue(conv->colsum + i * N, conv->wsum, per_channel ? nullptr : conv->bias, conv->qp_wt,
                                          conv->qp_in, conv->qp_out, K, out_mode, flags);
             epi.row_bias = per_channel ? conv->bias : nullptr;
-            rc = run_fc_gemm(conv->dev, M, N, Kp, conv->w, conv->col + i * N * Kp, epi,
+            if (batched) {
+                epi.ldc = N;
+                epi.col_block = (uint32_t)N;
+                epi.col_block_stride = M * N;
+            }
+            rc = run_fc_gemm(conv->dev, M, per * N, Kp, conv->w, conv->col + i * N * Kp, epi,
                              static_cast<uint8_t *>(out_dev) + (b0 + i) * out_stride, flags, nullptr, st);
             if (rc != LTQ_OK) return rc;
         }

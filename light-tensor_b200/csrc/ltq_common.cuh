@@ -79,13 +79,28 @@ struct Epilogue {
     void *more_out[LTQ_MAX_DESTS - 1];
     int n_more;
     int staged;                   // set by a launcher that gave its kernel a PeerStage area (see below)
+    // Column blocking (0 = off): output columns come in blocks of col_block, block b starting col_block_stride elements
+    // after block b-1, i.e. element (i, j) lives at (j / col_block) * col_block_stride + i*ldc + j % col_block.  This is
+    // how one GEMM over the patches of a whole batch writes NCHW: a block is one image's Ho*Wo output positions.
+    uint32_t col_block;
+    uint64_t col_block_stride;
 };
+
+// Element offset of (row, col).  With column blocking a chunk of consecutive columns must not straddle a block: the
+// tensor-core kernels handle chunks of 16 / 32 columns starting at multiples of 16, so col_block % 32 == 0 there.
+__device__ __forceinline__ uint64_t epilogue_offset(const Epilogue &e, uint64_t row, uint64_t col, uint64_t ldc)
+{
+    if (e.col_block == 0) return row * ldc + col;
+    const uint64_t b = col / e.col_block;
+    return b * e.col_block_stride + row * ldc + (col - b * e.col_block);
+}
 
 __device__ __forceinline__ uint64_t epilogue_pitch(const Epilogue &e, uint64_t N) { return e.ldc ? e.ldc : N; }
 // 16-byte stores need every row start aligned in every destination: pitch and bases multiples of 16 bytes.
 __device__ __forceinline__ bool epilogue_vec_ok(const Epilogue &e, const void *out, uint64_t N, uint32_t esize)
 {
-    bool ok = ((epilogue_pitch(e, N) * esize) % 16 == 0) && (((uintptr_t)out & 15) == 0);
+    bool ok = ((epilogue_pitch(e, N) * esize) % 16 == 0) && (((uintptr_t)out & 15) == 0) &&
+              ((e.col_block_stride * esize) % 16 == 0) && (e.col_block % 16 == 0);
     for (int d = 0; d < e.n_more; d++) ok = ok && (((uintptr_t)e.more_out[d] & 15) == 0);
     return ok;
 }

@@ -10,35 +10,41 @@
 namespace ltq {
 
 // One thread = 16 consecutive k of one patch row = one 16-byte store; the gather loads hit L1/L2 (a tap is re-read by up
-// to kh*kw patches).
+// to kh*kw patches).  The tap pointer is advanced incrementally (next kernel column, next kernel row, next channel)
+// and patches that lie entirely inside the image skip the per-tap bounds test.
 __global__ void __launch_bounds__(256) im2col_t_kernel(const uint8_t *__restrict__ im, uint64_t batches, ConvGeom g,
                                                       uint8_t *__restrict__ col_t)
 {
-    const uint32_t vec_per_row = g.Kp / 16;
-    const uint64_t rows = batches * g.Ho * g.Wo, total = rows * vec_per_row;
+    const uint32_t vec_per_row = g.Kp / 16, plane = g.Ho * g.Wo;
+    const uint64_t total = batches * plane * vec_per_row;
     const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
     const uint32_t khw = g.kh * g.kw;
+    const int64_t next_row = (int64_t)g.W - g.kw, next_chan = (int64_t)(g.H - g.kh) * g.W;
     for (uint64_t v = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += nth) {
         const uint64_t row = v / vec_per_row;
-        const uint32_t k0 = (uint32_t)(v % vec_per_row) * 16;
-        const uint64_t b = row / ((uint64_t)g.Ho * g.Wo);
-        const uint32_t n = (uint32_t)(row % ((uint64_t)g.Ho * g.Wo));
-        const uint32_t ho = n / g.Wo, wo = n % g.Wo;
-        const int64_t y0 = (int64_t)ho * g.sh - g.ph, x0 = (int64_t)wo * g.sw - g.pw;
-        const uint8_t *img = im + b * g.C * g.H * g.W;
-        uint32_t c = k0 / khw, r = k0 % khw, i = r / g.kw, j = r % g.kw;
+        const uint32_t k0 = (uint32_t)(v - row * vec_per_row) * 16;
+        const uint64_t b = row / plane;
+        const uint32_t n = (uint32_t)(row - b * plane);
+        const uint32_t ho = n / g.Wo, wo = n - ho * g.Wo;
+        const int32_t y0 = (int32_t)(ho * g.sh) - (int32_t)g.ph, x0 = (int32_t)(wo * g.sw) - (int32_t)g.pw;
+        const bool interior = y0 >= 0 && x0 >= 0 && (uint32_t)y0 + g.kh <= g.H && (uint32_t)x0 + g.kw <= g.W;
+        uint32_t c = k0 / khw, r = k0 - c * khw, i = r / g.kw, j = r - i * g.kw;
+        // tap (c, i, j) of this patch; may point outside the image (then it is never dereferenced)
+        const uint8_t *p = im + ((b * g.C + c) * g.H + (int64_t)y0 + i) * (int64_t)g.W + x0 + j;
+        const uint32_t left = g.K > k0 ? g.K - k0 : 0;
         uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int t = 0; t < 16; t++) {
             uint32_t byte = 0;
-            if (k0 + t < g.K) {
-                const int64_t y = y0 + i, x = x0 + j;
-                if (y >= 0 && y < (int64_t)g.H && x >= 0 && x < (int64_t)g.W) byte = img[((uint64_t)c * g.H + y) * g.W + x];
+            if ((uint32_t)t < left) {
+                if (interior || ((uint32_t)(y0 + (int32_t)i) < g.H && (uint32_t)(x0 + (int32_t)j) < g.W)) byte = *p;
+                p++;
                 if (++j == g.kw) {
                     j = 0;
+                    p += next_row;
                     if (++i == g.kh) {
                         i = 0;
-                        c++;
+                        p += next_chan;
                     }
                 }
             }

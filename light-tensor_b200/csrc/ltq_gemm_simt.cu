@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, ui
             const uint64_t col = n0 + tx + 16 * j;
             if (col >= N) continue;
             const int32_t v = epilogue_acc((uint32_t)acc[i][j], rt, epilogue_col_term(epi, c, col), relu);
-            const uint64_t o = row * epilogue_pitch(epi, N) + col;
+            const uint64_t o = epilogue_offset(epi, row, col, epilogue_pitch(epi, N));
             for (int d = -1; d < epi.n_more; d++) {
                 void *dst = d < 0 ? out : epi.more_out[d];
                 if (epi.out_mode == LTQ_OUT_U8)

@@ -175,7 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_ld_wait();
                     const uint32_t c0 = n0 + ch * 32;
                     if (row < M && c0 < N)
-                        epilogue_chunk<OUT, 32>(v, rt, col + ch * 32, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
+                        epilogue_chunk<OUT, 32>(v, rt, col + ch * 32, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc), vec_ok,
                                                 (N - c0) < 32u ? (int)(N - c0) : 32);
                 }
                 // all of this warp's reads of the accumulator are done -> hand the buffer back to the MMA warp
@@ -345,7 +345,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
         const uint64_t ldc = epilogue_pitch(epi, N);
         const bool vec_ok = epilogue_vec_ok(epi, out, N, sizeof(OutT));
-        const bool staged = epi.staged && vec_ok;
+        const bool staged = epi.staged && vec_ok && epi.col_block == 0;
         constexpr int COL0 = 128;                          // column split between the two warps of a quarter
         uint32_t as = 0, aph = 0;
         bool ok = true;
@@ -385,7 +385,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             epilogue_convert<OUT, 32>(v, rt, col + cc, c, relu, sat, res);
                             PeerStage::put<32>(stage, lane, (cc - bc0) * ESZ / 16, res, 32 * ESZ / 16);
                         } else if (row < M && c0 < N) {
-                            epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
+                            epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc), vec_ok,
                                                     (N - c0) < 32u ? (int)(N - c0) : 32);
                         }
                     } else {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
@@ -397,7 +397,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             epilogue_convert<OUT, 16>(v, rt, col + cc, c, relu, sat, res);
                             PeerStage::put<16>(stage, lane, (cc - bc0) * ESZ / 16, res, 16 * ESZ / 16);
                         } else if (row < M && c0 < N) {
-                            epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, (uint64_t)row * ldc + c0, vec_ok,
+                            epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc), vec_ok,
                                                     (N - c0) < 16u ? (int)(N - c0) : 16);
                         }
                     }
@@ -511,7 +511,7 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M
     const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
     const uint64_t pairs = tiles < (uint64_t)(sms / 2) ? tiles : (uint64_t)(sms / 2);
     Epilogue epi_l = epi;
-    epi_l.staged = (epi.n_more > 0 && STAGE_FITS) ? 1 : 0;
+    epi_l.staged = (epi.n_more > 0 && STAGE_FITS) ? 1 : 0;  // (local-only stores gain nothing from the stage: measured)
     const size_t smem = C::SMEM_BYTES + (epi_l.staged ? STAGE_BYTES : 0);
     gemm_tc_pair_kernel<PBN, OUT><<<(unsigned)(2 * pairs), P_THREADS, smem, stream>>>(
         ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi_l, out, status);
@@ -539,15 +539,16 @@ bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
     return tiles * 4 >= (uint64_t)(sms / 2) * 3;
 }
 
-int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores)
+int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores, bool chunks_aligned_32)
 {
     // Time ~ (waves of tiles over the CTA pairs) x (tile width).  Wider tiles reuse operands better, so a narrower one
     // must win by a clear margin (3 %).
     const uint64_t tm = (M + 2 * BM - 1) / (2 * BM), pairs = (uint64_t)(sms / 2);
-    int best = peer_stores ? 240 : 256;
+    int best = peer_stores ? 224 : 256;
     double best_cost = 1e30;
     for (int bn : {256, 240, 224, 192}) {
         if (peer_stores && bn == 256) continue;  // no room for the row-coalescing stage beside a 6 x 32 KB ring
+        if (chunks_aligned_32 && bn % 32 != 0) continue;  // column-blocked outputs: 32-column chunks start at multiples of 32
         const uint64_t tiles = tm * ((N + bn - 1) / bn);
         const double cost = (double)((tiles + pairs - 1) / pairs) * bn;
         if (cost < best_cost * 0.97) {

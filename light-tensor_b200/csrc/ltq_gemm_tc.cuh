@@ -31,7 +31,7 @@ int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K,
 // enough; tc_pair_pick_bn picks the tile width (256, 240, 224 or 192) that leaves the fullest last wave.  map_a uses
 // 128-row boxes, map_b boxes of bn / 2 rows (each CTA of a pair loads half of the tile's B rows).
 bool tc_pair_preferred(uint64_t M, uint64_t N, int sms);
-int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores = false);
+int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores = false, bool chunks_aligned_32 = false);
 cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
                                 uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
                                 cudaStream_t stream);

@@ -45,7 +45,8 @@ constexpr int LINE = 128;                  // bytes of K per line (one swizzle a
 constexpr int XROWS = 16;                  // activation rows as seen by the MMA (N = 16), TMEM columns per accumulator
 constexpr int TILE_M = 128;                // MMA M: weight rows per tile (upper bound)
 constexpr int MAX_STAGES = 16;
-constexpr int SMEM_LIMIT = 112 * 1024;     // two CTAs (this launch's and the next one's) share an SM
+constexpr int SMEM_HALF = 112 * 1024;      // chained launches: two CTAs (this launch's and the next one's) share an SM
+constexpr int SMEM_FULL = 220 * 1024;      // a launch on its own: one CTA per SM with as deep a ring as fits
 constexpr int OVERREAD = TILE_M * LINE;    // an MMA reads 128 rows from a tile's start whatever the band holds
 constexpr int NACC = 4;                    // independent partial accumulators per tile (summed in the epilogue)
 constexpr uint32_t TMEM_COLS = 2 * NACC * XROWS;  // two buffers of NACC accumulators of 16 columns = 128
@@ -62,7 +63,7 @@ struct Plan {
     bool ok;
 };
 
-Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms)
+Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms, size_t smem_limit)
 {
     Plan p{};
     const uint64_t octs = (N + 7) / 8;
@@ -90,7 +91,7 @@ Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms)
         const size_t after = (size_t)st * p.x_stage;
         const size_t slack = (after >= (size_t)OVERREAD ? 0 : (size_t)OVERREAD - after) + 1024;
         const size_t total = 1024 + (size_t)st * (p.w_stage + p.x_stage) + slack + 512;
-        if (total <= (size_t)SMEM_LIMIT) {
+        if (total <= smem_limit) {
             p.stages = st;
             p.slack = (uint32_t)slack;
             p.smem = total;
@@ -310,7 +311,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                             else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
                             else r = (OutT)a;
                             for (int d = -1; d < epi.n_more; d++)
-                                (d < 0 ? o : static_cast<OutT *>(epi.more_out[d]))[(size_t)m * ldc + n] = r;
+                                (d < 0 ? o : static_cast<OutT *>(epi.more_out[d]))[epilogue_offset(epi, (uint64_t)m, n, ldc)] = r;
                         }
                     }
                 }
@@ -351,7 +352,7 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_done[dev]) {
-        e = cudaFuncSetAttribute(gemv_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+        e = cudaFuncSetAttribute(gemv_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_FULL);
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
@@ -378,13 +379,15 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
 bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W)
 {
     return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 128 && K % 128 == 0 && K < (1ull << 31) &&
-           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148).ok;
+           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148, SMEM_HALF).ok;
 }
 
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
                         void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache, bool early_weights)
 {
-    const Plan p = make_plan(M, N, K, sms);
+    // A launch that will be followed closely by another one of its kind keeps to half an SM so that the two overlap;
+    // one that stands alone streams faster with a deeper ring.
+    const Plan p = make_plan(M, N, K, sms, early_weights ? SMEM_HALF : SMEM_FULL);
     if (!p.ok) return cudaErrorInvalidConfiguration;
     TcOperandMap mx;
     GemvWeightMaps local;

@@ -103,6 +103,8 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
     epi.ldc = 0;
     epi.n_more = 0;
     epi.staged = 0;
+    epi.col_block = 0;
+    epi.col_block_stride = 0;
     for (auto &m : epi.more_out) m = nullptr;
     epi.qpA_dev = nullptr;
     epi.sA = qparams[0].scale;
