@@ -668,8 +668,7 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     const uint64_t esize = out_mode == LTQ_OUT_U8 ? 1 : 4, out_stride = M * N * esize;
     for (uint64_t b0 = 0; b0 < batches; b0 += chunk) {
         const uint64_t nb = batches - b0 < chunk ? batches - b0 : chunk;
-        LTQ_CUDA_TRY(launch_im2col_t(x_dev + b0 * in_stride, nb, g, conv->col, st));
-        LTQ_CUDA_TRY(launch_row_sums(conv->col, nb * N, Kp, conv->colsum, st));
+        LTQ_CUDA_TRY(launch_im2col_t_sums(x_dev + b0 * in_stride, nb, g, conv->col, conv->colsum, st));
         // out[co, n] = weights[co, :] . patch[n, :]: the weights are the row operand (qparams[0] in the reference's call,
         // l-ten/conv2d.cpp:348-350), the patches the column operand.  When an image's Ho*Wo positions are a multiple of
         // 32 the patches of the whole chunk are ONE GEMM with N = nb*Ho*Wo whose epilogue writes column block b (image b)

@@ -320,6 +320,9 @@ struct ConvGeom {
     uint32_t C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo, K, Kp;
 };
 cudaError_t launch_im2col_t(const uint8_t *im, uint64_t batches, const ConvGeom &g, uint8_t *col_t, cudaStream_t stream);
+// The same gather plus the per-patch sums (colsum[b*Ho*Wo + n] = sum over k of col_t[b][n][k]) in one pass.
+cudaError_t launch_im2col_t_sums(const uint8_t *im, uint64_t batches, const ConvGeom &g, uint8_t *col_t, int32_t *colsum,
+                                 cudaStream_t stream);
 
 cudaError_t launch_min_max(const float *data, uint64_t len, float *minmax, cudaStream_t stream);
 cudaError_t launch_qparams_from_minmax(const float *minmax, ltq_qparams *qp, cudaStream_t stream);

@@ -535,8 +535,9 @@ cudaError_t launch_pair_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64
 bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
 {
     // Worth pairing once 256 x 256 tiles can occupy most CTA pairs of the device.
+    // (with at most 128 rows the second CTA of a pair would have nothing to do)
     const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + 255) / 256);
-    return tiles * 4 >= (uint64_t)(sms / 2) * 3;
+    return M > (uint64_t)BM && tiles * 4 >= (uint64_t)(sms / 2) * 3;
 }
 
 int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores, bool chunks_aligned_32)
