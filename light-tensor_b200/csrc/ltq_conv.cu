@@ -56,26 +56,26 @@ __global__ void __launch_bounds__(256) im2col_t_kernel(const uint8_t *__restrict
 
 // The fast path.  One CTA per (image, output row): the C x kh input rows that this output row's patches read are staged
 // in shared memory once (zero-padded left, right, above and below), then every thread assembles 16-byte units of patch
-// rows from it through a table of tap offsets and stores them, consecutive units of a patch by consecutive threads.
-// The patch sums that the GEMM epilogue needs (sum over k of every patch) are accumulated on the way, which saves a
-// second pass over the patch buffer.  Channels are processed in groups of `cg` (a multiple of 16 unless it covers all
-// channels, so that a group's taps fill whole 16-byte units).
-__global__ void __launch_bounds__(256) im2col_rows_kernel(const uint8_t *__restrict__ im, uint64_t batches, ConvGeom g,
+// rows from it and stores them, consecutive units of a patch by consecutive threads.  A thread keeps ONE unit position
+// (its 16 tap offsets live in registers) and walks along the output row, so a byte costs an add, a shared-memory load
+// and its share of the packing.  The patch sums that the GEMM epilogue needs (sum over k of every patch) are
+// accumulated on the way, which saves a second pass over the patch buffer.  Channels are processed in groups of `cg`
+// (a multiple of 16 unless it covers all channels, so that a group's taps fill whole 16-byte units).
+__global__ void __launch_bounds__(256, 4) im2col_rows_kernel(const uint8_t *__restrict__ im, uint64_t batches, ConvGeom g,
                                                          uint32_t cg, uint32_t Wp, uint8_t *__restrict__ col_t,
                                                          int32_t *__restrict__ colsum)
 {
     extern __shared__ __align__(16) uint8_t sm[];
     const uint32_t khw = g.kh * g.kw;
-    const uint32_t slab_bytes = (cg * g.kh * Wp + 1 + 15) & ~15u;      // + one zero byte for the padding taps
-    const uint32_t table_len = (cg * khw + 15) & ~15u;                // tap offsets of one channel group, padded
+    const uint32_t zero_idx = cg * g.kh * Wp;                          // Wp zero bytes: what padding taps read
+    const uint32_t slab_bytes = (zero_idx + Wp + 15) & ~15u;
     uint8_t *slab = sm;
-    uint16_t *koff = reinterpret_cast<uint16_t *>(sm + slab_bytes);
-    int32_t *psum = reinterpret_cast<int32_t *>(sm + slab_bytes + 2 * table_len);
-    const uint32_t zero_idx = cg * g.kh * Wp;
+    int32_t *psum = reinterpret_cast<int32_t *>(sm + slab_bytes);
     const uint32_t vec_per_row = g.Kp / 16;
     const uint64_t pairs = batches * g.Ho;
-    uint32_t table_for = 0xFFFFFFFFu;                                  // channel count the table was built for
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    for (uint32_t x = threadIdx.x; x < Wp; x += 256) slab[zero_idx + x] = 0;
     for (uint64_t pr = blockIdx.x; pr < pairs; pr += gridDim.x) {
         const uint64_t b = pr / g.Ho;
         const uint32_t ho = (uint32_t)(pr - b * g.Ho);
@@ -85,58 +85,76 @@ __global__ void __launch_bounds__(256) im2col_rows_kernel(const uint8_t *__restr
             const uint32_t cn = g.C - c0 < cg ? g.C - c0 : cg;
             const bool last = c0 + cn == g.C;
             __syncthreads();  // the previous group's (or output row's) readers are done with the slab
-            for (uint32_t idx = threadIdx.x; idx < cn * g.kh * Wp; idx += 256) {
-                const uint32_t x = idx % Wp, ri = idx / Wp, i = ri % g.kh, c = ri / g.kh;
-                const int32_t y = y0 + (int32_t)i, xx = (int32_t)x - (int32_t)g.pw;
-                uint8_t v = 0;
-                if ((uint32_t)y < g.H && (uint32_t)xx < g.W) v = im[((b * g.C + c0 + c) * g.H + (uint32_t)y) * (uint64_t)g.W + (uint32_t)xx];
-                slab[idx] = v;
-            }
-            if (threadIdx.x == 0) slab[zero_idx] = 0;
-            if (table_for != cn) {
-                for (uint32_t k = threadIdx.x; k < table_len; k += 256) {
-                    uint32_t off = zero_idx;
-                    if (k < cn * khw) {
-                        const uint32_t c = k / khw, r = k - c * khw, i = r / g.kw, j = r - i * g.kw;
-                        off = (c * g.kh + i) * Wp + j;
+            // stage: one warp per (channel, kernel row), lanes along the row; eight rows are fetched before any is
+            // stored so that the loads overlap (one row at a time this phase is pure global-memory latency)
+            {
+                constexpr int RB = 8;
+                const uint32_t nrows = cn * g.kh;
+                for (uint32_t rb = warp; rb < nrows; rb += 8 * RB) {
+                    const uint8_t *src[RB];
+                    bool row_ok[RB];
+#pragma unroll
+                    for (int m = 0; m < RB; m++) {
+                        const uint32_t ri = rb + 8 * m;
+                        const uint32_t c = ri / g.kh, i = ri - c * g.kh;
+                        const int32_t y = y0 + (int32_t)i;
+                        row_ok[m] = ri < nrows && (uint32_t)y < g.H;
+                        src[m] = im + ((b * g.C + c0 + (row_ok[m] ? c : 0u)) * g.H + (row_ok[m] ? (uint32_t)y : 0u)) * (uint64_t)g.W;
                     }
-                    koff[k] = (uint16_t)off;
+                    for (uint32_t x = lane; x < Wp; x += 32) {
+                        const uint32_t xx = x - g.pw;  // wraps for the left padding and then fails the test
+                        uint8_t v[RB];
+#pragma unroll
+                        for (int m = 0; m < RB; m++) v[m] = (row_ok[m] && xx < g.W) ? src[m][xx] : (uint8_t)0;
+#pragma unroll
+                        for (int m = 0; m < RB; m++)
+                            if (rb + 8 * m < nrows) slab[(rb + 8 * m) * Wp + x] = v[m];
+                    }
                 }
-                table_for = cn;
             }
             __syncthreads();
             // 16-byte units of this group: all whole units of its taps; the last group also writes the zero tail up to Kp
             const uint32_t u_lo = c0 * khw / 16;
             const uint32_t units = last ? vec_per_row - u_lo : cn * khw / 16;
-            uint8_t *dst_row0 = col_t + ((b * g.Ho + ho) * g.Wo) * (uint64_t)g.Kp;
-            for (uint32_t item = threadIdx.x; item < g.Wo * units; item += 256) {
-                const uint32_t wo = item / units, u = item - wo * units;
-                const uint32_t x_base = wo * g.sw;
-                uint32_t w4[4] = {0, 0, 0, 0};
-                if (u * 16 < table_len) {  // (units of the zero tail beyond the table stay zero)
-                    const uint4 o0 = reinterpret_cast<const uint4 *>(koff + u * 16)[0];
-                    const uint4 o1 = reinterpret_cast<const uint4 *>(koff + u * 16)[1];
-                    const uint32_t ow[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+            uint8_t *dst_row0 = col_t + ((b * g.Ho + ho) * g.Wo) * (uint64_t)g.Kp + (uint64_t)u_lo * 16;
+            // A warp takes one unit position u for 32 consecutive output columns, lane = column: the 32 lanes then read 32
+            // neighbouring bytes of the slab per tap (no bank conflicts), the tap offsets are warp-uniform, and the patch
+            // sums go to 32 different counters.
+            for (uint32_t u = warp; u < units; u += 8) {
+                uint32_t off[16];  // taps beyond the group's channels read the zero row
+                {
+                    const uint32_t k0 = u * 16;
+                    uint32_t c = k0 / khw, r = k0 - c * khw, i = r / g.kw, j = r - i * g.kw;
 #pragma unroll
                     for (int t = 0; t < 16; t++) {
-                        const uint32_t off = (ow[t >> 1] >> (16 * (t & 1))) & 0xFFFFu;
-                        // the zero byte is shared by all patches: it must not move with the output column
-                        const uint32_t byte = slab[off == zero_idx ? off : off + x_base];
-                        w4[t >> 2] |= byte << (8 * (t & 3));
+                        off[t] = c < cn ? (c * g.kh + i) * Wp + j : zero_idx;
+                        if (++j == g.kw) {
+                            j = 0;
+                            if (++i == g.kh) {
+                                i = 0;
+                                c++;
+                            }
+                        }
                     }
                 }
-                *reinterpret_cast<uint4 *>(dst_row0 + (uint64_t)wo * g.Kp + (uint64_t)(u_lo + u) * 16) =
-                    make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                const uint32_t ones = 0x01010101u;
-                const uint32_t ssum = __dp4a(w4[0], ones, __dp4a(w4[1], ones, __dp4a(w4[2], ones, __dp4a(w4[3], ones, 0u))));
-                if (ssum) atomicAdd(&psum[wo], (int32_t)ssum);
+                for (uint32_t wo = lane; wo < g.Wo; wo += 32) {
+                    const uint8_t *px = slab + wo * g.sw;
+                    uint32_t w4[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        w4[q] = (uint32_t)px[off[4 * q]] | ((uint32_t)px[off[4 * q + 1]] << 8) |
+                                ((uint32_t)px[off[4 * q + 2]] << 16) | ((uint32_t)px[off[4 * q + 3]] << 24);
+                    *reinterpret_cast<uint4 *>(dst_row0 + (uint64_t)wo * g.Kp + (uint64_t)u * 16) =
+                        make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                    const uint32_t ones = 0x01010101u;
+                    const uint32_t ssum = __dp4a(w4[0], ones, __dp4a(w4[1], ones, __dp4a(w4[2], ones, __dp4a(w4[3], ones, 0u))));
+                    if (ssum) atomicAdd(&psum[wo], (int32_t)ssum);
+                }
             }
         }
         __syncthreads();
         for (uint32_t w = threadIdx.x; w < g.Wo; w += 256) colsum[(b * g.Ho + ho) * g.Wo + w] = psum[w];
-        // (the next iteration's first __syncthreads orders these reads before psum is cleared again? no: clear comes
-        // first - so synchronise here)
-        __syncthreads();
+        __syncthreads();  // psum is cleared again at the top of the loop
     }
 }
 
@@ -150,7 +168,6 @@ struct Im2colPlan {
 static Im2colPlan plan_im2col_rows(const ConvGeom &g)
 {
     Im2colPlan p{};
-    const uint32_t khw = g.kh * g.kw;
     p.Wp = (g.Wo - 1) * g.sw + g.kw;           // columns a patch row can touch, starting at -pw
     if (p.Wp < g.W + g.pw) p.Wp = g.W + g.pw;  // (never narrower than what is staged)
     const uint64_t per_channel = (uint64_t)g.kh * p.Wp;
@@ -159,10 +176,9 @@ static Im2colPlan plan_im2col_rows(const ConvGeom &g)
     if (cg >= g.C) cg = g.C;
     else cg = cg / 16 * 16;                     // whole 16-byte units per group
     if (cg == 0) return p;
-    const uint64_t slab = (cg * per_channel + 1 + 15) & ~15ull, table = (cg * khw + 15) & ~15ull;
-    if (slab > 65535) return p;                 // tap offsets are 16 bit
+    const uint64_t slab = (cg * per_channel + p.Wp + 15) & ~15ull;
     p.cg = (uint32_t)cg;
-    p.smem = slab + 2 * table + 4 * (size_t)g.Wo;
+    p.smem = slab + 4 * (size_t)g.Wo;
     p.ok = p.smem <= 48 * 1024;
     return p;
 }
