@@ -121,6 +121,15 @@ int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t 
                          const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int device,
                          void *stream);
 
+/* The same product with the output modes and flags of ltq_layer_forward: int32 (the corrected accumulator; with zero
+ * points 0 the plain uint8 x uint8 -> int32 matrix product that Tensor::matmul lacks for UINT8,
+ * l-ten/math_fns.cpp:1295-1305), float ((sA*sB) * acc) or requantized uint8; LTQ_FLAG_RELU / LTQ_FLAG_SATURATE /
+ * LTQ_FLAG_FORCE_*.  C_dev holds M*N elements of the mode's type. */
+int ltq_quantized_matmul_ex(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                            const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, void *C_dev,
+                            const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int out_mode,
+                            unsigned flags, int device, void *stream);
+
 /* No counterpart in the reference: the same computation as ltq_quantized_matmul for callers that must not allocate
  * device memory and therefore have no workspace to pass -- code running inside another framework's pre-planned memory
  * region, latency-critical loops that cannot take the allocator's lock or an implicit synchronisation, processes

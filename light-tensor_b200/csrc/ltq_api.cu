@@ -299,11 +299,13 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
     return LTQ_OK;
 }
 
-int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
-                         const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, uint8_t *C_dev,
-                         const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int device,
-                         void *stream)
+int ltq_quantized_matmul_ex(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                            const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, void *C_dev,
+                            const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int out_mode,
+                            unsigned flags, int device, void *stream)
 {
+    LTQ_REQUIRE(out_mode == LTQ_OUT_U8 || out_mode == LTQ_OUT_F32 || out_mode == LTQ_OUT_I32, LTQ_ERR_INVALID_ARG,
+                "unknown out_mode %d", out_mode);
     LTQ_REQUIRE(alpha == 1 && beta == 0, LTQ_ERR_UNSUPPORTED,
                 "Support for alpha != 1 and beta != 0 not implemented");  // l-ten/math_fns.cpp:1331-1334
     LTQ_REQUIRE(A_dev && B_dev && C_dev && qparams && workspace_dev, LTQ_ERR_INVALID_ARG, "Invalid argument");
@@ -327,9 +329,9 @@ int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t 
         if (!tA) LTQ_CUDA_TRY(launch_row_sums(A_dev, M, K, asum, st));
         else LTQ_CUDA_TRY(launch_col_sums(A_dev, K, M, asum, st));
     }
-    Epilogue epi = make_epilogue(bsum, asum, bias_dev, qparams[0], qparams[1], qparams[2], K, LTQ_OUT_U8, 0);
+    Epilogue epi = make_epilogue(bsum, asum, bias_dev, qparams[0], qparams[1], qparams[2], K, out_mode, flags);
     if (!tA && tB && K > 0) {
-        rc = run_fc_gemm(dev, M, N, K, A_dev, B_dev, epi, C_dev, 0, nullptr, st);
+        rc = run_fc_gemm(dev, M, N, K, A_dev, B_dev, epi, C_dev, flags, nullptr, st);
         if (rc != LTQ_OK) return rc;
     } else {
         LTQ_CUDA_TRY(launch_gemm_simt(tA, tB, M, N, K, A_dev, B_dev, epi, C_dev, st));
@@ -338,6 +340,15 @@ int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t 
     LTQ_CUDA_TRY(launch_scale_i32(bsum, N, -(int32_t)qparams[0].zero_point, st));
     LTQ_CUDA_TRY(launch_scale_i32(asum, M, -(int32_t)qparams[1].zero_point, st));
     return LTQ_OK;
+}
+
+int ltq_quantized_matmul(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
+                         const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, uint8_t *C_dev,
+                         const ltq_qparams *qparams, const int32_t *bias_dev, int32_t *workspace_dev, int device,
+                         void *stream)
+{
+    return ltq_quantized_matmul_ex(transpose_A, transpose_B, M, N, K, alpha, A_dev, B_dev, beta, C_dev, qparams, bias_dev,
+                                   workspace_dev, LTQ_OUT_U8, 0, device, stream);
 }
 
 // ---- layer handle -----------------------------------------------------------------------------------------------------

@@ -376,6 +376,90 @@ Tensor Conv2d_q::forward(Tensor &input)
     return result;
 }
 
+// ---- checkpoint I/O -------------------------------------------------------------------------------------------------------
+namespace {
+const char CKPT_MAGIC[8] = {'L', 'T', 'Q', 'C', 'K', 'P', 'T', '1'};
+uint8_t dtype_code(dtype d) { return d == UINT8 ? 0 : (d == INT32 ? 1 : 2); }
+}  // namespace
+
+int save_checkpoint(const std::vector<Module *> &modules, const char *checkpoint_path)
+{
+    FILE *f = fopen(checkpoint_path, "wb");
+    if (!f) return -1;
+    bool ok = fwrite(CKPT_MAGIC, 1, 8, f) == 8;
+    const uint32_t n = (uint32_t)modules.size();
+    ok = ok && fwrite(&n, 4, 1, f) == 1;
+    for (Module *m : modules) {
+        std::vector<Tensor *> ts = m->get_all_weights();
+        const uint32_t nt = (uint32_t)ts.size();
+        ok = ok && fwrite(&nt, 4, 1, f) == 1;
+        for (Tensor *t : ts) {
+            Tensor host = t->to(CPU);
+            const uint8_t head[4] = {dtype_code(host.get_data_type()), 0, 0, 0};
+            const uint32_t nd = (uint32_t)host.get_ndims();
+            ok = ok && fwrite(head, 1, 4, f) == 4 && fwrite(&nd, 4, 1, f) == 1;
+            ok = ok && fwrite(host.get_sizes(), 8, nd, f) == nd;
+            const size_t bytes = host.get_numels() * dtype_size(host.get_data_type());
+            ok = ok && fwrite(host.get_data_ptr(), 1, bytes, f) == bytes;
+        }
+        QuantizationParams q[3];
+        m->get_qparams(q);
+        for (int i = 0; i < 3; i++) {
+            const uint8_t tail[4] = {q[i].zero_point, 0, 0, 0};
+            ok = ok && fwrite(&q[i].scale, 4, 1, f) == 1 && fwrite(tail, 1, 4, f) == 4;
+        }
+    }
+    ok = (fclose(f) == 0) && ok;
+    return ok ? 0 : -1;
+}
+
+int load_checkpoint(const std::vector<Module *> &modules, const char *checkpoint_path)
+{
+    FILE *f = fopen(checkpoint_path, "rb");
+    if (!f) return -1;
+    char magic[8];
+    uint32_t n = 0;
+    bool ok = fread(magic, 1, 8, f) == 8 && memcmp(magic, CKPT_MAGIC, 8) == 0 && fread(&n, 4, 1, f) == 1 &&
+              n == modules.size();
+    for (size_t mi = 0; ok && mi < modules.size(); mi++) {
+        Module *m = modules[mi];
+        std::vector<Tensor *> ts = m->get_all_weights();
+        uint32_t nt = 0;
+        ok = fread(&nt, 4, 1, f) == 1 && nt == ts.size();
+        for (size_t ti = 0; ok && ti < ts.size(); ti++) {
+            Tensor *t = ts[ti];
+            uint8_t head[4];
+            uint32_t nd = 0;
+            uint64_t dims[MAX_DIMS];
+            ok = fread(head, 1, 4, f) == 4 && fread(&nd, 4, 1, f) == 1 && nd == (uint32_t)t->get_ndims() && nd <= MAX_DIMS &&
+                 head[0] == dtype_code(t->get_data_type()) && fread(dims, 8, nd, f) == nd &&
+                 memcmp(dims, t->get_sizes(), 8 * nd) == 0;
+            if (!ok) break;
+            const size_t bytes = t->get_numels() * dtype_size(t->get_data_type());
+            if (t->get_device() == CPU) {
+                ok = fread(t->get_data_ptr(), 1, bytes, f) == bytes;
+            } else {
+                std::vector<uint8_t> buf(bytes);
+                ok = fread(buf.data(), 1, bytes, f) == bytes &&
+                     cudaMemcpy(t->get_data_ptr(), buf.data(), bytes, cudaMemcpyHostToDevice) == cudaSuccess;
+            }
+        }
+        QuantizationParams q[3];
+        for (int i = 0; ok && i < 3; i++) {
+            uint8_t tail[4];
+            ok = fread(&q[i].scale, 4, 1, f) == 1 && fread(tail, 1, 4, f) == 4;
+            q[i].zero_point = tail[0];
+        }
+        if (ok) {
+            m->set_qparams_in(q[0]);
+            m->set_qparams_params(&q[1], 1);
+            m->set_qparams_out(q[2]);
+        }
+    }
+    fclose(f);
+    return ok ? 0 : -1;
+}
+
 }  // namespace lten
 
 // ---- free functions ----------------------------------------------------------------------------------------------------

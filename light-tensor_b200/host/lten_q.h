@@ -90,6 +90,11 @@ public:
     virtual void set_qparams_in(QuantizationParams) {}
     virtual void set_qparams_out(QuantizationParams) {}
     virtual void set_qparams_params(QuantizationParams *, int) {}
+    // Additive: input, weight and output parameters of a quantized module (what a checkpoint has to carry).
+    virtual void get_qparams(QuantizationParams out[3]) const
+    {
+        out[0] = out[1] = out[2] = QuantizationParams{1.f, 0};
+    }
 
 protected:
     bool is_training_ = true;
@@ -114,6 +119,12 @@ public:
     void set_qparams_in(QuantizationParams qparams_in) { qparams_in_ = qparams_in; }
     void set_qparams_out(QuantizationParams qparams_out) { qparams_out_ = qparams_out; }
     void set_qparams_params(QuantizationParams *qparams, int count);
+    void get_qparams(QuantizationParams out[3]) const override
+    {
+        out[0] = qparams_in_;
+        out[1] = qparams_wt_;
+        out[2] = qparams_out_;
+    }
 
     // Additive: what the fused epilogue writes.  Defaults reproduce the reference (uint8, no ReLU, wrapping cast).
     void set_output(ltq_out_mode mode, bool relu = false, bool saturate = false);
@@ -159,6 +170,12 @@ public:
     void set_qparams_in(QuantizationParams qparams_in) { qparams_in_ = qparams_in; }
     void set_qparams_out(QuantizationParams qparams_out) { qparams_out_ = qparams_out; }
     void set_qparams_params(QuantizationParams *qparams, int count);
+    void get_qparams(QuantizationParams out[3]) const override
+    {
+        out[0] = qparams_in_;
+        out[1] = qparams_wt_;
+        out[2] = qparams_out_;
+    }
 
     // Additive.  bias_per_channel adds bias[c] per output channel; the default applies the bias the way the reference's
     // GEMM does, per output position, which it only defines while Ho*Wo <= channels_out.
@@ -173,6 +190,15 @@ private:
     ltq_out_mode out_mode_ = LTQ_OUT_U8;
     unsigned flags_ = 0;
 };
+
+// Checkpoint of quantized modules: every tensor of get_all_weights() with its own element size, then the three
+// QuantizationParams.  l-ten's NeuralNetwork::save_checkpoint / load_checkpoint (l-ten/net.h:130-265) assume four bytes
+// per element and keep no quantisation parameters; same return convention (0 = ok, -1 = failure).  Layout (little
+// endian): "LTQCKPT1", uint32 modules, per module { uint32 tensors, per tensor { uint8 dtype (0 uint8, 1 int32,
+// 2 float32), 3 zero bytes, uint32 ndims, uint64 dims[], data }, 3 x { float scale, uint8 zero_point, 3 zero bytes } }.
+// Modules may be on the CPU or on a GPU; after loading into GPU modules call to(GPU, index) again (or load before to()).
+int save_checkpoint(const std::vector<Module *> &modules, const char *checkpoint_path);
+int load_checkpoint(const std::vector<Module *> &modules, const char *checkpoint_path);
 
 }  // namespace lten
 

@@ -45,6 +45,8 @@ _SIGNATURES = {
     "ltq_interleave_column_blocks": (_int, [_vp, _vp, _u64, _u64, _u64, _int, _vp]),
     "ltq_quantized_matmul": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp, _vp,
                                     _int, _vp]),
+    "ltq_quantized_matmul_ex": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp, _vp,
+                                       _int, C.c_uint, _int, _vp]),
     "ltq_quantized_matmul_static": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp,
                                            _int, _vp]),
     "ltq_layer_create": (_int, [C.POINTER(_vp), _int, _u64, _u64]),

@@ -3,7 +3,7 @@ import ctypes as C
 
 import torch
 
-from ._binding import QParams, check, lib
+from ._binding import OUT_F32, OUT_I32, OUT_U8, QParams, check, lib
 
 
 def _stream(t):
@@ -113,6 +113,26 @@ def quantized_matmul(transpose_A, transpose_B, M, N, K, alpha, A, B, beta, C_out
                                      beta, C_out.data_ptr(), arr, None if bias is None else bias.data_ptr(),
                                      workspace.data_ptr(), d, _stream(A)))
     return C_out
+
+
+def matmul_u8(A, B, transpose_A=False, transpose_B=False, qparams=None, bias=None, out_mode=OUT_I32, flags=0):
+    """uint8 x uint8 matrix product on CUDA tensors (2-D, contiguous) with the transpose conventions of
+    quantized_matmul: A is [M,K] ([K,M] transposed), B is [K,N] ([N,K] transposed).  Default: the plain int32 product
+    (zero points 0) -- what ``Tensor::matmul`` has no implementation for with UINT8 tensors (l-ten/math_fns.cpp:1295-1305).
+    With ``qparams`` (three QuantizationParams) the zero-point-corrected product in the chosen output mode."""
+    assert A.dtype == torch.uint8 and B.dtype == torch.uint8 and A.dim() == 2 and B.dim() == 2
+    M, K = (A.shape[1], A.shape[0]) if transpose_A else A.shape
+    N = B.shape[0] if transpose_B else B.shape[1]
+    assert (B.shape[1] if transpose_B else B.shape[0]) == K, "inner dimensions differ"
+    d = _dev(A)
+    arr = (QParams * 3)(*(qparams or [QParams(1.0, 0)] * 3))
+    out = torch.empty((M, N), dtype={OUT_U8: torch.uint8, OUT_F32: torch.float32, OUT_I32: torch.int32}[out_mode],
+                      device=A.device)
+    ws = torch.empty(M + N, dtype=torch.int32, device=A.device)
+    check(lib().ltq_quantized_matmul_ex(int(transpose_A), int(transpose_B), M, N, K, 1, A.data_ptr(), B.data_ptr(), 0,
+                                        out.data_ptr(), arr, None if bias is None else bias.data_ptr(), ws.data_ptr(),
+                                        out_mode, flags, d, _stream(A)))
+    return out
 
 
 def quantized_matmul_static(transpose_A, transpose_B, M, N, K, alpha, A, B, beta, C_out, qparams, bias):

@@ -136,3 +136,29 @@ def test_pair_kernel_tile_widths(cuda, oracle, shape):
     got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_F32, force | ltq.FLAG_RELU)
     want = oracle.port.epilogue_f32(acc, 0.02, 0.005, relu=True)
     np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("tA,tB", [(False, False), (False, True), (True, False), (True, True)])
+def test_matmul_u8_plain_int32_product_and_modes(cuda, oracle, tA, tB):
+    """The generic uint8 matrix product (every transpose variant): plain int32 product with zero points 0, and the
+    corrected product in int32 / float / uint8 with qparams, against the oracle."""
+    import ltq
+    rng = np.random.default_rng(40 + 2 * tA + tB)
+    M, N, K = 70, 52, 96
+    A = rng.integers(0, 256, (K, M) if tA else (M, K), dtype=np.uint8)
+    B = rng.integers(0, 256, (N, K) if tB else (K, N), dtype=np.uint8)
+    Ad, Bd = cuda.from_numpy(A).cuda(), cuda.from_numpy(B).cuda()
+    plain = ltq.matmul_u8(Ad, Bd, tA, tB).cpu().numpy()
+    a2 = (A.T if tA else A).astype(np.int64)
+    b2 = (B if tB else B.T).astype(np.int64)
+    np.testing.assert_array_equal(plain, (a2 @ b2.T).astype(np.int32))
+    rows = [(0.02, 128), (0.005, 127), (0.9, 3)]
+    qps = [ltq.QParams(float(np.float32(s)), z) for s, z in rows]
+    bias = rng.integers(-9000, 9000, N, dtype=np.int32)
+    acc = oracle.port.acc_i32(A, B, M, N, K, 128, 127, bias=bias, tA=tA, tB=tB)
+    bd = cuda.from_numpy(bias).cuda()
+    np.testing.assert_array_equal(ltq.matmul_u8(Ad, Bd, tA, tB, qps, bd, ltq.OUT_I32).cpu().numpy(), acc)
+    np.testing.assert_array_equal(ltq.matmul_u8(Ad, Bd, tA, tB, qps, bd, ltq.OUT_F32, ltq.FLAG_RELU).cpu().numpy(),
+                                  oracle.port.epilogue_f32(acc, 0.02, 0.005, relu=True))
+    np.testing.assert_array_equal(ltq.matmul_u8(Ad, Bd, tA, tB, qps, bd, ltq.OUT_U8).cpu().numpy(),
+                                  oracle.port.epilogue_u8(acc, 0.02, 0.005, 0.9, 3))
