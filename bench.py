@@ -196,7 +196,7 @@ class Harness:
             self.dist.barrier()
             self.torch.cuda.synchronize()
 
-    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False, join=None):
+    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False, join=None, capture_stream=None):
         """ms per step over EXACTLY `steps` steps, CUDA events on the launching stream, max over ranks.  The steps are
         captured once into a CUDA graph (the kernels run for tens of microseconds; launching them one by one from
         Python would time the interpreter) and the graph is replayed once untimed before the timed replay.  With
@@ -212,7 +212,7 @@ class Harness:
         gr = None
         if graph:
             gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
+            with torch.cuda.graph(gr, stream=capture_stream):
                 for i in range(steps):
                     fn(warmup + i)
             gr.replay()
@@ -295,17 +295,41 @@ def run_linear(args):
     asum = [torch.empty(M, dtype=torch.int32, device=dev) for _ in range(sets)]
     outs = [torch.empty((M, N), dtype=out_dtype, device=dev) for _ in range(sets)]
 
-    def step(i):
+    def step_serial(i):
         s = i % sets
         ltq.quantize_rows(xs[s], qp=qps_x[s], q=xq[s], asum=asum[s])
         layers[s].forward(xq[s], out_mode, 0, asum=asum[s], out=outs[s])
+
+    # Software-pipelined step: while the GEMM of batch i runs (tensor-bound), a second stream quantises batch i+1
+    # (HBM-bound) on the SM resources the persistent GEMM CTAs leave free.  Every step still launches exactly one
+    # quantize_rows and one GEMM; batch i's quantised activations come from the step before (or, for the first step of
+    # a sequence, are produced up front).
+    side = torch.cuda.Stream(priority=0)             # lowest priority: fills what the GEMM leaves free
+    state = {"ready": None}
+
+    def step_overlap(i):
+        s, nxt = i % sets, (i + 1) % sets
+        main = torch.cuda.current_stream()
+        if state["ready"] != i:
+            ltq.quantize_rows(xs[s], qp=qps_x[s], q=xq[s], asum=asum[s])
+        fork = torch.cuda.Event()
+        fork.record(main)                            # batch i+1's buffers are free once everything before this is done
+        layers[s].forward(xq[s], out_mode, 0, asum=asum[s], out=outs[s])   # enqueued first: its CTAs take the SMs first
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            ltq.quantize_rows(xs[nxt], qp=qps_x[nxt], q=xq[nxt], asum=asum[nxt])
+        main.wait_stream(side)                       # join
+        state["ready"] = i + 1
+
+    step = step_serial if (args.no_overlap or wl == "skinny") else step_overlap
 
     def gemm_only(i):
         s = i % sets
         layers[s].forward(xq[s], out_mode, 0, asum=asum[s], out=outs[s])
 
     launches0 = ltq.kernel_launches()
-    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True,
+                      capture_stream=torch.cuda.Stream(priority=-1))
     # kernels per timed region: warm-up steps and the capture pass each launch the same list; replays re-run it
     launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
     ms_gemm = h.timed(gemm_only, args.steps, max(3, args.warmup), graph=not args.no_graph)
@@ -393,7 +417,8 @@ def run_linear(args):
     cfg = {"workload": workload_name(wl), "M_per_gpu": M, "N": N, "K": K,
            "sharding": "rows (M) per GPU, weights replicated, no collective" if world > 1 else "single GPU",
            "l2": f"rotating {sets} distinct input/weight/output sets, larger than L2 in total",
-           "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue",
+           "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue" +
+                   ("" if step is step_serial else "; batch i+1 is quantised on a second stream while batch i's GEMM runs"),
            "timing": "CUDA events around one replay of a CUDA graph holding exactly `steps` steps"
            if not args.no_graph else "CUDA events around `steps` eager launches"}
     quant_bytes = 5.0 * M * K + 4.0 * M  # fp32 in, uint8 out, one int32 row sum per row
@@ -593,6 +618,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="square_4096: quantise and multiply one after the other instead of overlapping batch i+1's quantisation with batch i's GEMM")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
