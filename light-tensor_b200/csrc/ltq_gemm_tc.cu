@@ -231,7 +231,7 @@ struct PCfg {
 }  // namespace
 
 template <int PBN, int OUT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 2)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
                     uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
