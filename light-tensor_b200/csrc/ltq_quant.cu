@@ -279,7 +279,7 @@ cudaError_t launch_dequantize(float *x, const uint8_t *q, uint64_t len, const lt
 // TPR threads cooperate on one row (TPR = 32: a warp; TPR = 256: the whole CTA).  Reads fp32 once, writes uint8 once
 // and one int32 per row: 5 bytes per element of HBM traffic, the minimum for this step.
 template <int TPR>
-__global__ void __launch_bounds__(256) quantize_rows_kernel(const float *__restrict__ x, uint64_t M, uint64_t K,
+__global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__restrict__ x, uint64_t M, uint64_t K,
                                                             float scale_h, float zpf_h,
                                                             const ltq_qparams *__restrict__ qp_dev,
                                                             uint8_t *__restrict__ q, int32_t *__restrict__ asum)
