@@ -300,8 +300,8 @@ def run_linear(args):
         ltq.quantize_rows(xs[s], qp=qps_x[s], q=xq[s], asum=asum[s])
         layers[s].forward(xq[s], out_mode, 0, asum=asum[s], out=outs[s])
 
-    # Software-pipelined step: while the GEMM of batch i runs (tensor-bound), a second stream quantises batch i+1
-    # (HBM-bound) on the SM resources the persistent GEMM CTAs leave free.  Every step still launches exactly one
+    # Software-pipelined step: while the GEMM of batch i runs (tensor-bound; for the skinny workload, weight streaming),
+    # a second stream quantises batch i+1 on the SM resources the persistent GEMM CTAs leave free.  Every step still launches exactly one
     # quantize_rows and one GEMM; batch i's quantised activations come from the step before (or, for the first step of
     # a sequence, are produced up front).
     side = torch.cuda.Stream(priority=0)             # lowest priority: fills what the GEMM leaves free
@@ -321,7 +321,7 @@ def run_linear(args):
         main.wait_stream(side)                       # join
         state["ready"] = i + 1
 
-    step = step_serial if (args.no_overlap or wl == "skinny") else step_overlap
+    step = step_serial if args.no_overlap else step_overlap
 
     def gemm_only(i):
         s = i % sets
@@ -619,7 +619,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true",
-                    help="square_4096: quantise and multiply one after the other instead of overlapping batch i+1's quantisation with batch i's GEMM")
+                    help="quantise and multiply one after the other instead of overlapping batch i+1's quantisation with batch i's GEMM")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

@@ -57,6 +57,27 @@ struct DeviceGuard {
         return LTQ_ERR_CUDA;                                                                                 \
     }
 
+// Launches `kernel` as a programmatic dependent of the kernel in front of it in the stream: its CTAs may become
+// resident (and run their set-up) while that kernel is still finishing.  The kernel itself must execute
+// griddepcontrol.wait before it touches anything the earlier kernel may have written, and griddepcontrol.launch_dependents
+// to release the kernel behind it the same way (ltq_ptx.cuh).  After a kernel that never releases its dependents, or
+// after anything that is not a kernel, this is an ordinary launch.
+template <typename... P, typename... A>
+inline cudaError_t launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 // ---- epilogue ------------------------------------------------------------------------------------------------------
 // Everything a kernel needs to turn raw = sum_k A[i,k]*B[j,k] into an output element.
 //   acc = raw - zA*bsum[j] - zB*asum[i] + K*zA*zB (+ bias[j])            l-ten/math_fns.cpp:1433-1473

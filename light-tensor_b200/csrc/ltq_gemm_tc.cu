@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
                uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
+    griddep_launch_dependents();
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need a 1024-byte aligned base.
@@ -87,6 +88,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Programmatic dependent launch: everything above ran while the kernel in front may still have been finishing;
+    // from here on its results (activations, row sums, device-side qparams) are read.
+    griddep_wait();
     const uint32_t tmem_base = s_misc[0];
 
     if (warp == 0) {
@@ -235,6 +239,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 2)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
                     uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
+    griddep_launch_dependents();
     using C = PCfg<PBN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -276,6 +281,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_before();
     __syncthreads();
     cluster_sync();  // the peer's barriers exist before anything is signalled across
+    griddep_wait();  // programmatic dependent launch: the set-up above overlapped the previous kernel's tail
     tc_fence_after();
     const uint32_t tmem_base = s_misc[0];
 
@@ -470,10 +476,10 @@ cudaError_t launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M,
     }
     const uint64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
-    gemm_tc_kernel<BN, OUT><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, (uint32_t)M, (uint32_t)N,
-                                                                          (uint32_t)K, epi, out, status);
+    cudaError_t e = launch_chained(gemm_tc_kernel<BN, OUT>, dim3(grid), dim3(NUM_THREADS), (size_t)C::SMEM_BYTES, stream, ma, mb,
+                                   (uint32_t)M, (uint32_t)N, (uint32_t)K, epi, out, status);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 template <int BN>
@@ -513,10 +519,10 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M
     Epilogue epi_l = epi;
     epi_l.staged = (epi.n_more > 0 && STAGE_FITS) ? 1 : 0;  // (local-only stores gain nothing from the stage: measured)
     const size_t smem = C::SMEM_BYTES + (epi_l.staged ? STAGE_BYTES : 0);
-    gemm_tc_pair_kernel<PBN, OUT><<<(unsigned)(2 * pairs), P_THREADS, smem, stream>>>(
-        ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi_l, out, status);
+    cudaError_t e = launch_chained(gemm_tc_pair_kernel<PBN, OUT>, dim3((unsigned)(2 * pairs)), dim3(P_THREADS), smem, stream,
+                                   ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi_l, out, status);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 template <int PBN>

@@ -5,6 +5,7 @@
 // Arithmetic follows l-ten/utils.cpp:198-286 operation for operation (IEEE divide, separate add, clamp, round half away
 // from zero); the file is compiled with -fmad=false so nothing is contracted.
 #include "ltq_common.cuh"
+#include "ltq_ptx.cuh"
 
 namespace ltq {
 
@@ -284,6 +285,9 @@ __global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__re
                                                             const ltq_qparams *__restrict__ qp_dev,
                                                             uint8_t *__restrict__ q, int32_t *__restrict__ asum)
 {
+    // launched as a programmatic dependent: release the kernel behind, then wait for the one in front
+    griddep_launch_dependents();
+    griddep_wait();
     float scale = scale_h, zpf = zpf_h;
     if (qp_dev) {
         scale = qp_dev->scale;
@@ -349,16 +353,17 @@ cudaError_t launch_quantize_rows(const float *x, uint64_t M, uint64_t K, const l
     float scale = qp_host ? qp_host->scale : 0.f;
     float zpf = qp_host ? (float)(int)qp_host->zero_point : 0.f;
     const uint64_t cap = (uint64_t)sm_count() * 8;
+    cudaError_t e;
     if (K <= 2048) {
         uint64_t want = (M + 7) / 8;
         int blocks = (int)(want > cap ? cap : want);
-        quantize_rows_kernel<32><<<blocks, 256, 0, stream>>>(x, M, K, scale, zpf, qp_dev, q, asum);
+        e = launch_chained(quantize_rows_kernel<32>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
     } else {
         int blocks = (int)(M > cap ? cap : M);
-        quantize_rows_kernel<256><<<blocks, 256, 0, stream>>>(x, M, K, scale, zpf, qp_dev, q, asum);
+        e = launch_chained(quantize_rows_kernel<256>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
     }
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 // ---- operand sums ---------------------------------------------------------------------------------------------------
@@ -366,6 +371,8 @@ cudaError_t launch_quantize_rows(const float *x, uint64_t M, uint64_t K, const l
 __global__ void __launch_bounds__(256) row_sums_kernel(const uint8_t *__restrict__ m, uint64_t rows, uint64_t cols,
                                                        int32_t *__restrict__ sums)
 {
+    griddep_launch_dependents();  // launched as a programmatic dependent, see launch_chained
+    griddep_wait();
     const int lane = threadIdx.x & 31;
     const uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
@@ -449,9 +456,9 @@ cudaError_t launch_row_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int3
     uint64_t want = (rows + 7) / 8;
     uint64_t cap = (uint64_t)sm_count() * 8;
     int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-    row_sums_kernel<<<blocks, 256, 0, stream>>>(m, rows, cols, sums);
+    cudaError_t e = launch_chained(row_sums_kernel, dim3(blocks), dim3(256), 0, stream, m, rows, cols, sums);
     count_launch();
-    return cudaGetLastError();
+    return e;
 }
 
 cudaError_t launch_col_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream)

@@ -224,3 +224,49 @@ def test_back_to_back_skinny_launches_respect_their_inputs(cuda, oracle):
         np.testing.assert_array_equal(mids[i].cpu().numpy(), mid_ref, err_msg=f"layer 1, iteration {i}")
         np.testing.assert_array_equal(outs[i].cpu().numpy(), out_ref, err_msg=f"layer 2, iteration {i}")
     l1.check()
+
+
+@pytest.mark.parametrize("M", [64, 300])
+def test_back_to_back_tensor_core_layers_respect_their_inputs(cuda, oracle, M):
+    """quantize_rows, the row-sum kernel and the tensor-core GEMMs are launched as programmatic dependents of the kernel
+    in front of them (their set-up overlaps its tail).  A three-layer chain, run many times without any synchronisation
+    and with every intermediate buffer reused, must still give the oracle's result each time."""
+    import ltq
+    rng = np.random.default_rng(23 + M)
+    dims = [784, 512, 256, 48]
+    ws = [rng.integers(0, 256, (dims[i + 1], dims[i]), dtype=np.uint8) for i in range(3)]
+    bs = [rng.integers(-4000, 4000, dims[i + 1], dtype=np.int32) for i in range(3)]
+    rows = [(0.02, 128), (0.004, 127), (2.5, 9), (0.003, 130), (30.0, 60), (0.005, 100), (300.0, 128)]
+    q_act = [ltq_qp(rows[0]), ltq_qp(rows[2]), ltq_qp(rows[4]), ltq_qp(rows[6])]
+    q_w = [ltq_qp(rows[1]), ltq_qp(rows[3]), ltq_qp(rows[5])]
+    layers = []
+    for i in range(3):
+        h = ltq.LayerHandle(0, dims[i], dims[i + 1])
+        h.set_weights(cuda.from_numpy(ws[i]).cuda(), cuda.from_numpy(bs[i]).cuda())
+        h.set_qparams(q_act[i], q_w[i], q_act[i + 1])
+        layers.append(h)
+    reps = 10
+    xs = [rng.normal(0, 0.8, (M, dims[0])).astype(np.float32) for _ in range(reps)]
+    xs_dev = [cuda.from_numpy(x).cuda() for x in xs]
+    xq = cuda.empty((M, dims[0]), dtype=cuda.uint8, device="cuda")
+    asum = cuda.empty(M, dtype=cuda.int32, device="cuda")
+    h1 = cuda.empty((M, dims[1]), dtype=cuda.uint8, device="cuda")       # reused by every iteration
+    h2 = cuda.empty((M, dims[2]), dtype=cuda.uint8, device="cuda")
+    outs = [cuda.empty((M, dims[3]), dtype=cuda.uint8, device="cuda") for _ in range(reps)]
+    cuda.cuda.synchronize()
+    for i in range(reps):
+        ltq.quantize_rows(xs_dev[i], qp=q_act[0], q=xq, asum=asum)
+        layers[0].forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=h1)
+        layers[1].forward(h1, ltq.OUT_U8, ltq.FLAG_RELU, out=h2)           # row sums computed by a kernel in between
+        layers[2].forward(h2, ltq.OUT_U8, 0, out=outs[i])
+    cuda.cuda.synchronize()
+    o_act = [qp_of(oracle, rows[0]), qp_of(oracle, rows[2]), qp_of(oracle, rows[4]), qp_of(oracle, rows[6])]
+    o_w = [qp_of(oracle, rows[1]), qp_of(oracle, rows[3]), qp_of(oracle, rows[5])]
+    for i in range(reps):
+        a = oracle.port.quantize_u8(xs[i], o_act[0])
+        for li in range(3):
+            acc = oracle.port.acc_i32(a, ws[li], M, dims[li + 1], dims[li], o_act[li].zero_point, o_w[li].zero_point, bias=bs[li])
+            a = oracle.port.epilogue_u8(acc, o_act[li].scale, o_w[li].scale, o_act[li + 1].scale, o_act[li + 1].zero_point,
+                                        relu=(li < 2))
+        np.testing.assert_array_equal(outs[i].cpu().numpy(), a, err_msg=f"iteration {i}")
+    layers[0].check()

@@ -43,7 +43,7 @@ def _run_layer(cuda, ltq, a, w, bias, qps, out_mode, flags, asum=None):
 
 SHAPES = [
     # (M, N, K)
-    (1, 8, 16), (1, 11008 // 8, 4096), (4, 100, 4096), (16, 264, 1040), (9, 72, 48), (16, 8, 8192), (5, 40, 6144), (3, 24, 16384),
+    (1, 8, 16), (1, 11008 // 8, 4096), (4, 100, 4096), (16, 264, 1040), (9, 72, 48), (16, 8, 8192), (5, 40, 6144), (3, 24, 16384), (4, 16, 32768),
     (16, 333, 384), (3, 7, 128), (12, 1001, 1152), (8, 596, 2048),
     (17, 10, 784), (64, 512, 784), (64, 10, 512), (128, 256, 128), (130, 300, 400), (256, 512, 1024),
     (300, 129, 2064), (128, 64, 16), (1, 1, 16), (77, 333, 112), (600, 520, 1152), (1024, 768, 512),
