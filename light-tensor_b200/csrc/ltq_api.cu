@@ -2,6 +2,7 @@
 // Nothing here computes on the host beyond scalar set-up; every data path is a CUDA kernel and every entry point fails
 // with LTQ_ERR_CUDA when no device is usable.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <cmath>
@@ -23,6 +24,12 @@ void set_error(const char *fmt, ...)
     va_start(ap, fmt);
     vsnprintf(g_err, sizeof g_err, fmt, ap);
     va_end(ap);
+}
+
+bool chained_launches_enabled()
+{
+    static const bool on = getenv("LTQ_NO_CHAINED_LAUNCH") == nullptr;
+    return on;
 }
 
 namespace {

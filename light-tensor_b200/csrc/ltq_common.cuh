@@ -62,6 +62,7 @@ struct DeviceGuard {
 // griddepcontrol.wait before it touches anything the earlier kernel may have written, and griddepcontrol.launch_dependents
 // to release the kernel behind it the same way (ltq_ptx.cuh).  After a kernel that never releases its dependents, or
 // after anything that is not a kernel, this is an ordinary launch.
+bool chained_launches_enabled();  // false when the environment variable LTQ_NO_CHAINED_LAUNCH is set (a debugging switch)
 template <typename... P, typename... A>
 inline cudaError_t launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&...args)
 {
@@ -74,7 +75,7 @@ inline cudaError_t launch_chained(void (*kernel)(P...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = chained_launches_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 
