@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__re
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const uint32_t i = i0 + u * TPR;
-                v4[u] = i < nvec ? __ldg(xv + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v4[u] = i < nvec ? __ldcs(xv + i) : make_float4(0.f, 0.f, 0.f, 0.f);  // read once: first out of L2
             }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
