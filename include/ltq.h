@@ -175,6 +175,21 @@ int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_
 int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
                       const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream);
 
+/* Chains of layers without a sum pass in between (no counterpart in the reference, which recomputes all sums inside
+ * every quantized_matmul call): with rowsum_dev set (int32 [M], NULL switches it off again), every later uint8-output
+ * forward of this layer also ADDS the sum of each output row's bytes to rowsum_dev[row] -- exactly the asum_dev the
+ * next layer's ltq_layer_forward wants.  The additions are atomic and accumulate: clear the array (cudaMemsetAsync on
+ * the same stream) before each forward.  Ignored for float / int32 output. */
+int ltq_layer_set_rowsum_output(ltq_layer *layer, int32_t *rowsum_dev);
+
+/* Housekeeping for such chains, so that they need no clearing launch either: every later forward of this layer also
+ * clears count int32 at array_dev (count 0 / NULL switches it off), after everything in front of it in the stream has
+ * finished and before anything behind it starts.  Meant for the rowsum array of ANOTHER layer of the chain whose
+ * consumer has already run: e.g. with layers L1 -> L2 -> L3, sums1 = rows of L1's output and sums2 = rows of L2's
+ * output, let L3 clear sums1 and L1 clear sums2.  The array must not be the one this layer accumulates into, nor the
+ * asum_dev passed to the same forward. */
+int ltq_layer_set_clear_on_forward(ltq_layer *layer, int32_t *array_dev, uint64_t count);
+
 /* ltq_layer_forward with the result written into several buffers at once, each holding rows of ld_out elements, at
  * column col_offset: element (i, j) of this layer's output goes to dests[d][i * ld_out + col_offset + j] for every d.
  * No counterpart in the reference (which runs on one device).  This is the exchange step of a COLUMN-SHARDED layer

@@ -79,6 +79,9 @@ Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *
     e.staged = 0;
     e.col_block = 0;
     e.col_block_stride = 0;
+    e.out_rowsum = nullptr;
+    e.clear_ptr = nullptr;
+    e.clear_count = 0;
     for (auto &m : e.more_out) m = nullptr;
     e.qpA_dev = nullptr;
     e.sA = qa.scale;
@@ -133,6 +136,9 @@ struct ltq_layer {
     int32_t *asum_ws = nullptr;    // activation row sums when the caller supplies none; grows with M like
     uint64_t asum_cap = 0;         // FullyConnected_q::workspace_ (l-ten/fully_connected.cpp:366-371)
     ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
+    int32_t *rowsum_out = nullptr; // optional: receives the row sums of uint8 outputs (ltq_layer_set_rowsum_output)
+    int32_t *clear_ptr = nullptr;  // optional: array cleared by every forward (ltq_layer_set_clear_on_forward)
+    uint32_t clear_count = 0;
     TcOperandMap map_w[4];         // weight tensor maps of the tensor-core kernels, one per box height, built on demand
     int map_w_next = 0;
     GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
@@ -445,12 +451,32 @@ static int layer_forward_impl(ltq_layer *layer, const uint8_t *x_dev, const int3
     Epilogue epi = make_epilogue(layer->wsum, asum_dev, layer->bias, layer->qp_in, layer->qp_wt, layer->qp_out, layer->K,
                                  out_mode, flags);
     epi.qpA_dev = qp_in_dev;
+    epi.out_rowsum = out_mode == LTQ_OUT_U8 ? layer->rowsum_out : nullptr;
+    epi.clear_ptr = layer->clear_ptr;
+    epi.clear_count = layer->clear_count;
     const uint64_t esize = out_mode == LTQ_OUT_U8 ? 1 : 4;
     epi.ldc = ld_out;
     epi.n_more = n_dests - 1;
     for (int d = 1; d < n_dests; d++) epi.more_out[d - 1] = static_cast<uint8_t *>(dests[d]) + col_offset * esize;
     return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi,
                        static_cast<uint8_t *>(dests[0]) + col_offset * esize, flags, layer, st);
+}
+
+int ltq_layer_set_rowsum_output(ltq_layer *layer, int32_t *rowsum_dev)
+{
+    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    layer->rowsum_out = rowsum_dev;
+    return LTQ_OK;
+}
+
+int ltq_layer_set_clear_on_forward(ltq_layer *layer, int32_t *array_dev, uint64_t count)
+{
+    LTQ_REQUIRE(layer && (array_dev || count == 0) && count < (1ull << 31), LTQ_ERR_INVALID_ARG, "Invalid argument");
+    LTQ_REQUIRE(!array_dev || array_dev != layer->rowsum_out, LTQ_ERR_INVALID_ARG,
+                "a forward cannot clear the array it accumulates its own row sums into");
+    layer->clear_ptr = count ? array_dev : nullptr;
+    layer->clear_count = (uint32_t)count;
+    return LTQ_OK;
 }
 
 int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,

@@ -106,7 +106,22 @@ struct Epilogue {
     // how one GEMM over the patches of a whole batch writes NCHW: a block is one image's Ho*Wo output positions.
     uint32_t col_block;
     uint64_t col_block_stride;
+    // uint8 output only: every kernel also ADDS the sum of each output row's bytes to out_rowsum[row] (atomically; the
+    // caller clears the array first).  These are the activation row sums the next layer's epilogue needs, so a chain
+    // of layers runs without a sum pass in between.
+    int32_t *out_rowsum;
+    // Housekeeping for such chains: the first CTA clears clear_count int32 at clear_ptr once the kernel in front has
+    // finished (typically the out_rowsum array of ANOTHER layer of the chain, so that no separate clearing launch is
+    // needed).  Nothing in this launch may use that array.
+    int32_t *clear_ptr;
+    uint32_t clear_count;
 };
+
+__device__ __forceinline__ void epilogue_housekeeping(const Epilogue &e)
+{
+    if (e.clear_ptr && blockIdx.x == 0 && blockIdx.y == 0)
+        for (uint32_t i = threadIdx.x; i < e.clear_count; i += blockDim.x) e.clear_ptr[i] = 0;
+}
 
 // Element offset of (row, col).  With column blocking a chunk of consecutive columns must not straddle a block: the
 // tensor-core kernels handle chunks of 16 / 32 columns starting at multiples of 16, so col_block % 32 == 0 there.
@@ -268,14 +283,30 @@ __device__ __forceinline__ void epilogue_store(const uint32_t (&res)[W], const E
     }
 }
 
+// Sum of the first `valid` output bytes of a converted uint8 chunk (W/4 packed words).
+template <int W>
+__device__ __forceinline__ uint32_t packed_byte_sum(const uint32_t (&res)[W], int valid)
+{
+    uint32_t s = 0;
+#pragma unroll
+    for (int g = 0; g < W / 4; g++) {
+        const int left = valid - 4 * g;  // bytes of this word that count
+        const uint32_t mask = left >= 4 ? 0xFFFFFFFFu : (left <= 0 ? 0u : (0xFFFFFFFFu >> (8 * (4 - left))));
+        s = __dp4a(res[g] & mask, 0x01010101u, s);
+    }
+    return s;
+}
+
+// Converts and stores one chunk; returns the sum of the uint8 values stored (0 for the other output modes).
 template <int OUT, int W>
-__device__ __forceinline__ void epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
-                                               const EpilogueConsts &c, bool relu, bool sat, const Epilogue &e, void *out,
-                                               uint64_t off, bool vec_ok, int valid)
+__device__ __forceinline__ uint32_t epilogue_chunk(uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
+                                                   const EpilogueConsts &c, bool relu, bool sat, const Epilogue &e, void *out,
+                                                   uint64_t off, bool vec_ok, int valid)
 {
     uint32_t res[W];
     epilogue_convert<OUT, W>(v, rt, col_smem, c, relu, sat, res);
     epilogue_store<OUT, W>(res, e, out, off, vec_ok, valid);
+    return OUT == 0 ? packed_byte_sum<W>(res, valid) : 0u;
 }
 
 // Row-coalescing stage for stores that leave the GPU.  In the accumulator layout a thread owns one output row, so a

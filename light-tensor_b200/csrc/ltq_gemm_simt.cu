@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, ui
                                                         const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
                                                         Epilogue epi, void *__restrict__ out)
 {
+    epilogue_housekeeping(epi);
     __shared__ uint32_t As[TM][LDW];
     __shared__ uint32_t Bs[TN][LDW];
     const uint64_t m0 = (uint64_t)blockIdx.x * TM, n0 = (uint64_t)blockIdx.y * TN;
@@ -75,6 +76,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, ui
         const uint64_t row = m0 + ty + 16 * i;
         if (row >= M) continue;
         const uint32_t rt = epilogue_row_term(epi, c, row);
+        uint32_t rsum = 0;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint64_t col = n0 + tx + 16 * j;
@@ -83,14 +85,18 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, ui
             const uint64_t o = epilogue_offset(epi, row, col, epilogue_pitch(epi, N));
             for (int d = -1; d < epi.n_more; d++) {
                 void *dst = d < 0 ? out : epi.more_out[d];
-                if (epi.out_mode == LTQ_OUT_U8)
-                    static_cast<uint8_t *>(dst)[o] = epilogue_u8(v, c, sat);
+                if (epi.out_mode == LTQ_OUT_U8) {
+                    const uint8_t b = epilogue_u8(v, c, sat);
+                    static_cast<uint8_t *>(dst)[o] = b;
+                    if (d < 0) rsum += b;
+                }
                 else if (epi.out_mode == LTQ_OUT_F32)
                     static_cast<float *>(dst)[o] = epilogue_f32(v, c);
                 else
                     static_cast<int32_t *>(dst)[o] = v;
             }
         }
+        if (epi.out_mode == LTQ_OUT_U8 && epi.out_rowsum) atomicAdd(&epi.out_rowsum[row], (int32_t)rsum);
     }
 }
 

@@ -91,6 +91,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Programmatic dependent launch: everything above ran while the kernel in front may still have been finishing;
     // from here on its results (activations, row sums, device-side qparams) are read.
     griddep_wait();
+    epilogue_housekeeping(epi);
     const uint32_t tmem_base = s_misc[0];
 
     if (warp == 0) {
@@ -172,6 +173,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (ok) {
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * BN;
+                uint32_t rsum = 0;  // sum of this row's uint8 outputs in this tile
 #pragma unroll 1
                 for (int ch = 0; ch < BN / 32; ch++) {
                     uint32_t v[32];
@@ -179,9 +181,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tmem_ld_wait();
                     const uint32_t c0 = n0 + ch * 32;
                     if (row < M && c0 < N)
-                        epilogue_chunk<OUT, 32>(v, rt, col + ch * 32, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc), vec_ok,
-                                                (N - c0) < 32u ? (int)(N - c0) : 32);
+                        rsum += epilogue_chunk<OUT, 32>(v, rt, col + ch * 32, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
+                                                        vec_ok, (N - c0) < 32u ? (int)(N - c0) : 32);
                 }
+                if (OUT == 0 && epi.out_rowsum && row < M) atomicAdd(&epi.out_rowsum[row], (int32_t)rsum);
                 // all of this warp's reads of the accumulator are done -> hand the buffer back to the MMA warp
                 tc_fence_before();
                 __syncwarp();
@@ -282,6 +285,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     cluster_sync();  // the peer's barriers exist before anything is signalled across
     griddep_wait();  // programmatic dependent launch: the set-up above overlapped the previous kernel's tail
+    epilogue_housekeeping(epi);
     tc_fence_after();
     const uint32_t tmem_base = s_misc[0];
 
@@ -376,6 +380,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 constexpr int ESZ = (int)sizeof(OutT), BLOCK_COLS = 128 / ESZ;   // 128 columns of uint8, 32 of 4 bytes
                 const bool rows_full = m0 + q * 32 + 32 <= M;
                 uint8_t *stage = s_stage + (warp - 2) * PeerStage::BYTES_PER_WARP;
+                uint32_t rsum = 0;  // sum of this row's uint8 outputs in this warp's half of the tile
 #pragma unroll 1
                 for (int cc = cb; cc < ce; cc += 32) {
                     const uint32_t c0 = n0 + cc;
@@ -390,9 +395,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             uint32_t res[32];
                             epilogue_convert<OUT, 32>(v, rt, col + cc, c, relu, sat, res);
                             PeerStage::put<32>(stage, lane, (cc - bc0) * ESZ / 16, res, 32 * ESZ / 16);
+                            if (OUT == 0) rsum += packed_byte_sum<32>(res, 32);
                         } else if (row < M && c0 < N) {
-                            epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc), vec_ok,
-                                                    (N - c0) < 32u ? (int)(N - c0) : 32);
+                            rsum += epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
+                                                            vec_ok, (N - c0) < 32u ? (int)(N - c0) : 32);
                         }
                     } else {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
                         uint32_t v[16];
@@ -402,9 +408,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             uint32_t res[16];
                             epilogue_convert<OUT, 16>(v, rt, col + cc, c, relu, sat, res);
                             PeerStage::put<16>(stage, lane, (cc - bc0) * ESZ / 16, res, 16 * ESZ / 16);
+                            if (OUT == 0) rsum += packed_byte_sum<16>(res, 16);
                         } else if (row < M && c0 < N) {
-                            epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc), vec_ok,
-                                                    (N - c0) < 16u ? (int)(N - c0) : 16);
+                            rsum += epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
+                                                            vec_ok, (N - c0) < 16u ? (int)(N - c0) : 16);
                         }
                     }
                     const int next = cc + 32 < ce ? cc + 32 : ce;
@@ -412,6 +419,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         PeerStage::flush(stage, lane, bcols * ESZ / 16, epi, out,
                                          ((uint64_t)(m0 + q * 32) * ldc + n0 + bc0) * ESZ, ldc * ESZ);
                 }
+                if (OUT == 0 && epi.out_rowsum && row < M) atomicAdd(&epi.out_rowsum[row], (int32_t)rsum);
                 // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)
                 tc_fence_before();
                 __syncwarp();

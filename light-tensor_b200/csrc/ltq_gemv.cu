@@ -268,6 +268,8 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         // ---------------- epilogue (warps 2..5): thread = weight row, register = token ----------------
         const uint32_t q = (uint32_t)warp & 3u;
         griddep_wait();  // the activation row sums (and device-side qparams) come from the previous kernel
+        if (blockIdx.x == 0 && epi.clear_ptr)  // chain housekeeping, see Epilogue::clear_ptr (128 epilogue threads)
+            for (uint32_t i = threadIdx.x - 64; i < epi.clear_count; i += 128) epi.clear_ptr[i] = 0;
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
@@ -301,17 +303,21 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * as);  // accumulator buffer may be overwritten
-                if (valid) {
+                // (all lanes run the loop: the optional row sums below are warp-wide reductions)
 #pragma unroll
-                    for (int m = 0; m < XROWS; m++) {
-                        if ((uint32_t)m < M) {
-                            const int32_t a = epilogue_acc(v[m], rt[m], ct, relu);
-                            OutT r;
-                            if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
-                            else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
-                            else r = (OutT)a;
+                for (int m = 0; m < XROWS; m++) {
+                    if ((uint32_t)m < M) {
+                        const int32_t a = epilogue_acc(v[m], rt[m], ct, relu);
+                        OutT r;
+                        if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
+                        else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
+                        else r = (OutT)a;
+                        if (valid)
                             for (int d = -1; d < epi.n_more; d++)
                                 (d < 0 ? o : static_cast<OutT *>(epi.more_out[d]))[epilogue_offset(epi, (uint64_t)m, n, ldc)] = r;
+                        if (OUT == 0 && epi.out_rowsum) {  // token m: this warp's 32 outputs add up first
+                            const uint32_t t32 = __reduce_add_sync(0xFFFFFFFFu, valid ? (uint32_t)r : 0u);
+                            if (lane == 0 && t32) atomicAdd(&epi.out_rowsum[m], (int32_t)t32);
                         }
                     }
                 }

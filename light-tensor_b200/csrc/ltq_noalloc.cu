@@ -105,6 +105,9 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
     epi.staged = 0;
     epi.col_block = 0;
     epi.col_block_stride = 0;
+    epi.out_rowsum = nullptr;
+    epi.clear_ptr = nullptr;
+    epi.clear_count = 0;
     for (auto &m : epi.more_out) m = nullptr;
     epi.qpA_dev = nullptr;
     epi.sA = qparams[0].scale;

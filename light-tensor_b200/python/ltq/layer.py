@@ -56,6 +56,19 @@ class LayerHandle:
                                       out.data_ptr(), self._stream()))
         return out
 
+    def set_rowsum_output(self, rowsum):
+        """int32 CUDA tensor [M] (or None): later uint8-output forwards add each output row's byte sum to it, which is the
+        ``asum`` the next layer wants.  Clear it before each forward (``rowsum.zero_()`` on the same stream)."""
+        self._rowsum = rowsum
+        check(lib().ltq_layer_set_rowsum_output(self._h, None if rowsum is None else rowsum.data_ptr()))
+
+    def set_clear_on_forward(self, array):
+        """int32 CUDA tensor (or None) that every later forward of this layer clears, ordered after everything in front
+        of it in the stream: the row-sum array of another layer of a chain whose consumer has already run."""
+        self._clear = array
+        check(lib().ltq_layer_set_clear_on_forward(self._h, None if array is None else array.data_ptr(),
+                                                   0 if array is None else array.numel()))
+
     def forward_scatter(self, x, dest_ptrs, ld_out, col_offset, out_mode=OUT_U8, flags=0, asum=None, qp_in_dev=None):
         """Like forward, but element (i, j) goes to ``dest_ptrs[d] + (i * ld_out + col_offset + j) * itemsize`` for
         every d.  dest_ptrs are raw device addresses (this GPU's buffer first, then peers' mapped buffers)."""

@@ -270,3 +270,93 @@ def test_back_to_back_tensor_core_layers_respect_their_inputs(cuda, oracle, M):
                                         relu=(li < 2))
         np.testing.assert_array_equal(outs[i].cpu().numpy(), a, err_msg=f"iteration {i}")
     layers[0].check()
+
+
+@pytest.mark.parametrize("path,shape", [
+    ("simt", (33, 48, 100)), ("tc", (200, 272, 256)), ("tc", (64, 512, 784)), ("tcpair", (300, 720, 128)),
+    ("tcpair", (2000, 2160, 64)), ("skinny", (5, 160, 256)), ("skinny", (16, 1000, 1024)),
+])
+def test_rowsum_output_equals_the_row_sums_of_the_uint8_result(cuda, path, shape):
+    """ltq_layer_set_rowsum_output: the epilogue adds each output row's byte sum to a caller-cleared array, on every
+    kernel path; float output leaves the array alone; a chain that uses it instead of the row-sum pass gives the same
+    bytes."""
+    import ltq
+    M, N, K = shape
+    force = {"simt": ltq.FLAG_FORCE_SIMT, "tc": ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_SINGLE,
+             "tcpair": ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR, "skinny": ltq.FLAG_FORCE_SKINNY}[path]
+    g = cuda.Generator(device="cuda").manual_seed(M + N + K)
+    x = cuda.randint(0, 256, (M, K), dtype=cuda.uint8, device="cuda", generator=g)
+    w = cuda.randint(0, 256, (N, K), dtype=cuda.uint8, device="cuda", generator=g)
+    h = ltq.LayerHandle(0, K, N)
+    h.set_weights(w)
+    h.set_qparams(ltq.QParams(0.02, 128), ltq.QParams(0.005, 127), ltq.QParams(0.5, 20))
+    sums = cuda.zeros(M, dtype=cuda.int32, device="cuda")
+    plain = h.forward(x, ltq.OUT_U8, force | ltq.FLAG_RELU)
+    h.set_rowsum_output(sums)
+    y = h.forward(x, ltq.OUT_U8, force | ltq.FLAG_RELU)
+    assert cuda.equal(y, plain)
+    assert cuda.equal(sums, y.to(cuda.int32).sum(1).to(cuda.int32))
+    h.forward(x, ltq.OUT_U8, force | ltq.FLAG_RELU)                       # accumulates: the caller clears
+    assert cuda.equal(sums, 2 * y.to(cuda.int32).sum(1).to(cuda.int32))
+    sums.zero_()
+    h.forward(x, ltq.OUT_F32, force)                                      # other output modes leave it alone
+    assert int(sums.abs().sum()) == 0
+    h.set_rowsum_output(None)
+    h.forward(x, ltq.OUT_U8, force)
+    assert int(sums.abs().sum()) == 0
+    # a second layer fed with (y, sums) equals the same layer computing the sums itself
+    h.set_rowsum_output(sums)
+    y = h.forward(x, ltq.OUT_U8, force | ltq.FLAG_RELU)
+    w2 = cuda.randint(0, 256, (64, N), dtype=cuda.uint8, device="cuda", generator=g)
+    h2 = ltq.LayerHandle(0, N, 64)
+    h2.set_weights(w2)
+    h2.set_qparams(ltq.QParams(0.5, 20), ltq.QParams(0.01, 100), ltq.QParams(1.0, 0))
+    assert cuda.equal(h2.forward(y, ltq.OUT_I32, 0, asum=sums), h2.forward(y, ltq.OUT_I32, 0))
+
+
+@pytest.mark.parametrize("M", [64, 12])
+def test_chain_with_epilogue_row_sums_and_clear_hooks(cuda, oracle, M):
+    """Three layers chained without any sum pass or clearing launch in between: layers 1 and 2 emit the row sums of their
+    outputs, layer 3 clears the first array and layer 1 (of the next batch) the second.  Several batches back to back
+    without synchronisation must each give the oracle's bytes."""
+    import ltq
+    rng = np.random.default_rng(77 + M)
+    dims = [256, 512, 384, 40]
+    ws = [rng.integers(0, 256, (dims[i + 1], dims[i]), dtype=np.uint8) for i in range(3)]
+    rows = [(0.02, 128), (0.004, 127), (2.5, 9), (0.003, 130), (30.0, 60), (0.005, 100), (300.0, 128)]
+    q_act = [ltq_qp(rows[0]), ltq_qp(rows[2]), ltq_qp(rows[4]), ltq_qp(rows[6])]
+    q_w = [ltq_qp(rows[1]), ltq_qp(rows[3]), ltq_qp(rows[5])]
+    layers = []
+    for i in range(3):
+        h = ltq.LayerHandle(0, dims[i], dims[i + 1])
+        h.set_weights(cuda.from_numpy(ws[i]).cuda())
+        h.set_qparams(q_act[i], q_w[i], q_act[i + 1])
+        layers.append(h)
+    sums = cuda.zeros((2, M), dtype=cuda.int32, device="cuda")
+    layers[0].set_rowsum_output(sums[0])
+    layers[1].set_rowsum_output(sums[1])
+    layers[2].set_clear_on_forward(sums[0])
+    layers[0].set_clear_on_forward(sums[1])
+    reps = 6
+    xs = [rng.integers(0, 256, (M, dims[0]), dtype=np.uint8) for _ in range(reps)]
+    xs_dev = [cuda.from_numpy(x).cuda() for x in xs]
+    h1 = cuda.empty((M, dims[1]), dtype=cuda.uint8, device="cuda")
+    h2 = cuda.empty((M, dims[2]), dtype=cuda.uint8, device="cuda")
+    outs = [cuda.empty((M, dims[3]), dtype=cuda.uint8, device="cuda") for _ in range(reps)]
+    cuda.cuda.synchronize()
+    for i in range(reps):
+        layers[0].forward(xs_dev[i], ltq.OUT_U8, ltq.FLAG_RELU, out=h1)
+        layers[1].forward(h1, ltq.OUT_U8, ltq.FLAG_RELU, asum=sums[0], out=h2)
+        layers[2].forward(h2, ltq.OUT_U8, 0, asum=sums[1], out=outs[i])
+    cuda.cuda.synchronize()
+    o_act = [qp_of(oracle, rows[0]), qp_of(oracle, rows[2]), qp_of(oracle, rows[4]), qp_of(oracle, rows[6])]
+    o_w = [qp_of(oracle, rows[1]), qp_of(oracle, rows[3]), qp_of(oracle, rows[5])]
+    for i in range(reps):
+        a = xs[i]
+        for li in range(3):
+            acc = oracle.port.acc_i32(a, ws[li], M, dims[li + 1], dims[li], o_act[li].zero_point, o_w[li].zero_point)
+            a = oracle.port.epilogue_u8(acc, o_act[li].scale, o_w[li].scale, o_act[li + 1].scale, o_act[li + 1].zero_point,
+                                        relu=(li < 2))
+        np.testing.assert_array_equal(outs[i].cpu().numpy(), a, err_msg=f"batch {i}")
+    with pytest.raises(ltq.LtqError):
+        layers[0].set_clear_on_forward(sums[0])      # its own accumulation target
