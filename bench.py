@@ -470,11 +470,14 @@ def run_mlp_block(args):
     if args.shard == "rows":
         hq = torch.empty((M, N1), dtype=torch.uint8, device=dev)
         y = torch.empty((M, N2), dtype=torch.float32, device=dev)
+        hsum = torch.zeros(M, dtype=torch.int32, device=dev)   # row sums of hq, left behind by layer 1's epilogue
+        l1.layer.set_rowsum_output(hsum)
 
         def step(i):
+            hsum.zero_()
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
             l1.layer.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=hq)
-            l2.layer.forward(hq, ltq.OUT_F32, 0, out=y)
+            l2.layer.forward(hq, ltq.OUT_F32, 0, asum=hsum, out=y)
     elif args.shard == "cols_fused":
         def step(i):
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
