@@ -33,26 +33,38 @@ ExceptionInfo::ExceptionInfo(const char *msg, const char *file, const char *func
 
 static size_t dtype_size(dtype t) { return t == UINT8 ? 1 : 4; }
 
-struct Tensor::Impl {
+// Device or host bytes shared by every handle and view that refers to them (the role of the reference-counted
+// TensorImpl storage in l-ten: `output = output.reshape(...)` must keep the bytes alive).
+struct Storage {
     void *data = nullptr;
     bool own = true;
-    uint64_t dims[MAX_DIMS] = {0};
-    int ndims = 0;
-    uint64_t numels = 0;
-    TensorOps ops;
-    ~Impl()
+    device dev = CPU;
+    int index = 0;
+    ~Storage()
     {
         if (!own || !data) return;
-        if (ops.device_type == GPU) {
+        if (dev == GPU) {
             int prev = 0;
             cudaGetDevice(&prev);
-            cudaSetDevice(ops.device_index);
+            cudaSetDevice(index);
             cudaFree(data);
             cudaSetDevice(prev);
         } else {
             free(data);
         }
     }
+};
+
+struct Tensor::Impl {
+    std::shared_ptr<Storage> storage;
+    void *data = nullptr;  // == storage->data
+    uint64_t dims[MAX_DIMS] = {0};
+    int ndims = 0;
+    uint64_t numels = 0;
+    TensorOps ops;
+    // Optional side-car left by the quantized layer that produced this tensor: int32 sums over the last dimension, one
+    // per row (numels / dims[ndims-1] of them).  The next quantized layer uses them instead of a sum pass.
+    std::shared_ptr<Tensor> row_sums;
 };
 
 void *Tensor::get_data_ptr() const { return impl_ ? impl_->data : nullptr; }
@@ -62,6 +74,14 @@ int Tensor::get_ndims() const { return impl_ ? impl_->ndims : 0; }
 dtype Tensor::get_data_type() const { return impl_->ops.data_type; }
 device Tensor::get_device() const { return impl_->ops.device_type; }
 int Tensor::get_device_index() const { return impl_->ops.device_index; }
+
+void Tensor::attach_row_sums(const Tensor &sums)
+{
+    if (!impl_) LTEN_ERR("Invalid argument");
+    impl_->row_sums = sums.defined() ? std::make_shared<Tensor>(sums) : nullptr;
+}
+
+const Tensor *Tensor::row_sums() const { return impl_ && impl_->row_sums ? impl_->row_sums.get() : nullptr; }
 
 Tensor AllocateTensor(const uint64_t *dims_ptr, int ndims, TensorOps *options_ptr)
 {
@@ -77,17 +97,21 @@ Tensor AllocateTensor(const uint64_t *dims_ptr, int ndims, TensorOps *options_pt
         im.numels *= dims_ptr[i];
     }
     const size_t bytes = im.numels * dtype_size(im.ops.data_type);
+    im.storage = std::make_shared<Storage>();
+    im.storage->dev = im.ops.device_type;
+    im.storage->index = im.ops.device_index;
     if (im.ops.device_type == GPU) {
         int prev = 0;
         LTEN_CUDA(cudaGetDevice(&prev));
         LTEN_CUDA(cudaSetDevice(im.ops.device_index));
-        LTEN_CUDA(cudaMalloc(&im.data, bytes ? bytes : 1));
-        LTEN_CUDA(cudaMemset(im.data, 0, bytes));
+        LTEN_CUDA(cudaMalloc(&im.storage->data, bytes ? bytes : 1));
+        LTEN_CUDA(cudaMemset(im.storage->data, 0, bytes));
         LTEN_CUDA(cudaSetDevice(prev));
     } else {
-        im.data = calloc(bytes ? bytes : 1, 1);
-        if (!im.data) LTEN_ERR("out of memory");
+        im.storage->data = calloc(bytes ? bytes : 1, 1);
+        if (!im.storage->data) LTEN_ERR("out of memory");
     }
+    im.data = im.storage->data;
     return t;
 }
 
@@ -109,8 +133,12 @@ Tensor TensorFromBuffer(const uint64_t *dims_ptr, int ndims, void *data_ptr, boo
         im.dims[i] = dims_ptr[i];
         im.numels *= dims_ptr[i];
     }
+    im.storage = std::make_shared<Storage>();
+    im.storage->data = data_ptr;
+    im.storage->own = own_memory;
+    im.storage->dev = im.ops.device_type;
+    im.storage->index = im.ops.device_index;
     im.data = data_ptr;
-    im.own = own_memory;
     return t;
 }
 
@@ -143,11 +171,12 @@ Tensor Tensor::reshape(const std::initializer_list<uint64_t> &dims) const
     for (uint64_t d : dims) n *= d;
     if (!impl_ || n != impl_->numels) LTEN_ERR("Invalid reshape dimensions");
     Tensor r = *this;
-    r.impl_ = std::make_shared<Impl>(*impl_);
-    r.impl_->own = false;  // a view; the original handle keeps the storage alive for as long as the caller holds it
+    r.impl_ = std::make_shared<Impl>(*impl_);  // a view: shares the storage, which lives as long as any handle does
     r.impl_->ndims = (int)dims.size();
     int i = 0;
     for (uint64_t d : dims) r.impl_->dims[i++] = d;
+    // sums over the last dimension stay valid only while the last dimension does
+    if (r.impl_->dims[r.impl_->ndims - 1] != impl_->dims[impl_->ndims - 1]) r.impl_->row_sums.reset();
     return r;
 }
 
@@ -255,9 +284,23 @@ Tensor FullyConnected_q::forward(Tensor &input)
 
     uint64_t rows = 1;  // every leading dimension folds into M: parameters are per tensor, rows are independent
     for (int d = 0; d < ndims - 1; d++) rows *= dims[d];
+    // Row sums: taken from the tensor if the layer that produced it left them, and left on the result for the next layer
+    // (uint8 output only), so that a chain of quantized layers runs without a sum pass in between.
+    const Tensor *in_sums = input.row_sums();
+    const int32_t *asum = in_sums && in_sums->get_numels() == rows ? static_cast<const int32_t *>(in_sums->get_data_ptr()) : nullptr;
+    Tensor out_sums;
+    if (out_mode_ == LTQ_OUT_U8) {
+        TensorOps so;
+        so.data_type = INT32;
+        so.device_type = GPU;
+        so.device_index = input.get_device_index();
+        out_sums = AllocateTensor({rows}, &so);  // zero-filled
+    }
+    LTQ_CALL(ltq_layer_set_rowsum_output(handle_, out_sums.defined() ? static_cast<int32_t *>(out_sums.get_data_ptr()) : nullptr));
     LTQ_CALL(ltq_layer_set_qparams(handle_, &qparams_in_, &qparams_wt_, &qparams_out_));
-    LTQ_CALL(ltq_layer_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), nullptr, rows, nullptr,
-                               out_mode_, flags_, result.get_data_ptr(), nullptr));
+    LTQ_CALL(ltq_layer_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), asum, rows, nullptr, out_mode_,
+                               flags_, result.get_data_ptr(), nullptr));
+    if (out_sums.defined()) result.attach_row_sums(out_sums);
     return result;
 }
 

@@ -63,6 +63,11 @@ public:
     Tensor to(device target_device, int target_device_index = 0) const;
     Tensor reshape(const std::initializer_list<uint64_t> &dims) const;
     bool defined() const { return impl_ != nullptr; }
+    // Additive: int32 sums over the last dimension (one per row) that a quantized layer leaves on its uint8 output, and
+    // the next quantized layer picks up instead of running a sum pass.  A reshape that changes the last dimension
+    // drops them; writing into the tensor's bytes by hand does not (detach them with attach_row_sums(Tensor())).
+    void attach_row_sums(const Tensor &sums);
+    const Tensor *row_sums() const;
 
 private:
     struct Impl;

@@ -181,8 +181,9 @@ int main()
     oracle_conv2d_q(xq.data(), B, 1, IMG, IMG, wcq.data(), nullptr, 0, CO, KH, KH, 0, 0, 1, 1, &oq_x, &oq_wc, &oq_a1, want1.data());
     CHECK(got1 == want1, "Conv2d_q output vs oracle");
 
-    Tensor flat = y1.reshape({(uint64_t)B, 1, 1, (uint64_t)FLAT});
-    Tensor y2 = fc1->forward(flat);
+    y1 = y1.reshape({(uint64_t)B, 1, 1, (uint64_t)FLAT});  // as QNet::forward does: the view must keep the bytes alive
+    Tensor y2 = fc1->forward(y1);
+    CHECK(y2.row_sums() != nullptr && y2.row_sums()->get_numels() == (uint64_t)B, "fc1 leaves row sums for fc2");
     std::vector<uint8_t> got2 = download<uint8_t>(y2), want2((size_t)B * H1);
     {
         std::vector<int32_t> ws(B + H1);
