@@ -171,7 +171,9 @@ int ltq_layer_set_qparams(ltq_layer *layer, const ltq_qparams *qp_in, const ltq_
  *             without a host round trip); NULL = use the value set by ltq_layer_set_qparams
  *   out_dev   uint8 / float / int32 [M,N] by out_mode
  * Kernel choice: M <= 16 with K % 128 == 0 -> weight-streaming kernel; otherwise the tcgen05 kernel
- * when K % 16 == 0; else the generic kernel. */
+ * when K % 16 == 0; else the generic kernel.
+ * Stream capture: with asum_dev == NULL the layer's own workspace grows (cudaMalloc) the first time a larger M is seen;
+ * pass asum_dev, or run the largest M once before capturing. */
 int ltq_layer_forward(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
                       const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *out_dev, void *stream);
 
