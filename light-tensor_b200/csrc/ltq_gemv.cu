@@ -303,21 +303,39 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * as);  // accumulator buffer may be overwritten
-                // (all lanes run the loop: the optional row sums below are warp-wide reductions)
+                const bool plain = epi.n_more == 0 && epi.col_block == 0 && !(OUT == 0 && epi.out_rowsum);
+                if (plain) {
+                    // one dense destination: the common case, kept free of the general path's loops
+                    if (valid) {
 #pragma unroll
-                for (int m = 0; m < XROWS; m++) {
-                    if ((uint32_t)m < M) {
-                        const int32_t a = epilogue_acc(v[m], rt[m], ct, relu);
-                        OutT r;
-                        if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
-                        else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
-                        else r = (OutT)a;
-                        if (valid)
-                            for (int d = -1; d < epi.n_more; d++)
-                                (d < 0 ? o : static_cast<OutT *>(epi.more_out[d]))[epilogue_offset(epi, (uint64_t)m, n, ldc)] = r;
-                        if (OUT == 0 && epi.out_rowsum) {  // token m: this warp's 32 outputs add up first
-                            const uint32_t t32 = __reduce_add_sync(0xFFFFFFFFu, valid ? (uint32_t)r : 0u);
-                            if (lane == 0 && t32) atomicAdd(&epi.out_rowsum[m], (int32_t)t32);
+                        for (int m = 0; m < XROWS; m++) {
+                            if ((uint32_t)m < M) {
+                                const int32_t a = epilogue_acc(v[m], rt[m], ct, relu);
+                                OutT r;
+                                if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
+                                else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
+                                else r = (OutT)a;
+                                o[(size_t)m * ldc + n] = r;
+                            }
+                        }
+                    }
+                } else {
+                    // several destinations, column-blocked output, row sums (warp-wide reductions: all lanes run the loop)
+#pragma unroll
+                    for (int m = 0; m < XROWS; m++) {
+                        if ((uint32_t)m < M) {
+                            const int32_t a = epilogue_acc(v[m], rt[m], ct, relu);
+                            OutT r;
+                            if (OUT == 0) r = (OutT)epilogue_u8(a, c, sat);
+                            else if (OUT == 1) r = (OutT)epilogue_f32(a, c);
+                            else r = (OutT)a;
+                            if (valid)
+                                for (int d = -1; d < epi.n_more; d++)
+                                    (d < 0 ? o : static_cast<OutT *>(epi.more_out[d]))[epilogue_offset(epi, (uint64_t)m, n, ldc)] = r;
+                            if (OUT == 0 && epi.out_rowsum) {  // token m: this warp's 32 outputs add up first
+                                const uint32_t t32 = __reduce_add_sync(0xFFFFFFFFu, valid ? (uint32_t)r : 0u);
+                                if (lane == 0 && t32) atomicAdd(&epi.out_rowsum[m], (int32_t)t32);
+                            }
                         }
                     }
                 }
