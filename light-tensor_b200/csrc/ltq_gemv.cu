@@ -14,18 +14,20 @@
 //    L consecutive K-major tiles [R rows][128 B] under the 128-byte swizzle, exactly the layout the MMA's shared-memory
 //    descriptors read, while each row contributes L x 128 contiguous bytes of DRAM per box.  Every ring stage holds a
 //    weight box and the matching box of the activation block (rows beyond M are zero-filled by TMA; the activations
-//    come out of L2, every CTA reads the same ones).  Nothing but the ring lives in shared memory, which keeps a CTA
-//    under half an SM: the CTA of the NEXT launch moves in beside it (see below);
+//    come out of L2, every CTA reads the same ones).  Nothing but the ring lives in shared memory: one CTA per SM with
+//    4-6 stages of 30-45 KB.  (A ring of half an SM, so that the next launch's CTA fits beside this one, was measured
+//    too: its hand-over is smoother but its stream is slower, 10.5 against 9.3 us on 45 MB of weights);
 //  * four epilogue warps read the accumulators with tcgen05.ld (thread = weight row, register = token), apply the fused
 //    epilogue (l-ten/math_fns.cpp:1469-1474) and store; for every token the 32 lanes of a warp write 32 consecutive
 //    outputs.  Accumulators are double buffered in TMEM.
 //
 //  * with `early_weights` the kernel is launched as a programmatic dependent of the kernel before it in the stream.
-//    Every CTA releases its dependents at once, so the next launch's CTAs become resident on the same SMs while this
-//    one is still streaming, and fill their rings with WEIGHTS straight away (the caller guarantees that nothing in
-//    flight writes them).  Everything that can depend on the previous kernel - the activation boxes, the activation
-//    row sums, every store - comes after griddepcontrol.wait.  In a chain of such launches the start-up (barrier
-//    set-up, first DRAM round trip) and the tail (last MMAs, epilogue) of neighbouring launches overlap.
+//    Every CTA releases its dependents at once, so the next launch's CTAs are scheduled the moment an SM's shared
+//    memory frees up, and fill their rings with WEIGHTS straight away (the caller guarantees that nothing in flight
+//    writes them) and ask the boxes behind the ring into L2.  Everything that can depend on the previous kernel - the
+//    activation boxes, the activation row sums, every store - comes after griddepcontrol.wait.  In a chain of such
+//    launches the start-up (barrier set-up, first DRAM round trip) of one launch overlaps the tail (last MMAs,
+//    epilogue, stragglers) of the one before.
 //
 // Every mbarrier wait is bounded (2 s by %globaltimer); on expiry a code is left in the device status word.
 #include <cuda.h>
@@ -45,18 +47,22 @@ constexpr int LINE = 128;                  // bytes of K per line (one swizzle a
 constexpr int XROWS = 16;                  // activation rows as seen by the MMA (N = 16), TMEM columns per accumulator
 constexpr int TILE_M = 128;                // MMA M: weight rows per tile (upper bound)
 constexpr int MAX_STAGES = 16;
-constexpr int SMEM_HALF = 112 * 1024;      // chained launches: two CTAs (this launch's and the next one's) share an SM
-constexpr int SMEM_FULL = 220 * 1024;      // a launch on its own: one CTA per SM with as deep a ring as fits
+constexpr int SMEM_FULL = 220 * 1024;      // one CTA per SM with as deep a ring as fits
 constexpr int OVERREAD = TILE_M * LINE;    // an MMA reads 128 rows from a tile's start whatever the band holds
 constexpr int NACC = 4;                    // independent partial accumulators per tile (summed in the epilogue)
 constexpr uint32_t TMEM_COLS = 2 * NACC * XROWS;  // two buffers of NACC accumulators of 16 columns = 128
-constexpr uint32_t PREFETCH_AHEAD = 16;    // boxes requested into L2 beyond the ring (~320 KB per CTA, ~47 MB per GPU)
+constexpr uint32_t PREFETCH_AHEAD = 6;     // boxes requested into L2 beyond the ring (~170-240 KB per CTA, 25-35 MB per
+                                           // GPU; 2-3 times as much already costs 10-20 % of the streaming rate)
+constexpr uint64_t BIG_WEIGHTS = 128ull << 20;  // weight bytes from which a launch is mostly steady-state streaming
+constexpr uint32_t BOX_SMALL_W = 40 * 1024;     // target bytes of a weight box below / from BIG_WEIGHTS
+constexpr uint32_t BOX_BIG_W = 32 * 1024;
 
 struct Plan {
     uint32_t grid, tiles_per_cta, tiles;   // tiles = grid * tiles_per_cta
     uint32_t oct_lo, oct_hi;               // a tile holds oct_lo or oct_hi groups of 8 rows (oct_hi <= 16)
     uint32_t lines;                        // lines per stage (per TMA box)
     uint32_t stages;
+    uint32_t prefetch;                     // boxes requested into L2 beyond the ring
     uint32_t w_stage, x_stage;             // bytes per stage: lines * oct_hi * 8 * 128 and lines * (8 or 16) * 128
     uint32_t slack;                        // bytes kept free behind the activation boxes for the MMA's over-reads
     size_t smem;
@@ -74,11 +80,17 @@ Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms, size_t smem_limit)
     p.oct_hi = (uint32_t)((octs + p.tiles - 1) / p.tiles);
     const uint32_t klines = (uint32_t)(K / LINE);
     const uint32_t line_bytes = p.oct_hi * 8 * LINE;
-    uint32_t L = (20u * 1024u) / line_bytes;  // boxes of ~20 KB: smaller tensor copies pay a fixed per-copy cost
+    // Box size, measured on B200 (M = 16, fp32 out, chained launches over distinct weights): every row should give
+    // DRAM at least 256 contiguous bytes per box (128-byte pieces at a pitch of K stream at ~5 TB/s, 256 and more at
+    // ~6 TB/s), and a weight matrix of a few tens of MB, whose launch is mostly start-up and hand-over, does best with
+    // boxes of ~40 KB, while a large one prefers ~30 KB and the deeper ring that leaves room for.
+    const uint32_t box_target = N * K < BIG_WEIGHTS ? BOX_SMALL_W : BOX_BIG_W;
+    uint32_t L = box_target / line_bytes;
     L = L < 1 ? 1 : (L > 4 ? 4 : L);
     if (L > klines) L = klines;
     p.lines = L;
     p.w_stage = L * line_bytes;
+    p.prefetch = PREFETCH_AHEAD;
     // Activation boxes hold 8 rows per line when M <= 8 (the MMA still reads 16 rows per line tile; rows 8..15 are then
     // the next line's rows, whose products land in TMEM columns that are never stored).
     p.x_stage = L * (uint32_t)(M > 8 ? 16 : 8) * LINE;
@@ -109,8 +121,8 @@ template <int OUT>
 __global__ void __launch_bounds__(THREADS, 2)
 gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w_lo,
             const __grid_constant__ CUtensorMap map_w_hi, uint32_t M, uint32_t N, uint32_t K, uint32_t tiles_per_cta,
-            uint32_t tiles, uint32_t oct_lo, uint32_t lines, uint32_t stages, uint32_t w_stage, uint32_t x_stage,
-            uint32_t slack, Epilogue epi, void *__restrict__ out, uint32_t *status)
+            uint32_t tiles, uint32_t oct_lo, uint32_t lines, uint32_t stages, uint32_t prefetch, uint32_t w_stage,
+            uint32_t x_stage, uint32_t slack, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
     // By every thread, first thing: the CTA counts as released once all of them have said so, and the next launch's CTAs
     // should move in (and start fetching their weights) as early as they can.
@@ -194,7 +206,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
         // are requested into L2, so that HBM keeps streaming through the hand-over between two launches (the wait for
         // the previous kernel, the first activation fetch, the previous kernel's last MMAs and epilogue) and the ring
         // later refills from L2.
-        for (uint32_t i = 0; i < PREFETCH_AHEAD && pf.t < t_end; i++) {
+        for (uint32_t i = 0; i < prefetch && pf.t < t_end; i++) {
             tma_prefetch_3d(pf.map, 0, (int32_t)pf.row0, (int32_t)(pf.kc * lines));
             advance(pf);
         }
@@ -393,7 +405,7 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
     e = cudaLaunchKernelEx(&cfg, gemv_kernel<OUT>, *reinterpret_cast<const CUtensorMap *>(mx.opaque),
                            *reinterpret_cast<const CUtensorMap *>(lo.opaque), *reinterpret_cast<const CUtensorMap *>(hi.opaque),
                            (uint32_t)M, (uint32_t)N, (uint32_t)K, p.tiles_per_cta, p.tiles, p.oct_lo, p.lines, p.stages,
-                           p.w_stage, p.x_stage, p.slack, epi, out, status);
+                           p.prefetch, p.w_stage, p.x_stage, p.slack, epi, out, status);
     count_launch();
     return e;
 }
@@ -403,15 +415,13 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
 bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W)
 {
     return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 128 && K % 128 == 0 && K < (1ull << 31) &&
-           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148, SMEM_HALF).ok;
+           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148, SMEM_FULL).ok;
 }
 
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
                         void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache, bool early_weights)
 {
-    // A launch that will be followed closely by another one of its kind keeps to half an SM so that the two overlap;
-    // one that stands alone streams faster with a deeper ring.
-    const Plan p = make_plan(M, N, K, sms, early_weights ? SMEM_HALF : SMEM_FULL);
+    const Plan p = make_plan(M, N, K, sms, SMEM_FULL);
     if (!p.ok) return cudaErrorInvalidConfiguration;
     TcOperandMap mx;
     GemvWeightMaps local;
