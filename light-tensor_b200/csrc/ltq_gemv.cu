@@ -131,7 +131,7 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
     const uint32_t raw0 = smem_u32(smem_raw);
     const uint32_t ring = (raw0 + 1023u) & ~1023u;                       // [stages][lines][rows][128 B]
     const uint32_t xs = ring + stages * w_stage;                         // [stages][lines][8 or 16][128 B]
-    const uint32_t xrows = M > 8 ? 16u : 8u;                             // rows per line tile of an activation box
+    const uint32_t xrows = x_stage / (lines * LINE);                             // rows per line tile of an activation box
     uint8_t *after = smem_raw + (xs - raw0) + stages * x_stage + slack;
     uint64_t *bars = reinterpret_cast<uint64_t *>(after);                // full[S] empty[S] tfull[2] tempty[2]
     uint32_t *misc = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 4);  // [0] tmem base, [1] abort flag
@@ -426,7 +426,7 @@ cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t
     TcOperandMap mx;
     GemvWeightMaps local;
     // activations: a box is [lines][8 or 16 rows][128 B]; rows >= M are out of bounds -> zeros
-    if (tc_make_map_lines(&mx, x, M, K, M > 8 ? 16 : 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
+    if (tc_make_map_lines(&mx, x, M, K, (int)(p.x_stage / (p.lines * LINE)), (int)p.lines) != 0) return cudaErrorInvalidValue;
     GemvWeightMaps *wm = cache ? cache : &local;
     if (!wm->lo.matches(W, N, K, (int)p.oct_lo * 8, (int)p.lines)) {
         if (tc_make_map_lines(&wm->lo, W, N, K, (int)p.oct_lo * 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
