@@ -69,6 +69,11 @@ int ltq_version(void);
 const char *ltq_last_error(void);
 /* Number of kernels this library has launched since load (all threads). */
 uint64_t ltq_kernel_launches(void);
+/* Name of the GEMM kernel the calling thread launched last, with its template arguments (tile width, output type), e.g.
+ * "gemm_tc_pair_kernel<256,u8>"; "" before the first one.  For tests, profiling and benchmark records: it names what
+ * the shape-based dispatch of ltq_layer_forward / ltq_quantized_matmul* actually chose.  No counterpart in the
+ * reference. */
+const char *ltq_last_kernel(void);
 
 /* ---- quantisation helpers (replace l-ten/utils.h:23-27 for device data) -------------------------------------- */
 
@@ -139,11 +144,17 @@ int ltq_quantized_matmul_ex(int transpose_A, int transpose_B, uint64_t M, uint64
  * allocating routine.  The first call on each device looks up the array's device address; make that first call
  * outside any stream capture.  All calls on a device share the scratch: it holds the previous call's sums on entry
  * (they are overwritten or cleared before use), and two calls whose kernels overlap on the GPU race on it -- issue
- * them on one stream, or otherwise order them.  Output C is identical to ltq_quantized_matmul's. */
+ * them on one stream, or otherwise order them.  Output C is identical to ltq_quantized_matmul's, and so is the kernel
+ * choice (weight-streaming, tcgen05 single CTA or CTA pair, dp4a).
+ * Failure path: the bounded waits inside these kernels report into a status word that also lives in the library
+ * image, not into the one ltq_device_check reads (creating that one allocates).  ltq_static_check reads and clears it
+ * without allocating: LTQ_OK, or LTQ_ERR_DEVICE_TIMEOUT when a wait ran out since the last check (C is then
+ * incomplete).  It synchronises `stream`. */
 #define LTQ_STATIC_WS_INTS (256 * 1024)
 int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
                                 const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, uint8_t *C_dev,
                                 const ltq_qparams *qparams, const int32_t *bias_dev, int device, void *stream);
+int ltq_static_check(int device, void *stream);
 
 /* ---- layer handle: what FullyConnected_q (l-ten/layers.h:69-106) keeps between calls ------------------------- */
 
@@ -271,6 +282,8 @@ int ltq_device_check(int device, void *stream);
  * the kernel returns normally; the next ltq_device_check / ltq_layer_check then reports LTQ_ERR_DEVICE_TIMEOUT and
  * clears it.  Nothing hangs or faults: this is how the bounded waits inside the GEMM kernels are exercised. */
 int ltq_selftest_bounded_wait(int device, uint32_t limit_us, void *stream);
+/* The same probe reporting into the status word of the allocation-free entry points (read by ltq_static_check). */
+int ltq_selftest_bounded_wait_static(int device, uint32_t limit_us, void *stream);
 
 #ifdef __cplusplus
 }

@@ -18,6 +18,15 @@ namespace ltq {
 std::atomic<uint64_t> g_launches{0};
 static thread_local char g_err[512] = "";
 
+static thread_local char g_kernel[96] = "";
+void note_kernel(const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_kernel, sizeof g_kernel, fmt, ap);
+    va_end(ap);
+}
+
 void set_error(const char *fmt, ...)
 {
     va_list ap;
@@ -36,11 +45,9 @@ namespace {
 
 constexpr int MAX_DEVICES = 64;
 
-struct DeviceState {
-    int sms = 0;
-    uint32_t *status = nullptr;  // device word: 0, or the code of the first bounded wait that expired
-};
-DeviceState g_dev[MAX_DEVICES];
+// sms; status = device word: 0, or the code of the first bounded wait that expired
+using DeviceState = GemmDevice;
+DeviceState g_dev[MAX_DEVICES] = {};
 std::mutex g_dev_mu;
 
 // Per-device constants and the status word, created on first use with that device current.
@@ -66,42 +73,12 @@ int device_state(int device, DeviceState **out)
     return LTQ_OK;
 }
 
-Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *bias, const ltq_qparams &qa,
-                       const ltq_qparams &qb, const ltq_qparams &qc, uint64_t K, int out_mode, unsigned flags)
-{
-    Epilogue e;
-    e.bsum = bsum;
-    e.asum = asum;
-    e.bias = bias;
-    e.row_bias = nullptr;
-    e.ldc = 0;
-    e.n_more = 0;
-    e.staged = 0;
-    e.col_block = 0;
-    e.col_block_stride = 0;
-    e.out_rowsum = nullptr;
-    e.clear_ptr = nullptr;
-    e.clear_count = 0;
-    for (auto &m : e.more_out) m = nullptr;
-    e.qpA_dev = nullptr;
-    e.sA = qa.scale;
-    e.sB = qb.scale;
-    e.sC = qc.scale;
-    e.zA = qa.zero_point;
-    e.zB = qb.zero_point;
-    e.zC = qc.zero_point;
-    e.K = (uint32_t)K;
-    e.out_mode = out_mode;
-    e.flags = flags & (LTQ_FLAG_RELU | LTQ_FLAG_SATURATE);
-    return e;
-}
-
 enum Path { PATH_SIMT, PATH_TC, PATH_SKINNY };
 
 // Kernel choice for the FullyConnected_q layout (A [M,K], B [N,K]).
-int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B, unsigned flags, Path *path)
+int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B, unsigned flags, int sms, Path *path)
 {
-    const bool tc_ok = tc_shape_ok(M, N, K, A, B), sk_ok = gemv_shape_ok(M, N, K, A, B);
+    const bool tc_ok = tc_shape_ok(M, N, K, A, B), sk_ok = gemv_shape_ok(M, N, K, A, B, sms);
     if (flags & LTQ_FLAG_FORCE_SIMT) {
         *path = PATH_SIMT;
     } else if (flags & LTQ_FLAG_FORCE_TC) {
@@ -169,6 +146,7 @@ extern "C" {
 
 int ltq_version(void) { return LTQ_VERSION; }
 const char *ltq_last_error(void) { return ltq::g_err; }
+const char *ltq_last_kernel(void) { return ltq::g_kernel; }
 uint64_t ltq_kernel_launches(void) { return g_launches.load(); }
 
 // ---- helpers ----------------------------------------------------------------------------------------------------------
@@ -263,12 +241,15 @@ int ltq_interleave_column_blocks(const void *gathered_dev, void *out_dev, uint64
     return LTQ_OK;
 }
 
-// ---- GEMM dispatch shared by the stateless call and the layer ------------------------------------------------------
-static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
-                       const Epilogue &epi, void *out, unsigned flags, ltq_layer *layer, cudaStream_t stream)
+}  // extern "C"
+
+// ---- GEMM dispatch shared by the stateless calls and the layer -------------------------------------------------------
+int ltq::run_fc_gemm(const GemmDevice &gd, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
+                     const Epilogue &epi, void *out, unsigned flags, ltq_layer *layer, cudaStream_t stream)
 {
+    const GemmDevice *dev = &gd;
     Path path;
-    int rc = choose_path(M, N, K, A, B, flags, &path);
+    int rc = choose_path(M, N, K, A, B, flags, dev->sms, &path);
     if (rc != LTQ_OK) return rc;
     switch (path) {
         case PATH_SKINNY:
@@ -307,10 +288,14 @@ static int run_fc_gemm(DeviceState *dev, uint64_t M, uint64_t N, uint64_t K, con
             break;
         }
         default:
+            LTQ_REQUIRE(simt_grid_ok(M, N), LTQ_ERR_TOO_LARGE, "M x N = %llu x %llu needs more than 2^31 - 1 tiles of 64 x 64",
+                        (unsigned long long)M, (unsigned long long)N);
             LTQ_CUDA_TRY(launch_gemm_simt(false, true, M, N, K, A, B, epi, out, stream));
     }
     return LTQ_OK;
 }
+
+extern "C" {
 
 int ltq_quantized_matmul_ex(int transpose_A, int transpose_B, uint64_t M, uint64_t N, uint64_t K, uint8_t alpha,
                             const uint8_t *A_dev, const uint8_t *B_dev, uint8_t beta, void *C_dev,
@@ -344,9 +329,11 @@ int ltq_quantized_matmul_ex(int transpose_A, int transpose_B, uint64_t M, uint64
     }
     Epilogue epi = make_epilogue(bsum, asum, bias_dev, qparams[0], qparams[1], qparams[2], K, out_mode, flags);
     if (!tA && tB && K > 0) {
-        rc = run_fc_gemm(dev, M, N, K, A_dev, B_dev, epi, C_dev, flags, nullptr, st);
+        rc = run_fc_gemm(*dev, M, N, K, A_dev, B_dev, epi, C_dev, flags, nullptr, st);
         if (rc != LTQ_OK) return rc;
     } else {
+        LTQ_REQUIRE(simt_grid_ok(M, N), LTQ_ERR_TOO_LARGE, "M x N = %llu x %llu needs more than 2^31 - 1 tiles of 64 x 64",
+                (unsigned long long)M, (unsigned long long)N);
         LTQ_CUDA_TRY(launch_gemm_simt(tA, tB, M, N, K, A_dev, B_dev, epi, C_dev, st));
     }
     // Leave the workspace as the reference does: sums already multiplied by the other operand's -zero_point.
@@ -458,7 +445,7 @@ static int layer_forward_impl(ltq_layer *layer, const uint8_t *x_dev, const int3
     epi.ldc = ld_out;
     epi.n_more = n_dests - 1;
     for (int d = 1; d < n_dests; d++) epi.more_out[d - 1] = static_cast<uint8_t *>(dests[d]) + col_offset * esize;
-    return run_fc_gemm(layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi,
+    return run_fc_gemm(*layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi,
                        static_cast<uint8_t *>(dests[0]) + col_offset * esize, flags, layer, st);
 }
 
@@ -729,7 +716,7 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
                 epi.col_block = (uint32_t)N;
                 epi.col_block_stride = M * N;
             }
-            rc = run_fc_gemm(conv->dev, M, per * N, Kp, conv->w, conv->col + i * N * Kp, epi,
+            rc = run_fc_gemm(*conv->dev, M, per * N, Kp, conv->w, conv->col + i * N * Kp, epi,
                              static_cast<uint8_t *>(out_dev) + (b0 + i) * out_stride, flags, nullptr, st);
             if (rc != LTQ_OK) return rc;
         }

@@ -15,6 +15,9 @@ namespace ltq {
 void set_error(const char *fmt, ...);
 extern std::atomic<uint64_t> g_launches;
 inline void count_launch(uint64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+// Name (with template arguments) of the GEMM kernel the calling thread launched last, for ltq_last_kernel().
+void note_kernel(const char *fmt, ...);
+inline const char *out_mode_name(int out_mode) { return out_mode == LTQ_OUT_U8 ? "u8" : (out_mode == LTQ_OUT_F32 ? "f32" : "i32"); }
 
 #define LTQ_CUDA_TRY(expr)                                                                                   \
     do {                                                                                                     \
@@ -116,6 +119,37 @@ struct Epilogue {
     int32_t *clear_ptr;
     uint32_t clear_count;
 };
+
+// The epilogue of a plain call: one dense [M, N] destination, no chain hooks.  Callers switch further fields on.
+inline Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *bias, const ltq_qparams &qa,
+                              const ltq_qparams &qb, const ltq_qparams &qc, uint64_t K, int out_mode, unsigned flags)
+{
+    Epilogue e;
+    e.bsum = bsum;
+    e.asum = asum;
+    e.bias = bias;
+    e.row_bias = nullptr;
+    e.ldc = 0;
+    e.n_more = 0;
+    e.staged = 0;
+    e.col_block = 0;
+    e.col_block_stride = 0;
+    e.out_rowsum = nullptr;
+    e.clear_ptr = nullptr;
+    e.clear_count = 0;
+    for (auto &m : e.more_out) m = nullptr;
+    e.qpA_dev = nullptr;
+    e.sA = qa.scale;
+    e.sB = qb.scale;
+    e.sC = qc.scale;
+    e.zA = qa.zero_point;
+    e.zB = qb.zero_point;
+    e.zC = qc.zero_point;
+    e.K = (uint32_t)K;
+    e.out_mode = out_mode;
+    e.flags = flags & (LTQ_FLAG_RELU | LTQ_FLAG_SATURATE);
+    return e;
+}
 
 __device__ __forceinline__ void epilogue_housekeeping(const Epilogue &e)
 {
@@ -349,10 +383,31 @@ struct PeerStage {
     }
 };
 
+// ---- GEMM dispatch (ltq_api.cu) -------------------------------------------------------------------------------------
+// What the dispatcher needs to know about the device: its SM count and the word that bounded waits report into.
+struct GemmDevice {
+    int sms;
+    uint32_t *status;
+};
+}  // namespace ltq
+struct ltq_layer;
+namespace ltq {
+// Kernel choice and launch for the FullyConnected_q layout (A [M,K], B [N,K], both K-contiguous): skinny kernel,
+// tcgen05 kernel (single CTA or CTA pair) or the generic dp4a kernel, by shape and LTQ_FLAG_FORCE_*.  `layer`
+// (optional) caches the weight tensor maps.  Allocates nothing.
+int run_fc_gemm(const GemmDevice &dev, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
+                const Epilogue &epi, void *out, unsigned flags, ltq_layer *layer, cudaStream_t stream);
+
 // ---- kernel launchers implemented in the other translation units --------------------------------------------------
 // Generic dp4a tile kernel: any M, N, K and any transpose combination.
 cudaError_t launch_gemm_simt(bool tA, bool tB, uint64_t M, uint64_t N, uint64_t K, const uint8_t *A, const uint8_t *B,
                              const Epilogue &epi, void *out, cudaStream_t stream);
+// Its 64 x 64 tiles are numbered along grid.x: at most 2^31 - 1 of them.
+inline bool simt_grid_ok(uint64_t M, uint64_t N)
+{
+    const uint64_t gx = (M + 63) / 64, gy = (N + 63) / 64;
+    return gx <= 0x7FFFFFFFull && gy <= 0x7FFFFFFFull && gx * gy <= 0x7FFFFFFFull;
+}
 
 // Operand sums. rows x cols uint8, contiguous along cols: sums[r] = sum_c m[r*cols + c].
 cudaError_t launch_row_sums(const uint8_t *m, uint64_t rows, uint64_t cols, int32_t *sums, cudaStream_t stream);

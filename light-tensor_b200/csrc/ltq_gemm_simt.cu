@@ -41,12 +41,13 @@ __device__ __forceinline__ void stage(uint32_t (*dst)[LDW], const uint8_t *__res
 
 __global__ void __launch_bounds__(256) gemm_simt_kernel(bool a_kc, bool b_kc, uint64_t M, uint64_t N, uint64_t K,
                                                         const uint8_t *__restrict__ A, const uint8_t *__restrict__ B,
-                                                        Epilogue epi, void *__restrict__ out)
+                                                        Epilogue epi, void *__restrict__ out, uint32_t tiles_m)
 {
     epilogue_housekeeping(epi);
     __shared__ uint32_t As[TM][LDW];
     __shared__ uint32_t Bs[TN][LDW];
-    const uint64_t m0 = (uint64_t)blockIdx.x * TM, n0 = (uint64_t)blockIdx.y * TN;
+    // tiles are numbered along grid.x (which reaches 2^31 - 1; grid.y stops at 65535), M tiles fastest
+    const uint64_t m0 = (uint64_t)(blockIdx.x % tiles_m) * TM, n0 = (uint64_t)(blockIdx.x / tiles_m) * TN;
     const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
 
     int32_t acc[4][4] = {};
@@ -107,10 +108,11 @@ cudaError_t launch_gemm_simt(bool tA, bool tB, uint64_t M, uint64_t N, uint64_t 
     // quantized_matmul's layouts: A is [M,K] unless transposed ([K,M]); B is [K,N] unless transposed ([N,K]).
     const bool a_kc = !tA, b_kc = tB;
     const uint64_t gx = (M + TM - 1) / TM, gy = (N + TN - 1) / TN;
-    if (gy > 65535 || gx > 0x7FFFFFFFull) return cudaErrorInvalidConfiguration;
-    dim3 grid((unsigned)gx, (unsigned)gy);
-    gemm_simt_kernel<<<grid, 256, 0, stream>>>(a_kc, b_kc, M, N, K, A, B, epi, out);
+    if (gx > 0x7FFFFFFFull || gy > 0x7FFFFFFFull || gx * gy > 0x7FFFFFFFull) return cudaErrorInvalidConfiguration;
+    dim3 grid((unsigned)(gx * gy));
+    gemm_simt_kernel<<<grid, 256, 0, stream>>>(a_kc, b_kc, M, N, K, A, B, epi, out, (uint32_t)gx);
     count_launch();
+    note_kernel("gemm_simt_kernel");
     return cudaGetLastError();
 }
 

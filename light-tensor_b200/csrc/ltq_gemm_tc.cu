@@ -487,6 +487,7 @@ cudaError_t launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M,
     cudaError_t e = launch_chained(gemm_tc_kernel<BN, OUT>, dim3(grid), dim3(NUM_THREADS), (size_t)C::SMEM_BYTES, stream, ma, mb,
                                    (uint32_t)M, (uint32_t)N, (uint32_t)K, epi, out, status);
     count_launch();
+    note_kernel("gemm_tc_kernel<%d,%s>", BN, out_mode_name(OUT));
     return e;
 }
 
@@ -530,6 +531,7 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M
     cudaError_t e = launch_chained(gemm_tc_pair_kernel<PBN, OUT>, dim3((unsigned)(2 * pairs)), dim3(P_THREADS), smem, stream,
                                    ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi_l, out, status);
     count_launch();
+    note_kernel("gemm_tc_pair_kernel<%d,%s>", PBN, out_mode_name(OUT));
     return e;
 }
 

@@ -407,15 +407,16 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
                            (uint32_t)M, (uint32_t)N, (uint32_t)K, p.tiles_per_cta, p.tiles, p.oct_lo, p.lines, p.stages,
                            p.prefetch, p.w_stage, p.x_stage, p.slack, epi, out, status);
     count_launch();
+    note_kernel("gemv_kernel<%s>", out_mode_name(OUT));
     return e;
 }
 
 }  // namespace
 
-bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W)
+bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W, int sms)
 {
     return M >= 1 && M <= 16 && N >= 1 && N < (1ull << 31) && K >= 128 && K % 128 == 0 && K < (1ull << 31) &&
-           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, 148, SMEM_FULL).ok;
+           (((uintptr_t)x & 15) == 0) && (((uintptr_t)W & 15) == 0) && make_plan(M, N, K, sms, SMEM_FULL).ok;
 }
 
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,

@@ -6,8 +6,9 @@
 namespace ltq {
 
 // True when the kernel can take the problem: 1 <= M <= 16, K a multiple of 128, 16-byte aligned bases, and a band of at
-// most 128 weight rows per tile with at least two ring stages in shared memory.
-bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W);
+// most 128 weight rows per tile with at least two ring stages in shared memory, on a device with `sms` SMs (the same
+// count launch_gemv is given: the two must agree on the plan).
+bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void *W, int sms);
 // x uint8 [M,K], W uint8 [N,K], both K-contiguous.
 // Weight tensor maps of the kernel (two box heights, because the row bands of the CTAs differ by at most one group of
 // 8 rows).  A caller that keeps one per weight matrix saves the host-side encoding on every call.

@@ -21,7 +21,8 @@ static_assert(LTQ_STATIC_WS_INTS_IMPL == LTQ_STATIC_WS_INTS, "header and impleme
 
 // Operand sums: [0, N) sums over K of the B operand, [N, N + M) sums over K of the A operand.
 static __device__ __align__(256) int32_t g_static_ws[LTQ_STATIC_WS_INTS_IMPL];
-// Status word for the bounded waits inside the GEMM kernels (the ordinary path allocates its own).
+// Status word for the bounded waits inside the GEMM kernels (the ordinary path allocates its own); zero at load,
+// read and cleared by ltq_static_check.
 static __device__ __align__(256) uint32_t g_static_status[64];
 
 namespace {
@@ -95,43 +96,49 @@ extern "C" int ltq_quantized_matmul_static(int transpose_A, int transpose_B, uin
         else LTQ_CUDA_TRY(launch_col_sums(A_dev, K, M, asum, st));
     }
 
-    Epilogue epi;
-    epi.bsum = bsum;
-    epi.asum = asum;
-    epi.bias = bias_dev;
-    epi.row_bias = nullptr;
-    epi.ldc = 0;
-    epi.n_more = 0;
-    epi.staged = 0;
-    epi.col_block = 0;
-    epi.col_block_stride = 0;
-    epi.out_rowsum = nullptr;
-    epi.clear_ptr = nullptr;
-    epi.clear_count = 0;
-    for (auto &m : epi.more_out) m = nullptr;
-    epi.qpA_dev = nullptr;
-    epi.sA = qparams[0].scale;
-    epi.sB = qparams[1].scale;
-    epi.sC = qparams[2].scale;
-    epi.zA = qparams[0].zero_point;
-    epi.zB = qparams[1].zero_point;
-    epi.zC = qparams[2].zero_point;
-    epi.K = (uint32_t)K;
-    epi.out_mode = LTQ_OUT_U8;
-    epi.flags = 0;
-
-    if (!tA && tB && K > 0 && gemv_shape_ok(M, N, K, A_dev, B_dev)) {
-        LTQ_CUDA_TRY(launch_gemv(A_dev, B_dev, M, N, K, epi, C_dev, sd->status, sd->sms, st, nullptr, false));
-    } else if (!tA && tB && K > 0 && tc_shape_ok(M, N, K, A_dev, B_dev)) {
-        const int bn = tc_pick_bn(M, N, sd->sms);
-        TcOperandMap map_a, map_b;  // encoded on the host into these stack objects; no device memory involved
-        int er = tc_make_map(&map_a, A_dev, M, K, 128);
-        LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the A operand (CUresult %d)", er);
-        er = tc_make_map(&map_b, B_dev, N, K, bn);
-        LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the B operand (CUresult %d)", er);
-        LTQ_CUDA_TRY(launch_gemm_tc(map_a, map_b, bn, M, N, K, epi, C_dev, sd->status, sd->sms, st));
+    // Same epilogue set-up and kernel choice as ltq_quantized_matmul (skinny, tcgen05 single CTA or CTA pair, dp4a):
+    // only the scratch and the status word differ.  Tensor maps are encoded on the host into stack objects.
+    const Epilogue epi = make_epilogue(bsum, asum, bias_dev, qparams[0], qparams[1], qparams[2], K, LTQ_OUT_U8, 0);
+    if (!tA && tB && K > 0) {
+        const GemmDevice gd{sd->sms, sd->status};
+        rc = run_fc_gemm(gd, M, N, K, A_dev, B_dev, epi, C_dev, 0, nullptr, st);
+        if (rc != LTQ_OK) return rc;
     } else {
+        LTQ_REQUIRE(simt_grid_ok(M, N), LTQ_ERR_TOO_LARGE, "M x N = %llu x %llu needs more than 2^31 - 1 tiles of 64 x 64",
+                    (unsigned long long)M, (unsigned long long)N);
         LTQ_CUDA_TRY(launch_gemm_simt(tA, tB, M, N, K, A_dev, B_dev, epi, C_dev, st));
     }
+    return LTQ_OK;
+}
+
+// Allocation-free counterpart of ltq_device_check for the calls above: their kernels report an expired bounded wait
+// into the library's built-in status word, which this reads back (into a host stack variable) and clears.
+extern "C" int ltq_static_check(int device, void *stream)
+{
+    LTQ_ENTER_DEVICE(device);
+    StaticDevice *sd;
+    int rc = static_device(device, &sd);
+    if (rc != LTQ_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t code = 0;
+    LTQ_CUDA_TRY(cudaMemcpyAsync(&code, sd->status, sizeof code, cudaMemcpyDeviceToHost, st));
+    LTQ_CUDA_TRY(cudaStreamSynchronize(st));
+    if (code) {
+        LTQ_CUDA_TRY(cudaMemsetAsync(sd->status, 0, sizeof code, st));
+        set_error("a bounded device-side wait expired inside an allocation-free call (code 0x%x: role %u, slot %u)", code,
+                  code >> 8, code & 0xFF);
+        return LTQ_ERR_DEVICE_TIMEOUT;
+    }
+    return LTQ_OK;
+}
+
+extern "C" int ltq_selftest_bounded_wait_static(int device, uint32_t limit_us, void *stream)
+{
+    LTQ_REQUIRE(limit_us >= 1 && limit_us <= 1000000, LTQ_ERR_INVALID_ARG, "limit must be between 1 us and 1 s");
+    LTQ_ENTER_DEVICE(device);
+    StaticDevice *sd;
+    int rc = static_device(device, &sd);
+    if (rc != LTQ_OK) return rc;
+    LTQ_CUDA_TRY(launch_bounded_wait_probe(sd->status, (uint64_t)limit_us * 1000ull, (cudaStream_t)stream));
     return LTQ_OK;
 }

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "ltq_version": (_int, []),
     "ltq_last_error": (C.c_char_p, []),
     "ltq_kernel_launches": (_u64, []),
+    "ltq_last_kernel": (C.c_char_p, []),
     "ltq_get_min_max": (_int, [_vp, _u64, _vp, _int, _vp]),
     "ltq_compute_qparams": (_int, [C.c_float, C.c_float, _qp]),
     "ltq_compute_qparams_dev": (_int, [_vp, _vp, _int, _vp]),
@@ -49,6 +50,8 @@ _SIGNATURES = {
                                        _int, C.c_uint, _int, _vp]),
     "ltq_quantized_matmul_static": (_int, [_int, _int, _u64, _u64, _u64, C.c_uint8, _vp, _vp, C.c_uint8, _vp, _qp, _vp,
                                            _int, _vp]),
+    "ltq_static_check": (_int, [_int, _vp]),
+    "ltq_selftest_bounded_wait_static": (_int, [_int, C.c_uint32, _vp]),
     "ltq_layer_create": (_int, [C.POINTER(_vp), _int, _u64, _u64]),
     "ltq_layer_destroy": (_int, [_vp]),
     "ltq_layer_set_weights": (_int, [_vp, _vp, _vp, _vp]),
@@ -104,6 +107,11 @@ def last_error():
 
 def kernel_launches():
     return int(lib().ltq_kernel_launches())
+
+
+def last_kernel():
+    """Name of the GEMM kernel this thread launched last (what the shape-based dispatch chose)."""
+    return lib().ltq_last_kernel().decode("ascii", "replace")
 
 
 def check(status):

@@ -360,3 +360,63 @@ def test_chain_with_epilogue_row_sums_and_clear_hooks(cuda, oracle, M):
         np.testing.assert_array_equal(outs[i].cpu().numpy(), a, err_msg=f"batch {i}")
     with pytest.raises(ltq.LtqError):
         layers[0].set_clear_on_forward(sums[0])      # its own accumulation target
+
+
+def test_mlp_block_shapes_sampled_rows(cuda, oracle):
+    """The 8192 -> 32768 -> 8192 block at its real widths (512 tokens): layer 1 uint8 + ReLU leaving the row sums of its
+    output behind, layer 2 fp32 fed with those sums, both on the kernel the dispatcher picks by shape (the CTA-pair
+    kernel).  64 random rows are pushed through both layers by the CPU oracle and compared bit for bit; the whole tensors
+    are compared with the dp4a kernel; and layer 2's K = 32768 is run once more with both zero points at 255, where
+    K*zA*zB sits 0.8 % under the int32 limit (l-ten/math_fns.cpp:1433-1434)."""
+    import ltq
+    M, K1, N1, N2 = 512, 8192, 32768, 8192
+    g = cuda.Generator(device="cuda").manual_seed(5)
+    x = cuda.randn((M, K1), generator=g, device="cuda")
+    w1 = cuda.randn((N1, K1), generator=g, device="cuda") * 0.01
+    w2 = cuda.randn((N2, N1), generator=g, device="cuda") * 0.01
+    b1 = cuda.randn(N1, generator=g, device="cuda") * 0.05
+    qx = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(x)))
+    qw1 = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(w1)))
+    qw2 = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(w2)))
+    qh = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(cuda.relu(x[:128] @ w1.t() + b1))))
+    xq, asum = ltq.quantize_rows(x, qp=qx)
+    w1q, w2q = ltq.Quantize(w1, qw1), ltq.Quantize(w2, qw2)
+    b1q = ltq.QuantizeInt32(b1, ltq.QParams(np.float32(qx.scale) * np.float32(qw1.scale), 0))
+    del x, w1, w2
+    l1 = ltq.LayerHandle(0, K1, N1)
+    l1.set_weights(w1q, b1q)
+    l1.set_qparams(qx, qw1, qh)
+    l2 = ltq.LayerHandle(0, N1, N2)
+    l2.set_weights(w2q, None)
+    l2.set_qparams(qh, qw2, ltq.QParams(1.0, 0))
+    hsum = cuda.zeros(M, dtype=cuda.int32, device="cuda")
+    l1.set_rowsum_output(hsum)
+    hq = l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum)
+    assert ltq.last_kernel().startswith("gemm_tc_pair_kernel<"), ltq.last_kernel()
+    y = l2.forward(hq, ltq.OUT_F32, 0, asum=hsum)
+    assert ltq.last_kernel().startswith("gemm_tc_pair_kernel<"), ltq.last_kernel()
+    l2.check()
+    assert cuda.equal(hsum, hq.to(cuda.int32).sum(1).to(cuda.int32))
+    # whole tensors against the dp4a kernel (which computes its own row sums for layer 2)
+    l1.set_rowsum_output(None)
+    assert cuda.equal(hq, l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU | ltq.FLAG_FORCE_SIMT, asum=asum))
+    assert cuda.equal(y, l2.forward(hq, ltq.OUT_F32, ltq.FLAG_FORCE_SIMT))
+    # 64 random rows through both layers on the CPU
+    rows = np.sort(np.random.default_rng(5).choice(M, 64, replace=False))
+    oqx, oqw1, oqw2, oqh = [oracle.qp(q.scale, q.zero_point) for q in (qx, qw1, qw2, qh)]
+    xq_h, w1_h, w2_h, b1_h = xq.cpu().numpy()[rows], w1q.cpu().numpy(), w2q.cpu().numpy(), b1q.cpu().numpy()
+    acc1 = oracle.port.acc_i32(xq_h, w1_h, 64, N1, K1, oqx.zero_point, oqw1.zero_point, bias=b1_h)
+    h_ref = oracle.port.epilogue_u8(acc1, oqx.scale, oqw1.scale, oqh.scale, oqh.zero_point, relu=True)
+    np.testing.assert_array_equal(hq.cpu().numpy()[rows], h_ref)
+    acc2 = oracle.port.acc_i32(h_ref, w2_h, 64, N2, N1, oqh.zero_point, oqw2.zero_point)
+    y_ref = oracle.port.epilogue_f32(acc2, oqh.scale, oqw2.scale)
+    np.testing.assert_array_equal(y.cpu().numpy()[rows].view(np.uint32), y_ref.view(np.uint32))
+    # K = 32768 with zA = zB = 255: K*zA*zB = 2 130 739 200 < 2^31 - 1; random bytes so that raw sums are large too
+    hr = cuda.randint(0, 256, (M, N1), dtype=cuda.uint8, device="cuda", generator=g)
+    l2.set_qparams(ltq.QParams(0.03, 255), ltq.QParams(0.002, 255), ltq.QParams(1.0, 0))
+    acc_dev = l2.forward(hr, ltq.OUT_I32, 0)
+    assert ltq.last_kernel().startswith("gemm_tc_pair_kernel<"), ltq.last_kernel()
+    assert cuda.equal(acc_dev, l2.forward(hr, ltq.OUT_I32, ltq.FLAG_FORCE_SIMT))
+    want = oracle.port.acc_i32(hr.cpu().numpy()[rows], w2_h, 64, N2, N1, 255, 255)
+    np.testing.assert_array_equal(acc_dev.cpu().numpy()[rows], want)
+    l2.check()
