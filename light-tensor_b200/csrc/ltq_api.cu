@@ -260,31 +260,39 @@ int ltq::run_fc_gemm(const GemmDevice &gd, uint64_t M, uint64_t N, uint64_t K, c
         case PATH_TC: {
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
                               ((flags & LTQ_FLAG_FORCE_TC_PAIR) || tc_pair_preferred(M, N, dev->sms));
-            // single CTA: B boxes of bn rows (bn = 64, 128, 256); pair: boxes of pbn / 2 rows (96 .. 128)
-            const int pbn = pair ? tc_pair_pick_bn(M, N, dev->sms, epi.n_more > 0, epi.col_block != 0) : 0;
-            const int bn = pair ? pbn / 2 : tc_pick_bn(M, N, dev->sms);
-            TcOperandMap map_a, tmp_b;
+            // single CTA: B boxes of bn rows (bn = 64, 128, 256); pair: boxes of bn / 2 rows (96 .. 128), and of bn / 4
+            // rows for the half-width items of the last round
+            const PairPlan plan = pair ? tc_pair_plan(M, N, dev->sms, epi.n_more > 0, epi.col_block != 0) : PairPlan{0, 0};
+            const int bn = pair ? plan.bn / 2 : tc_pick_bn(M, N, dev->sms);
+            TcOperandMap map_a, tmp_b[2];
             int er = tc_make_map(&map_a, A, M, K, 128);
             LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation operand (CUresult %d)", er);
-            TcOperandMap *map_b = &tmp_b;
-            if (layer) {
-                // one cached map per box height this layer has needed so far
-                map_b = nullptr;
-                for (auto &m : layer->map_w)
-                    if (m.matches(B, N, K, bn)) map_b = &m;
-                if (!map_b) {
-                    map_b = &layer->map_w[layer->map_w_next];
-                    layer->map_w_next = (layer->map_w_next + 1) % 4;
+            // weight maps: one cached per box height this layer has needed so far
+            TcOperandMap *maps_b[2] = {nullptr, nullptr};
+            const int heights[2] = {bn, (pair && plan.has_halves()) ? plan.bn / 4 : 0};
+            for (int k = 0; k < 2; k++) {
+                if (!heights[k]) continue;
+                TcOperandMap *mb = &tmp_b[k];
+                if (layer) {
+                    mb = nullptr;
+                    for (auto &m : layer->map_w)
+                        if (m.matches(B, N, K, heights[k])) mb = &m;
+                    if (!mb) {
+                        mb = &layer->map_w[layer->map_w_next];
+                        layer->map_w_next = (layer->map_w_next + 1) % 4;
+                    }
                 }
-            }
-            if (!map_b->matches(B, N, K, bn)) {
-                er = tc_make_map(map_b, B, N, K, bn);
-                LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
+                if (!mb->matches(B, N, K, heights[k])) {
+                    er = tc_make_map(mb, B, N, K, heights[k]);
+                    LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
+                }
+                maps_b[k] = mb;
             }
             if (pair)
-                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, *map_b, pbn, M, N, K, epi, out, dev->status, dev->sms, stream));
+                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, *maps_b[0], maps_b[1], plan, M, N, K, epi, out, dev->status, dev->sms,
+                                                 stream));
             else
-                LTQ_CUDA_TRY(launch_gemm_tc(map_a, *map_b, bn, M, N, K, epi, out, dev->status, dev->sms, stream));
+                LTQ_CUDA_TRY(launch_gemm_tc(map_a, *maps_b[0], bn, M, N, K, epi, out, dev->status, dev->sms, stream));
             break;
         }
         default:

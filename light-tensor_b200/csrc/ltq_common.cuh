@@ -180,6 +180,7 @@ __device__ __forceinline__ bool epilogue_vec_ok(const Epilogue &e, const void *o
 struct EpilogueConsts {
     uint32_t neg_zA, neg_zB, bc;  // -zA, -zB, K*zA*zB (mod 2^32)
     float rm, sAB, zCf;
+    bool rm_small;                // |rm| <= 0.5: |rm*acc + zC| stays below 2^31 for every int32 acc
 };
 
 __device__ __forceinline__ EpilogueConsts epilogue_consts(const Epilogue &e)
@@ -197,6 +198,7 @@ __device__ __forceinline__ EpilogueConsts epilogue_consts(const Epilogue &e)
     c.sAB = __fmul_rn(sA, e.sB);
     c.rm = __fdiv_rn(c.sAB, e.sC);  // l-ten/math_fns.cpp:1436: float, left to right
     c.zCf = (float)e.zC;
+    c.rm_small = fabsf(c.rm) <= 0.5f;  // false for NaN
     return c;
 }
 
@@ -246,7 +248,9 @@ __device__ __forceinline__ float epilogue_f32(int32_t acc, const EpilogueConsts 
 }
 
 // One chunk of W (32 or 16) accumulator columns of one output row -> output words: W/4 words of packed uint8 (OUT == 0)
-// or W words of float / int32 bits.  `res` has room for W words either way.
+// or W words of float / int32 bits.  `res` has room for W words either way.  Written for few instructions per element
+// (the epilogue is issue-bound): ReLU is a max against a uniform lower bound, the bytes are gathered with byte
+// permutes, and the "t >= 2^31" corner of the wrapping cast is only evaluated when rm is large enough to reach it.
 template <int OUT, int W>
 __device__ __forceinline__ void epilogue_convert(const uint32_t (&v)[W], uint32_t rt, const uint32_t *col_smem,
                                                  const EpilogueConsts &c, bool relu, bool sat, uint32_t (&res)[W])
@@ -261,22 +265,36 @@ __device__ __forceinline__ void epilogue_convert(const uint32_t (&v)[W], uint32_
         col[4 * g + 2] = t4.z;
         col[4 * g + 3] = t4.w;
     }
+    const int32_t lo = relu ? 0 : INT32_MIN;
     if (OUT == 0) {
+        if (!sat && c.rm_small) {
 #pragma unroll
-        for (int g = 0; g < W / 4; g++) {
-            uint32_t w = 0;
+            for (int g = 0; g < W / 4; g++) {
+                int32_t r[4];
 #pragma unroll
-            for (int b = 0; b < 4; b++) {
-                const int j = g * 4 + b;
-                const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
-                w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
+                for (int b = 0; b < 4; b++) {
+                    const int32_t a = max((int32_t)(v[4 * g + b] + rt + col[4 * g + b]), lo);
+                    r[b] = __float2int_rz(__fadd_rn(__fmul_rn(c.rm, __int2float_rn(a)), c.zCf));
+                }
+                res[g] = __byte_perm(__byte_perm((uint32_t)r[0], (uint32_t)r[1], 0x0040),
+                                     __byte_perm((uint32_t)r[2], (uint32_t)r[3], 0x0040), 0x5410);
             }
-            res[g] = w;
+        } else {
+#pragma unroll
+            for (int g = 0; g < W / 4; g++) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const int32_t a = max((int32_t)(v[4 * g + b] + rt + col[4 * g + b]), lo);
+                    w |= (uint32_t)epilogue_u8(a, c, sat) << (8 * b);
+                }
+                res[g] = w;
+            }
         }
     } else {
 #pragma unroll
         for (int j = 0; j < W; j++) {
-            const int32_t a = epilogue_acc(v[j], rt, col[j], relu);
+            const int32_t a = max((int32_t)(v[j] + rt + col[j]), lo);
             res[j] = (OUT == 1) ? __float_as_uint(epilogue_f32(a, c)) : (uint32_t)a;
         }
     }

@@ -13,6 +13,7 @@
 // Every wait on an mbarrier is bounded (wall-clock limit read from %globaltimer): on expiry the kernel records a code
 // in a device status word, stops issuing work, drains and frees its TMEM, and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <type_traits>
 
@@ -220,6 +221,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // Eight epilogue warps per CTA (two per TMEM lane quarter, splitting the columns) keep the exposed epilogue of a CTA's
 // last tile short.  PBN (256, 240, 224 or 192) is picked per problem so that the last wave of tiles is as full as
 // possible: integer tiles x CTA pairs rarely divide evenly, and a narrower tile can save a whole wave.
+//
+// Tail wave: work is a list of items handed out round-robin to the CTA pairs.  The first n_full tiles are one item
+// each; every tile behind them is TWO items of half the width (256 x PBN/2: an MMA with N = PBN/2, a B box of PBN/4
+// rows per CTA, same ring, same accumulator buffers).  The host chooses n_full so that the full tiles fill whole rounds
+// and the remainder runs as one round of half tiles: 4096^3 on 74 pairs is 3 rounds of 256 x 256 plus 68 half tiles
+// instead of 4 rounds, and the epilogue left exposed at the very end is that of a half tile.  Integer sums make every
+// tiling of the output bit-identical.
 namespace {
 
 constexpr int P_STAGES = 6;
@@ -231,16 +239,39 @@ struct PCfg {
     static constexpr int B_BYTES = (PBN / 2) * BK;  // this CTA's half of the tile's B rows
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int SMEM_BYTES = P_STAGES * STAGE_BYTES + 1024 + 2 * PBN * 4 + 256;
+    static constexpr bool HALVES = PBN == 256;      // half-width items exist for this tile width
     static_assert(B_BYTES % 1024 == 0, "swizzled tiles must stay 1024-byte aligned");
     static_assert(PBN % 16 == 0 && PBN >= 144 && PBN <= 256, "tile width");
 };
+
+// Work item `i` of a launch: tile row block, first column, and whether it is a half-width item.
+struct PairItem {
+    uint32_t tm, n0;
+    bool half;
+};
+template <int PBN>
+__device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t n_full, uint32_t tiles_n)
+{
+    PairItem it;
+    it.half = i >= n_full;
+    uint32_t t = i, sel = 0;
+    if (it.half) {
+        const uint32_t j = i - n_full;
+        t = n_full + (j >> 1);
+        sel = j & 1u;
+    }
+    it.tm = t / tiles_n;
+    it.n0 = (t % tiles_n) * PBN + sel * (PBN / 2);
+    return it;
+}
 
 }  // namespace
 
 template <int PBN, int OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 2)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, uint32_t M,
-                    uint32_t N, uint32_t K, Epilogue epi, void *__restrict__ out, uint32_t *status)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_b_half, uint32_t M, uint32_t N, uint32_t K, uint32_t n_full,
+                    Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
     griddep_launch_dependents();
     using C = PCfg<PBN>;
@@ -262,6 +293,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + PBN - 1) / PBN;
     const uint32_t num_tiles = tiles_m * tiles_n;
+    if (!C::HALVES || n_full > num_tiles) n_full = num_tiles;
+    const uint32_t num_items = n_full + 2 * (num_tiles - n_full);
     const uint32_t num_kb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -277,6 +310,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    if (warp == 0 && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        if (C::HALVES) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b_half) : "memory");
+    }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(s_misc), 512);
         tmem_relinquish_pair();
@@ -290,23 +328,25 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = s_misc[0];
 
     if (warp == 0) {
-        // ---------------- TMA producer (both CTAs): own A rows, own half of the B rows ----------------
+        // ---------------- TMA producer (both CTAs): own A rows, own half of the item's B rows ----------------
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
-                const int32_t m0 = (int32_t)((t / tiles_n) * (2 * BM) + rank * BM);
-                const int32_t n0 = (int32_t)((t % tiles_n) * PBN + rank * (PBN / 2));
+            for (uint32_t i = pair; ok && i < num_items; i += num_pairs) {
+                const PairItem it = pair_item<PBN>(i, n_full, tiles_n);
+                const uint32_t b_rows = it.half ? PBN / 4 : PBN / 2;
+                const CUtensorMap *mb = it.half ? &map_b_half : &map_b;
+                const int32_t m0 = (int32_t)(it.tm * (2 * BM) + rank * BM);
+                const int32_t n0 = (int32_t)(it.n0 + rank * b_rows);
+                const uint32_t tx = 2u * (uint32_t)(C::A_BYTES + b_rows * BK);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
                     if (!ok) break;
                     const uint32_t a_dst = ring + st * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
                     const uint32_t lbar = in_leader_cta(full0 + 8 * st);
-                    if (rank == 0) mbar_expect_tx(full0 + 8 * st, 2 * C::STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * st, tx);
                     tma_load_2d_pair(a_dst, &map_a, lbar, (int32_t)(kb * BK), m0);
-                    tma_load_2d_pair(b_dst, &map_b, lbar, (int32_t)(kb * BK), n0);
+                    tma_load_2d_pair(b_dst, mb, lbar, (int32_t)(kb * BK), n0);
                     if (++st == P_STAGES) { st = 0; ph ^= 1; }
                 }
             }
@@ -315,10 +355,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only): warp-uniform loop, one elected lane issues ----------------
         if (rank == 0) {
-            constexpr uint32_t idesc = make_idesc_i8(2 * BM, PBN);
+            constexpr uint32_t idesc_full = make_idesc_i8(2 * BM, PBN), idesc_half = make_idesc_i8(2 * BM, PBN / 2);
             uint32_t st = 0, ph = 0, as = 0, aph = 0;
             bool ok = true;
-            for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
+            for (uint32_t i = pair; ok && i < num_items; i += num_pairs) {
+                const uint32_t idesc = (C::HALVES && i >= n_full) ? idesc_half : idesc_full;
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
                 if (!ok) break;
                 tc_fence_after();
@@ -348,7 +389,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------- epilogue (warps 2..9 of both CTAs): own 128 rows; two warps share a lane quarter ------------
         const uint32_t q = (uint32_t)warp & 3u;            // TMEM lane quarter this warp may read
-        const uint32_t h = (uint32_t)(warp - 2) >> 2;      // 0: columns [0,128), 1: columns [128,PBN)
+        const uint32_t h = (uint32_t)(warp - 2) >> 2;      // 0: lower column range of the item, 1: upper
         const uint32_t et = threadIdx.x - 64;              // 0..255
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
@@ -356,13 +397,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint64_t ldc = epilogue_pitch(epi, N);
         const bool vec_ok = epilogue_vec_ok(epi, out, N, sizeof(OutT));
         const bool staged = epi.staged && vec_ok && epi.col_block == 0;
-        constexpr int COL0 = 128;                          // column split between the two warps of a quarter
+        constexpr int ESZ = (int)sizeof(OutT), BLOCK_COLS = 128 / ESZ;   // a staged block: 128 bytes per row
+        uint8_t *stage = s_stage + (warp - 2) * PeerStage::BYTES_PER_WARP;
         uint32_t as = 0, aph = 0;
         bool ok = true;
-        for (uint32_t t = pair; t < num_tiles; t += num_pairs) {
-            const uint32_t m0 = (t / tiles_n) * (2 * BM) + rank * BM, n0 = (t % tiles_n) * PBN;
+        for (uint32_t i = pair; i < num_items; i += num_pairs) {
+            const PairItem it = pair_item<PBN>(i, n_full, tiles_n);
+            const uint32_t m0 = it.tm * (2 * BM) + rank * BM, n0 = it.n0;
+            const int width = it.half ? PBN / 2 : PBN;
+            const int split = it.half ? PBN / 4 : 128;     // columns [0, split) go to the h = 0 warps, the rest to h = 1
             uint32_t *col = s_col + as * PBN;
-            for (uint32_t j = et; j < (uint32_t)PBN; j += 256) {
+            for (uint32_t j = et; j < (uint32_t)width; j += 256) {
                 const uint32_t gj = n0 + j;
                 col[j] = gj < N ? epilogue_col_term(epi, c, gj) : 0u;
             }
@@ -374,50 +419,44 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (ok) {
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * 256;
-                const int cb = h ? COL0 : 0, ce = h ? PBN : COL0;
-                // Blocks of 128 output bytes per row go through the row-coalescing stage when results leave the GPU and
-                // the warp's 32 rows and the block's columns are all inside the matrix; everything else is stored directly.
-                constexpr int ESZ = (int)sizeof(OutT), BLOCK_COLS = 128 / ESZ;   // 128 columns of uint8, 32 of 4 bytes
+                const int cb = h ? split : 0, ce = h ? width : split;
                 const bool rows_full = m0 + q * 32 + 32 <= M;
-                uint8_t *stage = s_stage + (warp - 2) * PeerStage::BYTES_PER_WARP;
-                uint32_t rsum = 0;  // sum of this row's uint8 outputs in this warp's half of the tile
-#pragma unroll 1
-                for (int cc = cb; cc < ce; cc += 32) {
+                uint32_t rsum = 0;  // sum of this row's uint8 outputs in this warp's part of the item
+                // One chunk of 16 accumulator columns.  Blocks of 128 output bytes per row go through the row-coalescing
+                // stage when results leave the GPU and the warp's 32 rows and the block's columns are all inside the
+                // matrix; everything else is stored directly.
+                auto chunk = [&](uint32_t (&v)[16], int cc) {
                     const uint32_t c0 = n0 + cc;
                     const int bc0 = cb + ((cc - cb) / BLOCK_COLS) * BLOCK_COLS;          // first column of cc's block
                     const int bcols = (ce - bc0) < BLOCK_COLS ? (ce - bc0) : BLOCK_COLS;  // its width
                     const bool via_stage = staged && rows_full && n0 + bc0 + bcols <= N;
-                    if (cc + 32 <= ce) {
-                        uint32_t v[32];
-                        tmem_ld32(taddr + cc, v);
-                        tmem_ld_wait();
-                        if (via_stage) {
-                            uint32_t res[32];
-                            epilogue_convert<OUT, 32>(v, rt, col + cc, c, relu, sat, res);
-                            PeerStage::put<32>(stage, lane, (cc - bc0) * ESZ / 16, res, 32 * ESZ / 16);
-                            if (OUT == 0) rsum += packed_byte_sum<32>(res, 32);
-                        } else if (row < M && c0 < N) {
-                            rsum += epilogue_chunk<OUT, 32>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
-                                                            vec_ok, (N - c0) < 32u ? (int)(N - c0) : 32);
-                        }
-                    } else {  // PBN = 240 or 208: one 16-column chunk is left in the upper half
-                        uint32_t v[16];
-                        tmem_ld16(taddr + cc, v);
-                        tmem_ld_wait();
-                        if (via_stage) {
-                            uint32_t res[16];
-                            epilogue_convert<OUT, 16>(v, rt, col + cc, c, relu, sat, res);
-                            PeerStage::put<16>(stage, lane, (cc - bc0) * ESZ / 16, res, 16 * ESZ / 16);
-                            if (OUT == 0) rsum += packed_byte_sum<16>(res, 16);
-                        } else if (row < M && c0 < N) {
-                            rsum += epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
-                                                            vec_ok, (N - c0) < 16u ? (int)(N - c0) : 16);
-                        }
+                    if (via_stage) {
+                        uint32_t res[16];
+                        epilogue_convert<OUT, 16>(v, rt, col + cc, c, relu, sat, res);
+                        PeerStage::put<16>(stage, lane, (cc - bc0) * ESZ / 16, res, 16 * ESZ / 16);
+                        if (OUT == 0) rsum += packed_byte_sum<16>(res, 16);
+                        const int next = cc + 16;
+                        if (next == ce || (next - cb) % BLOCK_COLS == 0)   // the block is complete
+                            PeerStage::flush(stage, lane, bcols * ESZ / 16, epi, out,
+                                             ((uint64_t)(m0 + q * 32) * ldc + n0 + bc0) * ESZ, ldc * ESZ);
+                    } else if (row < M && c0 < N) {
+                        rsum += epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
+                                                        vec_ok, (N - c0) < 16u ? (int)(N - c0) : 16);
                     }
-                    const int next = cc + 32 < ce ? cc + 32 : ce;
-                    if (via_stage && (next == ce || (next - cb) % BLOCK_COLS == 0))   // the block is complete
-                        PeerStage::flush(stage, lane, bcols * ESZ / 16, epi, out,
-                                         ((uint64_t)(m0 + q * 32) * ldc + n0 + bc0) * ESZ, ldc * ESZ);
+                };
+                // Two register buffers: the TMEM load of the next chunk is in flight while this one is converted.
+                uint32_t va[16], vb[16];
+                tmem_ld16(taddr + cb, va);
+#pragma unroll 1
+                for (int cc = cb; cc < ce; cc += 32) {
+                    tmem_ld_wait();
+                    if (cc + 16 < ce) tmem_ld16(taddr + cc + 16, vb);
+                    chunk(va, cc);
+                    if (cc + 16 < ce) {
+                        tmem_ld_wait();
+                        if (cc + 32 < ce) tmem_ld16(taddr + cc + 32, va);
+                        chunk(vb, cc + 16);
+                    }
                 }
                 if (OUT == 0 && epi.out_rowsum && row < M) atomicAdd(&epi.out_rowsum[row], (int32_t)rsum);
                 // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)
@@ -507,8 +546,9 @@ cudaError_t launch_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M,
 namespace {
 
 template <int PBN, int OUT>
-cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
-                        const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mbh, uint32_t n_full, uint64_t M,
+                        uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
+                        cudaStream_t stream)
 {
     using C = PCfg<PBN>;
     static bool attr_done[64] = {false};
@@ -524,25 +564,32 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M
         attr_done[dev] = true;
     }
     const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
-    const uint64_t pairs = tiles < (uint64_t)(sms / 2) ? tiles : (uint64_t)(sms / 2);
+    if (!C::HALVES || n_full > tiles) n_full = (uint32_t)tiles;
+    const uint64_t items = n_full + 2 * (tiles - n_full);
+    const uint64_t pairs = items < (uint64_t)(sms / 2) ? items : (uint64_t)(sms / 2);
     Epilogue epi_l = epi;
     epi_l.staged = (epi.n_more > 0 && STAGE_FITS) ? 1 : 0;  // (local-only stores gain nothing from the stage: measured)
     const size_t smem = C::SMEM_BYTES + (epi_l.staged ? STAGE_BYTES : 0);
     cudaError_t e = launch_chained(gemm_tc_pair_kernel<PBN, OUT>, dim3((unsigned)(2 * pairs)), dim3(P_THREADS), smem, stream,
-                                   ma, mb, (uint32_t)M, (uint32_t)N, (uint32_t)K, epi_l, out, status);
+                                   ma, mb, mbh, (uint32_t)M, (uint32_t)N, (uint32_t)K, n_full, epi_l, out, status);
     count_launch();
-    note_kernel("gemm_tc_pair_kernel<%d,%s>", PBN, out_mode_name(OUT));
+    if (items != tiles)
+        note_kernel("gemm_tc_pair_kernel<%d,%s> (%llu tiles + %llu half-width items)", PBN, out_mode_name(OUT),
+                    (unsigned long long)n_full, (unsigned long long)(items - n_full));
+    else
+        note_kernel("gemm_tc_pair_kernel<%d,%s>", PBN, out_mode_name(OUT));
     return e;
 }
 
 template <int PBN>
-cudaError_t launch_pair_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M, uint64_t N, uint64_t K,
-                            const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+cudaError_t launch_pair_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mbh, uint32_t n_full,
+                            uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
+                            cudaStream_t stream)
 {
     switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_pair<PBN, 0>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        case LTQ_OUT_F32: return launch_pair<PBN, 1>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        default: return launch_pair<PBN, 2>(ma, mb, M, N, K, epi, out, status, sms, stream);
+        case LTQ_OUT_U8: return launch_pair<PBN, 0>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
+        case LTQ_OUT_F32: return launch_pair<PBN, 1>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
+        default: return launch_pair<PBN, 2>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
     }
 }
 
@@ -556,37 +603,55 @@ bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
     return M > (uint64_t)BM && tiles * 4 >= (uint64_t)(sms / 2) * 3;
 }
 
-int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores, bool chunks_aligned_32)
+bool tail_split_enabled()
 {
-    // Time ~ (waves of tiles over the CTA pairs) x (tile width).  Wider tiles reuse operands better, so a narrower one
-    // must win by a clear margin (3 %).
+    static const bool on = getenv("LTQ_NO_TAIL_SPLIT") == nullptr;  // debugging / A-B switch
+    return on;
+}
+
+PairPlan tc_pair_plan(uint64_t M, uint64_t N, int sms, bool peer_stores, bool chunks_aligned_32)
+{
+    // Time ~ sum over the rounds of items handed to the CTA pairs of the round's item width.  Wider tiles reuse operands
+    // better, so a narrower one must win by a clear margin (3 %).  With 256-wide tiles the remainder behind the last
+    // whole round may run as half-width items.
     const uint64_t tm = (M + 2 * BM - 1) / (2 * BM), pairs = (uint64_t)(sms / 2);
-    int best = peer_stores ? 224 : 256;
+    PairPlan best{peer_stores ? 224 : 256, 0xFFFFFFFFu};
     double best_cost = 1e30;
     for (int bn : {256, 240, 224, 192}) {
         if (peer_stores && bn == 256) continue;  // no room for the row-coalescing stage beside a 6 x 32 KB ring
-        if (chunks_aligned_32 && bn % 32 != 0) continue;  // column-blocked outputs: 32-column chunks start at multiples of 32
+        if (chunks_aligned_32 && bn % 32 != 0) continue;  // column-blocked outputs: chunks must not straddle a block
         const uint64_t tiles = tm * ((N + bn - 1) / bn);
-        const double cost = (double)((tiles + pairs - 1) / pairs) * bn;
+        double cost = (double)((tiles + pairs - 1) / pairs) * bn;
+        uint32_t n_full = 0xFFFFFFFFu;
+        if (bn == 256 && tail_split_enabled() && tiles > pairs) {
+            const uint64_t whole = tiles / pairs, rem = tiles - whole * pairs;
+            if (rem != 0 && 2 * rem <= pairs) {  // the remainder fits one round of half tiles
+                cost = (double)whole * bn + bn / 2;
+                n_full = (uint32_t)(whole * pairs);
+            }
+        }
         if (cost < best_cost * 0.97) {
             best_cost = cost;
-            best = bn;
+            best = PairPlan{bn, n_full};
         }
     }
     return best;
 }
 
-cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
-                                uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
-                                cudaStream_t stream)
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, const TcOperandMap *map_b_half,
+                                const PairPlan &plan, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi, void *out,
+                                uint32_t *status, int sms, cudaStream_t stream)
 {
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(map_a.opaque);
     const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(map_b.opaque);
-    switch (bn) {
-        case 256: return launch_pair_out<256>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        case 240: return launch_pair_out<240>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        case 224: return launch_pair_out<224>(ma, mb, M, N, K, epi, out, status, sms, stream);
-        case 192: return launch_pair_out<192>(ma, mb, M, N, K, epi, out, status, sms, stream);
+    // without half-width items the third map is never dereferenced; pass the full-width one
+    const CUtensorMap &mbh = *reinterpret_cast<const CUtensorMap *>(map_b_half ? map_b_half->opaque : map_b.opaque);
+    const uint32_t n_full = map_b_half ? plan.n_full : 0xFFFFFFFFu;
+    switch (plan.bn) {
+        case 256: return launch_pair_out<256>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
+        case 240: return launch_pair_out<240>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
+        case 224: return launch_pair_out<224>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
+        case 192: return launch_pair_out<192>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -28,13 +28,20 @@ int tc_pick_bn(uint64_t M, uint64_t N, int sms);
 // Encodes a map; box_rows is 128 for the A operand and the tile width for the B operand. 0 on success.
 int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows);
 // CTA-pair variant (256 x bn tiles, tcgen05.mma.cta_group::2).  tc_pair_preferred says when the problem is large
-// enough; tc_pair_pick_bn picks the tile width (256, 240, 224 or 192) that leaves the fullest last wave.  map_a uses
-// 128-row boxes, map_b boxes of bn / 2 rows (each CTA of a pair loads half of the tile's B rows).
+// enough; tc_pair_plan picks the tile width (256, 240, 224 or 192) and, for 256, how many tiles run at full width
+// before the rest is handed out as half-width items (n_full = 0xFFFFFFFF: all of them), whichever leaves the fullest
+// last round.  map_a uses 128-row boxes, map_b boxes of bn / 2 rows (each CTA of a pair loads half of the tile's B
+// rows), map_b_half boxes of bn / 4 rows (needed only when the plan has half-width items; may be NULL otherwise).
+struct PairPlan {
+    int bn;
+    uint32_t n_full;
+    bool has_halves() const { return n_full != 0xFFFFFFFFu; }
+};
 bool tc_pair_preferred(uint64_t M, uint64_t N, int sms);
-int tc_pair_pick_bn(uint64_t M, uint64_t N, int sms, bool peer_stores = false, bool chunks_aligned_32 = false);
-cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, int bn, uint64_t M, uint64_t N,
-                                uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
-                                cudaStream_t stream);
+PairPlan tc_pair_plan(uint64_t M, uint64_t N, int sms, bool peer_stores = false, bool chunks_aligned_32 = false);
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, const TcOperandMap *map_b_half,
+                                const PairPlan &plan, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi, void *out,
+                                uint32_t *status, int sms, cudaStream_t stream);
 // 3-D view of the same kind of matrix for the weight-streaming kernel (K % 128 == 0): dims {128 B line, rows, K/128
 // lines}, box {128 B, box_rows, box_lines}.  One box lands in shared memory as [line][row][128 B]; with the 128-byte
 // swizzle the 16-byte chunk index is XORed with the low three bits of (line * box_rows + row), so the rows of a box

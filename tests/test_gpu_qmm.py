@@ -138,6 +138,34 @@ def test_pair_kernel_tile_widths(cuda, oracle, shape):
     np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("shape", [(2500, 2000, 192), (2560, 2048, 64), (4096, 4096, 128)])
+def test_pair_kernel_half_width_tail(cuda, oracle, shape):
+    """Shapes whose 256-wide tiles leave a short remainder behind the last whole round of CTA pairs: the remainder runs
+    as half-width items (ragged last rows and columns included).  All output modes against the oracle."""
+    import ltq
+    M, N, K = shape
+    rng = np.random.default_rng(M + N)
+    a = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    w = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    bias = rng.integers(-50000, 50000, N, dtype=np.int32)
+    qps = (ltq.QParams(0.02, 77), ltq.QParams(0.005, 131), ltq.QParams(0.9, 100))
+    acc = oracle.port.acc_i32(a, w, M, N, K, 77, 131, bias=bias)
+    force = ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR
+    np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_I32, force), acc)
+    assert "half-width items" in ltq.last_kernel(), ltq.last_kernel()
+    for fl in (0, ltq.FLAG_RELU, ltq.FLAG_SATURATE):
+        np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_U8, force | fl),
+                                      oracle.port.epilogue_u8(acc, 0.02, 0.005, 0.9, 100, relu=bool(fl & ltq.FLAG_RELU),
+                                                              saturate=bool(fl & ltq.FLAG_SATURATE)))
+    got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_F32, force | ltq.FLAG_RELU)
+    want = oracle.port.epilogue_f32(acc, 0.02, 0.005, relu=True)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    # a large real multiplier (rm > 0.5) takes the general cast, where t can pass 2^31
+    big = (ltq.QParams(300.0, 77), ltq.QParams(200.0, 131), ltq.QParams(0.01, 100))
+    np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, big, ltq.OUT_U8, force),
+                                  oracle.port.epilogue_u8(acc, 300.0, 200.0, 0.01, 100))
+
+
 @pytest.mark.parametrize("tA,tB", [(False, False), (False, True), (True, False), (True, True)])
 def test_matmul_u8_plain_int32_product_and_modes(cuda, oracle, tA, tB):
     """The generic uint8 matrix product (every transpose variant): plain int32 product with zero points 0, and the
