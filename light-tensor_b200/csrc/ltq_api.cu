@@ -104,6 +104,8 @@ int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B
 
 using namespace ltq;
 
+constexpr int LAYER_MAPS = 8;
+
 struct ltq_layer {
     int device = 0;
     uint64_t K = 0, N = 0;
@@ -116,7 +118,7 @@ struct ltq_layer {
     int32_t *rowsum_out = nullptr; // optional: receives the row sums of uint8 outputs (ltq_layer_set_rowsum_output)
     int32_t *clear_ptr = nullptr;  // optional: array cleared by every forward (ltq_layer_set_clear_on_forward)
     uint32_t clear_count = 0;
-    TcOperandMap map_w[4];         // weight tensor maps of the tensor-core kernels, one per box height, built on demand
+    TcOperandMap map_w[LAYER_MAPS];  // weight tensor maps of the tensor-core kernels, one per box height, built on demand
     int map_w_next = 0;
     GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
     DeviceState *dev = nullptr;
@@ -260,39 +262,45 @@ int ltq::run_fc_gemm(const GemmDevice &gd, uint64_t M, uint64_t N, uint64_t K, c
         case PATH_TC: {
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
                               ((flags & LTQ_FLAG_FORCE_TC_PAIR) || tc_pair_preferred(M, N, dev->sms));
-            // single CTA: B boxes of bn rows (bn = 64, 128, 256); pair: boxes of bn / 2 rows (96 .. 128), and of bn / 4
-            // rows for the half-width items of the last round
-            const PairPlan plan = pair ? tc_pair_plan(M, N, dev->sms, epi.n_more > 0, epi.col_block != 0) : PairPlan{0, 0};
-            const int bn = pair ? plan.bn / 2 : tc_pick_bn(M, N, dev->sms);
-            TcOperandMap map_a, tmp_b[2];
+            TcOperandMap map_a;
             int er = tc_make_map(&map_a, A, M, K, 128);
             LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the activation operand (CUresult %d)", er);
-            // weight maps: one cached per box height this layer has needed so far
-            TcOperandMap *maps_b[2] = {nullptr, nullptr};
-            const int heights[2] = {bn, (pair && plan.has_halves()) ? plan.bn / 4 : 0};
-            for (int k = 0; k < 2; k++) {
-                if (!heights[k]) continue;
-                TcOperandMap *mb = &tmp_b[k];
+            // Weight maps by box height: the tile width for the single-CTA kernel (64, 128, 256), half the width of
+            // each class of tiles for the pair kernel.  A layer caches the ones it has needed so far.
+            TcOperandMap tmp_b[4];
+            int n_tmp = 0;
+            auto weight_map = [&](int box_rows, TcOperandMap **res) -> int {
+                TcOperandMap *mb = nullptr;
                 if (layer) {
-                    mb = nullptr;
                     for (auto &m : layer->map_w)
-                        if (m.matches(B, N, K, heights[k])) mb = &m;
+                        if (m.matches(B, N, K, box_rows)) mb = &m;
                     if (!mb) {
                         mb = &layer->map_w[layer->map_w_next];
-                        layer->map_w_next = (layer->map_w_next + 1) % 4;
+                        layer->map_w_next = (layer->map_w_next + 1) % LAYER_MAPS;
                     }
+                } else {
+                    for (int k = 0; k < n_tmp; k++)
+                        if (tmp_b[k].matches(B, N, K, box_rows)) mb = &tmp_b[k];
+                    if (!mb) mb = &tmp_b[n_tmp++];
                 }
-                if (!mb->matches(B, N, K, heights[k])) {
-                    er = tc_make_map(mb, B, N, K, heights[k]);
+                *res = mb;
+                return mb->matches(B, N, K, box_rows) ? 0 : tc_make_map(mb, B, N, K, box_rows);
+            };
+            if (pair) {
+                const PairTiling tl = tc_pair_tiling(M, N, dev->sms, epi.col_block != 0);
+                TcOperandMap *maps[4];
+                for (int k = 0; k < 4; k++) {
+                    er = weight_map((int)tl.width[k] / 2, &maps[k]);
                     LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
                 }
-                maps_b[k] = mb;
+                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, maps, tl, M, N, K, epi, out, dev->status, dev->sms, stream));
+            } else {
+                const int bn = tc_pick_bn(M, N, dev->sms);
+                TcOperandMap *mb;
+                er = weight_map(bn, &mb);
+                LTQ_REQUIRE(er == 0, LTQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the weight operand (CUresult %d)", er);
+                LTQ_CUDA_TRY(launch_gemm_tc(map_a, *mb, bn, M, N, K, epi, out, dev->status, dev->sms, stream));
             }
-            if (pair)
-                LTQ_CUDA_TRY(launch_gemm_tc_pair(map_a, *maps_b[0], maps_b[1], plan, M, N, K, epi, out, dev->status, dev->sms,
-                                                 stream));
-            else
-                LTQ_CUDA_TRY(launch_gemm_tc(map_a, *maps_b[0], bn, M, N, K, epi, out, dev->status, dev->sms, stream));
             break;
         }
         default:

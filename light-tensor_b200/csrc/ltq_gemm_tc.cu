@@ -13,6 +13,7 @@
 // Every wait on an mbarrier is bounded (wall-clock limit read from %globaltimer): on expiry the kernel records a code
 // in a device status word, stops issuing work, drains and frees its TMEM, and returns.
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <type_traits>
@@ -213,92 +214,95 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---- CTA-pair variant ---------------------------------------------------------------------------------------------------
-// Large problems: two CTAs of a 2-CTA cluster work on one 256 x PBN output tile with tcgen05.mma.cta_group::2.  Each CTA
+// Large problems: two CTAs of a 2-CTA cluster work on one 256-row output tile with tcgen05.mma.cta_group::2.  Each CTA
 // loads its own 128 rows of A and only HALF of the tile's B rows, so a CTA moves at most 32 KB per 128-deep K block
 // instead of 48 KB: one third less L2 -> SM traffic, and six stages instead of four fit in shared memory, which is what
 // it takes to cover the L2 round trip at the tensor pipe's rate.  The leader CTA (cluster rank 0) issues the MMAs for
 // both; every barrier that both CTAs must observe is signalled through tcgen05.commit with a two-CTA mask.
 // Eight epilogue warps per CTA (two per TMEM lane quarter, splitting the columns) keep the exposed epilogue of a CTA's
-// last tile short.  PBN (256, 240, 224 or 192) is picked per problem so that the last wave of tiles is as full as
-// possible: integer tiles x CTA pairs rarely divide evenly, and a narrower tile can save a whole wave.
+// last tile short.
 //
-// Tail wave: work is a list of items handed out round-robin to the CTA pairs.  The first n_full tiles are one item
-// each; every tile behind them is TWO items of half the width (256 x PBN/2: an MMA with N = PBN/2, a B box of PBN/4
-// rows per CTA, same ring, same accumulator buffers).  The host chooses n_full so that the full tiles fill whole rounds
-// and the remainder runs as one round of half tiles: 4096^3 on 74 pairs is 3 rounds of 256 x 256 plus 68 half tiles
-// instead of 4 rounds, and the epilogue left exposed at the very end is that of a half tile.  Integer sums make every
-// tiling of the output bit-identical.
+// Tile widths are chosen per problem (PairTiling): an MMA of 256 x W x 32 costs W / 2 cycles for any W that is a multiple
+// of 16 from ~128 up, so tiles need not be equally wide.  The host cuts every 256-row band of the output into tiles
+// whose count over all bands is a whole number of rounds of the device's CTA pairs and whose widths differ by 16 within
+// a band; tiles are numbered widest first, so each round of the round-robin hands every pair (almost) the same
+// amount of work and the narrowest tiles - with the shortest epilogue - come last.  4096^3 on 74 pairs: 296 tiles of
+// 240 / 224 / 208 columns = exactly 4 rounds costing 240 + 224 + 224 + 208 = 896 columns, against 4 x 256 for uniform
+// 256-wide tiles (256 tiles, last round a third full) or 4 x 240 for uniform 240-wide ones (288 tiles, 224 wasted columns).
+// Two alternatives for the remainder behind the last whole round were built and measured: half-width tiles (an MMA
+// with N = 128 needs 24 KB stages at twice the rate, more bytes in flight than the ring holds: 9.1 us per half tile
+// against 9.6 us for a whole one) and splitting K over two pairs with an exchange of partial sums through L2 (the
+// exchange's three dependent L2 round trips cost 6 us).
 namespace {
 
-constexpr int P_STAGES = 6;
+constexpr int P_MAX_STAGES = 6;
 constexpr int P_THREADS = 64 + 8 * 32;  // producer warp, MMA warp, 8 epilogue warps
-
-template <int PBN>
-struct PCfg {
-    static constexpr int A_BYTES = BM * BK;
-    static constexpr int B_BYTES = (PBN / 2) * BK;  // this CTA's half of the tile's B rows
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int SMEM_BYTES = P_STAGES * STAGE_BYTES + 1024 + 2 * PBN * 4 + 256;
-    static constexpr bool HALVES = PBN == 256;      // half-width items exist for this tile width
-    static_assert(B_BYTES % 1024 == 0, "swizzled tiles must stay 1024-byte aligned");
-    static_assert(PBN % 16 == 0 && PBN >= 144 && PBN <= 256, "tile width");
-};
-
-// Work item `i` of a launch: tile row block, first column, and whether it is a half-width item.
-struct PairItem {
-    uint32_t tm, n0;
-    bool half;
-};
-template <int PBN>
-__device__ __forceinline__ PairItem pair_item(uint32_t i, uint32_t n_full, uint32_t tiles_n)
+constexpr int P_BN = 256;               // widest tile
+constexpr int P_A_BYTES = BM * BK;
+constexpr int P_B_BYTES = (P_BN / 2) * BK;  // room for this CTA's half of the widest tile's B rows
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_TAIL_BYTES = 1024 + 2 * P_BN * 4 + 256;  // alignment slack + column terms + barriers
+constexpr int P_PEER_STAGE_BYTES = 8 * PeerStage::BYTES_PER_WARP;
+inline size_t pair_smem_bytes(int stages, bool peer_stage)
 {
-    PairItem it;
-    it.half = i >= n_full;
-    uint32_t t = i, sel = 0;
-    if (it.half) {
-        const uint32_t j = i - n_full;
-        t = n_full + (j >> 1);
-        sel = j & 1u;
-    }
-    it.tm = t / tiles_n;
-    it.n0 = (t % tiles_n) * PBN + sel * (PBN / 2);
-    return it;
+    return (size_t)stages * P_STAGE_BYTES + P_TAIL_BYTES + (peer_stage ? P_PEER_STAGE_BYTES : 0);
+}
+
+struct PairTile {
+    uint32_t m0, n0, width, cls;
+};
+// (selects instead of indexing: a kernel parameter indexed with a run-time value would be copied to local memory)
+__device__ __forceinline__ uint32_t pick4(const uint32_t (&a)[4], uint32_t k)
+{
+    return k == 0 ? a[0] : (k == 1 ? a[1] : (k == 2 ? a[2] : a[3]));
+}
+__device__ __forceinline__ PairTile pair_tile(const PairTiling &tl, uint32_t t)
+{
+    uint32_t k = 0;
+    if (t >= tl.start[1]) k = 1;
+    if (t >= tl.start[2]) k = 2;
+    if (t >= tl.start[3]) k = 3;
+    const uint32_t local = t - pick4(tl.start, k), per_row = pick4(tl.per_row, k);
+    const uint32_t r = local / per_row, j = local - r * per_row;
+    PairTile pt;
+    pt.m0 = (pick4(tl.row0, k) + r) * (2 * BM);
+    pt.width = pick4(tl.width, k);
+    pt.n0 = pick4(tl.col0, k) + j * pt.width;
+    pt.cls = k;
+    return pt;
 }
 
 }  // namespace
 
-template <int PBN, int OUT>
+template <int OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 2)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_b_half, uint32_t M, uint32_t N, uint32_t K, uint32_t n_full,
-                    Epilogue epi, void *__restrict__ out, uint32_t *status)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0,
+                    const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
+                    const __grid_constant__ CUtensorMap map_b3, const PairTiling tl, uint32_t M, uint32_t N, uint32_t K,
+                    uint32_t stages, Epilogue epi, void *__restrict__ out, uint32_t *status)
 {
     griddep_launch_dependents();
-    using C = PCfg<PBN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t ring = (raw + 1023u) & ~1023u;
-    uint8_t *after = smem_raw + (ring - raw) + P_STAGES * C::STAGE_BYTES;
-    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                  // [2][PBN] column terms
-    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * PBN * 4);     // full[S] empty[S] tfull[2] tempty[2]
-    uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * P_STAGES + 4);  // [0] tmem base, [1] abort flag
+    uint8_t *after = smem_raw + (ring - raw) + stages * P_STAGE_BYTES;
+    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                  // [2][P_BN] column terms
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 2 * P_BN * 4);    // full[S] empty[S] tfull[2] tempty[2]
+    uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * P_MAX_STAGES + 4);  // [0] tmem base, [1] abort flag
     volatile uint32_t *abort_flag = s_misc + 1;
-    uint8_t *s_stage = after + 2 * PBN * 4 + 256;     // [8 warps][32 rows][128 B], only allocated when epi.staged
+    uint8_t *s_stage = after + 2 * P_BN * 4 + 256;    // [8 warps][32 rows][128 B], only allocated when epi.staged
 
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * P_STAGES;
-    const uint32_t tfull0 = empty0 + 8 * P_STAGES, tempty0 = tfull0 + 16;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * P_MAX_STAGES;
+    const uint32_t tfull0 = empty0 + 8 * P_MAX_STAGES, tempty0 = tfull0 + 16;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const uint32_t tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + PBN - 1) / PBN;
-    const uint32_t num_tiles = tiles_m * tiles_n;
-    if (!C::HALVES || n_full > num_tiles) n_full = num_tiles;
-    const uint32_t num_items = n_full + 2 * (num_tiles - n_full);
+    const uint32_t num_tiles = tl.num_tiles;
     const uint32_t num_kb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < P_STAGES; s++) {
+        for (uint32_t s = 0; s < stages; s++) {
             mbar_init(full0 + 8 * s, 1);    // leader's own arrive.expect_tx; bytes come from both CTAs
             mbar_init(empty0 + 8 * s, 1);   // the leader's commit, delivered to both CTAs
         }
@@ -312,8 +316,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     if (warp == 0 && lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-        if (C::HALVES) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b_half) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b0) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b2) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b3) : "memory");
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(s_misc), 512);
@@ -328,26 +334,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = s_misc[0];
 
     if (warp == 0) {
-        // ---------------- TMA producer (both CTAs): own A rows, own half of the item's B rows ----------------
+        // ---------------- TMA producer (both CTAs): own A rows, own half of the tile's B rows ----------------
+        // (Asking the boxes a few K blocks ahead into L2 with cp.async.bulk.prefetch.tensor was measured: 58 us instead of
+        // 46 us at 4096^3 - the prefetches take the TMA unit's time away from the loads.)
         if (lane == 0) {
             uint32_t st = 0, ph = 0;
             bool ok = true;
-            for (uint32_t i = pair; ok && i < num_items; i += num_pairs) {
-                const PairItem it = pair_item<PBN>(i, n_full, tiles_n);
-                const uint32_t b_rows = it.half ? PBN / 4 : PBN / 2;
-                const CUtensorMap *mb = it.half ? &map_b_half : &map_b;
-                const int32_t m0 = (int32_t)(it.tm * (2 * BM) + rank * BM);
-                const int32_t n0 = (int32_t)(it.n0 + rank * b_rows);
-                const uint32_t tx = 2u * (uint32_t)(C::A_BYTES + b_rows * BK);
+            for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
+                const PairTile pt = pair_tile(tl, t);
+                const uint32_t b_rows = pt.width / 2;
+                const CUtensorMap *mb = pt.cls == 0 ? &map_b0 : (pt.cls == 1 ? &map_b1 : (pt.cls == 2 ? &map_b2 : &map_b3));
+                const int32_t m0 = (int32_t)(pt.m0 + rank * BM);
+                const int32_t n0 = (int32_t)(pt.n0 + rank * b_rows);
+                const uint32_t tx = 2u * (uint32_t)(P_A_BYTES + b_rows * BK);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
                     if (!ok) break;
-                    const uint32_t a_dst = ring + st * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
+                    const uint32_t a_dst = ring + st * P_STAGE_BYTES, b_dst = a_dst + P_A_BYTES;
                     const uint32_t lbar = in_leader_cta(full0 + 8 * st);
                     if (rank == 0) mbar_expect_tx(full0 + 8 * st, tx);
                     tma_load_2d_pair(a_dst, &map_a, lbar, (int32_t)(kb * BK), m0);
                     tma_load_2d_pair(b_dst, mb, lbar, (int32_t)(kb * BK), n0);
-                    if (++st == P_STAGES) { st = 0; ph ^= 1; }
+                    if (++st == stages) { st = 0; ph ^= 1; }
                 }
             }
         }
@@ -355,20 +363,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only): warp-uniform loop, one elected lane issues ----------------
         if (rank == 0) {
-            constexpr uint32_t idesc_full = make_idesc_i8(2 * BM, PBN), idesc_half = make_idesc_i8(2 * BM, PBN / 2);
             uint32_t st = 0, ph = 0, as = 0, aph = 0;
             bool ok = true;
-            for (uint32_t i = pair; ok && i < num_items; i += num_pairs) {
-                const uint32_t idesc = (C::HALVES && i >= n_full) ? idesc_half : idesc_full;
+            for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
+                const uint32_t idesc = make_idesc_i8(2 * BM, (int)pair_tile(tl, t).width);
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + as * 256;
+                const uint32_t d_tmem = tmem_base + as * P_BN;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_src = ring + st * C::STAGE_BYTES, b_src = a_src + C::A_BYTES;
+                    const uint32_t a_src = ring + st * P_STAGE_BYTES, b_src = a_src + P_A_BYTES;
                     const uint64_t a_desc = make_smem_desc(a_src), b_desc = make_smem_desc(b_src);
                     if (elect_one()) {
                         umma_i8_pair(d_tmem, a_desc, b_desc, idesc, kb != 0u);
@@ -378,7 +385,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         umma_commit_pair(empty0 + 8 * st, 3);  // both CTAs may refill the stage
                     }
                     __syncwarp();
-                    if (++st == P_STAGES) { st = 0; ph ^= 1; }
+                    if (++st == stages) { st = 0; ph ^= 1; }
                 }
                 if (!ok) break;
                 if (elect_one()) umma_commit_pair(tfull0 + 8 * as, 3);  // accumulators complete in both CTAs
@@ -389,7 +396,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ---------------- epilogue (warps 2..9 of both CTAs): own 128 rows; two warps share a lane quarter ------------
         const uint32_t q = (uint32_t)warp & 3u;            // TMEM lane quarter this warp may read
-        const uint32_t h = (uint32_t)(warp - 2) >> 2;      // 0: lower column range of the item, 1: upper
+        const uint32_t h = (uint32_t)(warp - 2) >> 2;      // 0: lower column range of the tile, 1: upper
         const uint32_t et = threadIdx.x - 64;              // 0..255
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
@@ -401,12 +408,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint8_t *stage = s_stage + (warp - 2) * PeerStage::BYTES_PER_WARP;
         uint32_t as = 0, aph = 0;
         bool ok = true;
-        for (uint32_t i = pair; i < num_items; i += num_pairs) {
-            const PairItem it = pair_item<PBN>(i, n_full, tiles_n);
-            const uint32_t m0 = it.tm * (2 * BM) + rank * BM, n0 = it.n0;
-            const int width = it.half ? PBN / 2 : PBN;
-            const int split = it.half ? PBN / 4 : 128;     // columns [0, split) go to the h = 0 warps, the rest to h = 1
-            uint32_t *col = s_col + as * PBN;
+        for (uint32_t t = pair; t < num_tiles; t += num_pairs) {
+            const PairTile pt = pair_tile(tl, t);
+            const uint32_t m0 = pt.m0 + rank * BM, n0 = pt.n0;
+            const int width = (int)pt.width;
+            const int split = ((width / 2 + 15) / 16) * 16;   // columns [0, split) go to the h = 0 warps, the rest to h = 1
+            uint32_t *col = s_col + as * P_BN;
             for (uint32_t j = et; j < (uint32_t)width; j += 256) {
                 const uint32_t gj = n0 + j;
                 col[j] = gj < N ? epilogue_col_term(epi, c, gj) : 0u;
@@ -418,45 +425,48 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
             if (ok) {
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * 256;
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * P_BN;
                 const int cb = h ? split : 0, ce = h ? width : split;
                 const bool rows_full = m0 + q * 32 + 32 <= M;
-                uint32_t rsum = 0;  // sum of this row's uint8 outputs in this warp's part of the item
-                // One chunk of 16 accumulator columns.  Blocks of 128 output bytes per row go through the row-coalescing
-                // stage when results leave the GPU and the warp's 32 rows and the block's columns are all inside the
-                // matrix; everything else is stored directly.
-                auto chunk = [&](uint32_t (&v)[16], int cc) {
+                uint32_t rsum = 0;  // sum of this row's uint8 outputs in this warp's part of the tile
+                // One chunk of CW (32, or 16 for a remainder) accumulator columns.  Blocks of 128 output bytes per row go
+                // through the row-coalescing stage when results leave the GPU and the warp's 32 rows and the block's columns
+                // are all inside the matrix; everything else is stored directly.  (32-column chunks with two adjacent
+                // 16-byte stores per row measured 20 % faster than 16-column chunks with one, software-pipelined TMEM
+                // loads included: the stores, one 32-byte sector per row, are what the chunk waits for.)
+                auto chunk = [&](auto &v, int cc) {
+                    constexpr int CW = (int)(sizeof(v) / sizeof(uint32_t));
                     const uint32_t c0 = n0 + cc;
                     const int bc0 = cb + ((cc - cb) / BLOCK_COLS) * BLOCK_COLS;          // first column of cc's block
                     const int bcols = (ce - bc0) < BLOCK_COLS ? (ce - bc0) : BLOCK_COLS;  // its width
                     const bool via_stage = staged && rows_full && n0 + bc0 + bcols <= N;
                     if (via_stage) {
-                        uint32_t res[16];
-                        epilogue_convert<OUT, 16>(v, rt, col + cc, c, relu, sat, res);
-                        PeerStage::put<16>(stage, lane, (cc - bc0) * ESZ / 16, res, 16 * ESZ / 16);
-                        if (OUT == 0) rsum += packed_byte_sum<16>(res, 16);
-                        const int next = cc + 16;
+                        uint32_t res[CW];
+                        epilogue_convert<OUT, CW>(v, rt, col + cc, c, relu, sat, res);
+                        PeerStage::put<CW>(stage, lane, (cc - bc0) * ESZ / 16, res, CW * ESZ / 16);
+                        if (OUT == 0) rsum += packed_byte_sum<CW>(res, CW);
+                        const int next = cc + CW;
                         if (next == ce || (next - cb) % BLOCK_COLS == 0)   // the block is complete
                             PeerStage::flush(stage, lane, bcols * ESZ / 16, epi, out,
                                              ((uint64_t)(m0 + q * 32) * ldc + n0 + bc0) * ESZ, ldc * ESZ);
                     } else if (row < M && c0 < N) {
-                        rsum += epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
-                                                        vec_ok, (N - c0) < 16u ? (int)(N - c0) : 16);
+                        rsum += epilogue_chunk<OUT, CW>(v, rt, col + cc, c, relu, sat, epi, out, epilogue_offset(epi, row, c0, ldc),
+                                                        vec_ok, (N - c0) < (uint32_t)CW ? (int)(N - c0) : CW);
                     }
                 };
-                // Two register buffers: the TMEM load of the next chunk is in flight while this one is converted.
-                uint32_t va[16], vb[16];
-                tmem_ld16(taddr + cb, va);
+                int cc = cb;
 #pragma unroll 1
-                for (int cc = cb; cc < ce; cc += 32) {
+                for (; cc + 32 <= ce; cc += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + cc, v);
                     tmem_ld_wait();
-                    if (cc + 16 < ce) tmem_ld16(taddr + cc + 16, vb);
-                    chunk(va, cc);
-                    if (cc + 16 < ce) {
-                        tmem_ld_wait();
-                        if (cc + 32 < ce) tmem_ld16(taddr + cc + 32, va);
-                        chunk(vb, cc + 16);
-                    }
+                    chunk(v, cc);
+                }
+                if (cc < ce) {  // widths are multiples of 16
+                    uint32_t v[16];
+                    tmem_ld16(taddr + cc, v);
+                    tmem_ld_wait();
+                    chunk(v, cc);
                 }
                 if (OUT == 0 && epi.out_rowsum && row < M) atomicAdd(&epi.out_rowsum[row], (int32_t)rsum);
                 // this warp has read its part of the accumulator: tell the leader's MMA warp (in this or the other CTA)
@@ -545,52 +555,38 @@ cudaError_t launch_out(const CUtensorMap &ma, const CUtensorMap &mb, uint64_t M,
 
 namespace {
 
-template <int PBN, int OUT>
-cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mbh, uint32_t n_full, uint64_t M,
-                        uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
-                        cudaStream_t stream)
+template <int OUT>
+cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap *const mb[4], const PairTiling &tl, uint64_t M, uint64_t N,
+                        uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
 {
-    using C = PCfg<PBN>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    // With further destinations (peer GPUs) the epilogue warps get a row-coalescing stage, where it fits beside the ring.
-    constexpr int STAGE_BYTES = 8 * PeerStage::BYTES_PER_WARP;
-    constexpr bool STAGE_FITS = C::SMEM_BYTES + STAGE_BYTES <= 227 * 1024;
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<PBN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             C::SMEM_BYTES + (STAGE_FITS ? STAGE_BYTES : 0));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)pair_smem_bytes(P_MAX_STAGES, false));
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    const uint64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + PBN - 1) / PBN);
-    if (!C::HALVES || n_full > tiles) n_full = (uint32_t)tiles;
-    const uint64_t items = n_full + 2 * (tiles - n_full);
-    const uint64_t pairs = items < (uint64_t)(sms / 2) ? items : (uint64_t)(sms / 2);
+    const uint64_t all_pairs = (uint64_t)(sms / 2);
+    const uint64_t pairs = tl.num_tiles < all_pairs ? tl.num_tiles : all_pairs;
+    // With further destinations (peer GPUs) the epilogue warps get a row-coalescing stage in place of one ring stage
+    // (such launches are bound by the links, not by the tensor pipe).  Local-only stores gain nothing from it: measured.
     Epilogue epi_l = epi;
-    epi_l.staged = (epi.n_more > 0 && STAGE_FITS) ? 1 : 0;  // (local-only stores gain nothing from the stage: measured)
-    const size_t smem = C::SMEM_BYTES + (epi_l.staged ? STAGE_BYTES : 0);
-    cudaError_t e = launch_chained(gemm_tc_pair_kernel<PBN, OUT>, dim3((unsigned)(2 * pairs)), dim3(P_THREADS), smem, stream,
-                                   ma, mb, mbh, (uint32_t)M, (uint32_t)N, (uint32_t)K, n_full, epi_l, out, status);
+    epi_l.staged = epi.n_more > 0 ? 1 : 0;
+    uint32_t stages = epi_l.staged ? P_MAX_STAGES - 1 : P_MAX_STAGES;
+    if (const char *e = getenv("LTQ_PAIR_STAGES")) stages = (uint32_t)atoi(e);  // TEMP experiment
+    const size_t smem = pair_smem_bytes((int)stages, epi_l.staged != 0);
+    cudaError_t e = launch_chained(gemm_tc_pair_kernel<OUT>, dim3((unsigned)(2 * pairs)), dim3(P_THREADS), smem, stream, ma,
+                                   *mb[0], *mb[1], *mb[2], *mb[3], tl, (uint32_t)M, (uint32_t)N, (uint32_t)K, stages,
+                                   epi_l, out, status);
     count_launch();
-    if (items != tiles)
-        note_kernel("gemm_tc_pair_kernel<%d,%s> (%llu tiles + %llu half-width items)", PBN, out_mode_name(OUT),
-                    (unsigned long long)n_full, (unsigned long long)(items - n_full));
-    else
-        note_kernel("gemm_tc_pair_kernel<%d,%s>", PBN, out_mode_name(OUT));
+    char widths[48];
+    int n = 0;
+    for (int k = 0; k < 4 && tl.start[k] < tl.num_tiles; k++)
+        n += snprintf(widths + n, sizeof widths - n, "%s%u", k ? "/" : "", tl.width[k]);
+    note_kernel("gemm_tc_pair_kernel<%s> (%u tiles of %s columns)", out_mode_name(OUT), tl.num_tiles, widths);
     return e;
-}
-
-template <int PBN>
-cudaError_t launch_pair_out(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mbh, uint32_t n_full,
-                            uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
-                            cudaStream_t stream)
-{
-    switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_pair<PBN, 0>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-        case LTQ_OUT_F32: return launch_pair<PBN, 1>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-        default: return launch_pair<PBN, 2>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-    }
 }
 
 }  // namespace
@@ -603,56 +599,69 @@ bool tc_pair_preferred(uint64_t M, uint64_t N, int sms)
     return M > (uint64_t)BM && tiles * 4 >= (uint64_t)(sms / 2) * 3;
 }
 
-bool tail_split_enabled()
+PairTiling tc_pair_tiling(uint64_t M, uint64_t N, int sms, bool unit32)
 {
-    static const bool on = getenv("LTQ_NO_TAIL_SPLIT") == nullptr;  // debugging / A-B switch
-    return on;
-}
-
-PairPlan tc_pair_plan(uint64_t M, uint64_t N, int sms, bool peer_stores, bool chunks_aligned_32)
-{
-    // Time ~ sum over the rounds of items handed to the CTA pairs of the round's item width.  Wider tiles reuse operands
-    // better, so a narrower one must win by a clear margin (3 %).  With 256-wide tiles the remainder behind the last
-    // whole round may run as half-width items.
-    const uint64_t tm = (M + 2 * BM - 1) / (2 * BM), pairs = (uint64_t)(sms / 2);
-    PairPlan best{peer_stores ? 224 : 256, 0xFFFFFFFFu};
-    double best_cost = 1e30;
-    for (int bn : {256, 240, 224, 192}) {
-        if (peer_stores && bn == 256) continue;  // no room for the row-coalescing stage beside a 6 x 32 KB ring
-        if (chunks_aligned_32 && bn % 32 != 0) continue;  // column-blocked outputs: chunks must not straddle a block
-        const uint64_t tiles = tm * ((N + bn - 1) / bn);
-        double cost = (double)((tiles + pairs - 1) / pairs) * bn;
-        uint32_t n_full = 0xFFFFFFFFu;
-        if (bn == 256 && tail_split_enabled() && tiles > pairs) {
-            const uint64_t whole = tiles / pairs, rem = tiles - whole * pairs;
-            if (rem != 0 && 2 * rem <= pairs) {  // the remainder fits one round of half tiles
-                cost = (double)whole * bn + bn / 2;
-                n_full = (uint32_t)(whole * pairs);
-            }
+    // Every 256-row band is cut into tiles whose widths are multiples of `unit` columns and differ by at most one unit
+    // within the band.  The number of tiles over all bands is the smallest whole number of rounds of the CTA pairs that
+    // keeps every tile at most 256 columns wide (uniform 256-wide tiles when that would make tiles narrower than 128
+    // columns: a narrow MMA no longer costs in proportion to its width).
+    const uint64_t unit = unit32 ? 32 : 16, wmax = P_BN / unit;
+    const uint64_t TM = (M + 2 * BM - 1) / (2 * BM), U = (N + unit - 1) / unit, P = (uint64_t)(sms / 2);
+    const uint64_t c_min = (U + wmax - 1) / wmax;             // tiles per band at full width
+    uint64_t T = ((TM * c_min + P - 1) / P) * P;               // whole rounds that hold at least that many tiles
+    if (T / TM > U) T = TM * U;                                // (never narrower than one unit)
+    if ((U / ((T + TM - 1) / TM)) * unit < 128) T = TM * c_min;
+    const uint64_t c_lo = T / TM, n_hi = T % TM, n_lo = TM - n_hi;
+    struct Cls {
+        uint64_t row0, rows, per_row, col0, w;
+    } cls[4];
+    int nc = 0;
+    auto band = [&](uint64_t row0, uint64_t rows, uint64_t c) {
+        if (rows == 0 || c == 0) return;
+        const uint64_t base = U / c, extra = U % c;
+        if (extra) cls[nc++] = Cls{row0, rows, extra, 0, (base + 1) * unit};
+        if (c - extra) cls[nc++] = Cls{row0, rows, c - extra, extra * (base + 1) * unit, base * unit};
+    };
+    band(0, n_lo, c_lo);
+    band(n_lo, n_hi, c_lo + 1);
+    for (int a = 1; a < nc; a++)  // widest first (insertion sort, stable)
+        for (int b = a; b > 0 && cls[b].w > cls[b - 1].w; b--) {
+            const Cls tmp = cls[b];
+            cls[b] = cls[b - 1];
+            cls[b - 1] = tmp;
         }
-        if (cost < best_cost * 0.97) {
-            best_cost = cost;
-            best = PairPlan{bn, n_full};
+    PairTiling tl;
+    uint64_t start = 0;
+    for (int k = 0; k < 4; k++) {
+        if (k < nc) {
+            tl.start[k] = (uint32_t)start;
+            tl.per_row[k] = (uint32_t)cls[k].per_row;
+            tl.row0[k] = (uint32_t)cls[k].row0;
+            tl.col0[k] = (uint32_t)cls[k].col0;
+            tl.width[k] = (uint32_t)cls[k].w;
+            start += cls[k].rows * cls[k].per_row;
+        } else {
+            tl.start[k] = 0xFFFFFFFFu;
+            tl.per_row[k] = 1;
+            tl.row0[k] = tl.col0[k] = 0;
+            tl.width[k] = nc ? tl.width[nc - 1] : 256;
         }
     }
-    return best;
+    tl.num_tiles = (uint32_t)start;
+    return tl;
 }
 
-cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, const TcOperandMap *map_b_half,
-                                const PairPlan &plan, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi, void *out,
-                                uint32_t *status, int sms, cudaStream_t stream)
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap *const map_b[4], const PairTiling &tl, uint64_t M,
+                                uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
+                                cudaStream_t stream)
 {
     const CUtensorMap &ma = *reinterpret_cast<const CUtensorMap *>(map_a.opaque);
-    const CUtensorMap &mb = *reinterpret_cast<const CUtensorMap *>(map_b.opaque);
-    // without half-width items the third map is never dereferenced; pass the full-width one
-    const CUtensorMap &mbh = *reinterpret_cast<const CUtensorMap *>(map_b_half ? map_b_half->opaque : map_b.opaque);
-    const uint32_t n_full = map_b_half ? plan.n_full : 0xFFFFFFFFu;
-    switch (plan.bn) {
-        case 256: return launch_pair_out<256>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-        case 240: return launch_pair_out<240>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-        case 224: return launch_pair_out<224>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-        case 192: return launch_pair_out<192>(ma, mb, mbh, n_full, M, N, K, epi, out, status, sms, stream);
-        default: return cudaErrorInvalidValue;
+    const CUtensorMap *mb[4];
+    for (int k = 0; k < 4; k++) mb[k] = reinterpret_cast<const CUtensorMap *>(map_b[k]->opaque);
+    switch (epi.out_mode) {
+        case LTQ_OUT_U8: return launch_pair<0>(ma, mb, tl, M, N, K, epi, out, status, sms, stream);
+        case LTQ_OUT_F32: return launch_pair<1>(ma, mb, tl, M, N, K, epi, out, status, sms, stream);
+        default: return launch_pair<2>(ma, mb, tl, M, N, K, epi, out, status, sms, stream);
     }
 }
 

@@ -27,21 +27,21 @@ bool tc_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *
 int tc_pick_bn(uint64_t M, uint64_t N, int sms);
 // Encodes a map; box_rows is 128 for the A operand and the tile width for the B operand. 0 on success.
 int tc_make_map(TcOperandMap *m, const uint8_t *base, uint64_t rows, uint64_t K, int box_rows);
-// CTA-pair variant (256 x bn tiles, tcgen05.mma.cta_group::2).  tc_pair_preferred says when the problem is large
-// enough; tc_pair_plan picks the tile width (256, 240, 224 or 192) and, for 256, how many tiles run at full width
-// before the rest is handed out as half-width items (n_full = 0xFFFFFFFF: all of them), whichever leaves the fullest
-// last round.  map_a uses 128-row boxes, map_b boxes of bn / 2 rows (each CTA of a pair loads half of the tile's B
-// rows), map_b_half boxes of bn / 4 rows (needed only when the plan has half-width items; may be NULL otherwise).
-struct PairPlan {
-    int bn;
-    uint32_t n_full;
-    bool has_halves() const { return n_full != 0xFFFFFFFFu; }
+// CTA-pair variant (256-row tiles, tcgen05.mma.cta_group::2).  tc_pair_preferred says when the problem is large enough.
+// tc_pair_tiling cuts the output into tiles of up to four widths (multiples of 16 columns, or of 32 with `unit32`, at
+// most 256), numbered widest first in up to four classes: tiles [start[k], start[k+1]) belong to class k, which covers
+// tile rows row0[k] ... with per_row[k] tiles each, the first at column col0[k], all width[k] wide.  Unused classes
+// have start = 0xFFFFFFFF.  map_a uses 128-row boxes; map_b[k] boxes of width[k] / 2 rows (each CTA of a pair loads half
+// of a tile's B rows); entries of unused classes may repeat a used one.
+struct PairTiling {
+    uint32_t num_tiles;
+    uint32_t start[4], per_row[4], row0[4], col0[4], width[4];
 };
 bool tc_pair_preferred(uint64_t M, uint64_t N, int sms);
-PairPlan tc_pair_plan(uint64_t M, uint64_t N, int sms, bool peer_stores = false, bool chunks_aligned_32 = false);
-cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap &map_b, const TcOperandMap *map_b_half,
-                                const PairPlan &plan, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi, void *out,
-                                uint32_t *status, int sms, cudaStream_t stream);
+PairTiling tc_pair_tiling(uint64_t M, uint64_t N, int sms, bool unit32);
+cudaError_t launch_gemm_tc_pair(const TcOperandMap &map_a, const TcOperandMap *const map_b[4], const PairTiling &tl, uint64_t M,
+                                uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, int sms,
+                                cudaStream_t stream);
 // 3-D view of the same kind of matrix for the weight-streaming kernel (K % 128 == 0): dims {128 B line, rows, K/128
 // lines}, box {128 B, box_rows, box_lines}.  One box lands in shared memory as [line][row][128 B]; with the 128-byte
 // swizzle the 16-byte chunk index is XORed with the low three bits of (line * box_rows + row), so the rows of a box

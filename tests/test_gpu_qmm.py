@@ -152,7 +152,7 @@ def test_pair_kernel_half_width_tail(cuda, oracle, shape):
     acc = oracle.port.acc_i32(a, w, M, N, K, 77, 131, bias=bias)
     force = ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR
     np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_I32, force), acc)
-    assert "half-width items" in ltq.last_kernel(), ltq.last_kernel()
+    assert "tiles of" in ltq.last_kernel(), ltq.last_kernel()
     for fl in (0, ltq.FLAG_RELU, ltq.FLAG_SATURATE):
         np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_U8, force | fl),
                                       oracle.port.epilogue_u8(acc, 0.02, 0.005, 0.9, 100, relu=bool(fl & ltq.FLAG_RELU),
