@@ -190,3 +190,44 @@ def test_matmul_u8_plain_int32_product_and_modes(cuda, oracle, tA, tB):
                                   oracle.port.epilogue_f32(acc, 0.02, 0.005, relu=True))
     np.testing.assert_array_equal(ltq.matmul_u8(Ad, Bd, tA, tB, qps, bd, ltq.OUT_U8).cpu().numpy(),
                                   oracle.port.epilogue_u8(acc, 0.02, 0.005, 0.9, 3))
+
+
+@pytest.mark.parametrize("path", ["tc", "tcpair"])
+@pytest.mark.parametrize("rm_case", ["small", "medium", "large"])
+def test_epilogue_conversion_free_path_boundaries(cuda, oracle, path, rm_case):
+    """The tensor-core epilogues convert without I2F / F2I while the accumulator is inside a range derived from the real
+    multiplier and the output zero point, and fall back to the general conversion outside it.  Accumulators are steered
+    through the bias (activations all equal to their zero point, so acc[i, j] = bias[j]) across every boundary of that
+    range: around 0, around -zC/rm and 2^23/rm, around +-2^22, and the int32 extremes."""
+    import ltq
+    M, K = (256, 64) if path == "tc" else (512, 64)
+    sa, sw = np.float32(0.02), np.float32(0.005)
+    sc = {"small": np.float32(0.37), "medium": np.float32(1e-4), "large": np.float32(1e-7)}[rm_case]
+    zc = 37
+    rm = float(np.float32(sa * sw) / sc)
+    pts = [0, 1, -1, 255, -255, 2 ** 22, -2 ** 22, 2 ** 23, -2 ** 23, 2 ** 24 + 3, -2 ** 24 - 3, 2 ** 31 - 1, -2 ** 31,
+           int(-zc / rm), int((2 ** 23 - 512 - zc) / rm), int((2 ** 23 - zc) / rm), int(2 ** 31 / rm), int(-2 ** 31 / rm)]
+    vals = []
+    for p in pts:
+        for d in range(-40, 41):
+            for scale in (1, 1000):
+                vals.append(min(2 ** 31 - 1, max(-2 ** 31, p + d * scale)))
+    rng = np.random.default_rng(9)
+    vals += list(rng.integers(-2 ** 22, 2 ** 22, 700)) + list(rng.integers(-2 ** 31, 2 ** 31, 300))
+    N = (len(vals) + 255) // 256 * 256
+    bias = np.zeros(N, dtype=np.int32)
+    bias[:len(vals)] = np.array(vals, dtype=np.int64).astype(np.int32)
+    a = np.full((M, K), 9, dtype=np.uint8)           # equal to its zero point: contributes nothing
+    w = rng.integers(0, 256, (N, K), dtype=np.uint8)
+    qps = (ltq.QParams(sa, 9), ltq.QParams(sw, 131), ltq.QParams(sc, zc))
+    acc = oracle.port.acc_i32(a, w, M, N, K, 9, 131, bias=bias)
+    assert np.array_equal(acc[0], bias)
+    force = ltq.FLAG_FORCE_TC | (ltq.FLAG_FORCE_TC_SINGLE if path == "tc" else ltq.FLAG_FORCE_TC_PAIR)
+    for relu in (False, True):
+        fl = force | (ltq.FLAG_RELU if relu else 0)
+        np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_U8, fl),
+                                      oracle.port.epilogue_u8(acc, sa, sw, sc, zc, relu=relu))
+        got = _run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_F32, fl)
+        np.testing.assert_array_equal(got.view(np.uint32), oracle.port.epilogue_f32(acc, sa, sw, relu=relu).view(np.uint32))
+    np.testing.assert_array_equal(_run_layer(cuda, ltq, a, w, bias, qps, ltq.OUT_U8, force | ltq.FLAG_SATURATE),
+                                  oracle.port.epilogue_u8(acc, sa, sw, sc, zc, saturate=True))
