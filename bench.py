@@ -1,17 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the uint8 quantized fully-connected forward path (libltq, sm_100a).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload square_4096|skinny|mlp_block|mlp_mnist|conv] [--shard rows|cols|cols_fused]
-    python bench.py --impl reference ...      # the reference's own CPU code on the host cores
+    python bench.py [--gpus N] [--steps K] [--warmup W]          # everything the metric names, one JSON line
+    python bench.py --workload square_4096|skinny|mlp_block|mlp_mnist|conv [--shard rows|cols|cols_fused] ...
+    python bench.py --impl reference ...                          # the reference's own CPU code on the host cores
 
-One JSON line on stdout (rank 0).  A step is one pass of the hot path over one batch: activation quantise
-(fp32 -> uint8 + row sums, static calibrated qparams as the reference uses them) followed by the quantized GEMM with
-its fused epilogue.  `value` has the inputs resident in HBM; `e2e` is the same work through the FullyConnected_q
-mirror with pinned host buffers, host->device and device->host copies inside the timed region.
+One JSON line on stdout (rank 0).  The headline (`value`, `ms_per_step`, `roofline`, `e2e`, `cpu_baseline`) is the
+4096^3 quantized linear: a step is one pass of the hot path over one batch, activation quantise (fp32 -> uint8 + row
+sums, static calibrated qparams as the reference uses them) followed by the quantized GEMM with its fused epilogue.
+`value` has the inputs resident in HBM; `e2e` is the same work through the FullyConnected_q mirror with pinned host
+buffers, host->device and device->host copies inside the timed region.  The default run also measures the other parts
+of the metric and reports them as sections of the same line: `skinny` (M = 1 / 4 / 16 weight streaming, HBM GB/s),
+`mlp_mnist` (784-512-512-10, samples/s), `mlp_block_rows` (8192-32768-8192 over 65536 tokens, row-sharded over the
+ranks, strong scaling) and, with more than one rank, `mlp_block_cols` / `mlp_block_cols_fused` (column-sharded with an
+NCCL all-gather, and with the exchange fused into the GEMM epilogue).
 """
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -37,6 +44,28 @@ def peaks():
     return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
 
 
+def ncu_traffic(profile_md, kernel_launched):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, read from the ncu
+    summary committed under profiles/.  Returns (bytes or None, note): None when the summary is missing or was captured
+    on another kernel than the one this run launched, so that the figure cannot outlive a kernel change unnoticed."""
+    path = os.path.join(ROOT, "profiles", profile_md)
+    if not os.path.exists(path):
+        return None, f"profiles/{profile_md} not found"
+    text = open(path).read()
+    title = text.splitlines()[0]
+    unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    total = 0.0
+    for key in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+        m = re.search(r"`" + re.escape(key) + r"`\s*\|\s*([0-9.,]+)\s*([A-Za-z]+)", text)
+        if not m:
+            return None, f"profiles/{profile_md} has no {key}"
+        total += float(m.group(1).replace(",", "")) * unit.get(m.group(2), 1.0)
+    base = kernel_launched.split("<")[0]
+    if base not in title:
+        return None, f"profiles/{profile_md} covers '{title.lstrip('# ')}', this run launched {kernel_launched}"
+    return total, f"profiles/{profile_md}"
+
+
 class ClockSampler:
     """Samples nvidia-smi during the timed region (SM clock, throttle reasons)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -47,6 +76,7 @@ class ClockSampler:
         self.idx, self.rows, self.proc = gpu_index, [], None
 
     def start(self):
+        self.rows = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
@@ -69,6 +99,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        self.proc = None
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
@@ -126,7 +157,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    wl = args.workload
+    wl = "skinny" if args.workload == "skinny" else "square_4096"
     # size the sample so that warmup + steps finish within a couple of minutes
     t_probe, kind, m0, N, K = cpu_forward_seconds(wl, 8)
     per_row = t_probe / m0
@@ -164,9 +195,29 @@ def workload_name(wl):
 # ---------------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------------------------
-# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/ (same command lines as the bench, fewer steps).
-NCU_TRAFFIC = {"gemm_tc_pair_kernel": 34.5e6, "gemv_kernel": 45.3e6}
+def bind_to_gpu_numa_node(local_rank):
+    """Keeps this rank's host threads (and so the first touch of its pinned buffers) on the NUMA node its GPU hangs off.
+    Returns a short description for the JSON line; does nothing when the node cannot be determined."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev = torch.cuda.get_device_properties(local_rank).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return "numa node unknown (single node or not exposed)"
+        cpus = open(f"/sys/devices/system/node/node{node}/cpulist").read().strip()
+        ids = set()
+        for part in cpus.split(","):
+            a, _, b = part.partition("-")
+            ids.update(range(int(a), int(b or a) + 1))
+        ids &= os.sched_getaffinity(0)
+        if ids:
+            os.sched_setaffinity(0, ids)
+        return f"node {node}, cpus {cpus}"
+    except Exception as exc:  # noqa: BLE001 - best effort; the bench runs without it
+        return f"not bound ({type(exc).__name__})"
 
 
 class Harness:
@@ -183,6 +234,7 @@ class Harness:
             raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback (use --impl reference)")
         torch.cuda.set_device(self.local)
         self.dev = torch.device("cuda", self.local)
+        self.numa = bind_to_gpu_numa_node(self.local)
         self.dist = None
         if self.world > 1:
             import torch.distributed as dist
@@ -196,18 +248,30 @@ class Harness:
             self.dist.barrier()
             self.torch.cuda.synchronize()
 
-    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False, join=None, capture_stream=None):
+    def max_over_ranks(self, ms):
+        if self.dist is not None:
+            t = self.torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def timed(self, fn, steps, warmup, graph=True, sample_clocks=False, join=None, capture_stream=None, sustain_s=0.0,
+              local_only=False):
         """ms per step over EXACTLY `steps` steps, CUDA events on the launching stream, max over ranks.  The steps are
         captured once into a CUDA graph (the kernels run for tens of microseconds; launching them one by one from
         Python would time the interpreter) and the graph is replayed once untimed before the timed replay.  With
         `sample_clocks` nvidia-smi runs through the warm-up, the timed replay and ~0.4 s of further replays of the same
-        graph (the timed region alone is too short to catch more than a sample or two)."""
+        graph (the timed region alone is too short to catch more than a sample or two).  With `sustain_s` the same graph
+        is then replayed back to back for at least that long, timed with events as one region, and
+        `self.sustained` = {ms_per_step, seconds, sm_mhz} describes it.  `local_only`: no barrier / reduction (a
+        section that only rank 0 runs)."""
         torch = self.torch
+        sync = torch.cuda.synchronize if local_only else self.sync_all
         if sample_clocks and self.rank == 0:
             self.sampler.start()
         for i in range(warmup):
             fn(i)
-        self.sync_all()
+        sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         gr = None
         if graph:
@@ -216,7 +280,7 @@ class Harness:
                 for i in range(steps):
                     fn(warmup + i)
             gr.replay()
-            self.sync_all()
+            sync()
             e0.record()
             gr.replay()
             e1.record()
@@ -227,7 +291,7 @@ class Harness:
             if join is not None:
                 join()  # the timing stream waits for work the steps put on other streams
             e1.record()
-        self.sync_all()
+        sync()
         ms = e0.elapsed_time(e1)
         if sample_clocks:
             t_end = time.time() + 0.4
@@ -238,10 +302,24 @@ class Harness:
                     fn(0)
                 torch.cuda.synchronize()
             self.clocks = self.sampler.stop() if self.rank == 0 else None
-        if self.dist is not None:
-            t = torch.tensor([ms], device=self.dev)
-            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
-            ms = float(t.item())
+        if sustain_s > 0 and gr is not None:
+            # back-to-back replays without host synchronisation in between: the GPU stays under load for the whole region
+            reps = max(8, int(sustain_s / max(ms * 1e-3, 1e-6)) + 1)
+            if self.rank == 0:
+                self.sampler.start()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(reps):
+                gr.replay()
+            s1.record()
+            torch.cuda.synchronize()
+            clk = self.sampler.stop() if self.rank == 0 else None
+            tot = s0.elapsed_time(s1)
+            self.sustained = {"ms_per_step": tot / (reps * steps), "seconds": tot * 1e-3,
+                              "sm_mhz_median": clk["sm_mhz"] if clk else None,
+                              "reasons": clk["reasons"] if clk else None}
+        if not local_only:
+            ms = self.max_over_ranks(ms)
         return ms / steps
 
     def finish(self, line):
@@ -259,15 +337,33 @@ def base_line(h, args, value, unit, ms_step, scaling, config, **extra):
     return line
 
 
-def run_linear(args):
-    """square_4096 (default) and skinny: one quantized linear per step."""
+def h2d_ceiling_gbs(h, nbytes):
+    """Host->device rate of a copy of `nbytes` out of pinned memory with nothing else running, every rank at the same
+    time (GB/s, this rank; best of 5)."""
+    torch = h.torch
+    src = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=h.dev)
+    dst.copy_(src, non_blocking=True)
+    h.sync_all()
+    best = 0.0
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dst.copy_(src, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    return best
+
+
+# ---- the 4096^3 linear and the skinny linear ---------------------------------------------------------------------------
+def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=0.0):
+    """One quantized linear per step.  Returns a dict of measurements (times are max over ranks)."""
     import ltq
-    h = Harness(args)
-    torch, dev, world = h.torch, h.dev, h.world
-    pk = peaks()
-    wl = args.workload
+    torch, dev = h.torch, h.dev
+    steps = steps or args.steps
     if wl == "skinny":
-        M, K, N = args.m, 4096, 11008
+        M, K, N = m_rows, 4096, 11008
         out_mode, out_dtype = ltq.OUT_F32, torch.float32
         sets = 6       # 6 x 45 MB of weights: every step streams weights that are not in L2
     else:
@@ -277,7 +373,7 @@ def run_linear(args):
     g = torch.Generator(device=dev).manual_seed(1234 + h.rank)
     xs = [torch.randn((M, K), generator=g, device=dev) for _ in range(sets)]
     w32 = [torch.randn((N, K), generator=g, device=dev) * 0.02 for _ in range(sets)]
-    layers, qps_x = [], []
+    layers, qps_x, qps_w, qps_o, wqs = [], [], [], [], []
     for i in range(sets):
         qw = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(w32[i])))
         wq = ltq.Quantize(w32[i], qw)
@@ -290,6 +386,9 @@ def run_linear(args):
         lh.set_qparams(qx, qw, qo)
         layers.append(lh)
         qps_x.append(qx)
+        qps_w.append(qw)
+        qps_o.append(qo)
+        wqs.append(wq)
     del w32
     xq = [torch.empty((M, K), dtype=torch.uint8, device=dev) for _ in range(sets)]
     asum = [torch.empty(M, dtype=torch.int32, device=dev) for _ in range(sets)]
@@ -328,29 +427,37 @@ def run_linear(args):
         layers[s].forward(xq[s], out_mode, 0, asum=asum[s], out=outs[s])
 
     launches0 = ltq.kernel_launches()
-    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True,
+    ms_step = h.timed(step, steps, args.warmup, graph=not args.no_graph, sample_clocks=True,
                       capture_stream=torch.cuda.Stream(priority=-1))
     # kernels per timed region: warm-up steps and the capture pass each launch the same list; replays re-run it
-    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
-    ms_gemm = h.timed(gemm_only, args.steps, max(3, args.warmup), graph=not args.no_graph)
+    launches = (ltq.kernel_launches() - launches0) // (steps + args.warmup) * steps
+    clocks = getattr(h, "clocks", None)
+    h.sustained = None
+    ms_gemm = h.timed(gemm_only, steps, max(3, args.warmup), graph=not args.no_graph, sustain_s=sustain_s)
+    kernel = ltq.last_kernel()
+    sustained = h.sustained
     ms_quant = h.timed(lambda i: ltq.quantize_rows(xs[i % sets], qp=qps_x[i % sets], q=xq[i % sets], asum=asum[i % sets]),
-                       args.steps, 3, graph=not args.no_graph)
+                       steps, 3, graph=not args.no_graph)
     for lh in layers:
         lh.check()
 
-    ops = 2.0 * M * N * K
-    tops = ops / (ms_step * 1e-3) / 1e12 * world
-    gemm_tops = ops / (ms_gemm * 1e-3) / 1e12
+    res = dict(M=M, N=N, K=K, sets=sets, ms_step=ms_step, ms_gemm=ms_gemm, ms_quant=ms_quant, launches=int(launches),
+               kernel=kernel, clocks=clocks, sustained=sustained, step_overlapped=step is step_overlap,
+               esize=4 if out_mode == ltq.OUT_F32 else 1, e2e=None)
 
     # ---- end to end through the FullyConnected_q mirror with host buffers -----------------------------------------
-    esize = 4 if out_mode == ltq.OUT_F32 else 1
-    e2e = None
-    if not args.no_e2e:
+    if with_e2e and not args.no_e2e:
+        # The layer is built the way a user of the reference builds it: init(), quantized weights written through
+        # get_all_weights() on the host, qparams through the setters, then to("cuda").
         fc = ltq.FullyConnected_q(K, N, False)
         fc.init()
-        fc.weight_ptr_ = layers[0]._keep[0].view(1, 1, N, K)  # device weights already quantized above
-        fc._handle = layers[0]
+        fc.get_all_weights()[0].copy_(wqs[0].cpu().view(1, 1, N, K))
+        fc.set_qparams_in(qps_x[0])
+        fc.set_qparams_out(qps_o[0])
+        fc.set_qparams_params([qps_w[0]], 1)
+        fc.to("cuda", h.local)
         fc.set_output(out_mode)
+        ceiling = h2d_ceiling_gbs(h, M * K * 4)
         # Three streams (upload, compute, download) over two buffer sets: the upload of step i+1 and the download of
         # step i-1 run while step i computes, so a step costs what the slower PCIe direction costs.
         host_x = [torch.randn((M, K)).pin_memory() for _ in range(2)]
@@ -386,25 +493,67 @@ def run_linear(args):
             for st in (s_up, s_run, s_down):
                 torch.cuda.current_stream().wait_stream(st)
 
-        ms_e2e = h.timed(e2e_step, max(4, args.steps // 2), 4, graph=False, join=e2e_join)
-        fc._handle = None
-        e2e = {"value": ops / (ms_e2e * 1e-3) / 1e12 * world, "unit": "TOPS", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * esize}
+        ms_e2e = h.timed(e2e_step, max(4, steps // 2), 4, graph=False, join=e2e_join)
+        h2d, d2h = M * K * 4, M * N * res["esize"]
+        res["e2e"] = {"ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                      "pcie_gbs": {"h2d": h2d / (ms_e2e * 1e-3) / 1e9, "d2h": d2h / (ms_e2e * 1e-3) / 1e9},
+                      "h2d_ceiling_gbs": ceiling, "frac_of_h2d_ceiling": h2d / (ms_e2e * 1e-3) / 1e9 / ceiling,
+                      "bound": "host->device copy of the fp32 activations (PCIe); compute is "
+                               f"{ms_step / ms_e2e * 100:.1f} % of the step",
+                      "host_numa_binding": h.numa}
+    return res
+
+
+def skinny_roofline(r, pk, traffic, traffic_note):
+    M, N, K, esize = r["M"], r["N"], r["K"], r["esize"]
+    alg_bytes = N * K + M * K + esize * M * N + 8 * N + 4 * M  # weights + acts + out + (wsum, bias) + asum
+    achieved = alg_bytes / (r["ms_gemm"] * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+            "traffic": traffic, "traffic_source": traffic_note, "kernel": r["kernel"], "algorithmic_bytes": alg_bytes,
+            "ms": r["ms_gemm"], "peak_source": f"{pk['source']} HBM copy",
+            "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS}
+
+
+def run_linear(args, h=None, sections=False):
+    """square_4096 (default) and skinny: one quantized linear per step.  With `sections` (the default run) the other
+    parts of the metric are measured too and attached to the same line."""
+    import ltq
+    h = h or Harness(args)
+    world = h.world
+    pk = peaks()
+    wl = args.workload if args.workload in ("square_4096", "skinny") else "square_4096"
+    r = measure_linear(h, args, wl, m_rows=args.m, sustain_s=1.2 if wl == "square_4096" else 0.0)
+    M, N, K = r["M"], r["N"], r["K"]
+    ops = 2.0 * M * N * K
+    tops = ops / (r["ms_step"] * 1e-3) / 1e12 * world
+    gemm_tops = ops / (r["ms_gemm"] * 1e-3) / 1e12
+
+    e2e = None
+    if r["e2e"]:
+        e2e = dict(r["e2e"])
+        e2e.update(value=ops / (e2e["ms_per_step"] * 1e-3) / 1e12 * world, unit="TOPS")
 
     if wl == "skinny":
-        alg_bytes = N * K + M * K + esize * M * N + 8 * N + 4 * M  # weights + acts + out + (wsum, bias) + asum
-        achieved = alg_bytes / (ms_gemm * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "traffic": NCU_TRAFFIC["gemv_kernel"], "kernel": "gemv_kernel",
-                "algorithmic_bytes": alg_bytes, "ms": ms_gemm, "peak_source": f"{pk['source']} HBM copy",
-                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS}
+        traffic, note = ncu_traffic("gemv_kernel_skinny_m16.md", r["kernel"])
+        roof = skinny_roofline(r, pk, traffic, note)
     else:
-        int8_peak = 2.0 * pk["bf16_sustained"]  # no INT8 figure is measured on this pool: 2 x measured bf16 (sustained)
-        roof = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s",
-                "frac": gemm_tops / int8_peak, "traffic": NCU_TRAFFIC["gemm_tc_pair_kernel"],
-                "kernel": "gemm_tc_pair_kernel<240,u8>", "algorithmic_ops": ops, "ms": ms_gemm,
-                "peak_source": f"2 x {pk['source']} bf16 sustained ({pk['bf16_sustained']} TFLOP/s); 2 x burst would "
-                               f"be {2 * pk['bf16']}", "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS}
+        traffic, note = ncu_traffic("gemm_tc_pair_kernel_square4096.md", r["kernel"])
+        # The kernel is timed in isolation (a graph of `steps` launches, ~1 ms): the denominator is the burst figure.
+        # No INT8 GEMM is measured on this pool, so the proxy is 2 x the measured bf16 burst rate.
+        int8_peak = 2.0 * pk["bf16"]
+        roof = {"bound": "tensor", "achieved": gemm_tops, "peak": int8_peak, "unit": "TOP/s", "frac": gemm_tops / int8_peak,
+                "traffic": traffic, "traffic_source": note, "kernel": r["kernel"], "algorithmic_ops": ops, "ms": r["ms_gemm"],
+                "peak_source": f"2 x {pk['source']} bf16 burst ({pk['bf16']} TFLOP/s), the rate for a kernel timed alone",
+                "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS}
+        if r["sustained"]:
+            s = r["sustained"]
+            s_tops = ops / (s["ms_per_step"] * 1e-3) / 1e12
+            roof["sustained"] = {"tops": s_tops, "ms": s["ms_per_step"], "seconds": s["seconds"],
+                                 "sm_mhz_median": s["sm_mhz_median"], "reasons": s["reasons"],
+                                 "frac_of_2x_bf16_sustained": s_tops / (2.0 * pk["bf16_sustained"]),
+                                 "frac_of_nominal_4500": s_tops / NOMINAL_INT8_TOPS,
+                                 "us_x_mhz": (s["ms_per_step"] * 1e3 * s["sm_mhz_median"]) if s["sm_mhz_median"] else None,
+                                 "note": "the same graph of GEMM launches replayed back to back for `seconds`"}
 
     cpu = None
     if h.rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -416,28 +565,100 @@ def run_linear(args):
 
     cfg = {"workload": workload_name(wl), "M_per_gpu": M, "N": N, "K": K,
            "sharding": "rows (M) per GPU, weights replicated, no collective" if world > 1 else "single GPU",
-           "l2": f"rotating {sets} distinct input/weight/output sets, larger than L2 in total",
+           "l2": f"rotating {r['sets']} distinct input/weight/output sets, larger than L2 in total",
            "step": "quantize_rows (fp32->u8 + row sums) + quantized GEMM with fused epilogue" +
-                   ("" if step is step_serial else "; batch i+1 is quantised on a second stream while batch i's GEMM runs"),
+                   ("; batch i+1 is quantised on a second stream while batch i's GEMM runs" if r["step_overlapped"] else ""),
            "timing": "CUDA events around one replay of a CUDA graph holding exactly `steps` steps"
            if not args.no_graph else "CUDA events around `steps` eager launches"}
     quant_bytes = 5.0 * M * K + 4.0 * M  # fp32 in, uint8 out, one int32 row sum per row
-    h.finish(base_line(h, args, tops, "TOPS", ms_step, "weak", cfg, gemm_only={"ms": ms_gemm, "tops": gemm_tops},
-                       quantize_only={"ms": ms_quant, "gbs": quant_bytes / (ms_quant * 1e-3) / 1e9,
-                                      "frac_of_hbm_peak": quant_bytes / (ms_quant * 1e-3) / 1e9 / pk["hbm_gbs"]},
-                       roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=int(launches),
-                       clocks=getattr(h, "clocks", None)))
+    extra = {}
+    if sections:
+        extra = run_sections(h, args, pk)
+    h.finish(base_line(h, args, tops, "TOPS", r["ms_step"], "weak", cfg,
+                       gemm_only={"ms": r["ms_gemm"], "tops": gemm_tops},
+                       quantize_only={"ms": r["ms_quant"], "gbs": quant_bytes / (r["ms_quant"] * 1e-3) / 1e9,
+                                      "frac_of_hbm_peak": quant_bytes / (r["ms_quant"] * 1e-3) / 1e9 / pk["hbm_gbs"]},
+                       roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=r["launches"], clocks=r["clocks"], **extra))
 
 
-def run_mlp_block(args):
-    """8192 -> 32768 -> 8192 quantized MLP block with ReLU over M_total tokens (configs[4]), sharded over the ranks by
-    activation rows (no collective) or by weight columns (all-gather of output slices over NCCL + relayout).  Total work
-    is fixed, so scaling is strong."""
+def run_sections(h, args, pk):
+    """The parts of the metric beside the headline: skinny M = 1 / 4 / 16 (HBM GB/s), the MNIST-shaped MLP (samples/s)
+    and the 8192-32768-8192 block sharded over the ranks.  Each section is timed like the headline (CUDA graph, events,
+    max over ranks); a section that fails reports its error instead of taking the line down."""
+    out = {}
+
+    def guarded(name, fn):
+        try:
+            out[name] = fn()
+        except Exception as exc:  # noqa: BLE001
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        h.torch.cuda.synchronize()
+        import gc
+        gc.collect()
+        h.torch.cuda.empty_cache()
+
+    def skinny():
+        res = {"config": "configs[3]: K=4096, N=11008, fp32 out, 6 rotating 45 MB weight sets (every launch streams its "
+                         "weights from HBM); us = weight-streaming kernel alone, step_us = quantize_rows + kernel, per GPU"}
+        traffic, note = None, None
+        for m in (1, 4, 16):
+            r = measure_linear(h, args, "skinny", m_rows=m, with_e2e=False)
+            if traffic is None:
+                traffic, note = ncu_traffic("gemv_kernel_skinny_m16.md", r["kernel"])
+            roof = skinny_roofline(r, pk, traffic, note)
+            res[f"m{m}"] = {"us": r["ms_gemm"] * 1e3, "gbs": roof["achieved"], "frac_of_measured": roof["frac"],
+                            "frac_of_nominal": roof["frac_of_nominal_8TBs"], "step_us": r["ms_step"] * 1e3,
+                            "algorithmic_bytes": roof["algorithmic_bytes"], "kernel": r["kernel"]}
+        res["traffic"] = traffic
+        res["traffic_source"] = note
+        return res
+
+    def mnist():
+        r = measure_mlp_mnist(h, args)
+        return {"config": "configs[0]: 784-512-512-10, batch 64, independent replicas (one batch stream per GPU)",
+                "us_per_batch": r["ms_step"] * 1e3, "samples_per_s": 64 * h.world / (r["ms_step"] * 1e-3),
+                "gpu_launches_per_batch": r["launches_per_step"], "kernels": r["kernels"]}
+
+    def block(shard):
+        def run():
+            steps = max(2, min(args.steps, 4))
+            r = measure_mlp_block(h, args, shard, 65536, 8192, steps=steps, warmup=3)
+            d = {"config": f"configs[4]: 8192->32768->8192, 65536 tokens in total, sharding {shard}; strong scaling",
+                 "ms": r["ms_step"], "tops": r["tops"], "samples_per_s": 65536 / (r["ms_step"] * 1e-3),
+                 "kernel": r["kernel"], "timing": r["timing"], "clocks": r["clocks"], "steps": steps}
+            if shard == "rows" and h.world > 1:
+                # the same 65536 tokens on rank 0 alone, in the same run, for the speed-up
+                h.sync_all()
+                n1 = measure_mlp_block(h, args, "rows", 65536, 8192, steps=2, warmup=2, alone=True) if h.rank == 0 else None
+                h.sync_all()
+                if n1:
+                    d["n1_ms_same_run"] = n1["ms_step"]
+                    d["speedup_vs_n1"] = n1["ms_step"] / r["ms_step"]
+            if shard != "rows":
+                d["nvlink_egress_bytes_per_gpu_per_step"] = r["egress_bytes"]
+            return d
+        return run
+
+    guarded("skinny", skinny)
+    guarded("mlp_mnist", mnist)
+    guarded("mlp_block_rows", block("rows"))
+    if h.world > 1:
+        guarded("mlp_block_cols", block("cols"))
+        guarded("mlp_block_cols_fused", block("cols_fused"))
+    return out
+
+
+# ---- 8192 -> 32768 -> 8192 block ---------------------------------------------------------------------------------------
+def measure_mlp_block(h, args, shard, Mt, d_model, steps, warmup, alone=False):
+    """8192 -> 32768 -> 8192 quantized MLP block with ReLU over Mt tokens (configs[4]), sharded over the ranks by
+    activation rows (no collective) or by weight columns (all-gather of output slices over NCCL + relayout, or the
+    exchange fused into the GEMM epilogue).  Total work is fixed, so scaling is strong.  `alone`: this rank runs all Mt
+    tokens by itself, without touching the process group."""
     import ltq
     from ltq import sharded
-    h = Harness(args)
-    torch, dev, world, rank = h.torch, h.dev, h.world, h.rank
-    Mt, K1, N1, N2 = args.m_total, args.d_model, 4 * args.d_model, args.d_model
+    torch, dev = h.torch, h.dev
+    world, rank = (1, 0) if alone else (h.world, h.rank)
+    K1, N1, N2 = d_model, 4 * d_model, d_model
     g = torch.Generator(device=dev).manual_seed(77)          # weights identical on every rank
     w1 = torch.randn((N1, K1), generator=g, device=dev) * 0.01
     w2 = torch.randn((N2, N1), generator=g, device=dev) * 0.01
@@ -451,34 +672,40 @@ def run_mlp_block(args):
     hid = torch.relu(sample @ w1.t())
     qh = ltq.ops.qparams_from_dev(ltq.compute_qparams_dev(ltq.GetMinMax(hid)))
     del w1, w2, hid, sample
-    if args.shard == "rows":
+    egress = 0
+    if shard == "rows":
         r0, r1 = sharded.shard_range(Mt, rank, world)
         M = r1 - r0
-        l1 = sharded.RowShardedLinear(w1q, None, qx, qw1, qh)
-        l2 = sharded.RowShardedLinear(w2q, None, qh, qw2, ltq.QParams(1.0, 0))
+        l1 = ltq.LayerHandle(h.local, K1, N1)
+        l1.set_weights(w1q, None)
+        l1.set_qparams(qx, qw1, qh)
+        l2 = ltq.LayerHandle(h.local, N1, N2)
+        l2.set_weights(w2q, None)
+        l2.set_qparams(qh, qw2, ltq.QParams(1.0, 0))
     else:
         M = Mt
-        fused = args.shard == "cols_fused"
+        fused = shard == "cols_fused"
         l1 = sharded.ColShardedLinear(w1q, None, N1, qx, qw1, qh, fused=fused, max_rows=M, out_mode=ltq.OUT_U8)
         l2 = sharded.ColShardedLinear(w2q, None, N2, qh, qw2, ltq.QParams(1.0, 0), fused=fused, max_rows=M,
                                       out_mode=ltq.OUT_F32)
         del w1q, w2q
-    gx = torch.Generator(device=dev).manual_seed(1000 + (rank if args.shard == "rows" else 0))
+        egress = (world - 1) * (M * (N1 // world) * 1 + M * (N2 // world) * 4)
+    gx = torch.Generator(device=dev).manual_seed(1000 + (rank if shard == "rows" else 0))
     x = torch.randn((M, K1), generator=gx, device=dev)
     xq = torch.empty((M, K1), dtype=torch.uint8, device=dev)
     asum = torch.empty(M, dtype=torch.int32, device=dev)
-    if args.shard == "rows":
+    if shard == "rows":
         hq = torch.empty((M, N1), dtype=torch.uint8, device=dev)
         y = torch.empty((M, N2), dtype=torch.float32, device=dev)
         hsum = torch.zeros(M, dtype=torch.int32, device=dev)   # row sums of hq, left behind by layer 1's epilogue
-        l1.layer.set_rowsum_output(hsum)
+        l1.set_rowsum_output(hsum)
 
         def step(i):
             hsum.zero_()
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
-            l1.layer.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=hq)
-            l2.layer.forward(hq, ltq.OUT_F32, 0, asum=hsum, out=y)
-    elif args.shard == "cols_fused":
+            l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=hq)
+            l2.forward(hq, ltq.OUT_F32, 0, asum=hsum, out=y)
+    elif shard == "cols_fused":
         def step(i):
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
             hh = l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU)      # epilogue stores into every rank's buffer
@@ -499,11 +726,26 @@ def run_mlp_block(args):
 
     launches0 = ltq.kernel_launches()
     # NCCL collectives are not captured here: the column-sharded step is timed over eager launches
-    use_graph = (not args.no_graph) and args.shard == "rows"
-    ms_step = h.timed(step, args.steps, args.warmup, graph=use_graph, sample_clocks=True)
-    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
+    use_graph = (not args.no_graph) and shard == "rows"
+    ms_step = h.timed(step, steps, warmup, graph=use_graph, sample_clocks=not alone, local_only=alone)
+    launches = (ltq.kernel_launches() - launches0) // (steps + warmup) * steps
+    kernel = ltq.last_kernel()
+    if shard == "rows":
+        l1.check()
+    elif hasattr(l1, "close"):
+        l1.close()
+        l2.close()
     ops = 2.0 * Mt * (K1 * N1 + N1 * N2)
-    tops = ops / (ms_step * 1e-3) / 1e12
+    return dict(ms_step=ms_step, tops=ops / (ms_step * 1e-3) / 1e12, launches=int(launches), M=M, kernel=kernel,
+                clocks=None if alone else getattr(h, "clocks", None), egress_bytes=egress,
+                timing="CUDA graph replay" if use_graph else "eager launches (NCCL inside the step)")
+
+
+def run_mlp_block(args):
+    h = Harness(args)
+    Mt, K1 = args.m_total, args.d_model
+    N1, N2 = 4 * K1, K1
+    r = measure_mlp_block(h, args, args.shard, Mt, K1, steps=args.steps, warmup=args.warmup)
     cfg = {"workload": f"mlp_block (configs[4]): {K1}->{N1}->{N2} with ReLU, {Mt} tokens in total, uint8 hidden "
                        "activations via fused requant, fp32 output",
            "sharding": {"rows": "activation rows split over the ranks, weights replicated, no collective",
@@ -512,21 +754,20 @@ def run_mlp_block(args):
                         "cols_fused": "weight columns split over the ranks, the GEMM epilogue stores each rank's columns "
                                       "into every rank's output buffer over NVLink (peer stores), one 4-byte all-reduce "
                                       "per layer as the barrier"}[args.shard],
-           "M_per_gpu": M, "l2": "operands far larger than L2 (x, hidden and output are each >= 0.25 GB per rank)",
-           "step": "quantize_rows + layer 1 (uint8, ReLU) + layer 2 (fp32)",
-           "timing": "CUDA graph replay" if use_graph else "eager launches (NCCL inside the step)"}
-    h.finish(base_line(h, args, tops, "TOPS", ms_step, "strong", cfg, samples_per_s=Mt / (ms_step * 1e-3),
-                       gpu_launches=int(launches), clocks=getattr(h, "clocks", None), e2e=None, roofline=None,
+           "M_per_gpu": r["M"], "l2": "operands far larger than L2 (x, hidden and output are each >= 0.25 GB per rank)",
+           "step": "quantize_rows + layer 1 (uint8, ReLU) + layer 2 (fp32)", "timing": r["timing"]}
+    h.finish(base_line(h, args, r["tops"], "TOPS", r["ms_step"], "strong", cfg, samples_per_s=Mt / (r["ms_step"] * 1e-3),
+                       gpu_launches=r["launches"], clocks=r["clocks"], kernel=r["kernel"], e2e=None, roofline=None,
                        cpu_baseline=None))
 
 
-def run_mlp_mnist(args):
-    """MNIST-shaped 784-512-512-10 MLP, batch 64 (configs[0]): three launches per batch; every rank is an independent
-    replica with its own batch stream."""
+# ---- MNIST-shaped MLP ---------------------------------------------------------------------------------------------------
+def measure_mlp_mnist(h, args):
+    """MNIST-shaped 784-512-512-10 MLP, batch 64 (configs[0]); every rank is an independent replica with its own batch
+    stream."""
     import ltq
     from ltq import workloads
-    h = Harness(args)
-    torch, dev, world = h.torch, h.dev, h.world
+    torch, dev = h.torch, h.dev
     x, layers = workloads.mlp_mnist(seed=0, batch=64)
     xd = torch.from_numpy(x).to(dev)
     acts = [xd]
@@ -555,24 +796,40 @@ def run_mlp_mnist(args):
     hs[1].set_rowsum_output(sums[1])        # rows of h2, read by layer 3, cleared by layer 1 of the next batch
     hs[2].set_clear_on_forward(sums[0])
     hs[0].set_clear_on_forward(sums[1])
+    kernels = []
 
     def step(i):
         ltq.quantize_rows(xd, qp=qa[0], q=xq, asum=asum)
         hs[0].forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=h1)
+        if i == 0:
+            kernels.append(ltq.last_kernel())
         hs[1].forward(h1, ltq.OUT_U8, ltq.FLAG_RELU, asum=sums[0], out=h2)
+        if i == 0:
+            kernels.append(ltq.last_kernel())
         hs[2].forward(h2, ltq.OUT_F32, 0, asum=sums[1], out=y)
+        if i == 0:
+            kernels.append(ltq.last_kernel())
 
+    steps = max(args.steps, 20)
     launches0 = ltq.kernel_launches()
-    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
-    launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
+    ms_step = h.timed(step, steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    launches = (ltq.kernel_launches() - launches0) // (steps + args.warmup)
+    return dict(ms_step=ms_step, launches_per_step=int(launches), steps=steps, kernels=kernels,
+                clocks=getattr(h, "clocks", None))
+
+
+def run_mlp_mnist(args):
+    h = Harness(args)
+    r = measure_mlp_mnist(h, args)
     ops = 2.0 * 64 * (784 * 512 + 512 * 512 + 512 * 10)
     cfg = {"workload": "mlp_mnist (configs[0]): 784-512-512-10, batch 64, uint8 hidden activations with fused ReLU, "
                        "fp32 logits", "sharding": "independent replicas, one batch stream per GPU",
            "l2": "the whole model (0.67 MB) is L2-resident by nature; this configuration is launch-latency bound",
            "step": "quantize_rows + 3 quantized linears whose epilogues emit the next layer's row sums (4 kernels)", "timing": "CUDA graph replay"}
-    h.finish(base_line(h, args, ops / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
-                       samples_per_s=64 * world / (ms_step * 1e-3), gpu_launches=int(launches),
-                       clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))
+    args.steps = r["steps"]
+    h.finish(base_line(h, args, ops / (r["ms_step"] * 1e-3) / 1e12 * h.world, "TOPS", r["ms_step"], "weak", cfg,
+                       samples_per_s=64 * h.world / (r["ms_step"] * 1e-3), gpu_launches=r["launches_per_step"] * r["steps"],
+                       clocks=r["clocks"], kernels=r["kernels"], e2e=None, roofline=None, cpu_baseline=None))
 
 
 def run_conv(args):
@@ -620,7 +877,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ltq", choices=["ltq", "reference"])
-    ap.add_argument("--workload", default="square_4096", choices=["square_4096", "skinny", "mlp_block", "mlp_mnist", "conv"])
+    ap.add_argument("--workload", default="all", choices=["all", "square_4096", "skinny", "mlp_block", "mlp_mnist", "conv"],
+                    help="all (default): the 4096^3 headline plus the skinny / mlp_mnist / mlp_block sections")
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
     ap.add_argument("--m-total", type=int, default=65536, help="tokens of the mlp_block workload (all ranks together)")
     ap.add_argument("--d-model", type=int, default=8192, help="width of the mlp_block workload (hidden = 4x)")
@@ -641,7 +899,7 @@ def main():
     elif args.workload == "conv":
         run_conv(args)
     else:
-        run_linear(args)
+        run_linear(args, sections=args.workload == "all")
 
 
 if __name__ == "__main__":

@@ -166,6 +166,23 @@ class ColShardedLinear:
             self._turn = 0
             self._flag = torch.zeros(1, dtype=torch.int32, device=w_loc.device)
 
+    def close(self):
+        """Releases the peer-mapped buffers of the fused form.  Collective: every rank calls it, after its last forward;
+        nobody unmaps or frees before everyone has finished computing, and nobody frees before everyone has unmapped."""
+        if not self.fused:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for b in self._bufs:
+            for p in b._opened:
+                lib().ltq_peer_close(p, b.device_index)
+            b._opened = []
+        dist.barrier(group=self.group)
+        for b in self._bufs:
+            b.close()
+        self._bufs = []
+        self.fused = False
+
     def forward(self, x_q, out_mode=OUT_U8, flags=0, out=None, gathered=None, local=None):
         M = x_q.shape[0]
         nloc = self.n1 - self.n0
