@@ -226,6 +226,71 @@ int ltq_peer_free(void *dev_ptr, int device);
 int ltq_peer_open(const unsigned char *handle64, int device, void **peer_ptr);
 int ltq_peer_close(void *peer_ptr, int device);
 
+/* ---- one host thread, several devices ---------------------------------------------------------------------------------
+ * l-ten's API is single-threaded and names a device per tensor (TensorOps::device_index, handle arrays of MAX_DEVICES = 8,
+ * l-ten/globals.h:15,89-124) but has no multi-device code for this path.  These entry points let such a caller run a
+ * sharded quantized layer: one NCCL communicator and one stream per device, created together (ncclCommInitAll), and
+ * calls that take one pointer per device.  NCCL is loaded at run time (libnccl.so.2) the first time a group is created.
+ * Work is enqueued on the group's own streams (ltq_comm_stream) and the calls return without waiting; whatever produced
+ * the inputs on other streams must have finished, or be ordered before, by the caller.  ltq_comm_synchronize waits. */
+typedef struct ltq_comm ltq_comm;
+
+/* devices: ndev distinct device indices, or NULL for 0 .. ndev-1.  1 <= ndev <= LTQ_MAX_DESTS. */
+int ltq_comm_init_all(ltq_comm **comm, int ndev, const int *devices);
+int ltq_comm_destroy(ltq_comm *comm);
+int ltq_comm_size(const ltq_comm *comm);
+int ltq_comm_device(const ltq_comm *comm, int index);      /* device index of member `index`, -1 if out of range */
+void *ltq_comm_stream(const ltq_comm *comm, int index);    /* its cudaStream_t */
+
+/* Waits until every device's stream has drained.  While waiting it polls the communicators (ncclCommGetAsyncError): on
+ * an asynchronous error, or when timeout_ms (0 = no limit) runs out, every communicator is aborted (ncclCommAbort), so
+ * that collectives stuck on a lost peer return, and the call fails with LTQ_ERR_CUDA / LTQ_ERR_DEVICE_TIMEOUT.  After
+ * that the group only accepts ltq_comm_destroy. */
+int ltq_comm_synchronize(ltq_comm *comm, uint32_t timeout_ms);
+
+/* Row (M) sharding: device d holds a full replica of the layer (layers[d], created on that device) and rows[d] rows of
+ * the activations x_dev[d] uint8 [rows[d], K]; it writes the same rows of the output to out_dev[d].  Nothing is
+ * exchanged (parameters are per tensor, rows are independent).  asum_dev / qp_in_dev: per-device arrays as in
+ * ltq_layer_forward, or NULL. */
+int ltq_linear_forward_rowsharded(ltq_comm *comm, ltq_layer *const *layers, const uint8_t *const *x_dev,
+                                  const int32_t *const *asum_dev, const uint64_t *rows, const ltq_qparams *const *qp_in_dev,
+                                  int out_mode, unsigned flags, void *const *out_dev);
+
+/* The one exchange row sharding needs, and only under dynamic activation quantisation: the per-tensor min / max must be
+ * those of ALL rows for the sharded result to equal the single-device one.  minmax_dev[d]: two floats on device d
+ * (from ltq_get_min_max over its rows, enqueued on the group's stream); replaced in place by the global {min, max}. */
+int ltq_comm_allreduce_minmax(ltq_comm *comm, float *const *minmax_dev);
+
+/* Column (N) sharding: device d holds weight rows (output features) [d*n, (d+1)*n) as layers[d] (all with the same n =
+ * N / ndev and the same K) and the FULL activations x_dev[d] uint8 [M, K].  Each device computes its [M, n] slice into
+ * local_dev[d], the slices are all-gathered (ncclAllGather inside one group) into gathered_dev[d] ([ndev][M][n]) and
+ * re-laid out into out_dev[d], row-major [M, N], on every device.  With ndev = 1 the result goes straight to out_dev. */
+int ltq_linear_forward_colsharded_allgather(ltq_comm *comm, ltq_layer *const *layers, const uint8_t *const *x_dev,
+                                            const int32_t *const *asum_dev, uint64_t M, const ltq_qparams *const *qp_in_dev,
+                                            int out_mode, unsigned flags, void *const *local_dev, void *const *gathered_dev,
+                                            void *const *out_dev);
+
+/* What a group does with its devices and communicators, as a table of functions.  The default (backend = NULL) is NCCL
+ * and CUDA streams.  Tests install a fake to exercise the watchdog of ltq_comm_synchronize and the bookkeeping without a
+ * GPU: groups created while a fake is installed make no CUDA or NCCL call at all.  Return values: 0 = success;
+ * stream_query: 0 = idle, 1 = busy, negative = error; comm_get_async_error stores a non-zero code when the
+ * communicator has failed.  all_reduce_f32's op: 0 = min, 1 = max. */
+typedef struct ltq_comm_backend {
+    int (*comm_init_all)(void **comms, int ndev, const int *devices);
+    int (*comm_destroy)(void *comm);
+    int (*comm_abort)(void *comm);
+    int (*comm_get_async_error)(void *comm, int *async_error);
+    int (*all_gather)(const void *send, void *recv, uint64_t bytes, void *comm, void *stream);
+    int (*all_reduce_f32)(const void *send, void *recv, uint64_t count, int op, void *comm, void *stream);
+    int (*group_start)(void);
+    int (*group_end)(void);
+    int (*stream_create)(int device, void **stream);
+    int (*stream_destroy)(int device, void *stream);
+    int (*stream_query)(int device, void *stream);
+    const char *(*error_string)(int code);
+} ltq_comm_backend;
+int ltq_comm_set_backend(const ltq_comm_backend *backend);
+
 /* Reads (and clears) the layer's device status word: LTQ_OK, or LTQ_ERR_DEVICE_TIMEOUT when a bounded wait inside a
  * kernel ran out since the last check.  Synchronises `stream`. */
 int ltq_layer_check(ltq_layer *layer, void *stream);

@@ -12,6 +12,7 @@
 #include "ltq_common.cuh"
 #include "ltq_gemm_tc.cuh"
 #include "ltq_gemv.cuh"
+#include "ltq_layer.cuh"
 
 namespace ltq {
 
@@ -103,26 +104,6 @@ int choose_path(uint64_t M, uint64_t N, uint64_t K, const void *A, const void *B
 }  // namespace ltq
 
 using namespace ltq;
-
-constexpr int LAYER_MAPS = 8;
-
-struct ltq_layer {
-    int device = 0;
-    uint64_t K = 0, N = 0;
-    const uint8_t *w = nullptr;
-    const int32_t *bias = nullptr;
-    int32_t *wsum = nullptr;       // [N] sum_k W[j,k]
-    int32_t *asum_ws = nullptr;    // activation row sums when the caller supplies none; grows with M like
-    uint64_t asum_cap = 0;         // FullyConnected_q::workspace_ (l-ten/fully_connected.cpp:366-371)
-    ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
-    int32_t *rowsum_out = nullptr; // optional: receives the row sums of uint8 outputs (ltq_layer_set_rowsum_output)
-    int32_t *clear_ptr = nullptr;  // optional: array cleared by every forward (ltq_layer_set_clear_on_forward)
-    uint32_t clear_count = 0;
-    TcOperandMap map_w[LAYER_MAPS];  // weight tensor maps of the tensor-core kernels, one per box height, built on demand
-    int map_w_next = 0;
-    GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
-    DeviceState *dev = nullptr;
-};
 
 // Grow-only device buffer, same policy as the reference's col buffer and workspace.
 template <typename T>

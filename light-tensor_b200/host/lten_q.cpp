@@ -83,6 +83,16 @@ void Tensor::attach_row_sums(const Tensor &sums)
 
 const Tensor *Tensor::row_sums() const { return impl_ && impl_->row_sums ? impl_->row_sums.get() : nullptr; }
 
+bool Tensor::unique() const { return impl_ && impl_.use_count() == 1 && impl_->storage.use_count() == 1; }
+
+bool Tensor::matches(const uint64_t *dims, int ndims, const TensorOps &ops) const
+{
+    if (!impl_ || impl_->ndims != ndims || impl_->ops.data_type != ops.data_type || impl_->ops.device_type != ops.device_type ||
+        impl_->ops.device_index != ops.device_index)
+        return false;
+    return memcmp(impl_->dims, dims, sizeof(uint64_t) * ndims) == 0;
+}
+
 Tensor AllocateTensor(const uint64_t *dims_ptr, int ndims, TensorOps *options_ptr)
 {
     if (ndims < 1 || ndims > MAX_DIMS) LTEN_ERR("Invalid number of dimensions");
@@ -261,6 +271,24 @@ void FullyConnected_q::to(device target_device, int target_device_index)
     }
 }
 
+// Output buffers are recycled: a forward hands out the tensor it handed out last time if the caller has let go of it
+// (no cudaMalloc, no synchronising cudaMemset per call, and the addresses stay the same from call to call, which is
+// what stream overlap and graph capture need).  A tensor the caller still holds is never touched.
+Tensor FullyConnected_q::take_output(const uint64_t *dims, int ndims, const TensorOps &ops, Tensor *cache)
+{
+    if (cache->defined() && cache->unique() && cache->matches(dims, ndims, ops)) {
+        cache->attach_row_sums(Tensor());
+        return *cache;
+    }
+    *cache = AllocateTensor(dims, ndims, const_cast<TensorOps *>(&ops));
+    return *cache;
+}
+
+void FullyConnected_q::check()
+{
+    if (handle_) LTQ_CALL(ltq_layer_check(handle_, stream_));
+}
+
 Tensor FullyConnected_q::forward(Tensor &input)
 {
     // the reference's checks, messages and order: l-ten/fully_connected.cpp:330-348
@@ -280,7 +308,7 @@ Tensor FullyConnected_q::forward(Tensor &input)
     options.data_type = out_mode_ == LTQ_OUT_U8 ? UINT8 : (out_mode_ == LTQ_OUT_F32 ? FLOAT32 : INT32);
     options.device_type = GPU;
     options.device_index = input.get_device_index();
-    Tensor result = AllocateTensor(dims, ndims, &options);
+    Tensor result = take_output(dims, ndims, options, &cached_result_);
 
     uint64_t rows = 1;  // every leading dimension folds into M: parameters are per tensor, rows are independent
     for (int d = 0; d < ndims - 1; d++) rows *= dims[d];
@@ -294,14 +322,120 @@ Tensor FullyConnected_q::forward(Tensor &input)
         so.data_type = INT32;
         so.device_type = GPU;
         so.device_index = input.get_device_index();
-        out_sums = AllocateTensor({rows}, &so);  // zero-filled
+        const uint64_t sdims[1] = {rows};
+        out_sums = take_output(sdims, 1, so, &cached_sums_);
+        // the epilogue accumulates into it: cleared in stream order, without stopping the host
+        int prev = 0;
+        LTEN_CUDA(cudaGetDevice(&prev));
+        LTEN_CUDA(cudaSetDevice(so.device_index));
+        LTEN_CUDA(cudaMemsetAsync(out_sums.get_data_ptr(), 0, rows * sizeof(int32_t), static_cast<cudaStream_t>(stream_)));
+        LTEN_CUDA(cudaSetDevice(prev));
     }
     LTQ_CALL(ltq_layer_set_rowsum_output(handle_, out_sums.defined() ? static_cast<int32_t *>(out_sums.get_data_ptr()) : nullptr));
     LTQ_CALL(ltq_layer_set_qparams(handle_, &qparams_in_, &qparams_wt_, &qparams_out_));
     LTQ_CALL(ltq_layer_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), asum, rows, nullptr, out_mode_,
-                               flags_, result.get_data_ptr(), nullptr));
+                               flags_, result.get_data_ptr(), stream_));
     if (out_sums.defined()) result.attach_row_sums(out_sums);
     return result;
+}
+
+// ---- DeviceGroup -------------------------------------------------------------------------------------------------------
+DeviceGroup::DeviceGroup(const std::vector<int> &device_indices) : devices_(device_indices)
+{
+    LTQ_CALL(ltq_comm_init_all(&comm_, (int)devices_.size(), devices_.data()));
+}
+
+DeviceGroup::~DeviceGroup() { ltq_comm_destroy(comm_); }
+
+void *DeviceGroup::stream(int i) const { return ltq_comm_stream(comm_, i); }
+
+void DeviceGroup::synchronize(uint32_t timeout_ms) { LTQ_CALL(ltq_comm_synchronize(comm_, timeout_ms)); }
+
+static uint64_t fold_rows(const Tensor &t)
+{
+    uint64_t rows = 1;
+    for (int d = 0; d < t.get_ndims() - 1; d++) rows *= t.get_sizes()[d];
+    return rows;
+}
+
+std::vector<Tensor> DeviceGroup::forward_rowsharded(const std::vector<FullyConnected_q *> &replicas, std::vector<Tensor> &inputs)
+{
+    const int n = size();
+    if ((int)replicas.size() != n || (int)inputs.size() != n) LTEN_ERR("one layer replica and one input per device of the group");
+    std::vector<ltq_layer *> layers(n);
+    std::vector<const uint8_t *> xs(n);
+    std::vector<uint64_t> rows(n);
+    std::vector<void *> outs(n);
+    std::vector<Tensor> results(n);
+    const ltq_out_mode mode = replicas[0]->out_mode_;
+    for (int d = 0; d < n; d++) {
+        FullyConnected_q *fc = replicas[d];
+        const Tensor &x = inputs[d];
+        if (!fc->handle_ || x.get_ndims() < 2 || x.get_device() != GPU || x.get_device_index() != devices_[d] ||
+            x.get_data_type() != UINT8 || x.get_sizes()[x.get_ndims() - 1] != fc->input_features_ || fc->out_mode_ != mode)
+            LTEN_ERR("Input tensor device type or data type are not the same as this layer's parameters");
+        uint64_t dims[MAX_DIMS];
+        memcpy(dims, x.get_sizes(), sizeof(uint64_t) * x.get_ndims());
+        dims[x.get_ndims() - 1] = fc->output_features_;
+        TensorOps o;
+        o.data_type = mode == LTQ_OUT_U8 ? UINT8 : (mode == LTQ_OUT_F32 ? FLOAT32 : INT32);
+        o.device_type = GPU;
+        o.device_index = devices_[d];
+        results[d] = fc->take_output(dims, x.get_ndims(), o, &fc->cached_result_);
+        LTQ_CALL(ltq_layer_set_rowsum_output(fc->handle_, nullptr));
+        LTQ_CALL(ltq_layer_set_qparams(fc->handle_, &fc->qparams_in_, &fc->qparams_wt_, &fc->qparams_out_));
+        layers[d] = fc->handle_;
+        xs[d] = static_cast<const uint8_t *>(x.get_data_ptr());
+        rows[d] = fold_rows(x);
+        outs[d] = results[d].get_data_ptr();
+    }
+    LTQ_CALL(ltq_linear_forward_rowsharded(comm_, layers.data(), xs.data(), nullptr, rows.data(), nullptr, mode,
+                                           replicas[0]->flags_, outs.data()));
+    return results;
+}
+
+std::vector<Tensor> DeviceGroup::forward_colsharded(const std::vector<FullyConnected_q *> &slices, std::vector<Tensor> &inputs)
+{
+    const int n = size();
+    if ((int)slices.size() != n || (int)inputs.size() != n) LTEN_ERR("one layer slice and one input per device of the group");
+    const ltq_out_mode mode = slices[0]->out_mode_;
+    const dtype dt = mode == LTQ_OUT_U8 ? UINT8 : (mode == LTQ_OUT_F32 ? FLOAT32 : INT32);
+    const uint64_t M = fold_rows(inputs[0]), n_loc = slices[0]->output_features_;
+    std::vector<ltq_layer *> layers(n);
+    std::vector<const uint8_t *> xs(n);
+    std::vector<void *> locals(n), gathered(n), outs(n);
+    std::vector<Tensor> results(n), keep;
+    for (int d = 0; d < n; d++) {
+        FullyConnected_q *fc = slices[d];
+        const Tensor &x = inputs[d];
+        if (!fc->handle_ || x.get_ndims() < 2 || x.get_device() != GPU || x.get_device_index() != devices_[d] ||
+            x.get_data_type() != UINT8 || x.get_sizes()[x.get_ndims() - 1] != fc->input_features_ || fc->out_mode_ != mode ||
+            fc->output_features_ != n_loc || fold_rows(x) != M)
+            LTEN_ERR("Input tensor device type or data type are not the same as this layer's parameters");
+        uint64_t dims[MAX_DIMS];
+        memcpy(dims, x.get_sizes(), sizeof(uint64_t) * x.get_ndims());
+        dims[x.get_ndims() - 1] = n_loc * (uint64_t)n;
+        TensorOps o;
+        o.data_type = dt;
+        o.device_type = GPU;
+        o.device_index = devices_[d];
+        results[d] = AllocateTensor(dims, x.get_ndims(), &o);
+        Tensor loc = AllocateTensor({M, n_loc}, &o), gat = AllocateTensor({(uint64_t)n, M, n_loc}, &o);
+        keep.push_back(loc);
+        keep.push_back(gat);
+        LTQ_CALL(ltq_layer_set_rowsum_output(fc->handle_, nullptr));
+        LTQ_CALL(ltq_layer_set_qparams(fc->handle_, &fc->qparams_in_, &fc->qparams_wt_, &fc->qparams_out_));
+        layers[d] = fc->handle_;
+        xs[d] = static_cast<const uint8_t *>(x.get_data_ptr());
+        locals[d] = loc.get_data_ptr();
+        gathered[d] = gat.get_data_ptr();
+        outs[d] = results[d].get_data_ptr();
+    }
+    LTQ_CALL(ltq_linear_forward_colsharded_allgather(comm_, layers.data(), xs.data(), nullptr, M, nullptr, mode,
+                                                     slices[0]->flags_, locals.data(), gathered.data(), outs.data()));
+    // the scratch tensors are released when this returns: their kernels must have run by then
+    synchronize();
+    return results;
 }
 
 // ---- Conv2d_q ----------------------------------------------------------------------------------------------------------

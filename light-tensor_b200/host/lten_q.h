@@ -68,6 +68,10 @@ public:
     // drops them; writing into the tensor's bytes by hand does not (detach them with attach_row_sums(Tensor())).
     void attach_row_sums(const Tensor &sums);
     const Tensor *row_sums() const;
+    // Additive: true when this handle is the only one referring to its bytes, and whether it has the given shape and
+    // placement (what a layer asks before it recycles an output it handed out earlier).
+    bool unique() const;
+    bool matches(const uint64_t *dims, int ndims, const TensorOps &ops) const;
 
 private:
     struct Impl;
@@ -133,8 +137,20 @@ public:
 
     // Additive: what the fused epilogue writes.  Defaults reproduce the reference (uint8, no ReLU, wrapping cast).
     void set_output(ltq_out_mode mode, bool relu = false, bool saturate = false);
+    // Additive: the CUDA stream (cudaStream_t) forward() enqueues its kernels on.  Default NULL: the legacy default
+    // stream, which orders them with l-ten's own synchronous CUDA calls.  forward() never synchronises; with a
+    // stream of its own a layer overlaps with copies and with other layers, and can be captured into a CUDA graph once
+    // a forward of the same shape has run (output buffers are recycled, see forward()).
+    void set_stream(void *stream) { stream_ = stream; }
+    void *get_stream() const { return stream_; }
+    // Additive: LTQ_ERR_DEVICE_TIMEOUT surfaced as an exception if a bounded device-side wait expired since the last call.
+    void check();
 
 private:
+    friend class DeviceGroup;
+    // Result (and, for uint8 results, row-sum) tensors of the shape asked for: the ones handed out by the previous
+    // forward when the caller has dropped them by now, fresh ones otherwise.
+    Tensor take_output(const uint64_t *dims, int ndims, const TensorOps &ops, Tensor *cache);
     uint64_t input_features_, output_features_;
     Tensor *weight_ptr_ = nullptr, *bias_ptr_ = nullptr;
     bool use_bias_;
@@ -142,6 +158,36 @@ private:
     ltq_layer *handle_ = nullptr;  // created by to(GPU), never by the constructor
     ltq_out_mode out_mode_ = LTQ_OUT_U8;
     unsigned flags_ = 0;
+    void *stream_ = nullptr;
+    Tensor cached_result_, cached_sums_;
+};
+
+// One host thread driving a quantized layer over several GPUs (additive: l-ten has no multi-device code on this path,
+// but its API is exactly this model - a device index per tensor, handle arrays of MAX_DEVICES, l-ten/globals.h:15,89-124).
+// Wraps ltq_comm: one NCCL communicator and one stream per device.  Work is enqueued on the group's streams; call
+// synchronize() before reading results on the host or from other streams.
+class DeviceGroup {
+public:
+    explicit DeviceGroup(const std::vector<int> &device_indices);
+    ~DeviceGroup();
+    DeviceGroup(const DeviceGroup &) = delete;
+    DeviceGroup &operator=(const DeviceGroup &) = delete;
+    int size() const { return (int)devices_.size(); }
+    int device(int i) const { return devices_[i]; }
+    void *stream(int i) const;
+    // Waits for every device; on an NCCL error or after timeout_ms (0 = none) aborts the communicators and throws.
+    void synchronize(uint32_t timeout_ms = 0);
+    // Row (M) sharding: replicas[d] is a copy of the layer moved to device(d) (full weights), inputs[d] holds that
+    // device's rows, {..., rows_d, K} uint8.  Returns each device's rows of the output.  Nothing is exchanged.
+    std::vector<Tensor> forward_rowsharded(const std::vector<FullyConnected_q *> &replicas, std::vector<Tensor> &inputs);
+    // Column (N) sharding: slices[d] is a layer of out_features / size() outputs holding weight rows
+    // [d * n, (d + 1) * n) on device(d); inputs[d] is the FULL activation tensor on that device.  The slices' outputs are
+    // all-gathered over NCCL and re-laid out: every device gets the full {..., M, N} result.
+    std::vector<Tensor> forward_colsharded(const std::vector<FullyConnected_q *> &slices, std::vector<Tensor> &inputs);
+
+private:
+    std::vector<int> devices_;
+    ltq_comm *comm_ = nullptr;
 };
 
 // Quantized 2-D convolution, l-ten/layers.h:453-524 and l-ten/conv2d.cpp:238-406.  The reference computes it on the CPU

@@ -3,6 +3,7 @@
 // int32 with scale s_in * s_wt through get_all_weights(), move the layers to the GPU, Quantize the input, chain
 // FullyConnected_q::forward, Dequantize.  Every layer output is compared byte for byte with the CPU oracle
 // (oracle/ltq_oracle.c, test infrastructure), and the layer's argument checks are exercised with the reference's messages.
+#include <cuda_runtime.h>
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -229,6 +230,112 @@ int main()
         for (size_t i = 0; i < got.size(); i++) same = same && got[i] == s * (float)(acc[i] > 0 ? acc[i] : 0);
         CHECK(same, "F32+ReLU epilogue == scale * max(acc, 0)");
         layers[0]->set_output(LTQ_OUT_U8);
+    }
+
+    // ---- a stream of the caller's, recycled output buffers ----
+    {
+        cudaStream_t st;
+        cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+        cudaDeviceSynchronize();
+        layers[0]->set_stream(st);
+        void *first = nullptr;
+        std::vector<uint8_t> ref;
+        bool same_ptr = true, same_bytes = true;
+        for (int it = 0; it < 4; it++) {
+            Tensor y = layers[0]->forward(q_input);      // dropped at the end of the iteration: the next one reuses its bytes
+            cudaStreamSynchronize(st);
+            std::vector<uint8_t> got = download<uint8_t>(y);
+            if (it == 0) {
+                first = y.get_data_ptr();
+                ref = got;
+            }
+            same_ptr = same_ptr && y.get_data_ptr() == first;
+            same_bytes = same_bytes && got == ref;
+        }
+        CHECK(same_ptr, "forward() recycles the output it handed out before once the caller has dropped it");
+        CHECK(same_bytes, "results on a caller stream are the same every time");
+        Tensor held = layers[0]->forward(q_input);
+        Tensor other = layers[0]->forward(q_input);
+        CHECK(held.get_data_ptr() != other.get_data_ptr(), "an output the caller still holds is not reused");
+        cudaStreamSynchronize(st);
+        CHECK(download<uint8_t>(held) == ref && download<uint8_t>(other) == ref, "both outputs are complete");
+        layers[0]->check();
+        layers[0]->set_stream(nullptr);
+        cudaStreamDestroy(st);
+    }
+
+    // ---- one host thread, every visible GPU: row- and column-sharded layer 1 against the oracle ----
+    {
+        int ndev = 0;
+        cudaGetDeviceCount(&ndev);
+        if (ndev > 4) ndev = 4;
+        std::vector<int> devs;
+        for (int d = 0; d < ndev; d++) devs.push_back(d);
+        DeviceGroup group(devs);
+        const uint64_t K = dims[0], N = 512 / ndev * ndev, nloc = N / ndev;   // layer 1's first N outputs
+        const uint64_t Mtot = B;
+        oracle_qparams qp3[3] = {{qp_act[0].scale, qp_act[0].zero_point}, {qp_w[0].scale, qp_w[0].zero_point},
+                                 {qp_act[1].scale, qp_act[1].zero_point}};
+        std::vector<uint8_t> want((size_t)Mtot * N), xin = download<uint8_t>(q_input);
+        std::vector<int32_t> ws(Mtot + N);
+        oracle_quantized_matmul(0, 1, Mtot, N, K, 1, xin.data(), Wq[0].data(), 0, want.data(), qp3, bq[0].data(), ws.data());
+        // rows: full replica on every device, the batch split
+        {
+            std::vector<FullyConnected_q *> reps;
+            std::vector<Tensor> ins;
+            for (int d = 0; d < ndev; d++) {
+                FullyConnected_q *fc = new FullyConnected_q(K, N, true);
+                fc->init();
+                memcpy(fc->get_all_weights()[0]->get_data_ptr(), Wq[0].data(), (size_t)N * K);
+                memcpy(fc->get_all_weights()[1]->get_data_ptr(), bq[0].data(), (size_t)N * 4);
+                fc->set_qparams_in(qp_act[0]);
+                fc->set_qparams_out(qp_act[1]);
+                fc->set_qparams_params(&qp_w[0], 1);
+                fc->to(GPU, d);
+                reps.push_back(fc);
+                const uint64_t r0 = Mtot * d / ndev, r1 = Mtot * (d + 1) / ndev;
+                TensorOps o;
+                o.data_type = UINT8;
+                Tensor host = TensorFromBuffer({1, r1 - r0, K}, xin.data() + r0 * K, false, &o);
+                ins.push_back(host.to(GPU, d));
+            }
+            std::vector<Tensor> outs = group.forward_rowsharded(reps, ins);
+            group.synchronize(20000);
+            std::vector<uint8_t> got;
+            for (auto &t : outs) {
+                std::vector<uint8_t> part = download<uint8_t>(t);
+                got.insert(got.end(), part.begin(), part.end());
+            }
+            CHECK(got == want, "row-sharded layer over the device group vs oracle");
+            for (auto fc : reps) delete fc;
+        }
+        // columns: a slice of the weight rows on every device, the whole batch everywhere, NCCL all-gather
+        {
+            std::vector<FullyConnected_q *> sl;
+            std::vector<Tensor> ins;
+            for (int d = 0; d < ndev; d++) {
+                FullyConnected_q *fc = new FullyConnected_q(K, nloc, true);
+                fc->init();
+                memcpy(fc->get_all_weights()[0]->get_data_ptr(), Wq[0].data() + (size_t)d * nloc * K, (size_t)nloc * K);
+                memcpy(fc->get_all_weights()[1]->get_data_ptr(), bq[0].data() + (size_t)d * nloc, (size_t)nloc * 4);
+                fc->set_qparams_in(qp_act[0]);
+                fc->set_qparams_out(qp_act[1]);
+                fc->set_qparams_params(&qp_w[0], 1);
+                fc->to(GPU, d);
+                sl.push_back(fc);
+                TensorOps o;
+                o.data_type = UINT8;
+                Tensor host = TensorFromBuffer({1, Mtot, K}, xin.data(), false, &o);
+                ins.push_back(host.to(GPU, d));
+            }
+            std::vector<Tensor> outs = group.forward_colsharded(sl, ins);
+            group.synchronize(20000);
+            bool all = true;
+            for (auto &t : outs) all = all && download<uint8_t>(t) == want;
+            CHECK(all, "column-sharded layer (all-gather over the device group) vs oracle on every device");
+            for (auto fc : sl) delete fc;
+        }
+        printf("device group of %d: row- and column-sharded forward checked\n", ndev);
     }
 
     // ---- argument checks, reference messages (fully_connected.cpp:330-348) ----

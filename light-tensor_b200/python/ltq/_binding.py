@@ -65,6 +65,19 @@ _SIGNATURES = {
     "ltq_peer_free": (_int, [_vp, _int]),
     "ltq_peer_open": (_int, [C.c_char_p, _int, C.POINTER(_vp)]),
     "ltq_peer_close": (_int, [_vp, _int]),
+    "ltq_comm_init_all": (_int, [C.POINTER(_vp), _int, C.POINTER(_int)]),
+    "ltq_comm_destroy": (_int, [_vp]),
+    "ltq_comm_size": (_int, [_vp]),
+    "ltq_comm_device": (_int, [_vp, _int]),
+    "ltq_comm_stream": (_vp, [_vp, _int]),
+    "ltq_comm_synchronize": (_int, [_vp, C.c_uint32]),
+    "ltq_linear_forward_rowsharded": (_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_u64),
+                                             C.POINTER(_vp), _int, C.c_uint, C.POINTER(_vp)]),
+    "ltq_comm_allreduce_minmax": (_int, [_vp, C.POINTER(_vp)]),
+    "ltq_linear_forward_colsharded_allgather": (_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _u64,
+                                                       C.POINTER(_vp), _int, C.c_uint, C.POINTER(_vp), C.POINTER(_vp),
+                                                       C.POINTER(_vp)]),
+    "ltq_comm_set_backend": (_int, [_vp]),
     "ltq_conv2d_create": (_int, [C.POINTER(_vp), _int] + [_u64] * 8),
     "ltq_conv2d_destroy": (_int, [_vp]),
     "ltq_conv2d_set_weights": (_int, [_vp, _vp, _vp, _vp]),
