@@ -636,6 +636,8 @@ def run_sections(h, args, pk):
                     d["speedup_vs_n1"] = n1["ms_step"] / r["ms_step"]
             if shard != "rows":
                 d["nvlink_egress_bytes_per_gpu_per_step"] = r["egress_bytes"]
+            if shard == "cols_multicast":
+                d["multicast_in_use"] = r["multicast"]
             return d
         return run
 
@@ -645,6 +647,7 @@ def run_sections(h, args, pk):
     if h.world > 1:
         guarded("mlp_block_cols", block("cols"))
         guarded("mlp_block_cols_fused", block("cols_fused"))
+        guarded("mlp_block_cols_multicast", block("cols_multicast"))
     return out
 
 
@@ -684,12 +687,15 @@ def measure_mlp_block(h, args, shard, Mt, d_model, steps, warmup, alone=False):
         l2.set_qparams(qh, qw2, ltq.QParams(1.0, 0))
     else:
         M = Mt
-        fused = shard == "cols_fused"
-        l1 = sharded.ColShardedLinear(w1q, None, N1, qx, qw1, qh, fused=fused, max_rows=M, out_mode=ltq.OUT_U8)
+        fused = shard in ("cols_fused", "cols_multicast")
+        mc = shard == "cols_multicast"
+        l1 = sharded.ColShardedLinear(w1q, None, N1, qx, qw1, qh, fused=fused, max_rows=M, out_mode=ltq.OUT_U8, multicast=mc)
         l2 = sharded.ColShardedLinear(w2q, None, N2, qh, qw2, ltq.QParams(1.0, 0), fused=fused, max_rows=M,
-                                      out_mode=ltq.OUT_F32)
+                                      out_mode=ltq.OUT_F32, multicast=mc)
         del w1q, w2q
-        egress = (world - 1) * (M * (N1 // world) * 1 + M * (N2 // world) * 4)
+        copies = 1 if (mc and l1.multicast) else world - 1     # a multicast store leaves the GPU once
+        egress = copies * (M * (N1 // world) * 1 + M * (N2 // world) * 4)
+        mc_in_use = bool(mc and l1.multicast)
     gx = torch.Generator(device=dev).manual_seed(1000 + (rank if shard == "rows" else 0))
     x = torch.randn((M, K1), generator=gx, device=dev)
     xq = torch.empty((M, K1), dtype=torch.uint8, device=dev)
@@ -705,7 +711,7 @@ def measure_mlp_block(h, args, shard, Mt, d_model, steps, warmup, alone=False):
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
             l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU, asum=asum, out=hq)
             l2.forward(hq, ltq.OUT_F32, 0, asum=hsum, out=y)
-    elif shard == "cols_fused":
+    elif fused:
         def step(i):
             ltq.quantize_rows(x, qp=qx, q=xq, asum=asum)
             hh = l1.forward(xq, ltq.OUT_U8, ltq.FLAG_RELU)      # epilogue stores into every rank's buffer
@@ -738,6 +744,7 @@ def measure_mlp_block(h, args, shard, Mt, d_model, steps, warmup, alone=False):
     ops = 2.0 * Mt * (K1 * N1 + N1 * N2)
     return dict(ms_step=ms_step, tops=ops / (ms_step * 1e-3) / 1e12, launches=int(launches), M=M, kernel=kernel,
                 clocks=None if alone else getattr(h, "clocks", None), egress_bytes=egress,
+                multicast=(shard == "cols_multicast" and mc_in_use),
                 timing="CUDA graph replay" if use_graph else "eager launches (NCCL inside the step)")
 
 
@@ -753,7 +760,9 @@ def run_mlp_block(args):
                                 "after each layer",
                         "cols_fused": "weight columns split over the ranks, the GEMM epilogue stores each rank's columns "
                                       "into every rank's output buffer over NVLink (peer stores), one 4-byte all-reduce "
-                                      "per layer as the barrier"}[args.shard],
+                                      "per layer as the barrier",
+                        "cols_multicast": "as cols_fused, the stores going once to an NVLink multicast address that "
+                                          "NVSwitch replicates to every rank (multimem.st)"}[args.shard],
            "M_per_gpu": r["M"], "l2": "operands far larger than L2 (x, hidden and output are each >= 0.25 GB per rank)",
            "step": "quantize_rows + layer 1 (uint8, ReLU) + layer 2 (fp32)", "timing": r["timing"]}
     h.finish(base_line(h, args, r["tops"], "TOPS", r["ms_step"], "strong", cfg, samples_per_s=Mt / (r["ms_step"] * 1e-3),
@@ -882,7 +891,7 @@ def main():
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
     ap.add_argument("--m-total", type=int, default=65536, help="tokens of the mlp_block workload (all ranks together)")
     ap.add_argument("--d-model", type=int, default=8192, help="width of the mlp_block workload (hidden = 4x)")
-    ap.add_argument("--shard", default="rows", choices=["rows", "cols", "cols_fused"], help="mlp_block partitioning")
+    ap.add_argument("--shard", default="rows", choices=["rows", "cols", "cols_fused", "cols_multicast"], help="mlp_block partitioning")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")

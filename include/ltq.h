@@ -64,6 +64,7 @@ typedef enum ltq_out_mode {
 #define LTQ_FLAG_FORCE_TC_PAIR 0x800u   /* with the tcgen05 path: the 2-CTA (cta_group::2) 256 x 256 tile kernel */
 #define LTQ_FLAG_FORCE_TC_SINGLE 0x1000u/* with the tcgen05 path: the single-CTA kernel */
 #define LTQ_FLAG_FORCE_SKINNY 0x400u/* weight-streaming kernel (needs M <= 16, K % 128 == 0) */
+#define LTQ_FLAG_MULTICAST_DEST 0x2000u /* ltq_layer_forward_scatter only: dests[0] is an NVLink multicast address */
 
 int ltq_version(void);
 const char *ltq_last_error(void);
@@ -212,7 +213,12 @@ int ltq_layer_set_clear_on_forward(ltq_layer *layer, int32_t *array_dev, uint64_
  * n_dests <= LTQ_MAX_DESTS.  The call only orders its own stores: before any rank READS its buffer, every rank's
  * call must have completed (a stream-ordered collective of any size, or a host barrier after a stream sync), and a
  * buffer must not be rewritten while another rank may still read it (alternate two buffers).
- * 16-byte stores are used when ld_out * element size, col_offset * element size and all bases are multiples of 16. */
+ * 16-byte stores are used when ld_out * element size, col_offset * element size and all bases are multiples of 16.
+ * With LTQ_FLAG_MULTICAST_DEST, dests holds ONE address of an NVLink multicast mapping (NVSwitch replicates every store
+ * into the buffer of each GPU bound to it, this GPU's included; e.g. the multicast pointer of a symmetric-memory
+ * allocation): every rank then sends its columns once instead of once per peer.  Stores are issued as multimem.st in
+ * 16-byte pieces, so the 16-byte conditions above must hold and out_features * element size must be a multiple of 16;
+ * only the tensor-core kernels take it (K % 16 == 0, M > 16 or K % 128 != 0), anything else is LTQ_ERR_UNSUPPORTED. */
 int ltq_layer_forward_scatter(ltq_layer *layer, const uint8_t *x_dev, const int32_t *asum_dev, uint64_t M,
                               const ltq_qparams *qp_in_dev, int out_mode, unsigned flags, void *const *dests, int n_dests,
                               uint64_t ld_out, uint64_t col_offset, void *stream);

@@ -440,6 +440,18 @@ static int layer_forward_impl(ltq_layer *layer, const uint8_t *x_dev, const int3
     epi.clear_count = layer->clear_count;
     const uint64_t esize = out_mode == LTQ_OUT_U8 ? 1 : 4;
     epi.ldc = ld_out;
+    if (flags & LTQ_FLAG_MULTICAST_DEST) {
+        LTQ_REQUIRE(n_dests == 1, LTQ_ERR_INVALID_ARG, "a multicast destination is the only destination");
+        Path path;
+        int rc = choose_path(M, layer->N, layer->K, x_dev, layer->w, flags, layer->dev->sms, &path);
+        if (rc != LTQ_OK) return rc;
+        LTQ_REQUIRE(path == PATH_TC && (ld_out * esize) % 16 == 0 && (col_offset * esize) % 16 == 0 && (layer->N * esize) % 16 == 0 &&
+                        ((uintptr_t)dests[0] & 15) == 0,
+                    LTQ_ERR_UNSUPPORTED,
+                    "multicast stores need the tensor-core kernel (K %% 16 == 0, more than 16 rows) and 16-byte aligned rows, "
+                    "column offset and slice width");
+        epi.mc = 1;
+    }
     epi.n_more = n_dests - 1;
     for (int d = 1; d < n_dests; d++) epi.more_out[d - 1] = static_cast<uint8_t *>(dests[d]) + col_offset * esize;
     return run_fc_gemm(*layer->dev, M, layer->N, layer->K, x_dev, layer->w, epi,

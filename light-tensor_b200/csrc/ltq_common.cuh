@@ -104,6 +104,9 @@ struct Epilogue {
     void *more_out[LTQ_MAX_DESTS - 1];
     int n_more;
     int staged;                   // set by a launcher that gave its kernel a PeerStage area (see below)
+    // `out` is an NVLink multicast address: one store reaches the buffer of every GPU bound to it (this GPU's included),
+    // issued as multimem.st in whole 16-byte pieces.  Set together with `staged` by the tensor-core launchers only.
+    int mc;
     // Column blocking (0 = off): output columns come in blocks of col_block, block b starting col_block_stride elements
     // after block b-1, i.e. element (i, j) lives at (j / col_block) * col_block_stride + i*ldc + j % col_block.  This is
     // how one GEMM over the patches of a whole batch writes NCHW: a block is one image's Ho*Wo output positions.
@@ -132,6 +135,7 @@ inline Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const in
     e.ldc = 0;
     e.n_more = 0;
     e.staged = 0;
+    e.mc = 0;
     e.col_block = 0;
     e.col_block_stride = 0;
     e.out_rowsum = nullptr;
@@ -300,37 +304,46 @@ __device__ __forceinline__ void epilogue_convert(const uint32_t (&v)[W], uint32_
     }
 }
 
+// 16 bytes to an ordinary address, or to all GPUs behind a multicast address (the bits travel unchanged).
+__device__ __forceinline__ void store16(void *dst, const uint4 &v, bool mc)
+{
+    if (mc)
+        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z),
+                     "r"(v.w)
+                     : "memory");
+    else
+        *reinterpret_cast<uint4 *>(dst) = v;
+}
+
 // The same chunk stored into every destination at element offset `off` (16-byte stores when vec_ok and the chunk is
 // complete, element by element otherwise).
 template <int OUT, int W>
 __device__ __forceinline__ void epilogue_store(const uint32_t (&res)[W], const Epilogue &e, void *out, uint64_t off,
                                                bool vec_ok, int valid)
 {
-    if (OUT == 0) {
-        for (int d = -1; d < e.n_more; d++) {
-            uint8_t *dst = static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + off;
-            if (vec_ok && valid == W) {
-                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+    constexpr int PER16 = OUT == 0 ? 16 : 4;  // elements per 16-byte piece
+    const bool mc = e.mc != 0;
+    for (int d = -1; d < e.n_more; d++) {
+        void *base = d < 0 ? out : e.more_out[d];
+        if (vec_ok) {
+            // whole 16-byte pieces as vectors (all of them when the chunk is complete), the rest element by element
+            uint8_t *dst = static_cast<uint8_t *>(base) + off * (OUT == 0 ? 1 : 4);
 #pragma unroll
-                for (int g = 0; g < W / 16; g++) d4[g] = make_uint4(res[4 * g], res[4 * g + 1], res[4 * g + 2], res[4 * g + 3]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < W; j++)
-                    if (j < valid) dst[j] = (uint8_t)(res[j >> 2] >> (8 * (j & 3)));
-            }
+            for (int g = 0; g < W / PER16; g++)
+                if ((g + 1) * PER16 <= valid)
+                    store16(dst + 16 * g, make_uint4(res[4 * g], res[4 * g + 1], res[4 * g + 2], res[4 * g + 3]), mc && d < 0);
         }
-    } else {
-        for (int d = -1; d < e.n_more; d++) {
-            uint32_t *dst = static_cast<uint32_t *>(d < 0 ? out : e.more_out[d]) + off;
-            if (vec_ok && valid == W) {
-                uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+        const int done = vec_ok ? (valid / PER16) * PER16 : 0;
+        if (OUT == 0) {
+            uint8_t *dst = static_cast<uint8_t *>(base) + off;
 #pragma unroll
-                for (int g = 0; g < W / 4; g++) d4[g] = make_uint4(res[4 * g], res[4 * g + 1], res[4 * g + 2], res[4 * g + 3]);
-            } else {
+            for (int j = 0; j < W; j++)
+                if (j >= done && j < valid) dst[j] = (uint8_t)(res[j >> 2] >> (8 * (j & 3)));
+        } else {
+            uint32_t *dst = static_cast<uint32_t *>(base) + off;
 #pragma unroll
-                for (int j = 0; j < W; j++)
-                    if (j < valid) dst[j] = res[j];
-            }
+            for (int j = 0; j < W; j++)
+                if (j >= done && j < valid) dst[j] = res[j];
         }
     }
 }
@@ -394,7 +407,7 @@ struct PeerStage {
                 const uint4 val = *reinterpret_cast<const uint4 *>(stage + r * 128 + ((u ^ (r & 7)) << 4));
                 const uint64_t o = off_bytes + (uint64_t)r * pitch_bytes + (uint64_t)u * 16;
                 for (int d = -1; d < e.n_more; d++)
-                    *reinterpret_cast<uint4 *>(static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + o) = val;
+                    store16(static_cast<uint8_t *>(d < 0 ? out : e.more_out[d]) + o, val, e.mc != 0 && d < 0);
             }
         }
         __syncwarp();

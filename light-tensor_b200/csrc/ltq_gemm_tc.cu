@@ -573,7 +573,7 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap *const mb[4], c
     // With further destinations (peer GPUs) the epilogue warps get a row-coalescing stage in place of one ring stage
     // (such launches are bound by the links, not by the tensor pipe).  Local-only stores gain nothing from it: measured.
     Epilogue epi_l = epi;
-    epi_l.staged = epi.n_more > 0 ? 1 : 0;
+    epi_l.staged = (epi.n_more > 0 || epi.mc) ? 1 : 0;
     uint32_t stages = epi_l.staged ? P_MAX_STAGES - 1 : P_MAX_STAGES;
     if (const char *e = getenv("LTQ_PAIR_STAGES")) stages = (uint32_t)atoi(e);  // TEMP experiment
     const size_t smem = pair_smem_bytes((int)stages, epi_l.staged != 0);

@@ -18,7 +18,7 @@ import ctypes as C
 import torch
 import torch.distributed as dist
 
-from ._binding import OUT_F32, OUT_I32, OUT_U8, QParams, check, lib
+from ._binding import FLAG_MULTICAST_DEST, OUT_F32, OUT_I32, OUT_U8, QParams, check, lib
 
 _OUT_DTYPE = {OUT_U8: torch.uint8, OUT_F32: torch.float32, OUT_I32: torch.int32}
 
@@ -103,6 +103,27 @@ class PeerBuffer:
             self._own = None
 
 
+class MulticastBuffer:
+    """One device buffer per rank behind an NVLink multicast mapping: a store to ``mc_ptr`` lands in every rank's
+    buffer (NVSwitch replicates it), so a rank sends its data once however many peers there are.  The buffers, the
+    multicast object and their exchange between the ranks come from ``torch.distributed``'s symmetric memory (NCCL
+    process groups on NVSwitch systems); ``mc_ptr`` is 0 where the system has no multicast support, and the caller
+    falls back to peer stores.  Collective: every rank of the group must construct it at the same point."""
+
+    def __init__(self, nbytes, device_index, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.nbytes = int(nbytes)
+        grp = group if group is not None else dist.group.WORLD
+        self.local = symm.empty(self.nbytes, dtype=torch.uint8, device=torch.device("cuda", device_index))
+        self._hdl = symm.rendezvous(self.local, grp)
+        self.mc_ptr = int(self._hdl.multicast_ptr or 0)      # 0 where the system has no multicast support
+        self.ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+
+    def close(self):
+        self._hdl = None
+        self.local = None
+
+
 def _wrap_device_memory(ptr, nbytes, device_index, owner):
     """uint8 CUDA tensor over memory this module allocated itself (no copy; `owner` is kept alive by the tensor)."""
     class _Iface:
@@ -136,10 +157,13 @@ class ColShardedLinear:
     ``forward`` returns the full ``[M, N]`` output on every rank."""
 
     def __init__(self, w_q_full_or_local, bias_q, N_total, qp_in, qp_wt, qp_out, backend=None, group=None, is_local=False,
-                 fused=False, max_rows=0, out_mode=OUT_U8):
+                 fused=False, max_rows=0, out_mode=OUT_U8, multicast=False):
         """``fused=True``: no all-gather; the GEMM epilogue stores this rank's columns straight into every rank's
         ``[max_rows, N]`` output buffer over NVLink (peer-mapped memory, two buffers used alternately), followed by one
-        tiny stream-ordered collective as the barrier.  Needs the CUDA backend and ``max_rows``/``out_mode`` up front."""
+        tiny stream-ordered collective as the barrier.  Needs the CUDA backend and ``max_rows``/``out_mode`` up front.
+        ``multicast=True`` (with ``fused``): the buffers sit behind an NVLink multicast mapping and each rank issues ONE
+        store per piece of output (``multimem.st``) that NVSwitch replicates to every rank, instead of one per peer;
+        falls back to peer stores where multicast is not available (``self.multicast`` tells which is in use)."""
         self.backend = backend or CudaBackend()
         self.group = group
         self.world = dist.get_world_size(group)
@@ -162,7 +186,17 @@ class ColShardedLinear:
             self.max_rows, self.out_mode = int(max_rows), out_mode
             self._esize = torch.empty(0, dtype=_OUT_DTYPE[out_mode]).element_size()
             dev = w_loc.device.index
-            self._bufs = [PeerBuffer(self.max_rows * self.N * self._esize, dev, group) for _ in range(2)]
+            nbytes = self.max_rows * self.N * self._esize
+            self.multicast = False
+            if multicast:
+                bufs = [MulticastBuffer(nbytes, dev, group) for _ in range(2)]
+                if all(b.mc_ptr for b in bufs):
+                    self._bufs, self.multicast = bufs, True
+                else:
+                    for b in bufs:
+                        b.close()
+            if not self.multicast:
+                self._bufs = [PeerBuffer(nbytes, dev, group) for _ in range(2)]
             self._turn = 0
             self._flag = torch.zeros(1, dtype=torch.int32, device=w_loc.device)
 
@@ -173,6 +207,13 @@ class ColShardedLinear:
             return
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
+        if self.multicast:
+            # nobody lets go of its part of the multicast mapping while another rank may still store through it
+            for b in self._bufs:
+                b.close()
+            dist.barrier(group=self.group)
+            self._bufs, self.fused = [], False
+            return
         for b in self._bufs:
             for p in b._opened:
                 lib().ltq_peer_close(p, b.device_index)
@@ -207,9 +248,13 @@ class ColShardedLinear:
             raise ValueError("fused column sharding was set up for another out_mode or fewer rows")
         buf = self._bufs[self._turn]
         self._turn ^= 1
-        # this rank's pointer first (the kernel's primary destination), then the peers'
-        ptrs = [buf.ptrs[self.rank]] + [p for r, p in enumerate(buf.ptrs) if r != self.rank]
-        self.layer.forward_scatter(x_q, ptrs, self.N, self.n0, out_mode, flags)
+        if self.multicast:
+            # one destination: the multicast address (this rank's own buffer is behind it too)
+            self.layer.forward_scatter(x_q, [buf.mc_ptr], self.N, self.n0, out_mode, flags | FLAG_MULTICAST_DEST)
+        else:
+            # this rank's pointer first (the kernel's primary destination), then the peers'
+            ptrs = [buf.ptrs[self.rank]] + [p for r, p in enumerate(buf.ptrs) if r != self.rank]
+            self.layer.forward_scatter(x_q, ptrs, self.N, self.n0, out_mode, flags)
         self._barrier(x_q.device)
         return buf.local[:M * self.N * self._esize].view(_OUT_DTYPE[out_mode]).view(M, self.N)
 

@@ -116,3 +116,69 @@ def test_fused_column_sharding_two_ranks_over_ipc(cuda):
     mp.spawn(_fused_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     for r in range(world):
         assert results.get(r) == "ok", results.get(r)
+
+
+def _multicast_worker(rank, world, port, results):
+    for p in (ROOT, os.path.join(ROOT, "light-tensor_b200", "python")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = str(rank), str(world)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import oracle
+        import ltq
+        from ltq import sharded
+        rng = np.random.default_rng(78)   # same stream on every rank: replicated inputs
+        M, K, N = 1100, 256, 1024         # more than 16 rows: tensor-core kernels; 1100 leaves a ragged last row block
+        w = rng.integers(0, 256, (N, K), dtype=np.uint8)
+        bias = rng.integers(-3000, 3000, N, dtype=np.int32)
+        rows = [(0.02, 128), (0.005, 127), (0.9, 12)]
+        qps = [ltq.QParams(float(np.float32(s)), z) for s, z in rows]
+        oqs = [oracle.qp(np.float32(s), z) for s, z in rows]
+        for mode, pair in ((ltq.OUT_U8, False), (ltq.OUT_F32, False), (ltq.OUT_U8, True)):
+            col = sharded.ColShardedLinear(torch.from_numpy(w).cuda(), torch.from_numpy(bias).cuda(), N, *qps, fused=True,
+                                           max_rows=M, out_mode=mode, multicast=True)
+            used = col.multicast
+            flags = (ltq.FLAG_FORCE_TC | ltq.FLAG_FORCE_TC_PAIR) if pair else 0
+            for it in range(4):
+                x = rng.integers(0, 256, (M - 40 * (it % 2), K), dtype=np.uint8)
+                got = col.forward(torch.from_numpy(x).cuda(), mode, flags)
+                torch.cuda.synchronize()
+                acc = oracle.port.acc_i32(x, w, x.shape[0], N, K, 128, 127, bias=bias)
+                want = (oracle.port.epilogue_u8(acc, 0.02, 0.005, 0.9, 12) if mode == ltq.OUT_U8
+                        else oracle.port.epilogue_f32(acc, 0.02, 0.005))
+                g = got.cpu().numpy()
+                assert np.array_equal(g.view(np.uint32) if mode == ltq.OUT_F32 else g,
+                                      want.view(np.uint32) if mode == ltq.OUT_F32 else want), \
+                    f"rank {rank} mode {mode} pair {pair} iteration {it}: result differs (multicast={used})"
+                dist.barrier()
+            col.close()
+        results[rank] = "ok multicast" if used else "ok peer stores"
+    except Exception:
+        import traceback
+        results[rank] = traceback.format_exc()
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_fused_column_sharding_through_an_nvlink_multicast_address(cuda):
+    """Two ranks on two GPUs (skipped with fewer): the fused exchange with every rank's columns stored ONCE to a multicast
+    address that NVSwitch replicates into both ranks' buffers.  Where the system offers no multicast the same code falls
+    back to peer stores and the result must be the same."""
+    if cuda.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_multicast_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    for r in range(world):
+        assert str(results.get(r)).startswith("ok"), results.get(r)
+    print("multicast test:", dict(results))
