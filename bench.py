@@ -617,7 +617,11 @@ def run_sections(h, args, pk):
         r = measure_mlp_mnist(h, args)
         return {"config": "configs[0]: 784-512-512-10, batch 64, independent replicas (one batch stream per GPU)",
                 "us_per_batch": r["ms_step"] * 1e3, "samples_per_s": 64 * h.world / (r["ms_step"] * 1e-3),
-                "gpu_launches_per_batch": r["launches_per_step"], "kernels": r["kernels"]}
+                "gpu_launches_per_batch": r["launches_per_step"], "kernels": r["kernels"],
+                "path": "fused chain: Quantize + 3 layers in one launch (ltq_mlp_forward)",
+                "layer_by_layer": {"us_per_batch": r["ms_layerwise"] * 1e3, "gpu_launches_per_batch": r["launches_layerwise"],
+                                   "kernels": r["kernels_layerwise"]},
+                "fused_output_equals_layer_by_layer": r["fused_equals_layerwise"]}
 
     def block(shard):
         def run():
@@ -821,10 +825,31 @@ def measure_mlp_mnist(h, args):
 
     steps = max(args.steps, 20)
     launches0 = ltq.kernel_launches()
-    ms_step = h.timed(step, steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    ms_layerwise = h.timed(step, steps, args.warmup, graph=not args.no_graph, sample_clocks=False)
+    launches_layerwise = (ltq.kernel_launches() - launches0) // (steps + args.warmup)
+    # the same batch through the fused chain: Quantize + the three layers in ONE launch (clusters of 8 CTAs, activations
+    # in distributed shared memory)
+    for lh in hs:
+        lh.set_rowsum_output(None)
+        lh.set_clear_on_forward(None)
+    mlp = ltq.FusedMLP(hs)
+    flags = [ltq.FLAG_RELU, ltq.FLAG_RELU, 0]
+    y_ref = y.clone()
+    kernels_fused = []
+
+    def step_fused(i):
+        mlp.forward(xd, flags, ltq.OUT_F32, out=y)
+        if i == 0:
+            kernels_fused.append(ltq.last_kernel())
+
+    launches0 = ltq.kernel_launches()
+    ms_step = h.timed(step_fused, steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
     launches = (ltq.kernel_launches() - launches0) // (steps + args.warmup)
-    return dict(ms_step=ms_step, launches_per_step=int(launches), steps=steps, kernels=kernels,
-                clocks=getattr(h, "clocks", None))
+    same = bool(torch.equal(y, y_ref))
+    hs[0].check()
+    return dict(ms_step=ms_step, launches_per_step=int(launches), steps=steps, kernels=kernels_fused,
+                ms_layerwise=ms_layerwise, launches_layerwise=int(launches_layerwise), kernels_layerwise=kernels,
+                fused_equals_layerwise=same, clocks=getattr(h, "clocks", None))
 
 
 def run_mlp_mnist(args):
@@ -834,7 +859,8 @@ def run_mlp_mnist(args):
     cfg = {"workload": "mlp_mnist (configs[0]): 784-512-512-10, batch 64, uint8 hidden activations with fused ReLU, "
                        "fp32 logits", "sharding": "independent replicas, one batch stream per GPU",
            "l2": "the whole model (0.67 MB) is L2-resident by nature; this configuration is launch-latency bound",
-           "step": "quantize_rows + 3 quantized linears whose epilogues emit the next layer's row sums (4 kernels)", "timing": "CUDA graph replay"}
+           "step": "fused chain (ltq_mlp_forward): Quantize + 3 quantized linears in one launch; the layer-by-layer "
+                   f"form (4 kernels) takes {r['ms_layerwise'] * 1e3:.2f} us per batch", "timing": "CUDA graph replay"}
     args.steps = r["steps"]
     h.finish(base_line(h, args, ops / (r["ms_step"] * 1e-3) / 1e12 * h.world, "TOPS", r["ms_step"], "weak", cfg,
                        samples_per_s=64 * h.world / (r["ms_step"] * 1e-3), gpu_launches=r["launches_per_step"] * r["steps"],

@@ -232,6 +232,27 @@ int ltq_peer_free(void *dev_ptr, int device);
 int ltq_peer_open(const unsigned char *handle64, int device, void **peer_ptr);
 int ltq_peer_close(void *peer_ptr, int device);
 
+/* ---- a chain of layers in one launch ----------------------------------------------------------------------------------
+ * The reference runs a quantized network as one kernel-sized step per layer with the activations going through memory
+ * in between (tests/nn_tests.cpp:630-640, 930-963).  For a small multi-layer perceptron that is all launch latency.  A
+ * fused chain runs Quantize(input) and 2 to 4 FullyConnected_q layers as ONE launch per batch: clusters of 8 CTAs keep
+ * the weights and the activations in (distributed) shared memory, every 64 rows of the batch one cluster.  The result
+ * is bit-identical to ltq_quantize_rows_u8 + ltq_layer_forward layer by layer.  No counterpart in the reference.
+ *
+ * layers: handles with weights bound (ltq_layer_set_weights) on one device, layer l+1 taking layer l's outputs; the chain
+ * borrows them (keep them alive, and create the chain again after rebinding weights).  Quantisation parameters are read
+ * from the layers at every forward: qp_in of layers[0] quantises the input, qp_out of layer l must equal qp_in of layer
+ * l+1 for the chain to mean what the layer-by-layer path means.  LTQ_ERR_UNSUPPORTED when a chain does not fit (K not a
+ * multiple of 16, a layer wider than 2048 outputs, or weights + activations beyond one cluster's shared memory: a chain
+ * of about 0.75 M weights fits); run it layer by layer then. */
+typedef struct ltq_mlp ltq_mlp;
+int ltq_mlp_create(ltq_mlp **mlp, ltq_layer *const *layers, int n_layers);
+int ltq_mlp_destroy(ltq_mlp *mlp);
+/* x_dev float32 [M, in_features of layers[0]]; hidden layers write uint8 (kept on chip), the last layer writes out_dev
+ * [M, out_features] in out_mode.  layer_flags: n_layers entries of LTQ_FLAG_RELU / LTQ_FLAG_SATURATE, or NULL for none. */
+int ltq_mlp_forward(ltq_mlp *mlp, const float *x_dev, uint64_t M, const unsigned *layer_flags, int out_mode, void *out_dev,
+                    void *stream);
+
 /* ---- one host thread, several devices ---------------------------------------------------------------------------------
  * l-ten's API is single-threaded and names a device per tensor (TensorOps::device_index, handle arrays of MAX_DEVICES = 8,
  * l-ten/globals.h:15,89-124) but has no multi-device code for this path.  These entry points let such a caller run a

@@ -124,7 +124,7 @@ struct Epilogue {
 };
 
 // The epilogue of a plain call: one dense [M, N] destination, no chain hooks.  Callers switch further fields on.
-inline Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *bias, const ltq_qparams &qa,
+__host__ __device__ inline Epilogue make_epilogue(const int32_t *bsum, const int32_t *asum, const int32_t *bias, const ltq_qparams &qa,
                               const ltq_qparams &qb, const ltq_qparams &qc, uint64_t K, int out_mode, unsigned flags)
 {
     Epilogue e;

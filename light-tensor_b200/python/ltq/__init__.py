@@ -12,7 +12,7 @@ from ._binding import (LtqError, QParams, lib, lib_path, last_error, last_kernel
                        DECLARED_SYMBOLS)
 from .ops import (GetMinMax, ComputeQuantizationParams, compute_qparams_dev, Quantize, QuantizeInt32, Dequantize,
                   quantize_rows, row_sums, quantized_matmul, quantized_matmul_static, matmul_u8)
-from .layer import Conv2d_q, ConvHandle, FullyConnected_q, LayerHandle
+from .layer import Conv2d_q, ConvHandle, FullyConnected_q, FusedMLP, LayerHandle
 from .calibration import MinMaxObserver, calibrate, quantize_module
 from .checkpoint import load_checkpoint, save_checkpoint
 from .group import DeviceGroup
@@ -21,5 +21,5 @@ __all__ = [
     "LtqError", "QParams", "lib", "lib_path", "last_error", "last_kernel", "kernel_launches", "OUT_U8", "OUT_F32", "OUT_I32",
     "FLAG_RELU", "FLAG_SATURATE", "FLAG_BIAS_PER_CHANNEL", "FLAG_FORCE_SIMT", "FLAG_FORCE_TC", "FLAG_FORCE_SKINNY", "FLAG_FORCE_TC_PAIR", "FLAG_FORCE_TC_SINGLE", "FLAG_MULTICAST_DEST", "DECLARED_SYMBOLS",
     "GetMinMax", "ComputeQuantizationParams", "compute_qparams_dev", "Quantize", "QuantizeInt32", "Dequantize",
-    "quantize_rows", "row_sums", "quantized_matmul", "quantized_matmul_static", "matmul_u8", "FullyConnected_q", "LayerHandle", "Conv2d_q", "ConvHandle", "MinMaxObserver", "calibrate", "quantize_module", "save_checkpoint", "load_checkpoint", "DeviceGroup",
+    "quantize_rows", "row_sums", "quantized_matmul", "quantized_matmul_static", "matmul_u8", "FullyConnected_q", "LayerHandle", "FusedMLP", "Conv2d_q", "ConvHandle", "MinMaxObserver", "calibrate", "quantize_module", "save_checkpoint", "load_checkpoint", "DeviceGroup",
 ]

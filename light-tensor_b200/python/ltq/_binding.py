@@ -66,6 +66,9 @@ _SIGNATURES = {
     "ltq_peer_free": (_int, [_vp, _int]),
     "ltq_peer_open": (_int, [C.c_char_p, _int, C.POINTER(_vp)]),
     "ltq_peer_close": (_int, [_vp, _int]),
+    "ltq_mlp_create": (_int, [C.POINTER(_vp), C.POINTER(_vp), _int]),
+    "ltq_mlp_destroy": (_int, [_vp]),
+    "ltq_mlp_forward": (_int, [_vp, _vp, _u64, C.POINTER(C.c_uint), _int, _vp, _vp]),
     "ltq_comm_init_all": (_int, [C.POINTER(_vp), _int, C.POINTER(_int)]),
     "ltq_comm_destroy": (_int, [_vp]),
     "ltq_comm_size": (_int, [_vp]),

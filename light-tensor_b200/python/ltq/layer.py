@@ -83,6 +83,40 @@ class LayerHandle:
         check(lib().ltq_layer_check(self._h, self._stream()))
 
 
+class FusedMLP:
+    """``ltq_mlp``: Quantize(input) and a chain of 2 to 4 quantized linear layers as one kernel launch per batch (clusters
+    of 8 CTAs, activations kept in distributed shared memory).  ``layers``: LayerHandles with weights and qparams set,
+    layer l+1 consuming layer l's uint8 output.  Raises LtqError(-2) when the chain does not fit one cluster."""
+
+    def __init__(self, layers):
+        self.layers = list(layers)           # borrowed by the library: keep them alive
+        self._h = C.c_void_p()
+        arr = (C.c_void_p * len(self.layers))(*[l._h.value for l in self.layers])
+        check(lib().ltq_mlp_create(C.byref(self._h), arr, len(self.layers)))
+
+    def close(self):
+        if self._h:
+            lib().ltq_mlp_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def forward(self, x, layer_flags=None, out_mode=OUT_U8, out=None):
+        """x: float32 CUDA [M, K0] (contiguous).  Returns [M, N_last] in the dtype of out_mode."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+        M = x.shape[0]
+        if out is None:
+            out = torch.empty((M, self.layers[-1].N), dtype=_OUT_DTYPE[out_mode], device=x.device)
+        fl = None if layer_flags is None else (C.c_uint * len(self.layers))(*layer_flags)
+        check(lib().ltq_mlp_forward(self._h, x.data_ptr(), M, fl, out_mode, out.data_ptr(),
+                                    C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)))
+        return out
+
+
 class FullyConnected_q:
     """Quantized fully-connected layer, same surface as l-ten's (l-ten/layers.h:69-106,
     l-ten/fully_connected.cpp:295-446): uint8 weights ``{1,1,N,K}``, int32 bias ``{N}``, three per-tensor
