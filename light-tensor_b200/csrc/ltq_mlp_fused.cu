@@ -19,6 +19,14 @@
 //    and no CTA leaves before the whole cluster is done (a peer may still be writing into its shared memory).
 //
 // Integer sums are exact whatever the order, so the result equals the layer-by-layer path bit for bit.
+//
+// Measured on the 784-512-512-10 network, batch 64 (B200, a CUDA graph of back-to-back launches): 13.5 us per batch
+// against 16.5 us layer by layer.  After the grid dependency resolves: input quantise and its exchange 3.7 us; per hidden
+// layer 0.6-0.9 us of MMAs and 2.6 us of epilogue and exchange, about 1 us of which is the cluster-scope fence in front of
+// the hand-over arrival; last layer 1 us.  A variant with clusters of 4, the weights streamed through a ring and whole
+// activation slabs sent with bulk copies (cp.async.bulk shared::cta -> shared::cluster) instead of 16-byte remote stores
+// was built and measured at 18.3 us: with both operands 128 rows tall in one SM's shared memory its MMAs take 140 cycles
+// instead of 70, and every CTA quantises twice as many input rows.
 #include <cuda.h>
 
 #include <new>
