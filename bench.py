@@ -357,7 +357,7 @@ def h2d_ceiling_gbs(h, nbytes):
 
 
 # ---- the 4096^3 linear and the skinny linear ---------------------------------------------------------------------------
-def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=0.0):
+def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=0.0, next_hint=True):
     """One quantized linear per step.  Returns a dict of measurements (times are max over ranks)."""
     import ltq
     torch, dev = h.torch, h.dev
@@ -390,6 +390,11 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
         qps_o.append(qo)
         wqs.append(wq)
     del w32
+    if wl == "skinny" and next_hint:
+        # the steps visit the layers in a fixed order, like the layers of a network: each one names its successor, so
+        # that its weight-streaming kernel asks the start of the next weights into L2 (ltq_layer_set_next)
+        for i in range(sets):
+            layers[i].set_next(layers[(i + 1) % sets])
     xq = [torch.empty((M, K), dtype=torch.uint8, device=dev) for _ in range(sets)]
     asum = [torch.empty(M, dtype=torch.int32, device=dev) for _ in range(sets)]
     outs = [torch.empty((M, N), dtype=out_dtype, device=dev) for _ in range(sets)]
@@ -440,6 +445,7 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
                        steps, 3, graph=not args.no_graph)
     for lh in layers:
         lh.check()
+        lh.set_next(None)
 
     res = dict(M=M, N=N, K=K, sets=sets, ms_step=ms_step, ms_gemm=ms_gemm, ms_quant=ms_quant, launches=int(launches),
                kernel=kernel, clocks=clocks, sustained=sustained, step_overlapped=step is step_overlap,
@@ -599,16 +605,22 @@ def run_sections(h, args, pk):
 
     def skinny():
         res = {"config": "configs[3]: K=4096, N=11008, fp32 out, 6 rotating 45 MB weight sets (every launch streams its "
-                         "weights from HBM); us = weight-streaming kernel alone, step_us = quantize_rows + kernel, per GPU"}
+                         "weights from HBM), visited in a fixed order with each layer naming the next (ltq_layer_set_next); "
+                         "us = weight-streaming kernel alone, step_us = quantize_rows + kernel, per GPU; "
+                         "us_without_next_hint = the kernel alone with no layer naming its successor; "
+                         "graphs of at least 60 launches"}
         traffic, note = None, None
         for m in (1, 4, 16):
-            r = measure_linear(h, args, "skinny", m_rows=m, with_e2e=False)
+            r = measure_linear(h, args, "skinny", m_rows=m, with_e2e=False, steps=max(args.steps, 60))
             if traffic is None:
                 traffic, note = ncu_traffic("gemv_kernel_skinny_m16.md", r["kernel"])
             roof = skinny_roofline(r, pk, traffic, note)
             res[f"m{m}"] = {"us": r["ms_gemm"] * 1e3, "gbs": roof["achieved"], "frac_of_measured": roof["frac"],
                             "frac_of_nominal": roof["frac_of_nominal_8TBs"], "step_us": r["ms_step"] * 1e3,
                             "algorithmic_bytes": roof["algorithmic_bytes"], "kernel": r["kernel"]}
+            if m == 16:
+                r0 = measure_linear(h, args, "skinny", m_rows=m, with_e2e=False, steps=max(args.steps, 60), next_hint=False)
+                res[f"m{m}"]["us_without_next_hint"] = r0["ms_gemm"] * 1e3
         res["traffic"] = traffic
         res["traffic_source"] = note
         return res

@@ -204,6 +204,16 @@ int ltq_layer_set_rowsum_output(ltq_layer *layer, int32_t *rowsum_dev);
  * asum_dev passed to the same forward. */
 int ltq_layer_set_clear_on_forward(ltq_layer *layer, int32_t *array_dev, uint64_t count);
 
+/* A hint for chains of layers at small batch (M <= 16), where each forward is bound by reading the layer's weights
+ * once from device memory: `next` is the layer whose forward follows `layer`'s on the same stream (QNet::forward,
+ * tests/nn_tests.cpp:630-640, calls its layers in a fixed order).  The weight-streaming kernel of `layer` then asks
+ * the first part of `next`'s weights into the L2 cache once all of its own reads are on their way, so that memory
+ * keeps streaming while `layer` finishes and `next` starts.  Purely a performance hint: results are unchanged, and it
+ * is ignored by the other kernels and when the two layers' shapes do not divide over the SMs alike.  The hint
+ * records next's weight pointer and shape as they are NOW; set it again after rebinding next's weights, and clear it
+ * (next = NULL) before those weights are freed.  Both layers must be on the same device. */
+int ltq_layer_set_next(ltq_layer *layer, const ltq_layer *next);
+
 /* ltq_layer_forward with the result written into several buffers at once, each holding rows of ld_out elements, at
  * column col_offset: element (i, j) of this layer's output goes to dests[d][i * ld_out + col_offset + j] for every d.
  * No counterpart in the reference (which runs on one device).  This is the exchange step of a COLUMN-SHARDED layer

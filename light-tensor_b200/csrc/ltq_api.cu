@@ -237,8 +237,9 @@ int ltq::run_fc_gemm(const GemmDevice &gd, uint64_t M, uint64_t N, uint64_t K, c
     switch (path) {
         case PATH_SKINNY:
             // a layer's weights are fixed between ltq_layer_set_weights calls (which synchronise), so they may be streamed early
+            if (layer) layer->next.cache = &layer->map_next_gemv;  // (the handle may have been moved since the hint was set)
             LTQ_CUDA_TRY(launch_gemv(A, B, M, N, K, epi, out, dev->status, dev->sms, stream, layer ? &layer->map_w_gemv : nullptr,
-                                     layer != nullptr));
+                                     layer != nullptr, layer && layer->next.W ? &layer->next : nullptr));
             break;
         case PATH_TC: {
             const bool pair = !(flags & LTQ_FLAG_FORCE_TC_SINGLE) &&
@@ -472,6 +473,21 @@ int ltq_layer_set_clear_on_forward(ltq_layer *layer, int32_t *array_dev, uint64_
                 "a forward cannot clear the array it accumulates its own row sums into");
     layer->clear_ptr = count ? array_dev : nullptr;
     layer->clear_count = (uint32_t)count;
+    return LTQ_OK;
+}
+
+int ltq_layer_set_next(ltq_layer *layer, const ltq_layer *next)
+{
+    LTQ_REQUIRE(layer, LTQ_ERR_INVALID_ARG, "Invalid argument");
+    layer->next = ltq::GemvNext();
+    layer->map_next_gemv = ltq::GemvWeightMaps();
+    if (!next) return LTQ_OK;
+    LTQ_REQUIRE(next->device == layer->device, LTQ_ERR_INVALID_ARG, "ltq_layer_set_next: the two layers are on different devices");
+    LTQ_REQUIRE(next->w, LTQ_ERR_INVALID_ARG, "ltq_layer_set_next: the next layer has no weights bound");
+    layer->next.W = next->w;
+    layer->next.N = next->N;
+    layer->next.K = next->K;
+    layer->next.boxes = ltq::GEMV_NEXT_BOXES;
     return LTQ_OK;
 }
 

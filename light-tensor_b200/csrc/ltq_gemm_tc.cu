@@ -575,7 +575,6 @@ cudaError_t launch_pair(const CUtensorMap &ma, const CUtensorMap *const mb[4], c
     Epilogue epi_l = epi;
     epi_l.staged = (epi.n_more > 0 || epi.mc) ? 1 : 0;
     uint32_t stages = epi_l.staged ? P_MAX_STAGES - 1 : P_MAX_STAGES;
-    if (const char *e = getenv("LTQ_PAIR_STAGES")) stages = (uint32_t)atoi(e);  // TEMP experiment
     const size_t smem = pair_smem_bytes((int)stages, epi_l.staged != 0);
     cudaError_t e = launch_chained(gemm_tc_pair_kernel<OUT>, dim3((unsigned)(2 * pairs)), dim3(P_THREADS), smem, stream, ma,
                                    *mb[0], *mb[1], *mb[2], *mb[3], tl, (uint32_t)M, (uint32_t)N, (uint32_t)K, stages,

@@ -114,6 +114,12 @@ Plan make_plan(uint64_t M, uint64_t N, uint64_t K, int sms, size_t smem_limit)
     return p;
 }
 
+// Band geometry of the launch that follows (GemvNext), as the kernel needs it to name that launch's first boxes.
+struct NextBand {
+    uint32_t boxes;  // 0: no hint
+    uint32_t tiles_per_cta, tiles, octs, oct_lo, lines, chunks;
+};
+
 }  // namespace
 
 // OUT: 0 = uint8, 1 = float, 2 = int32 (ltq_out_mode).
@@ -122,7 +128,8 @@ __global__ void __launch_bounds__(THREADS, 2)
 gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w_lo,
             const __grid_constant__ CUtensorMap map_w_hi, uint32_t M, uint32_t N, uint32_t K, uint32_t tiles_per_cta,
             uint32_t tiles, uint32_t oct_lo, uint32_t lines, uint32_t stages, uint32_t prefetch, uint32_t w_stage,
-            uint32_t x_stage, uint32_t slack, Epilogue epi, void *__restrict__ out, uint32_t *status)
+            uint32_t x_stage, uint32_t slack, Epilogue epi, void *__restrict__ out, uint32_t *status,
+            const __grid_constant__ CUtensorMap map_n_lo, const __grid_constant__ CUtensorMap map_n_hi, NextBand nx)
 {
     // By every thread, first thing: the CTA counts as released once all of them have said so, and the next launch's CTAs
     // should move in (and start fetching their weights) as early as they can.
@@ -242,6 +249,19 @@ gemv_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ C
                 if (pf.t < t_end) {
                     tma_prefetch_3d(pf.map, 0, (int32_t)pf.row0, (int32_t)(pf.kc * lines));
                     advance(pf);
+                }
+            }
+            // Everything this launch reads is on its way.  The CTA that takes this CTA's place in the next launch will
+            // want the first boxes of the same band of the next weight matrix: ask them into L2 now, behind this
+            // launch's own requests, so that they arrive while this CTA is busy with its last MMAs and its epilogue.
+            if (nx.boxes && !*abort_flag) {
+                uint32_t t = blockIdx.x * nx.tiles_per_cta, kc = 0;
+                const uint32_t t_last = t + nx.tiles_per_cta;
+                for (uint32_t i = 0; i < nx.boxes && t < t_last; i++) {
+                    const uint32_t o0 = (uint32_t)(((uint64_t)t * nx.octs) / nx.tiles);
+                    const uint32_t o1 = (uint32_t)(((uint64_t)(t + 1) * nx.octs) / nx.tiles);
+                    tma_prefetch_3d((o1 - o0) == nx.oct_lo ? &map_n_lo : &map_n_hi, 0, (int32_t)(o0 * 8), (int32_t)(kc * nx.lines));
+                    if (++kc == nx.chunks) { kc = 0; t++; }
                 }
             }
         }
@@ -383,7 +403,7 @@ namespace {
 template <int OUT>
 cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOperandMap &hi, const Plan &p, uint64_t M,
                      uint64_t N, uint64_t K, const Epilogue &epi, void *out, uint32_t *status, cudaStream_t stream,
-                     bool early_weights)
+                     bool early_weights, const TcOperandMap &nlo, const TcOperandMap &nhi, const NextBand &nx)
 {
     // The opt-in shared-memory size is set once per device: the kernel runs for a few microseconds and a runtime
     // attribute call per launch would cost as much as the launch.
@@ -422,7 +442,8 @@ cudaError_t launch_t(const TcOperandMap &mx, const TcOperandMap &lo, const TcOpe
     e = cudaLaunchKernelEx(&cfg, gemv_kernel<OUT>, *reinterpret_cast<const CUtensorMap *>(mx.opaque),
                            *reinterpret_cast<const CUtensorMap *>(lo.opaque), *reinterpret_cast<const CUtensorMap *>(hi.opaque),
                            (uint32_t)M, (uint32_t)N, (uint32_t)K, p.tiles_per_cta, p.tiles, p.oct_lo, p.lines, p.stages,
-                           p.prefetch, p.w_stage, p.x_stage, p.slack, epi, out, status);
+                           p.prefetch, p.w_stage, p.x_stage, p.slack, epi, out, status,
+                           *reinterpret_cast<const CUtensorMap *>(nlo.opaque), *reinterpret_cast<const CUtensorMap *>(nhi.opaque), nx);
     count_launch();
     note_kernel("gemv_kernel<%s>", out_mode_name(OUT));
     return e;
@@ -437,7 +458,8 @@ bool gemv_shape_ok(uint64_t M, uint64_t N, uint64_t K, const void *x, const void
 }
 
 cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t N, uint64_t K, const Epilogue &epi,
-                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache, bool early_weights)
+                        void *out, uint32_t *status, int sms, cudaStream_t stream, GemvWeightMaps *cache, bool early_weights,
+                        const GemvNext *next)
 {
     const Plan p = make_plan(M, N, K, sms, SMEM_FULL);
     if (!p.ok) return cudaErrorInvalidConfiguration;
@@ -452,10 +474,35 @@ cudaError_t launch_gemv(const uint8_t *x, const uint8_t *W, uint64_t M, uint64_t
     if (!wm->hi.matches(W, N, K, (int)p.oct_hi * 8, (int)p.lines)) {
         if (tc_make_map_lines(&wm->hi, W, N, K, (int)p.oct_hi * 8, (int)p.lines) != 0) return cudaErrorInvalidValue;
     }
+    // The launch behind this one (a hint): its plan must put the same band on the same CTA index for the boxes asked into
+    // L2 to be the ones that CTA's successor reads first.  Without a usable hint the kernel gets this launch's own maps
+    // (never dereferenced: boxes = 0).
+    NextBand nx{};
+    const TcOperandMap *nlo = &wm->lo, *nhi = &wm->hi;
+    GemvWeightMaps next_local;
+    if (next && next->W && next->boxes && (((uintptr_t)next->W & 15) == 0) && next->K >= 128 && next->K % 128 == 0 &&
+        next->N >= 1 && next->N < (1ull << 31) && next->K < (1ull << 31)) {
+        const Plan q = make_plan(M, next->N, next->K, sms, SMEM_FULL);
+        if (q.ok && q.grid == p.grid) {
+            GemvWeightMaps *nm = next->cache ? next->cache : &next_local;
+            bool ok = true;
+            if (!nm->lo.matches(next->W, next->N, next->K, (int)q.oct_lo * 8, (int)q.lines))
+                ok = tc_make_map_lines(&nm->lo, next->W, next->N, next->K, (int)q.oct_lo * 8, (int)q.lines) == 0;
+            if (ok && !nm->hi.matches(next->W, next->N, next->K, (int)q.oct_hi * 8, (int)q.lines))
+                ok = tc_make_map_lines(&nm->hi, next->W, next->N, next->K, (int)q.oct_hi * 8, (int)q.lines) == 0;
+            if (ok) {
+                const uint32_t klines = (uint32_t)(next->K / LINE);
+                nx = NextBand{next->boxes, q.tiles_per_cta, q.tiles, (uint32_t)((next->N + 7) / 8), q.oct_lo, q.lines,
+                              (klines + q.lines - 1) / q.lines};
+                nlo = &nm->lo;
+                nhi = &nm->hi;
+            }
+        }
+    }
     switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_t<0>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights);
-        case LTQ_OUT_F32: return launch_t<1>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights);
-        default: return launch_t<2>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights);
+        case LTQ_OUT_U8: return launch_t<0>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights, *nlo, *nhi, nx);
+        case LTQ_OUT_F32: return launch_t<1>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights, *nlo, *nhi, nx);
+        default: return launch_t<2>(mx, wm->lo, wm->hi, p, M, N, K, epi, out, status, stream, early_weights, *nlo, *nhi, nx);
     }
 }
 

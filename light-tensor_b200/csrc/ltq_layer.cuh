@@ -22,5 +22,7 @@ struct ltq_layer {
     ltq::TcOperandMap map_w[LAYER_MAPS];  // weight tensor maps of the tensor-core kernels, one per box height, built on demand
     int map_w_next = 0;
     ltq::GemvWeightMaps map_w_gemv;     // weight tensor maps of the skinny kernel
+    ltq::GemvNext next;                 // weights of the layer that runs after this one (ltq_layer_set_next), with
+    ltq::GemvWeightMaps map_next_gemv;  // their tensor maps as the skinny kernel of THIS layer needs them
     ltq::GemmDevice *dev = nullptr;  // the device's SM count and status word
 };

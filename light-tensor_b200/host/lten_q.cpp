@@ -256,6 +256,13 @@ void FullyConnected_q::set_output(ltq_out_mode mode, bool relu, bool saturate)
     flags_ = (relu ? LTQ_FLAG_RELU : 0u) | (saturate ? LTQ_FLAG_SATURATE : 0u);
 }
 
+void FullyConnected_q::set_next(const FullyConnected_q *next)
+{
+    if (!handle_) LTEN_ERR("set_next: the layer is not on the GPU");
+    if (next && !next->handle_) LTEN_ERR("set_next: the next layer is not on the GPU");
+    if (ltq_layer_set_next(handle_, next ? next->handle_ : nullptr) != LTQ_OK) LTEN_ERR(ltq_last_error());
+}
+
 void FullyConnected_q::to(device target_device, int target_device_index)
 {
     if (!weight_ptr_) LTEN_ERR("init() has not been called");

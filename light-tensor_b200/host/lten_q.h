@@ -145,6 +145,10 @@ public:
     void *get_stream() const { return stream_; }
     // Additive: LTQ_ERR_DEVICE_TIMEOUT surfaced as an exception if a bounded device-side wait expired since the last call.
     void check();
+    // Additive, a performance hint for networks run at small batch: `next` is the layer whose forward() follows this
+    // one's (nullptr clears).  Both must already be on the GPU; call again after either moves, and clear it before
+    // `next` is destroyed.  Results are unchanged (ltq_layer_set_next).
+    void set_next(const FullyConnected_q *next);
 
 private:
     friend class DeviceGroup;

@@ -61,6 +61,7 @@ _SIGNATURES = {
     "ltq_layer_check": (_int, [_vp, _vp]),
     "ltq_layer_set_rowsum_output": (_int, [_vp, _vp]),
     "ltq_layer_set_clear_on_forward": (_int, [_vp, _vp, _u64]),
+    "ltq_layer_set_next": (_int, [_vp, _vp]),
     "ltq_layer_forward_scatter": (_int, [_vp, _vp, _vp, _u64, _vp, _int, C.c_uint, C.POINTER(_vp), _int, _u64, _u64, _vp]),
     "ltq_peer_alloc": (_int, [C.POINTER(_vp), _u64, _int, C.c_char_p]),
     "ltq_peer_free": (_int, [_vp, _int]),

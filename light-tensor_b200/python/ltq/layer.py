@@ -69,6 +69,13 @@ class LayerHandle:
         check(lib().ltq_layer_set_clear_on_forward(self._h, None if array is None else array.data_ptr(),
                                                    0 if array is None else array.numel()))
 
+    def set_next(self, nxt):
+        """Hint for chains at small batch: ``nxt`` (a LayerHandle or None) is the layer whose forward follows this one's
+        on the same stream; the weight-streaming kernel then asks the start of its weights into L2 while it finishes.
+        Results are unchanged.  Set it again after ``nxt.set_weights``; pass None before ``nxt``'s weights are freed."""
+        self._next = nxt  # keeps the weights it points at alive
+        check(lib().ltq_layer_set_next(self._h, None if nxt is None else nxt._h))
+
     def forward_scatter(self, x, dest_ptrs, ld_out, col_offset, out_mode=OUT_U8, flags=0, asum=None, qp_in_dev=None):
         """Like forward, but element (i, j) goes to ``dest_ptrs[d] + (i * ld_out + col_offset + j) * itemsize`` for
         every d.  dest_ptrs are raw device addresses (this GPU's buffer first, then peers' mapped buffers)."""

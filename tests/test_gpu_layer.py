@@ -226,6 +226,55 @@ def test_back_to_back_skinny_launches_respect_their_inputs(cuda, oracle):
     l1.check()
 
 
+@pytest.mark.parametrize("M", [1, 9, 16])
+def test_next_layer_hint_leaves_results_unchanged(cuda, oracle, M):
+    """ltq_layer_set_next: a layer that names its successor asks the start of the successor's weights into L2 from
+    inside its own weight-streaming kernel.  A chain l1 -> l2 -> l3 -> l1 ... with every hint set (same split over the
+    SMs for l1 / l2, a different one for l3, which the hint must survive), run back to back, against the oracle; then
+    with the hints cleared; a layer without weights is refused as a successor."""
+    import ltq
+    rng = np.random.default_rng(400 + M)
+    K, N1, N2, N3, reps = 1024, 2048, 1536, 512, 6
+    w1 = rng.integers(0, 256, (N1, K), dtype=np.uint8)
+    w2 = rng.integers(0, 256, (N2, N1), dtype=np.uint8)
+    w3 = rng.integers(0, 256, (N3, N2), dtype=np.uint8)
+    rows = [(0.02, 128), (0.005, 127), (3.0, 7), (0.004, 120), (40.0, 100), (0.003, 131), (500.0, 90)]
+    q_in, q_w1, q_a, q_w2, q_b, q_w3, q_out = [ltq_qp(r) for r in rows]
+    ls = [ltq.LayerHandle(0, K, N1), ltq.LayerHandle(0, N1, N2), ltq.LayerHandle(0, N2, N3)]
+    for l, w, qs in zip(ls, (w1, w2, w3), ((q_in, q_w1, q_a), (q_a, q_w2, q_b), (q_b, q_w3, q_out))):
+        l.set_weights(cuda.from_numpy(w).cuda())
+        l.set_qparams(*qs)
+    empty = ltq.LayerHandle(0, K, N1)
+    with pytest.raises(ltq.LtqError):
+        ls[0].set_next(empty)
+    xq = [rng.integers(0, 256, (M, K), dtype=np.uint8) for _ in range(reps)]
+    xq_dev = [cuda.from_numpy(x).cuda() for x in xq]
+    o = [qp_of(oracle, r) for r in rows]
+    want = []
+    for i in range(reps):
+        a, _ = oracle.port.quantized_matmul(xq[i], w1, M, N1, K, [o[0], o[1], o[2]])
+        b, _ = oracle.port.quantized_matmul(a, w2, M, N2, N1, [o[2], o[3], o[4]])
+        c, _ = oracle.port.quantized_matmul(b, w3, M, N3, N2, [o[4], o[5], o[6]])
+        want.append(c)
+    for hinted in (True, False):
+        for i, l in enumerate(ls):
+            l.set_next(ls[(i + 1) % 3] if hinted else None)
+        outs = []
+        cuda.cuda.synchronize()
+        for i in range(reps):   # 3 dependent weight-streaming launches per iteration, nothing in between
+            a = ls[0].forward(xq_dev[i], ltq.OUT_U8, ltq.FLAG_FORCE_SKINNY)
+            b = ls[1].forward(a, ltq.OUT_U8, ltq.FLAG_FORCE_SKINNY)
+            outs.append(ls[2].forward(b, ltq.OUT_U8, ltq.FLAG_FORCE_SKINNY))
+            assert ltq.last_kernel().startswith("gemv_kernel")
+        cuda.cuda.synchronize()
+        for i in range(reps):
+            np.testing.assert_array_equal(outs[i].cpu().numpy(), want[i], err_msg=f"hinted={hinted}, iteration {i}")
+        for l in ls:
+            l.check()
+    for l in ls:
+        l.set_next(None)
+
+
 @pytest.mark.parametrize("M", [64, 300])
 def test_back_to_back_tensor_core_layers_respect_their_inputs(cuda, oracle, M):
     """quantize_rows, the row-sum kernel and the tensor-core GEMMs are launched as programmatic dependents of the kernel

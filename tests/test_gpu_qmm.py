@@ -139,9 +139,10 @@ def test_pair_kernel_tile_widths(cuda, oracle, shape):
 
 
 @pytest.mark.parametrize("shape", [(2500, 2000, 192), (2560, 2048, 64), (4096, 4096, 128)])
-def test_pair_kernel_half_width_tail(cuda, oracle, shape):
-    """Shapes whose 256-wide tiles leave a short remainder behind the last whole round of CTA pairs: the remainder runs
-    as half-width items (ragged last rows and columns included).  All output modes against the oracle."""
+def test_pair_kernel_ragged_tile_widths(cuda, oracle, shape):
+    """Shapes whose 256-wide tiles would leave a short remainder behind the last whole round of CTA pairs: the pair
+    kernel cuts every band into tiles of up to four different widths instead (ragged last rows and columns included).
+    All output modes against the oracle."""
     import ltq
     M, N, K = shape
     rng = np.random.default_rng(M + N)
