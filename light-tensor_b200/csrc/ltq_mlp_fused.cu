@@ -75,28 +75,19 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
     return r;
 }
-__device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v)
+// Bulk copy from this CTA's shared memory into another CTA's (both 16-byte aligned, a multiple of 16 bytes); the bytes
+// are counted on that CTA's mbarrier, so data and "it has arrived" travel together: no fence, no separate arrival.
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster)
 {
-    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_cluster), "r"(src_local), "r"(bytes), "r"(bar_cluster)
+                 : "memory");
 }
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
-{
-    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-// One arrival on a barrier of another CTA of the cluster; everything this thread wrote (or has observed) before is
-// visible to whoever acquires the barrier's completion.
-__device__ __forceinline__ void arrive_cluster(uint32_t cluster_bar)
-{
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-// Hand-over by a whole warp: every lane orders its own remote stores at cluster scope, the lanes meet, and one lane
-// arrives on the barrier at `bar_local` in every CTA of the cluster.
-__device__ __forceinline__ void warp_arrive_all_ctas(uint32_t bar_local, int lane)
-{
-    asm volatile("fence.acq_rel.cluster;" ::: "memory");
-    __syncwarp();
-    if (lane < CL) arrive_cluster(map_to_cta(bar_local, (uint32_t)lane));
-}
+// The two halves of the cluster-wide barrier (every thread of every CTA arrives once, then waits once).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// Barrier among the four epilogue warps only (the MMA and weight warps do not take part).
+__device__ __forceinline__ void epilogue_warps_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ bool try_wait_cluster(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -131,12 +122,20 @@ __device__ __forceinline__ bool wait_cluster(uint32_t bar, volatile uint32_t *ab
     }
 }
 
-// Byte offset of element (row, k) inside an activation tile: 128-byte-wide K slabs of ROWS rows, 16-byte pieces XORed
-// with the row's low three bits (what TMA's 128-byte swizzle produces and the MMA descriptor expects).
-__device__ __forceinline__ uint32_t act_offset(uint32_t row, uint32_t k)
+// Byte offset of element (row, k) inside the FIRST activation tile (the quantised input): 8-row groups, each holding all
+// of its `slabs` 128-byte-wide K slabs as 1 KB atoms (8 rows x 128 bytes, 16-byte pieces XORed with the row's low three
+// bits: the 128-byte swizzle of the MMA descriptor, whose stride between row groups is slabs KB).  The 8 rows a CTA
+// quantises are ONE contiguous piece, sent to each other CTA as a single bulk copy (a copy per slab was measured first:
+// 49 + 7 copies queue for 1.4 us on the SM's one copy unit).
+__device__ __forceinline__ uint32_t act_offset(uint32_t row, uint32_t k, uint32_t slabs)
 {
-    return (k >> 7) * SLAB + row * 128 + ((((k >> 4) & 7u) ^ (row & 7u)) << 4) + (k & 15u);
+    return ((row >> 3) * slabs + (k >> 7)) * 1024 + (row & 7u) * 128 + ((((k >> 4) & 7u) ^ (row & 7u)) << 4) + (k & 15u);
 }
+// ... and inside the tiles BETWEEN layers: no swizzle, [K / 16][ROWS rows][16 bytes] (core matrices of 8 rows x 16 bytes,
+// 128 bytes apart along the rows, CHUNK bytes apart along K).  The n output features a CTA produces are n / 16
+// consecutive chunks: one contiguous piece, whatever n is, and a warp's 32 rows of a chunk are 512 consecutive bytes.
+constexpr uint32_t CHUNK = ROWS * 16;
+__device__ __forceinline__ uint32_t mid_offset(uint32_t row, uint32_t k) { return (k >> 4) * CHUNK + row * 16 + (k & 15u); }
 
 }  // namespace
 
@@ -162,16 +161,26 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
     if (threadIdx.x == 0) {
         for (int l = 0; l < MAX_LAYERS; l++) {
             mbar_init(bar0 + 8 * l, 1);
-            // every writing warp of every CTA of the cluster arrives once per hand-over: the input quantise is done by all 8
-            // warps of a CTA, a layer's output is written by the 4 epilogue warps.  (One arrival per THREAD was measured
-            // first: 1024-2048 remote arrivals queueing on one barrier word took 4-5 us per hand-over.)
-            mbar_init(bar0 + 32 + 8 * l, l == 0 ? CL * (THREADS / 32) : CL * 4);
+            // Hand-over barriers: ONE local arrival (this CTA's own part of the tile is written) plus the bytes the other
+            // CTAs send with bulk copies.  (Remote stores + a cluster-scope fence + one remote arrival per warp were
+            // measured first: the fence alone cost ~1 us per hand-over; one arrival per thread, 4-5 us.)
+            mbar_init(bar0 + 32 + 8 * l, 1);
             mbar_init(bar0 + 64 + 8 * l, 1);
+        }
+        // input tile: every other CTA sends its 8 rows of every slab and their 8 row sums
+        mbar_expect_tx_only(bar0 + 32, (CL - 1) * (P.L[0].slabs * 1024 + 32));  // (its 8 rows = one piece of slabs KB)
+        for (int l = 0; l + 1 < P.n_layers; l++) {
+            // tile behind layer l: 512 bytes of partial row sums from everybody, n / 16 chunks from every CTA with columns
+            const uint32_t senders = (P.L[l].N + P.L[l].n - 1) / P.L[l].n;
+            const uint32_t others = senders - (cta < senders ? 1u : 0u);
+            mbar_expect_tx_only(bar0 + 32 + 8 * (l + 1), (CL - 1) * 512 + others * (P.L[l].n / 16) * CHUNK);
         }
         misc[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // both partial-row-sum tables start at zero (layer 0 uses one slot of sixteen)
+    for (uint32_t i = threadIdx.x; i < 2u * CL * 2 * ROWS; i += THREADS) reinterpret_cast<uint32_t *>(base_ptr + P.asum_off)[i] = 0;
     if (warp == 2) {
         tmem_alloc(smem_u32(misc), P.tmem_cols);
         tmem_relinquish();
@@ -209,22 +218,34 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
     const uint32_t tmem_base = misc[0];
     griddep_wait();  // from here on: the input, the row-sum / bias vectors and the output may depend on the previous kernel
 
-    // ---- input quantise: CTA c takes rows 8c .. 8c+7 of the cluster's 64, a warp per row, and writes every CTA's copy ----
+    // ---- input quantise: CTA c takes rows 8c .. 8c+7 of the cluster's 64, a warp per row, into its own tile; the 8 rows
+    //      (1 KB of every slab) and their sums then go to the other CTAs as bulk copies ----
     {
         const MlpLayer &l0 = P.L[0];
         const uint32_t r = cta * 8 + (uint32_t)warp;         // row inside the cluster's block
         const float inv = quant_screen_inv(in_scale);
+        uint8_t *tile = base_ptr + P.act_off[0];
         uint32_t s = 0;
         if (r < rows_here) {
             const float *xr = x + (size_t)(row_base + r) * l0.K;
             const bool vec = ((l0.K & 3u) == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
             if (vec) {
-                for (uint32_t i = lane; i < l0.K / 4; i += 32) {
-                    const uint32_t p = quant4_u8(__ldcs(reinterpret_cast<const float4 *>(xr) + i), in_scale, in_zpf, inv);
-                    s = __dp4a(p, 0x01010101u, s);
-                    const uint32_t off = P.act_off[0] + act_offset(r, 4 * i);
+                // all of a pass's loads first (8 x 16 bytes per lane in flight), then the arithmetic: the row is a dependent
+                // chain of global-memory round trips otherwise
+                for (uint32_t i0 = lane; i0 < l0.K / 4; i0 += 32 * 8) {
+                    float4 v[8];
 #pragma unroll
-                    for (uint32_t c = 0; c < (uint32_t)CL; c++) st_cluster_u32(map_to_cta(base + off, c), p);
+                    for (uint32_t u = 0; u < 8; u++)
+                        if (i0 + 32 * u < l0.K / 4) v[u] = __ldcs(reinterpret_cast<const float4 *>(xr) + i0 + 32 * u);
+#pragma unroll
+                    for (uint32_t u = 0; u < 8; u++) {
+                        const uint32_t i = i0 + 32 * u;
+                        if (i < l0.K / 4) {
+                            const uint32_t p = quant4_u8(v[u], in_scale, in_zpf, inv);
+                            s = __dp4a(p, 0x01010101u, s);
+                            *reinterpret_cast<uint32_t *>(tile + act_offset(r, 4 * i, l0.slabs)) = p;
+                        }
+                    }
                 }
             } else {
                 // one byte at a time would race on the 4-byte words; each lane builds whole words from up to 4 elements
@@ -235,20 +256,26 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                         p |= q << (8 * b);
                         s += q;
                     }
-                    const uint32_t off = P.act_off[0] + act_offset(r, 4 * i);
-#pragma unroll
-                    for (uint32_t c = 0; c < (uint32_t)CL; c++) st_cluster_u32(map_to_cta(base + off, c), p);
+                    *reinterpret_cast<uint32_t *>(tile + act_offset(r, 4 * i, l0.slabs)) = p;
                 }
             }
         }
         for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-        // the row's sum goes into slot 0 of the partial-sum table (the other 15 slots of layer 0 are zero)
-        if (lane < 16) {
-            const uint32_t off = P.asum_off + ((0 * CL * 2 + lane) * ROWS + r) * 4;
-#pragma unroll
-            for (uint32_t c = 0; c < (uint32_t)CL; c++) st_cluster_u32(map_to_cta(base + off, c), lane == 0 ? s : 0u);
+        // the row's sum goes into slot 0 of the partial-sum table (the other 15 slots of layer 0 stay zero)
+        if (lane == 0) reinterpret_cast<uint32_t *>(base_ptr + P.asum_off)[r] = s;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // plain stores -> the copy engine's reads
+        __syncthreads();
+        if (warp == 0 && lane < CL) {
+            if ((uint32_t)lane == cta) {
+                mbar_arrive(bar0 + 32);
+            } else {
+                const uint32_t bar_there = map_to_cta(bar0 + 32, (uint32_t)lane);
+                const uint32_t t = base + P.act_off[0] + cta * l0.slabs * 1024;
+                bulk_copy_to_cta(map_to_cta(t, (uint32_t)lane), t, l0.slabs * 1024, bar_there);
+                const uint32_t a = base + P.asum_off + cta * 32;
+                bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, 32, bar_there);
+            }
         }
-        warp_arrive_all_ctas(bar0 + 32, lane);
     }
 
     // ---- layers ----
@@ -258,10 +285,17 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
         const bool last = l == P.n_layers - 1;
         const bool have_cols = cta * ly.n < ly.N;
         const uint32_t a_tile = base + P.act_off[l & 1];
+        // The last hand-over has been issued by everybody once the last layer starts.  A CTA may leave when every CTA of the
+        // cluster has RECEIVED everything sent to it (copies still landing in a CTA that has exited would hit whoever got
+        // its shared memory next): each CTA's MMA warp says so after its wait below, all other threads right away, and
+        // the matching wait is at the very end - the barrier's round trip passes under the last layer.
+        if (last && warp != 2) cluster_arrive();
         if (warp == 2) {
-            // MMA issuer: needs this layer's activations (from all CTAs) and this CTA's weight slice
+            // MMA issuer: needs this layer's activations (from all CTAs) and this CTA's weight slice.  It waits for the
+            // activations even when this CTA has no columns of the layer, so that every byte sent here has landed.
+            ok = ok && __all_sync(0xFFFFFFFFu, wait_cluster(bar0 + 32 + 8 * l, abort_flag, status, 0xA00u | l));
+            if (last) cluster_arrive();
             if (have_cols) {
-                ok = ok && __all_sync(0xFFFFFFFFu, wait_cluster(bar0 + 32 + 8 * l, abort_flag, status, 0xA00u | l));
                 ok = ok && __all_sync(0xFFFFFFFFu, mbar_wait(bar0 + 8 * l, 0, abort_flag, status, 0xB00u | l));
                 if (ok) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // peers' plain stores -> tensor-core reads
@@ -269,10 +303,18 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                     const uint32_t idesc = make_idesc_i8(128, (int)ly.n);
                     if (elect_one()) {
                         for (uint32_t s = 0; s < ly.slabs; s++) {
-                            const uint64_t a_desc = make_smem_desc(a_tile + s * SLAB);
                             const uint64_t b_desc = make_smem_desc(base + ly.w_off + s * ly.n * 128);
+                            if (l == 0) {
+                                const uint64_t a_desc = make_smem_desc_sbo(a_tile + s * 1024, ly.slabs * 1024);   // groups of 8 rows: slabs KB apart
 #pragma unroll
-                            for (int k = 0; k < 4; k++) umma_i8(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, (s | k) != 0u);
+                                for (int k = 0; k < 4; k++) umma_i8(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, (s | k) != 0u);
+                            } else {
+                                // 32 bytes of K = two chunks of the unswizzled tile
+                                const uint64_t a_desc = make_smem_desc_plain(a_tile + s * 8 * CHUNK, CHUNK, 128);
+#pragma unroll
+                                for (int k = 0; k < 4; k++)
+                                    umma_i8(tmem_base, a_desc + (uint64_t)((2u * k * CHUNK) >> 4), b_desc + 2u * k, idesc, (s | k) != 0u);
+                            }
                         }
                         umma_commit(bar0 + 64 + 8 * l);
                     }
@@ -318,9 +360,8 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                             epilogue_convert<0, 16>(v, rt, col + cc, c, relu, sat, res);
                             rsum += packed_byte_sum<16>(res, valid);
                             // columns beyond N meet zero weights in the next layer; whatever is written there is harmless
-                            const uint32_t off = P.act_off[(l + 1) & 1] + act_offset(r, gcol);
-#pragma unroll
-                            for (uint32_t p = 0; p < (uint32_t)CL; p++) st_cluster_v4(map_to_cta(base + off, p), res[0], res[1], res[2], res[3]);
+                            *reinterpret_cast<uint4 *>(base_ptr + P.act_off[(l + 1) & 1] + mid_offset(r, gcol)) =
+                                make_uint4(res[0], res[1], res[2], res[3]);
                         } else if (r < rows_here) {
                             const uint64_t o = (uint64_t)(row_base + r) * ly.N + gcol;
                             epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, e, out, o, false, valid);
@@ -330,12 +371,25 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                 }
             }
             if (!last) {
-                // partial row sum of this CTA's columns (this warp's half) for the next layer, then the hand-over: one
-                // arrival per warp on every CTA's barrier, whether or not this CTA had columns
-                const uint32_t off = P.asum_off + ((((l + 1) & 1) * CL * 2 + cta * 2 + h) * ROWS + r) * 4;
-#pragma unroll
-                for (uint32_t p = 0; p < (uint32_t)CL; p++) st_cluster_u32(map_to_cta(base + off, p), rsum);
-                warp_arrive_all_ctas(bar0 + 32 + 8 * (l + 1), lane);
+                // partial row sum of this CTA's columns (this warp's half) for the next layer (zero without columns), then
+                // the hand-over: this CTA's chunks of the next tile and its 2 x 64 partial sums go to the other CTAs
+                reinterpret_cast<uint32_t *>(base_ptr + P.asum_off)[(((l + 1) & 1) * CL * 2 + cta * 2 + h) * ROWS + r] = rsum;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                epilogue_warps_sync();
+                if (warp == 0 && lane < CL) {
+                    const uint32_t bar_next = bar0 + 32 + 8 * (l + 1);
+                    if ((uint32_t)lane == cta) {
+                        mbar_arrive(bar_next);
+                    } else {
+                        const uint32_t bar_there = map_to_cta(bar_next, (uint32_t)lane);
+                        if (have_cols) {
+                            const uint32_t a = base + P.act_off[(l + 1) & 1] + cta * (ly.n / 16) * CHUNK;
+                            bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, (ly.n / 16) * CHUNK, bar_there);
+                        }
+                        const uint32_t a = base + P.asum_off + ((((l + 1) & 1) * CL * 2 + cta * 2) * ROWS) * 4;
+                        bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, 512, bar_there);
+                    }
+                }
             }
         }
         // The accumulator columns are reused by the next layer: the MMA warp may only go on once the epilogue warps have
@@ -344,11 +398,11 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
         ok = ok && !*abort_flag;
     }
 
-    // Teardown: peers may still be writing into this CTA's shared memory or arriving on its barriers until every CTA of
-    // the cluster is here.
+    // Teardown: nobody leaves before every CTA of the cluster has everything that was sent to it (the arrivals were
+    // made at the start of the last layer).
     tc_fence_before();
     __syncthreads();
-    cluster_sync();
+    cluster_wait();
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, P.tmem_cols);
@@ -429,7 +483,11 @@ int ltq_mlp_create(ltq_mlp **mlp, ltq_layer *const *layers, int n_layers)
         ly.slabs = (ly.K + 127) / 128;
         if (ly.K % 16 != 0 || (reinterpret_cast<uintptr_t>(layers[l]->w) & 15)) why = "K must be a multiple of 16 and the weights 16-byte aligned";
         if (ly.n > 256) why = "more than 2048 output features in a layer";
-        if (ly.slabs * SLAB > act_bytes[l & 1]) act_bytes[l & 1] = ly.slabs * SLAB;
+        // the input tile is ly.slabs swizzled slabs; a tile between layers holds 8 chunks per slab of the consumer's K and
+        // must also take n / 16 chunks from each of the producer's CTAs
+        uint32_t tile = ly.slabs * SLAB;
+        if (l > 0 && CL * (P.L[l - 1].n / 16) * CHUNK > tile) tile = CL * (P.L[l - 1].n / 16) * CHUNK;
+        if (tile > act_bytes[l & 1]) act_bytes[l & 1] = tile;
         if (ly.n > max_n) max_n = ly.n;
     }
     uint32_t off = 0;
@@ -453,6 +511,8 @@ int ltq_mlp_create(ltq_mlp **mlp, ltq_layer *const *layers, int n_layers)
     P.bar_off = off;
     off += 96 + 16;
     P.smem_bytes = off + 1024;                   // alignment slack
+    // the first layer's MMA reads 16 row groups of the input tile (8 exist): slabs KB apart, all inside the allocation
+    if (P.smem_bytes < P.act_off[0] + 16 * P.L[0].slabs * 1024 + 2048) P.smem_bytes = P.act_off[0] + 16 * P.L[0].slabs * 1024 + 2048;
     P.tmem_cols = 32;
     while (P.tmem_cols < max_n) P.tmem_cols *= 2;
     // a weight slab tile of n rows x 128 B must start on a 1024-byte boundary for the swizzled descriptor: n % 8 == 0 holds

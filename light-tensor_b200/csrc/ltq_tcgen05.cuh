@@ -83,6 +83,30 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr)
     return d;
 }
 
+// The same with the 8-row groups `sbo` bytes apart (a multiple of 1024) instead of back to back.
+__device__ __forceinline__ uint64_t make_smem_desc_sbo(uint32_t smem_addr, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(sbo >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// The same for an UNSWIZZLED K-major tile: core matrices of 8 rows x 16 bytes (128 contiguous bytes), `sbo` bytes from one
+// group of 8 rows to the next and `lbo` bytes from one 16-byte step along K to the next (an 8-bit MMA reads two).
+__device__ __forceinline__ uint64_t make_smem_desc_plain(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // bits [0,14)
+    d |= (uint64_t)(lbo >> 4) << 16;                      // leading byte offset
+    d |= (uint64_t)(sbo >> 4) << 32;                      // stride byte offset
+    d |= (uint64_t)1 << 46;                               // version
+    return d;                                             // layout type 0: no swizzle
+}
+
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1,
                                             int32_t c2)
 {

@@ -644,6 +644,65 @@ int load_checkpoint(const std::vector<Module *> &modules, const char *checkpoint
     return ok ? 0 : -1;
 }
 
+// ---- calibration / quantisation set-up -----------------------------------------------------------------------------------
+void MinMaxObserver::update(const Tensor &x)
+{
+    if (!x.defined() || x.get_device() != GPU || x.get_data_type() != FLOAT32) LTEN_ERR("MinMaxObserver: FLOAT32 GPU tensor expected");
+    float mn, mx;
+    ::GetMinMax((float *)x.get_data_ptr(), x.get_numels(), &mn, &mx);
+    if (mn < min_) min_ = mn;
+    if (mx > max_) max_ = mx;
+}
+
+QuantizationParams MinMaxObserver::qparams() const
+{
+    if (!seen()) LTEN_ERR("MinMaxObserver: no data has been observed");
+    QuantizationParams qp;
+    ::ComputeQuantizationParams(min_, max_, &qp);
+    return qp;
+}
+
+QuantizationParams quantize_module(Module &q_mod, const Tensor &weight, const Tensor *bias, QuantizationParams qp_in,
+                                   QuantizationParams qp_out)
+{
+    std::vector<Tensor *> tensors = q_mod.get_all_weights();
+    if (tensors.empty() || !tensors[0] || !tensors[0]->defined()) LTEN_ERR("quantize_module: init() has not been called");
+    if (!weight.defined() || weight.get_device() != GPU || weight.get_data_type() != FLOAT32)
+        LTEN_ERR("quantize_module: FLOAT32 GPU weight tensor expected");
+    if (weight.get_numels() != tensors[0]->get_numels()) LTEN_ERR("quantize_module: weight size does not match the module");
+    QuantizationParams qps[2];
+    int count = 0;
+    float mn, mx;
+    ::GetMinMax((float *)weight.get_data_ptr(), weight.get_numels(), &mn, &mx);
+    ::ComputeQuantizationParams(mn, mx, &qps[0]);
+    TensorOps o;
+    o.device_type = GPU;
+    o.device_index = weight.get_device_index();
+    o.data_type = UINT8;
+    Tensor wq = AllocateTensor({weight.get_numels()}, &o);
+    ::Quantize((float *)weight.get_data_ptr(), (uint8_t *)wq.get_data_ptr(), weight.get_numels(), &qps[0]);
+    LTEN_CUDA(cudaMemcpy(tensors[0]->get_data_ptr(), wq.get_data_ptr(), weight.get_numels(), cudaMemcpyDefault));
+    count = 1;
+    if (tensors.size() > 1) {
+        if (!bias) LTEN_ERR("quantize_module: the module uses a bias but none was given");
+        if (!bias->defined() || bias->get_device() != GPU || bias->get_data_type() != FLOAT32)
+            LTEN_ERR("quantize_module: FLOAT32 GPU bias tensor expected");
+        if (bias->get_numels() != tensors[1]->get_numels()) LTEN_ERR("quantize_module: bias size does not match the module");
+        // arXiv:1712.05877: the bias shares the accumulator's scale, s_in * s_wt, with zero point 0 (nn_tests.cpp:824-826)
+        qps[1].scale = qp_in.scale * qps[0].scale;
+        qps[1].zero_point = 0;
+        o.data_type = INT32;
+        Tensor bq = AllocateTensor({bias->get_numels()}, &o);
+        ::Quantize((float *)bias->get_data_ptr(), (int *)bq.get_data_ptr(), bias->get_numels(), &qps[1]);
+        LTEN_CUDA(cudaMemcpy(tensors[1]->get_data_ptr(), bq.get_data_ptr(), bias->get_numels() * sizeof(int32_t), cudaMemcpyDefault));
+        count = 2;
+    }
+    q_mod.set_qparams_in(qp_in);
+    q_mod.set_qparams_out(qp_out);
+    q_mod.set_qparams_params(qps, count);
+    return qps[0];
+}
+
 }  // namespace lten
 
 // ---- free functions ----------------------------------------------------------------------------------------------------

@@ -252,6 +252,32 @@ private:
 // endian): "LTQCKPT1", uint32 modules, per module { uint32 tensors, per tensor { uint8 dtype (0 uint8, 1 int32,
 // 2 float32), 3 zero bytes, uint32 ndims, uint64 dims[], data }, 3 x { float scale, uint8 zero_point, 3 zero bytes } }.
 // Modules may be on the CPU or on a GPU; after loading into GPU modules call to(GPU, index) again (or load before to()).
+// Calibration and quantisation set-up, the step in front of the quantized layers.  l-ten has no helper for this: its
+// quantized test repeats it per network (tests/nn_tests.cpp:538-608 for the running statistics, :786-884 for the
+// per-layer set-up).  These two package exactly that recipe, computing on the device.
+//
+// Running minimum / maximum over the FLOAT32 GPU tensors shown to update() (the test's blob_statistics +
+// update_statistics, seeded with +/-FLT_MAX), turned into QuantizationParams by ComputeQuantizationParams.
+class MinMaxObserver {
+public:
+    void update(const Tensor &x);
+    bool seen() const { return min_ <= max_; }
+    float min() const { return min_; }
+    float max() const { return max_; }
+    QuantizationParams qparams() const;  // throws if nothing has been observed
+
+private:
+    float min_ = 3.402823466e+38f, max_ = -3.402823466e+38f;
+};
+
+// Fills a freshly init()-ed quantized module (FullyConnected_q or Conv2d_q) from float parameters held on a GPU, the
+// way tests/nn_tests.cpp:808-834 does for each layer: weights -> GetMinMax -> ComputeQuantizationParams -> Quantize
+// (uint8) written through get_all_weights()[0]; bias -> int32 with scale s_in * s_wt and zero point 0 written through
+// get_all_weights()[1]; then set_qparams_in / set_qparams_out / set_qparams_params.  Returns the weight parameters.
+// `bias` may be nullptr only for a module built without one.  Call to(GPU, idx) afterwards, as the reference's flow does.
+QuantizationParams quantize_module(Module &q_mod, const Tensor &weight, const Tensor *bias, QuantizationParams qp_in,
+                                   QuantizationParams qp_out);
+
 int save_checkpoint(const std::vector<Module *> &modules, const char *checkpoint_path);
 int load_checkpoint(const std::vector<Module *> &modules, const char *checkpoint_path);
 

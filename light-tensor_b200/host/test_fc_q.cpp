@@ -166,9 +166,40 @@ int main()
         oracle_quantize_i32(bias[l].data(), bq_o.data(), bq_o.size(), &ob);
         CHECK(wq_o == Wq[l], "weight Quantize vs oracle");
         CHECK(bq_o == bq[l], "bias Quantize vs oracle");
+        // the packaged form of the same set-up (lten::quantize_module) writes the same bytes and parameters
+        {
+            FullyConnected_q twin(dims[l], dims[l + 1], true);
+            twin.init();
+            Tensor wf = upload(W[l], {(uint64_t)W[l].size()}, FLOAT32);
+            Tensor bf = upload(bias[l], {(uint64_t)bias[l].size()}, FLOAT32);
+            QuantizationParams got_w = quantize_module(twin, wf, &bf, qp_act[l], qp_act[l + 1]);
+            QuantizationParams q3[3];
+            twin.get_qparams(q3);
+            CHECK(got_w.scale == qp_wts[0].scale && got_w.zero_point == qp_wts[0].zero_point, "quantize_module: weight parameters");
+            CHECK(q3[0].scale == qp_act[l].scale && q3[2].scale == qp_act[l + 1].scale && q3[1].scale == qp_wts[0].scale,
+                  "quantize_module: layer parameters");
+            std::vector<Tensor *> tw = twin.get_all_weights();
+            CHECK(memcmp(tw[0]->get_data_ptr(), Wq[l].data(), Wq[l].size()) == 0, "quantize_module: weight bytes");
+            CHECK(memcmp(tw[1]->get_data_ptr(), bq[l].data(), bq[l].size() * sizeof(int32_t)) == 0, "quantize_module: bias words");
+        }
         fc->train(false);
         fc->to(GPU, 0);
         layers.push_back(fc);
+    }
+    {   // MinMaxObserver: running statistics over two pieces equal GetMinMax over the whole
+        std::vector<float> a(W[0].begin(), W[0].begin() + W[0].size() / 2), b(W[0].begin() + W[0].size() / 2, W[0].end());
+        Tensor ta = upload(a, {(uint64_t)a.size()}, FLOAT32), tb = upload(b, {(uint64_t)b.size()}, FLOAT32);
+        Tensor tw = upload(W[0], {(uint64_t)W[0].size()}, FLOAT32);
+        MinMaxObserver obs;
+        CHECK(!obs.seen(), "MinMaxObserver starts empty");
+        obs.update(ta);
+        obs.update(tb);
+        float mn, mx;
+        GetMinMax((float *)tw.get_data_ptr(), tw.get_numels(), &mn, &mx);
+        QuantizationParams want, got = obs.qparams();
+        ComputeQuantizationParams(mn, mx, &want);
+        CHECK(obs.min() == mn && obs.max() == mx && got.scale == want.scale && got.zero_point == want.zero_point,
+              "MinMaxObserver over two pieces");
     }
 
     // ---- inference (nn_tests.cpp:930-963) ----
