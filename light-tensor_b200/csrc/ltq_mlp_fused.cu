@@ -2,31 +2,44 @@
 // MLP run batch after batch (the reference's QNet loop, tests/nn_tests.cpp:630-640 and 930-963: quantise the input, then
 // FullyConnected_q after FullyConnected_q, each a kernel launch and a round trip of the activations through memory).
 //
-// One cluster of 8 CTAs handles up to 64 rows of the batch and keeps everything on chip between the layers:
+// One cluster of 8 CTAs handles 16, 32 or 64 rows of the batch (few rows per cluster while the batch is small: every
+// hand-over moves rows x features bytes into every CTA) and keeps everything on chip between the layers:
 //
-//  * every CTA holds, for every layer, a slice of n = ceil(N / 8 / 16) * 16 weight rows (output features), loaded once
+//  * every CTA holds, for every layer, a slice of n weight rows (output features; N / 8 rounded up to 16), loaded once
 //    at the start by TMA into 128-byte-swizzled K-major tiles - the weights are a layer's static data and are fetched
 //    before the programmatic-launch dependency on the previous kernel is waited for;
-//  * the CTAs quantise the fp32 input together (8 rows each, a warp per row, the reference's Quantize arithmetic) and
-//    write the bytes - and the row sums the zero-point correction needs - straight into the shared memory of all 8
-//    CTAs (distributed shared memory stores), in the layout the tensor core reads;
-//  * per layer, one warp issues tcgen05.mma (128 x n x 32, uint8 x uint8 -> int32 in TMEM; rows 64..127 of the
-//    activation operand are whatever lies behind the tile and their results are never read), four warps run the fused
-//    epilogue of l-ten's quantized_matmul (l-ten/math_fns.cpp:1433-1474) and write the uint8 result slice into the
-//    activation tile of the next layer in all 8 CTAs; the last layer's result goes to global memory;
-//  * hand-over between layers is an mbarrier per CTA and layer that counts one arrival (release at cluster scope) from
-//    every thread that wrote into this CTA; nothing waits on anything outside its own cluster, every wait is bounded,
-//    and no CTA leaves before the whole cluster is done (a peer may still be writing into its shared memory).
+//  * the CTAs quantise the fp32 input together: CTA c takes the 128-column slab c of all rows (the reference's Quantize
+//    arithmetic, every load issued before the arithmetic starts) into its own copy of the input tile;
+//  * per layer, one warp issues tcgen05.mma (128 x n x 32, uint8 x uint8 -> int32 in TMEM; rows beyond the cluster's own
+//    are whatever lies behind the tile and their results are never read), four warps run the fused epilogue of l-ten's
+//    quantized_matmul (l-ten/math_fns.cpp:1433-1474) and write the uint8 result slice into their own copy of the next
+//    layer's activation tile; the last layer's result goes to global memory;
+//  * hand-over: what a CTA produced for the next tile is one contiguous piece (a K slab of the input tile; n / 16 chunks
+//    of a tile between layers, which are unswizzled - core matrices of 8 rows x 16 bytes - so that any slice of features
+//    is contiguous).  The CTA sends that piece, and the partial row sums of its bytes that the next layer's zero-point
+//    correction needs, to each of the other seven with bulk copies through distributed shared memory (cp.async.bulk
+//    shared::cta -> shared::cluster), which count their bytes on the receiver's mbarrier: data and "it is there" arrive
+//    together, no cluster-scope fence, no remote arrival.  Nothing waits on anything outside its own cluster, every
+//    wait is bounded, and no CTA leaves before every CTA has received what was sent to it.
 //
 // Integer sums are exact whatever the order, so the result equals the layer-by-layer path bit for bit.
 //
-// Measured on the 784-512-512-10 network, batch 64 (B200, a CUDA graph of back-to-back launches): 13.5 us per batch
-// against 16.5 us layer by layer.  After the grid dependency resolves: input quantise and its exchange 3.7 us; per hidden
-// layer 0.6-0.9 us of MMAs and 2.6 us of epilogue and exchange, about 1 us of which is the cluster-scope fence in front of
-// the hand-over arrival; last layer 1 us.  A variant with clusters of 4, the weights streamed through a ring and whole
-// activation slabs sent with bulk copies (cp.async.bulk shared::cta -> shared::cluster) instead of 16-byte remote stores
-// was built and measured at 18.3 us: with both operands 128 rows tall in one SM's shared memory its MMAs take 140 cycles
-// instead of 70, and every CTA quantises twice as many input rows.
+// Measured on the 784-512-512-10 network, batch 64 (B200, a CUDA graph of back-to-back launches), per batch, against
+// 15.1-16.7 us layer by layer (4 launches):
+//   13.5 us  first form: 64 rows per cluster, rows of the input split over the CTAs, results written into all 8 CTAs with
+//            16-byte remote stores, then fence.acq_rel.cluster (~1 us per hand-over) and one remote arrival per warp
+//            (one per thread: 4-5 us per hand-over);
+//   11.3 us  bulk copies instead (no fence, no arrivals), input loads issued ahead of the arithmetic, the cluster barrier
+//            at the end split around the last layer;
+//    9.3-9.5 us  16 rows per cluster (4 clusters), input split by K slab instead of by row (one piece per CTA: with a piece
+//            per slab and row group the 56 copies queued for 1.4 us on the SM's copy unit, ~40 ns per copy).
+// What is left is a chain of latencies (after the grid dependency resolves: ~2.2 us until the first MMA, per hidden
+// layer 0.6-0.9 us of MMAs + ~0.9 us epilogue + ~0.5 us to issue the copies + ~0.3 us until they have landed, ~1 us from the
+// last store to the next launch's start).  Two further steps were built, measured on the same box and left out, because
+// neither changed the time: bytes and sums of a hand-over in ONE copy (7 copies instead of 14 per hand-over), and a
+// conversion-free uint8 epilogue (integer / float bit tricks in place of the two conversion instructions per element).
+// A variant with clusters of 4, the weights streamed through a ring, was built and measured at 18.3 us: with both
+// operands 128 rows tall in one SM's shared memory its MMAs take 140 cycles instead of 70.
 #include <cuda.h>
 
 #include <new>
@@ -42,7 +55,7 @@ namespace ltq {
 namespace {
 
 constexpr int CL = 8;               // CTAs per cluster
-constexpr int ROWS = 64;            // batch rows per cluster
+constexpr int ROWS = 64;            // batch rows per cluster, at most (the layout is planned for this many)
 constexpr int MAX_LAYERS = 4;
 constexpr int THREADS = 256;        // warps 0,1,4,5: epilogue (TMEM lanes 0..63); 2: MMA issuer; 3: weight loads; all: input quantise
 constexpr int SLAB = ROWS * 128;    // one 128-byte-wide K slab of an activation tile
@@ -67,6 +80,7 @@ struct MlpParams {
     uint32_t tmem_cols;
     uint32_t smem_bytes;
     int out_mode;                   // of the last layer
+    uint32_t rows;                  // batch rows per cluster (16, 32 or ROWS), chosen per call
 };
 
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
@@ -122,20 +136,18 @@ __device__ __forceinline__ bool wait_cluster(uint32_t bar, volatile uint32_t *ab
     }
 }
 
-// Byte offset of element (row, k) inside the FIRST activation tile (the quantised input): 8-row groups, each holding all
-// of its `slabs` 128-byte-wide K slabs as 1 KB atoms (8 rows x 128 bytes, 16-byte pieces XORed with the row's low three
-// bits: the 128-byte swizzle of the MMA descriptor, whose stride between row groups is slabs KB).  The 8 rows a CTA
-// quantises are ONE contiguous piece, sent to each other CTA as a single bulk copy (a copy per slab was measured first:
-// 49 + 7 copies queue for 1.4 us on the SM's one copy unit).
-__device__ __forceinline__ uint32_t act_offset(uint32_t row, uint32_t k, uint32_t slabs)
+// Byte offset of element (row, k) inside the FIRST activation tile (the quantised input): 128-byte-wide K slabs of R
+// rows, 16-byte pieces XORed with the row's low three bits (the 128-byte swizzle of the MMA descriptor).  A slab is one
+// contiguous piece of R x 128 bytes: CTA c quantises slab c (c + 8, ...) of all rows and sends it as one bulk copy.
+// (Rows per CTA, a piece per slab, was measured first: 49 + 7 copies queue for 1.4 us on the SM's one copy unit.)
+__device__ __forceinline__ uint32_t act_offset(uint32_t row, uint32_t k, uint32_t R)
 {
-    return ((row >> 3) * slabs + (k >> 7)) * 1024 + (row & 7u) * 128 + ((((k >> 4) & 7u) ^ (row & 7u)) << 4) + (k & 15u);
+    return (k >> 7) * (R * 128) + row * 128 + ((((k >> 4) & 7u) ^ (row & 7u)) << 4) + (k & 15u);
 }
-// ... and inside the tiles BETWEEN layers: no swizzle, [K / 16][ROWS rows][16 bytes] (core matrices of 8 rows x 16 bytes,
-// 128 bytes apart along the rows, CHUNK bytes apart along K).  The n output features a CTA produces are n / 16
+// ... and inside the tiles BETWEEN layers: no swizzle, [K / 16][R rows][16 bytes] (core matrices of 8 rows x 16 bytes,
+// 128 bytes apart along the rows, R * 16 bytes apart along K).  The n output features a CTA produces are n / 16
 // consecutive chunks: one contiguous piece, whatever n is, and a warp's 32 rows of a chunk are 512 consecutive bytes.
-constexpr uint32_t CHUNK = ROWS * 16;
-__device__ __forceinline__ uint32_t mid_offset(uint32_t row, uint32_t k) { return (k >> 4) * CHUNK + row * 16 + (k & 15u); }
+__device__ __forceinline__ uint32_t mid_offset(uint32_t row, uint32_t k, uint32_t R) { return (k >> 4) * (R * 16) + row * 16 + (k & 15u); }
 
 }  // namespace
 
@@ -155,8 +167,10 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
     volatile uint32_t *abort_flag = misc + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = cluster_ctarank();
-    const uint32_t row_base = (blockIdx.x / CL) * ROWS;     // first batch row of this cluster
-    const uint32_t rows_here = M - row_base < (uint32_t)ROWS ? M - row_base : (uint32_t)ROWS;
+    const uint32_t R = P.rows;                              // batch rows per cluster: 16, 32 or 64
+    const uint32_t chunk = R * 16;                          // one 16-byte step along K of a tile between layers
+    const uint32_t row_base = (blockIdx.x / CL) * R;        // first batch row of this cluster
+    const uint32_t rows_here = M - row_base < R ? M - row_base : R;
 
     if (threadIdx.x == 0) {
         for (int l = 0; l < MAX_LAYERS; l++) {
@@ -167,19 +181,20 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
             mbar_init(bar0 + 32 + 8 * l, 1);
             mbar_init(bar0 + 64 + 8 * l, 1);
         }
-        // input tile: every other CTA sends its 8 rows of every slab and their 8 row sums
-        mbar_expect_tx_only(bar0 + 32, (CL - 1) * (P.L[0].slabs * 1024 + 32));  // (its 8 rows = one piece of slabs KB)
+        // Every hand-over brings 512 bytes of partial row sums from each other CTA, plus: for the input tile the slabs the
+        // others quantise; for the tile behind layer l, n / 16 chunks from every other CTA that has columns of layer l.
+        const uint32_t slabs0 = P.L[0].slabs, mine0 = cta < slabs0 ? (slabs0 - cta + CL - 1) / CL : 0u;
+        mbar_expect_tx_only(bar0 + 32, (CL - 1) * 512 + (slabs0 - mine0) * R * 128);
         for (int l = 0; l + 1 < P.n_layers; l++) {
-            // tile behind layer l: 512 bytes of partial row sums from everybody, n / 16 chunks from every CTA with columns
             const uint32_t senders = (P.L[l].N + P.L[l].n - 1) / P.L[l].n;
             const uint32_t others = senders - (cta < senders ? 1u : 0u);
-            mbar_expect_tx_only(bar0 + 32 + 8 * (l + 1), (CL - 1) * 512 + others * (P.L[l].n / 16) * CHUNK);
+            mbar_expect_tx_only(bar0 + 32 + 8 * (l + 1), (CL - 1) * 512 + others * (P.L[l].n / 16) * chunk);
         }
         misc[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    // both partial-row-sum tables start at zero (layer 0 uses one slot of sixteen)
+    // both partial-row-sum tables start at zero (16 slots of ROWS sums each; whoever has nothing to add leaves zeros)
     for (uint32_t i = threadIdx.x; i < 2u * CL * 2 * ROWS; i += THREADS) reinterpret_cast<uint32_t *>(base_ptr + P.asum_off)[i] = 0;
     if (warp == 2) {
         tmem_alloc(smem_u32(misc), P.tmem_cols);
@@ -218,51 +233,54 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
     const uint32_t tmem_base = misc[0];
     griddep_wait();  // from here on: the input, the row-sum / bias vectors and the output may depend on the previous kernel
 
-    // ---- input quantise: CTA c takes rows 8c .. 8c+7 of the cluster's 64, a warp per row, into its own tile; the 8 rows
-    //      (1 KB of every slab) and their sums then go to the other CTAs as bulk copies ----
+    // ---- input quantise: CTA c takes the 128-column slab c (c + 8, ...) of all R rows into its own tile - warp w rows
+    //      w, w + 8, ..., a lane four columns, every load of a slab issued before the arithmetic - and sends each slab and
+    //      its partial row sums (slot 2c of the table) to the other CTAs as bulk copies ----
     {
         const MlpLayer &l0 = P.L[0];
-        const uint32_t r = cta * 8 + (uint32_t)warp;         // row inside the cluster's block
         const float inv = quant_screen_inv(in_scale);
         uint8_t *tile = base_ptr + P.act_off[0];
-        uint32_t s = 0;
-        if (r < rows_here) {
-            const float *xr = x + (size_t)(row_base + r) * l0.K;
-            const bool vec = ((l0.K & 3u) == 0) && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0);
-            if (vec) {
-                // all of a pass's loads first (8 x 16 bytes per lane in flight), then the arithmetic: the row is a dependent
-                // chain of global-memory round trips otherwise
-                for (uint32_t i0 = lane; i0 < l0.K / 4; i0 += 32 * 8) {
-                    float4 v[8];
+        uint32_t *sums = reinterpret_cast<uint32_t *>(base_ptr + P.asum_off) + (cta * 2) * ROWS;
+        const bool vec = ((l0.K & 3u) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+        uint32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};          // row sums of rows warp, warp + 8, ... over this CTA's slabs
+        for (uint32_t sl = cta; sl < l0.slabs; sl += CL) {
+            const uint32_t k = sl * 128 + 4 * lane;          // this lane's four columns
+            float4 v[8];
 #pragma unroll
-                    for (uint32_t u = 0; u < 8; u++)
-                        if (i0 + 32 * u < l0.K / 4) v[u] = __ldcs(reinterpret_cast<const float4 *>(xr) + i0 + 32 * u);
-#pragma unroll
-                    for (uint32_t u = 0; u < 8; u++) {
-                        const uint32_t i = i0 + 32 * u;
-                        if (i < l0.K / 4) {
-                            const uint32_t p = quant4_u8(v[u], in_scale, in_zpf, inv);
-                            s = __dp4a(p, 0x01010101u, s);
-                            *reinterpret_cast<uint32_t *>(tile + act_offset(r, 4 * i, l0.slabs)) = p;
-                        }
+            for (uint32_t u = 0; u < 8; u++) {
+                const uint32_t r = (uint32_t)warp + 8 * u;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < rows_here && k < l0.K) {
+                    const float *xr = x + (size_t)(row_base + r) * l0.K + k;
+                    if (vec) {
+                        v[u] = __ldcs(reinterpret_cast<const float4 *>(xr));
+                    } else {
+                        v[u].x = xr[0];
+                        if (k + 1 < l0.K) v[u].y = xr[1];
+                        if (k + 2 < l0.K) v[u].z = xr[2];
+                        if (k + 3 < l0.K) v[u].w = xr[3];
                     }
                 }
-            } else {
-                // one byte at a time would race on the 4-byte words; each lane builds whole words from up to 4 elements
-                for (uint32_t i = lane; i < (l0.K + 3) / 4; i += 32) {
-                    uint32_t p = 0;
-                    for (uint32_t b = 0; b < 4 && 4 * i + b < l0.K; b++) {
-                        const uint32_t q = quant_u8(xr[4 * i + b], in_scale, in_zpf, inv);
-                        p |= q << (8 * b);
-                        s += q;
-                    }
-                    *reinterpret_cast<uint32_t *>(tile + act_offset(r, 4 * i, l0.slabs)) = p;
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 8; u++) {
+                const uint32_t r = (uint32_t)warp + 8 * u;
+                if (r < rows_here && k < l0.K) {
+                    uint32_t p = quant4_u8(v[u], in_scale, in_zpf, inv);
+                    if (k + 4 > l0.K) p &= 0xFFFFFFFFu >> (8 * (k + 4 - l0.K));   // columns beyond K: bytes that count for nothing
+                    acc[u] = __dp4a(p, 0x01010101u, acc[u]);
+                    *reinterpret_cast<uint32_t *>(tile + act_offset(r, k, R)) = p;
                 }
             }
         }
-        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-        // the row's sum goes into slot 0 of the partial-sum table (the other 15 slots of layer 0 stay zero)
-        if (lane == 0) reinterpret_cast<uint32_t *>(base_ptr + P.asum_off)[r] = s;
+        if (cta < l0.slabs) {
+#pragma unroll
+            for (uint32_t u = 0; u < 8; u++) {
+                uint32_t t = acc[u];
+                for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+                if (lane == 0 && (uint32_t)warp + 8 * u < R) sums[warp + 8 * u] = t;
+            }
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // plain stores -> the copy engine's reads
         __syncthreads();
         if (warp == 0 && lane < CL) {
@@ -270,10 +288,12 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                 mbar_arrive(bar0 + 32);
             } else {
                 const uint32_t bar_there = map_to_cta(bar0 + 32, (uint32_t)lane);
-                const uint32_t t = base + P.act_off[0] + cta * l0.slabs * 1024;
-                bulk_copy_to_cta(map_to_cta(t, (uint32_t)lane), t, l0.slabs * 1024, bar_there);
-                const uint32_t a = base + P.asum_off + cta * 32;
-                bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, 32, bar_there);
+                for (uint32_t sl = cta; sl < l0.slabs; sl += CL) {
+                    const uint32_t t = base + P.act_off[0] + sl * R * 128;
+                    bulk_copy_to_cta(map_to_cta(t, (uint32_t)lane), t, R * 128, bar_there);
+                }
+                const uint32_t a = base + P.asum_off + (cta * 2) * ROWS * 4;
+                bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, 512, bar_there);
             }
         }
     }
@@ -305,15 +325,15 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                         for (uint32_t s = 0; s < ly.slabs; s++) {
                             const uint64_t b_desc = make_smem_desc(base + ly.w_off + s * ly.n * 128);
                             if (l == 0) {
-                                const uint64_t a_desc = make_smem_desc_sbo(a_tile + s * 1024, ly.slabs * 1024);   // groups of 8 rows: slabs KB apart
+                                const uint64_t a_desc = make_smem_desc(a_tile + s * R * 128);
 #pragma unroll
                                 for (int k = 0; k < 4; k++) umma_i8(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, (s | k) != 0u);
                             } else {
                                 // 32 bytes of K = two chunks of the unswizzled tile
-                                const uint64_t a_desc = make_smem_desc_plain(a_tile + s * 8 * CHUNK, CHUNK, 128);
+                                const uint64_t a_desc = make_smem_desc_plain(a_tile + s * 8 * chunk, chunk, 128);
 #pragma unroll
                                 for (int k = 0; k < 4; k++)
-                                    umma_i8(tmem_base, a_desc + (uint64_t)((2u * k * CHUNK) >> 4), b_desc + 2u * k, idesc, (s | k) != 0u);
+                                    umma_i8(tmem_base, a_desc + (uint64_t)((2u * k * chunk) >> 4), b_desc + 2u * k, idesc, (s | k) != 0u);
                             }
                         }
                         umma_commit(bar0 + 64 + 8 * l);
@@ -347,11 +367,15 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                 if (ok) {
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((q * 32u) << 16);
+                    uint32_t vn[16];
+                    if (cb < ce) tmem_ld16(taddr + cb, vn);
 #pragma unroll 1
                     for (uint32_t cc = cb; cc < ce; cc += 16) {
                         uint32_t v[16];
-                        tmem_ld16(taddr + cc, v);
                         tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) v[j] = vn[j];
+                        if (cc + 16 < ce) tmem_ld16(taddr + cc + 16, vn);   // the next chunk travels while this one is converted
                         const uint32_t gcol = cta * ly.n + cc;          // first output feature of the chunk
                         if (gcol >= ly.N) continue;
                         const int valid = ly.N - gcol < 16u ? (int)(ly.N - gcol) : 16;
@@ -360,8 +384,9 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                             epilogue_convert<0, 16>(v, rt, col + cc, c, relu, sat, res);
                             rsum += packed_byte_sum<16>(res, valid);
                             // columns beyond N meet zero weights in the next layer; whatever is written there is harmless
-                            *reinterpret_cast<uint4 *>(base_ptr + P.act_off[(l + 1) & 1] + mid_offset(r, gcol)) =
-                                make_uint4(res[0], res[1], res[2], res[3]);
+                            if (r < R)   // (TMEM lanes beyond the cluster's rows hold products of whatever lay behind the tile)
+                                *reinterpret_cast<uint4 *>(base_ptr + P.act_off[(l + 1) & 1] + mid_offset(r, gcol, R)) =
+                                    make_uint4(res[0], res[1], res[2], res[3]);
                         } else if (r < rows_here) {
                             const uint64_t o = (uint64_t)(row_base + r) * ly.N + gcol;
                             epilogue_chunk<OUT, 16>(v, rt, col + cc, c, relu, sat, e, out, o, false, valid);
@@ -383,8 +408,8 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant
                     } else {
                         const uint32_t bar_there = map_to_cta(bar_next, (uint32_t)lane);
                         if (have_cols) {
-                            const uint32_t a = base + P.act_off[(l + 1) & 1] + cta * (ly.n / 16) * CHUNK;
-                            bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, (ly.n / 16) * CHUNK, bar_there);
+                            const uint32_t a = base + P.act_off[(l + 1) & 1] + cta * (ly.n / 16) * chunk;
+                            bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, (ly.n / 16) * chunk, bar_there);
                         }
                         const uint32_t a = base + P.asum_off + ((((l + 1) & 1) * CL * 2 + cta * 2) * ROWS) * 4;
                         bulk_copy_to_cta(map_to_cta(a, (uint32_t)lane), a, 512, bar_there);
@@ -436,7 +461,7 @@ cudaError_t launch_mlp(const ltq_mlp *m, const float *x, uint64_t M, float scale
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    const unsigned clusters = (unsigned)((M + ROWS - 1) / ROWS);
+    const unsigned clusters = (unsigned)((M + m->P.rows - 1) / m->P.rows);
     auto mp = [&](int l) -> const CUtensorMap & {
         return *reinterpret_cast<const CUtensorMap *>(m->maps[l < m->n_layers ? l : 0].opaque);
     };
@@ -486,7 +511,7 @@ int ltq_mlp_create(ltq_mlp **mlp, ltq_layer *const *layers, int n_layers)
         // the input tile is ly.slabs swizzled slabs; a tile between layers holds 8 chunks per slab of the consumer's K and
         // must also take n / 16 chunks from each of the producer's CTAs
         uint32_t tile = ly.slabs * SLAB;
-        if (l > 0 && CL * (P.L[l - 1].n / 16) * CHUNK > tile) tile = CL * (P.L[l - 1].n / 16) * CHUNK;
+        if (l > 0 && CL * (P.L[l - 1].n / 16) * (ROWS * 16u) > tile) tile = CL * (P.L[l - 1].n / 16) * (ROWS * 16u);
         if (tile > act_bytes[l & 1]) act_bytes[l & 1] = tile;
         if (ly.n > max_n) max_n = ly.n;
     }
@@ -511,8 +536,9 @@ int ltq_mlp_create(ltq_mlp **mlp, ltq_layer *const *layers, int n_layers)
     P.bar_off = off;
     off += 96 + 16;
     P.smem_bytes = off + 1024;                   // alignment slack
-    // the first layer's MMA reads 16 row groups of the input tile (8 exist): slabs KB apart, all inside the allocation
-    if (P.smem_bytes < P.act_off[0] + 16 * P.L[0].slabs * 1024 + 2048) P.smem_bytes = P.act_off[0] + 16 * P.L[0].slabs * 1024 + 2048;
+    // an MMA reads 128 rows from the start of a slab or chunk, whatever the cluster's row count: 16 KB from the input tile's
+    // last slab, 2 KB from a later tile's last chunk - all inside the allocation
+    if (P.smem_bytes < P.act_off[1] + act_bytes[1] + 16 * 1024 + 2048) P.smem_bytes = P.act_off[1] + act_bytes[1] + 16 * 1024 + 2048;
     P.tmem_cols = 32;
     while (P.tmem_cols < max_n) P.tmem_cols *= 2;
     // a weight slab tile of n rows x 128 B must start on a 1024-byte boundary for the swizzled descriptor: n % 8 == 0 holds
@@ -568,6 +594,10 @@ int ltq_mlp_forward(ltq_mlp *mlp, const float *x_dev, uint64_t M, const unsigned
         LTQ_REQUIRE(bc <= 0x7FFFFFFFull, LTQ_ERR_UNSUPPORTED, "K*zA*zB = %llu does not fit an int", (unsigned long long)bc);
     }
     P.out_mode = out_mode;
+    // Rows per cluster: a small batch is spread over more clusters (every hand-over moves rows x features bytes into
+    // every CTA, and the SM-to-SM copies are what a layer waits for); a large one gets the full 64 rows per cluster.
+    const uint64_t sms = (uint64_t)mlp->layers[0]->dev->sms;
+    P.rows = ((M + 15) / 16) * CL <= sms ? 16u : (((M + 31) / 32) * CL <= sms ? 32u : (uint32_t)ROWS);
     const ltq_layer *l0 = mlp->layers[0];
     const float scale = l0->qp_in.scale, zpf = (float)(int)l0->qp_in.zero_point;
     cudaStream_t st = (cudaStream_t)stream;

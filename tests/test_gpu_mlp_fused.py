@@ -75,6 +75,47 @@ def test_fused_chain_vs_oracle_and_layer_by_layer(cuda, oracle, dims, batch, las
     mlp.close()
 
 
+@pytest.mark.parametrize("relu", [True, False])
+@pytest.mark.parametrize("batch", [64, 9, 300])
+def test_fused_chain_hidden_epilogue_across_the_accumulator_range(cuda, oracle, relu, batch):
+    """The hidden layers' uint8 conversion takes a shortcut that is exact only for accumulators within +-2^22 and
+    non-negative results, and must fall back to the reference sequence elsewhere.  Biases steer whole columns to both
+    sides of every boundary (around +-2^22, far beyond it, results that wrap below 0 or above 255), with and without
+    ReLU; every layer's bytes feed the next, so one wrong byte changes the output."""
+    import ltq
+    rng = np.random.default_rng(77 + batch + int(relu))
+    dims = (256, 512, 256, 64)
+    L = len(dims) - 1
+    ws = [rng.integers(0, 256, (dims[i + 1], dims[i]), dtype=np.uint8) for i in range(L)]
+    edges = np.array([0, 1, -1, (1 << 22) - 3, 1 << 22, (1 << 22) + 5, -(1 << 22) + 2, -(1 << 22) - 1, 1 << 23, -(1 << 23),
+                      1 << 26, -(1 << 26), (1 << 31) - 1 - (1 << 24), -(1 << 31) + (1 << 24), 3000, -3000], dtype=np.int64)
+    bs = []
+    for i in range(L):
+        b = rng.integers(-60000, 60000, dims[i + 1]).astype(np.int64)
+        pick = rng.choice(dims[i + 1], size=len(edges) * 4, replace=False)
+        b[pick] = np.repeat(edges, 4) + rng.integers(-40, 40, len(pick))
+        bs.append(b.astype(np.int32))
+    # output scales that make rm = sA * sB / sC 0.3 .. 0.4: the shortcut applies (rm <= 0.5) and results spread over many
+    # multiples of 256, so the wrapped bytes carry every accumulator's low bits into the next layer
+    acts = [(0.02, 128), (0.0002, 3), (2e-6, 200), (3e-8, 17)]
+    wqp = [(0.004, 117), (0.003, 131), (0.005, 125)]
+    layers = []
+    for i in range(L):
+        h = ltq.LayerHandle(0, dims[i], dims[i + 1])
+        h.set_weights(cuda.from_numpy(ws[i]).cuda(), cuda.from_numpy(bs[i]).cuda())
+        h.set_qparams(ltq_qp(acts[i]), ltq_qp(wqp[i]), ltq_qp(acts[i + 1]))
+        layers.append(h)
+    x = rng.normal(0, 0.9, (batch, dims[0])).astype(np.float32)
+    relus = [relu] * (L - 1) + [False]
+    flags = [ltq.FLAG_RELU if r else 0 for r in relus]
+    mlp = ltq.FusedMLP(layers)
+    got = mlp.forward(cuda.from_numpy(x).cuda(), flags, ltq.OUT_I32).cpu().numpy()
+    layers[0].check()
+    want = _oracle_chain(oracle, ws, bs, acts, wqp, x, relus, "i32")
+    np.testing.assert_array_equal(got, want)
+    mlp.close()
+
+
 def test_fused_chain_matches_the_reference_fixture(cuda, golden):
     """784-512-512-10, batch 64: the bytes FullyConnected_q::forward of the reference produced, layer after layer."""
     import ltq
