@@ -12,6 +12,7 @@
 #include "ltq_common.cuh"
 #include "ltq_gemm_tc.cuh"
 #include "ltq_gemv.cuh"
+#include "ltq_conv_direct.cuh"
 #include "ltq_layer.cuh"
 
 namespace ltq {
@@ -575,6 +576,13 @@ struct ltq_conv2d {
     uint64_t colsum_cap = 0;
     ltq_qparams qp_in{1.f, 0}, qp_wt{1.f, 0}, qp_out{1.f, 0};
     DeviceState *dev = nullptr;
+    // The path without a patch buffer (ltq_conv_direct.cu), where the geometry allows it: the weights reordered to
+    // (kernel row, kernel column, channel) with their tensor map, and the NHWC copy of the input, which grows like `col`.
+    uint8_t *w_direct = nullptr;
+    ltq::TcOperandMap map_w_direct;
+    bool direct_ready = false;
+    uint8_t *x_nhwc = nullptr;
+    uint64_t x_nhwc_cap = 0;
 };
 
 // Patch-buffer budget of one pass over a chunk of the batch.
@@ -611,7 +619,10 @@ int ltq_conv2d_create(ltq_conv2d **conv, int device, uint64_t channels_in, uint6
     c->dev = dev;
     cudaError_t e = cudaMalloc(&c->wsum, channels_out * sizeof(int32_t));
     if (e == cudaSuccess && c->Kp != c->K) e = cudaMalloc(&c->w_pad, channels_out * c->Kp);
+    if (e == cudaSuccess && conv_direct_weights_ok(channels_in, channels_out, kernel_h, kernel_w, stride_h, stride_w))
+        e = cudaMalloc(&c->w_direct, conv_direct_weight_bytes(channels_in, channels_out, kernel_h, kernel_w));
     if (e != cudaSuccess) {
+        cudaFree(c->w_pad);
         cudaFree(c->wsum);
         delete c;
         set_error("cudaMalloc of the convolution's weight buffers failed: %s", cudaGetErrorString(e));
@@ -629,6 +640,8 @@ int ltq_conv2d_destroy(ltq_conv2d *conv)
     cudaFree(conv->w_pad);
     cudaFree(conv->col);
     cudaFree(conv->colsum);
+    cudaFree(conv->w_direct);
+    cudaFree(conv->x_nhwc);
     delete conv;
     return LTQ_OK;
 }
@@ -647,6 +660,12 @@ int ltq_conv2d_set_weights(ltq_conv2d *conv, const uint8_t *w_dev, const int32_t
         conv->w = w_dev;
     }
     LTQ_CUDA_TRY(launch_row_sums(conv->w, conv->Cout, conv->Kp, conv->wsum, st));
+    conv->direct_ready = false;
+    if (conv->w_direct) {
+        LTQ_CUDA_TRY(conv_direct_prepare_weights(w_dev, conv->w_direct, &conv->map_w_direct, conv->Cin, conv->Cout, conv->kh,
+                                                 conv->kw, st));
+        conv->direct_ready = true;
+    }
     LTQ_CUDA_TRY(cudaStreamSynchronize(st));
     return LTQ_OK;
 }
@@ -698,6 +717,21 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     if (batches == 0 || N == 0) return LTQ_OK;
     LTQ_ENTER_DEVICE(conv->device);
     cudaStream_t st = (cudaStream_t)stream;
+
+    // Without a patch buffer where the geometry allows (and no kernel is forced, and the bias is per channel or absent):
+    // transpose the input to NHWC, then one kernel for the whole batch.
+    if (conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
+        (per_channel || !conv->bias) && conv_direct_shape_ok(batches, height_in, width_in, Ho, Wo)) {
+        rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, batches * conv->Cin * height_in * width_in, st, "the NHWC copy of the input");
+        if (rc != LTQ_OK) return rc;
+        LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));
+        // positions are the rows here: A = input (its patch sums come out of the kernel), B = weights
+        Epilogue epi = make_epilogue(conv->wsum, nullptr, conv->bias, conv->qp_in, conv->qp_wt, conv->qp_out, K, out_mode, flags);
+        LTQ_CUDA_TRY(launch_conv_direct(conv->x_nhwc, conv->map_w_direct, batches, conv->Cin, height_in, width_in, conv->Cout,
+                                        conv->kh, conv->kw, conv->ph, conv->pw, Ho, Wo, epi, out_dev, conv->dev->status,
+                                        conv->dev->sms, st));
+        return LTQ_OK;
+    }
 
     uint64_t chunk = CONV_COL_BYTES / (N * Kp);
     chunk = chunk < 1 ? 1 : (chunk > batches ? batches : chunk);

@@ -1,0 +1,450 @@
+// Conv2d_q without a patch buffer (l-ten/conv2d.cpp:352-367 gathers every patch into a [K, Ho*Wo] buffer per image,
+// l-ten/im_col.h:5-33, and multiplies; the first GPU form here did the same for the whole batch: 58 MB written and read
+// again for 6.4 MB of input).  For stride 1 and a channel count that is a multiple of 64 the patches never exist:
+//
+//  * the product does not care in which order K is walked as long as both operands agree, so K is taken as
+//    (kernel row, kernel column, channel) instead of the reference's (channel, kernel row, kernel column).  The weights
+//    are reordered once (ltq_conv2d_set_weights); the input is transposed NCHW -> NHWC per call (6.4 MB for the bench
+//    shape, one small kernel).  In NHWC the 64 channels of one pixel are 64 contiguous bytes, and for ONE kernel tap
+//    (i, j) the patch slice of every output position of an output row is simply the input row shifted by (i - pad, j - pad);
+//  * a tile is `rpt` whole output rows of one image (rpt * Wo <= 128 positions, the MMA's M).  For every tap and every
+//    64-channel chunk ONE TMA tensor copy over the 4-D view {channel, x, y, image} brings the [positions][64 bytes]
+//    slice into a ring stage, 64-byte swizzled as the MMA descriptor wants it; coordinates that fall outside the image
+//    (the padding) are filled with zeros by the copy unit, which is exactly the reference's padding byte.  Only the
+//    channel coordinate is the innermost one and it is always a multiple of 64, so the shifts by +-1 pixel cost nothing;
+//  * the positions are the MMA's rows, the output channels its columns (the roles l-ten's call has the other way round;
+//    the integer sum is the same): tcgen05.mma 128 x (Cout + 16) x 32, two per ring stage.  The reordered weights of all
+//    taps stay resident in shared memory.  Sixteen extra weight rows are appended, the first of them all ones: its
+//    accumulator column is the sum of the patch's bytes, which the zero-point correction needs - so the patch sums
+//    come out of the tensor core too, in the thread that needs them;
+//  * epilogue: thread = output position, the usual fused arithmetic of quantized_matmul (l-ten/math_fns.cpp:1433-1474)
+//    through the shared helpers, stores straight into NCHW (for one channel the 32 positions of a warp are consecutive
+//    addresses).  Accumulators are double buffered in TMEM; one persistent CTA per SM; every wait is bounded.
+//
+// Everything else (other strides, channel counts, wide rows, the reference's position-indexed bias) keeps the patch-buffer
+// path in ltq_conv.cu.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "ltq_common.cuh"
+#include "ltq_conv_direct.cuh"
+#include "ltq_gemm_tc.cuh"
+#include "ltq_tcgen05.cuh"
+
+namespace ltq {
+
+namespace {
+
+constexpr int THREADS = 192;            // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
+constexpr int CCH = 64;                 // channels per K chunk = bytes per row of an operand tile (64-byte swizzle)
+constexpr int STAGE_BYTES = 128 * CCH;  // one ring stage: up to 128 positions x 64 bytes
+constexpr int MAX_STAGES = 12;
+constexpr int EXTRA = 16;               // weight rows appended behind the output channels (row 0 of them: all ones)
+constexpr uint32_t TMEM_COLS = 256;     // two accumulators of up to 128 columns
+constexpr size_t SMEM_BUDGET = 200 * 1024;
+
+struct DirectGeom {
+    uint32_t B, Ho, Wo, rpt, tiles_per_image, tiles;
+    uint32_t taps, kw, ph, pw, cchunks;   // kh * kw, kernel width, padding, Cin / 64
+    uint32_t Cout, Npad;                  // output channels, Cout + 16
+    uint32_t stages;
+};
+
+// Shared-memory matrix descriptor for a K-major operand tile with rows of 64 bytes laid out by TMA with the 64-byte
+// swizzle: 8-row groups 512 bytes apart, layout type 4.  The tile base is 512-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc_sw64(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1,
+                                            int32_t c2, int32_t c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// NCHW -> NHWC for `batches` images: one CTA per (image, row), the row's C x W bytes staged in shared memory.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xt, uint32_t C,
+                                                           uint32_t H, uint32_t W)
+{
+    griddep_launch_dependents();
+    extern __shared__ uint8_t s[];                       // [C][pitch]
+    const uint32_t h = blockIdx.x, b = blockIdx.y, pitch = W | 1u;   // odd: the transposed reads below hit distinct banks
+    griddep_wait();
+    const uint8_t *src = x + ((size_t)b * C * H + h) * W;
+    if ((W & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0) {
+        const uint32_t ww = W / 4;
+        for (uint32_t i = threadIdx.x; i < C * ww; i += blockDim.x) {
+            const uint32_t c = i / ww, w4 = (i - c * ww) * 4;
+            const uint32_t v = *reinterpret_cast<const uint32_t *>(src + (size_t)c * H * W + w4);
+            uint8_t *d = s + c * pitch + w4;
+            d[0] = (uint8_t)v;
+            d[1] = (uint8_t)(v >> 8);
+            d[2] = (uint8_t)(v >> 16);
+            d[3] = (uint8_t)(v >> 24);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < C * W; i += blockDim.x) {
+            const uint32_t c = i / W, w = i - c * W;
+            s[c * pitch + w] = src[(size_t)c * H * W + w];
+        }
+    }
+    __syncthreads();
+    uint32_t *dst = reinterpret_cast<uint32_t *>(xt + ((size_t)b * H + h) * W * C);   // C % 64 == 0: word aligned
+    const uint32_t cw = C / 4;
+    for (uint32_t j = threadIdx.x; j < W * cw; j += blockDim.x) {
+        const uint32_t w = j / cw, c4 = (j - w * cw) * 4;
+        const uint32_t v = (uint32_t)s[c4 * pitch + w] | ((uint32_t)s[(c4 + 1) * pitch + w] << 8) |
+                           ((uint32_t)s[(c4 + 2) * pitch + w] << 16) | ((uint32_t)s[(c4 + 3) * pitch + w] << 24);
+        dst[j] = v;
+    }
+}
+
+// wr[n][(i * kw + j) * C + c] = w[n][(c * kh + i) * kw + j] for n < Cout; row Cout: all ones; rows Cout+1 .. Cout+15: zero.
+__global__ void reorder_weights_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ wr, uint32_t Cout, uint32_t C,
+                                       uint32_t kh, uint32_t kw)
+{
+    const uint32_t K = C * kh * kw;
+    const uint64_t total = (uint64_t)(Cout + EXTRA) * K;
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t n = (uint32_t)(idx / K), k = (uint32_t)(idx - (uint64_t)n * K);
+        uint8_t v;
+        if (n < Cout) {
+            const uint32_t tap = k / C, c = k - tap * C, i = tap / kw, j = tap - i * kw;
+            v = w[(size_t)n * K + ((size_t)c * kh + i) * kw + j];
+        } else {
+            v = n == Cout ? 1 : 0;
+        }
+        wr[idx] = v;
+    }
+}
+
+}  // namespace
+
+// OUT: 0 = uint8, 1 = float, 2 = int32 (ltq_out_mode).
+template <int OUT>
+__global__ void __launch_bounds__(THREADS, 1)
+conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const DirectGeom g,
+                   const Epilogue epi, void *__restrict__ out, uint32_t *status)
+{
+    griddep_launch_dependents();
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw0 = smem_u32(smem_raw);
+    const uint32_t ring = (raw0 + 1023u) & ~1023u;                             // [stages][128 positions][64 B]
+    const uint32_t wsm = ring + g.stages * STAGE_BYTES;                        // [taps * cchunks][Npad rows][64 B]
+    const uint32_t nchunks = g.taps * g.cchunks, wtile = g.Npad * CCH;
+    uint8_t *after = smem_raw + (wsm - raw0) + nchunks * wtile;
+    uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                     // [128] column terms
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 128 * 4);            // full[S] empty[S] tfull[2] tempty[2] wfull
+    uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 5);  // [0] tmem base, [1] abort flag
+    volatile uint32_t *abort_flag = s_misc + 1;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES;
+    const uint32_t tfull0 = empty0 + 8 * MAX_STAGES, tempty0 = tfull0 + 16, wfull = tempty0 + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < g.stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(tfull0 + 8 * s, 1);
+            mbar_init(tempty0 + 8 * s, 4);  // one arrival per epilogue warp
+        }
+        mbar_init(wfull, 1);
+        s_misc[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the reordered weights are static data: on their way before the kernel in front has finished
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        mbar_expect_tx(wfull, nchunks * wtile);
+        for (uint32_t ch = 0; ch < nchunks; ch++) tma_load_2d(wsm + ch * wtile, &map_w, wfull, (int32_t)(ch * CCH), 0);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(s_misc), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    griddep_wait();   // the transposed input comes from the kernel in front
+    const uint32_t tmem_base = s_misc[0];
+    const uint32_t box_bytes = g.rpt * g.Wo * CCH;   // a copy always delivers its whole box (zeros outside the image)
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t st = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < g.tiles; t += gridDim.x) {
+                const uint32_t b = t / g.tiles_per_image, ho0 = (t - b * g.tiles_per_image) * g.rpt;
+                for (uint32_t tap = 0; ok && tap < g.taps; tap++) {
+                    const int32_t y = (int32_t)(ho0 + tap / g.kw) - (int32_t)g.ph, x0 = (int32_t)(tap % g.kw) - (int32_t)g.pw;
+                    for (uint32_t cc = 0; cc < g.cchunks; cc++) {
+                        ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
+                        if (!ok) break;
+                        mbar_expect_tx(full0 + 8 * st, box_bytes);
+                        tma_load_4d(ring + st * STAGE_BYTES, &map_x, full0 + 8 * st, (int32_t)(cc * CCH), x0, y, (int32_t)b);
+                        if (++st == g.stages) { st = 0; ph ^= 1; }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
+        const uint32_t idesc = make_idesc_i8(128, (int)g.Npad);
+        uint32_t st = 0, ph = 0, as = 0, aph = 0;
+        bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(wfull, 0, abort_flag, status, 0x600u));
+        for (uint32_t t = blockIdx.x; ok && t < g.tiles; t += gridDim.x) {
+            ok = __all_sync(0xFFFFFFFFu, mbar_wait(tempty0 + 8 * as, aph ^ 1, abort_flag, status, 0x200u | as));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + as * 128;
+            for (uint32_t ch = 0; ch < nchunks; ch++) {
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t a_desc = make_smem_desc_sw64(ring + st * STAGE_BYTES), b_desc = make_smem_desc_sw64(wsm + ch * wtile);
+                if (elect_one()) {
+                    umma_i8(d_tmem, a_desc, b_desc, idesc, ch != 0u);
+                    umma_i8(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);   // the second 32 bytes of K of the 64-byte rows
+                    umma_commit(empty0 + 8 * st);
+                }
+                __syncwarp();
+                if (++st == g.stages) { st = 0; ph ^= 1; }
+            }
+            if (!ok) break;
+            if (elect_one()) umma_commit(tfull0 + 8 * as);
+            __syncwarp();
+            if (++as == 2) { as = 0; aph ^= 1; }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5 = 128 threads): thread = output position ----------------
+        const uint32_t q = (uint32_t)warp & 3u;
+        const uint32_t et = threadIdx.x - 64;
+        const EpilogueConsts c = epilogue_consts(epi);
+        const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
+        using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
+        OutT *o = static_cast<OutT *>(out);
+        // column terms (-zA * wsum[channel] + bias[channel]): the same for every tile
+        for (uint32_t j = et; j < 128u; j += 128) s_col[j] = j < g.Cout ? epilogue_col_term(epi, c, j) : 0u;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const uint32_t p = q * 32 + lane;                 // position inside the tile
+        const size_t plane = (size_t)g.Ho * g.Wo;
+        uint32_t as = 0, aph = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; t < g.tiles; t += gridDim.x) {
+            const uint32_t b = t / g.tiles_per_image, ho0 = (t - b * g.tiles_per_image) * g.rpt;
+            const uint32_t rows = g.Ho - ho0 < g.rpt ? g.Ho - ho0 : g.rpt;
+            const bool valid = p < rows * g.Wo;
+            if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * 128;
+                uint32_t v[16];
+                tmem_ld16(taddr + g.Cout, v);             // the all-ones weight row: v[0] = sum of this position's patch bytes
+                tmem_ld_wait();
+                const uint32_t rt = c.neg_zB * v[0] + c.bc;
+                OutT *dst = o + (size_t)b * g.Cout * plane + (size_t)ho0 * g.Wo + p;
+#pragma unroll 1
+                for (uint32_t ch = 0; ch < g.Cout; ch += 16) {
+                    tmem_ld16(taddr + ch, v);
+                    tmem_ld_wait();
+                    uint32_t res[16];
+                    epilogue_convert<OUT, 16>(v, rt, s_col + ch, c, relu, sat, res);
+                    if (valid) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            if (OUT == 0) dst[(size_t)(ch + j) * plane] = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                            else if (OUT == 1) dst[(size_t)(ch + j) * plane] = (OutT)__uint_as_float(res[j]);
+                            else dst[(size_t)(ch + j) * plane] = (OutT)(int32_t)res[j];
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * as);
+            }
+            if (++as == 2) { as = 0; aph ^= 1; }
+        }
+    }
+
+    // Teardown: nobody leaves before every role is done with TMEM and shared memory.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0 && lane == 0 && *abort_flag) {
+        // after a timeout copies issued by this thread may still be landing in this CTA's shared memory
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+size_t direct_smem(uint32_t stages, uint32_t nchunks, uint32_t Npad)
+{
+    return 1024 + (size_t)stages * STAGE_BYTES + (size_t)nchunks * Npad * CCH + 128 * 4 + (2 * MAX_STAGES + 5) * 8 + 16;
+}
+
+template <int OUT>
+cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const DirectGeom &g, const Epilogue &epi, void *out,
+                          uint32_t *status, int sms, cudaStream_t stream)
+{
+    const size_t smem = direct_smem(g.stages, g.taps * g.cchunks, g.Npad);
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_done[dev]) {
+        e = cudaFuncSetAttribute(conv_direct_kernel<OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BUDGET);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    const unsigned grid = g.tiles < (uint32_t)sms ? g.tiles : (unsigned)sms;
+    e = launch_chained(conv_direct_kernel<OUT>, dim3(grid), dim3(THREADS), smem, stream, mx, mw, g, epi, out, status);
+    count_launch();
+    note_kernel("conv_direct_kernel<%s> (%u tiles of %u rows x %u)", out_mode_name(OUT), g.tiles, g.rpt, g.Wo);
+    return e;
+}
+
+}  // namespace
+
+bool conv_direct_weights_ok(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw)
+{
+    if (sh != 1 || sw != 1 || Cin % CCH != 0 || Cout % 16 != 0 || Cout + EXTRA > 128) return false;
+    const uint64_t nchunks = kh * kw * (Cin / CCH);
+    // the weights of all taps stay in shared memory beside a ring of at least 4 stages
+    return nchunks < (1u << 16) && direct_smem(4, (uint32_t)nchunks, (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET && encode_fn() != nullptr;
+}
+
+size_t conv_direct_weight_bytes(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw) { return (Cout + EXTRA) * Cin * kh * kw; }
+
+cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, TcOperandMap *map, uint64_t Cin, uint64_t Cout, uint64_t kh,
+                                        uint64_t kw, cudaStream_t stream)
+{
+    reorder_weights_kernel<<<256, 256, 0, stream>>>(w, wr, (uint32_t)Cout, (uint32_t)Cin, (uint32_t)kh, (uint32_t)kw);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    count_launch();
+    const uint64_t K = Cin * kh * kw, Npad = Cout + EXTRA;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Npad};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)CCH, (cuuint32_t)Npad};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(reinterpret_cast<CUtensorMap *>(map->opaque), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, wr, dims, strides, box,
+                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    map->base = wr;
+    map->rows = Npad;
+    map->K = K;
+    map->box_rows = (int)Npad;
+    map->box_lines = 0;
+    return cudaSuccess;
+}
+
+bool conv_direct_shape_ok(uint64_t batches, uint64_t H, uint64_t W, uint64_t Ho, uint64_t Wo)
+{
+    return Wo >= 1 && Wo <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31);
+}
+
+cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream)
+{
+    // one CTA per (row, image); the grid's y extent holds 65535 images per launch
+    const size_t pitch = W | 1u, smem = C * pitch;
+    if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(nchw_to_nhwc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    for (uint64_t b0 = 0; b0 < batches; b0 += 65535) {
+        const uint64_t nb = batches - b0 < 65535 ? batches - b0 : 65535;
+        cudaError_t e = launch_chained(nchw_to_nhwc_kernel, dim3((unsigned)H, (unsigned)nb), dim3(256), smem, stream,
+                                       x + b0 * C * H * W, xt + b0 * C * H * W, (uint32_t)C, (uint32_t)H, (uint32_t)W);
+        if (e != cudaSuccess) return e;
+        count_launch();
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
+                               uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
+                               const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+{
+    DirectGeom g;
+    g.B = (uint32_t)batches;
+    g.Ho = (uint32_t)Ho;
+    g.Wo = (uint32_t)Wo;
+    g.rpt = (uint32_t)(128 / Wo);
+    if (g.rpt > Ho) g.rpt = (uint32_t)Ho;
+    if (g.rpt > 256) g.rpt = 256;
+    g.tiles_per_image = (uint32_t)((Ho + g.rpt - 1) / g.rpt);
+    if ((uint64_t)g.tiles_per_image * batches >= (1ull << 31)) return cudaErrorInvalidConfiguration;
+    g.tiles = g.tiles_per_image * g.B;
+    g.taps = (uint32_t)(kh * kw);
+    g.kw = (uint32_t)kw;
+    g.ph = (uint32_t)ph;
+    g.pw = (uint32_t)pw;
+    g.cchunks = (uint32_t)(Cin / CCH);
+    g.Cout = (uint32_t)Cout;
+    g.Npad = (uint32_t)Cout + EXTRA;
+    g.stages = MAX_STAGES;
+    while (g.stages > 4 && direct_smem(g.stages, g.taps * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;
+    // the input as {channel, x, y, image}; a box is 64 channels of rpt output rows' worth of pixels
+    alignas(64) CUtensorMap mx;
+    cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batches};
+    cuuint64_t strides[3] = {(cuuint64_t)Cin, (cuuint64_t)(W * Cin), (cuuint64_t)(H * W * Cin)};
+    cuuint32_t box[4] = {(cuuint32_t)CCH, (cuuint32_t)Wo, g.rpt, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(xt), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(map_w.opaque);
+    switch (epi.out_mode) {
+        case LTQ_OUT_U8: return launch_direct<0>(mx, mw, g, epi, out, status, sms, stream);
+        case LTQ_OUT_F32: return launch_direct<1>(mx, mw, g, epi, out, status, sms, stream);
+        default: return launch_direct<2>(mx, mw, g, epi, out, status, sms, stream);
+    }
+}
+
+}  // namespace ltq

@@ -1,0 +1,26 @@
+// Host-visible interface of the patch-buffer-free Conv2d_q path (ltq_conv_direct.cu).
+#pragma once
+#include "ltq_common.cuh"
+#include "ltq_gemm_tc.cuh"
+
+namespace ltq {
+
+// Static eligibility (known when the layer is created): stride 1, input channels a multiple of 64, output channels a
+// multiple of 16 and at most 112, and the reordered weights of all kernel taps fit in shared memory beside the ring.
+bool conv_direct_weights_ok(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw);
+// Bytes of the reordered weight buffer: (Cout + 16) rows of Cin * kh * kw.
+size_t conv_direct_weight_bytes(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw);
+// Reorders w [Cout][Cin][kh][kw] into wr [Cout + 16][kh][kw][Cin] (the extra rows: ones, then zeros) and encodes its map.
+cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, TcOperandMap *map, uint64_t Cin, uint64_t Cout, uint64_t kh,
+                                        uint64_t kw, cudaStream_t stream);
+// Per-call eligibility: an output row fits one tile (Wo <= 128).
+bool conv_direct_shape_ok(uint64_t batches, uint64_t H, uint64_t W, uint64_t Ho, uint64_t Wo);
+// x [B][C][H][W] -> xt [B][H][W][C].
+cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream);
+// out [B][Cout][Ho][Wo] from the transposed input.  `epi`: A = input (patch sums come from the kernel itself: asum
+// unused), B = weights (bsum = their sums per output channel, bias per output channel or nullptr).
+cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
+                               uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
+                               const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream);
+
+}  // namespace ltq

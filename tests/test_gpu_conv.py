@@ -75,6 +75,44 @@ def test_conv_matches_oracle(cuda, oracle, shape):
     np.testing.assert_array_equal(got, want)
 
 
+@pytest.mark.parametrize("shape", [
+    # B, Cin, H, W, Cout, kh, kw, ph, pw
+    (2, 64, 12, 20, 32, 3, 3, 1, 1),       # 6 output rows per tile, two tiles per image
+    (3, 64, 56, 56, 64, 3, 3, 1, 1),       # the benchmark's geometry: 2 rows of 56 per tile
+    (1, 128, 9, 9, 48, 3, 3, 0, 0),        # two channel chunks per tap, no padding, 7 x 7 output in one tile
+    (5, 64, 7, 7, 16, 1, 1, 0, 0),         # 1 x 1 kernel
+    (2, 64, 30, 30, 32, 5, 5, 2, 2),       # 25 taps (77 KB of reordered weights resident)
+    (1, 64, 5, 130, 16, 3, 3, 1, 0),       # Wo = 128: one output row per tile; padding in y only
+])
+@pytest.mark.parametrize("mode", ["u8", "f32", "i32"])
+def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
+    """Stride 1 and a multiple of 64 input channels take the kernel that never builds the patches (K walked as kernel row,
+    kernel column, channel; patch sums from an all-ones weight row).  Against the oracle, bit for bit, with and without
+    the per-channel bias and ReLU, and against the patch-buffer path on the same device."""
+    import ltq
+    B, Cin, H, W, Cout, kh, kw, ph, pw = shape
+    rng = np.random.default_rng(sum(shape) + len(mode))
+    c = dict(Cin=Cin, Cout=Cout, kh=kh, kw=kw, ph=ph, pw=pw, sh=1, sw=1,
+             x=rng.integers(0, 256, (B, Cin, H, W), dtype=np.uint8),
+             w=rng.integers(0, 256, (Cout, Cin * kh * kw), dtype=np.uint8))
+    rows = [(0.02, 128), (0.005, 127), (4.0, 3)]
+    qps = [ltq_qp(r) for r in rows]
+    out_mode = {"u8": ltq.OUT_U8, "f32": ltq.OUT_F32, "i32": ltq.OUT_I32}[mode]
+    bias = rng.integers(-30000, 30000, Cout, dtype=np.int32)
+    for use_bias, relu in ((False, False), (True, False), (True, True)):
+        flags = (ltq.FLAG_BIAS_PER_CHANNEL if use_bias else 0) | (ltq.FLAG_RELU if relu else 0)
+        got = _conv(cuda, ltq, c, qps, flags=flags, out_mode=out_mode, bias=bias if use_bias else None)
+        assert ltq.last_kernel().startswith("conv_direct_kernel<"), ltq.last_kernel()
+        old = _conv(cuda, ltq, c, qps, flags=flags | ltq.FLAG_FORCE_SIMT, out_mode=out_mode, bias=bias if use_bias else None)
+        assert not ltq.last_kernel().startswith("conv_direct_kernel<")
+        np.testing.assert_array_equal(got.view(np.uint32) if mode == "f32" else got, old.view(np.uint32) if mode == "f32" else old)
+        if mode == "u8" and not relu:
+            want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], bias=bias if use_bias else None,
+                                        ph=ph, pw=pw, sh=1, sw=1, bias_per_channel=use_bias)
+            np.testing.assert_array_equal(got, want)
+    assert ltq.lib().ltq_device_check(0, None) == 0
+
+
 def test_reference_bias_indexing_is_refused_beyond_its_tensor(cuda):
     import ltq
     h = ltq.ConvHandle(0, 2, 4, 3, 3)
