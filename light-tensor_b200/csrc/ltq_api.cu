@@ -721,7 +721,8 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     // Without a patch buffer where the geometry allows (and no kernel is forced, and the bias is per channel or absent):
     // transpose the input to NHWC, then one kernel for the whole batch.
     if (conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
-        (per_channel || !conv->bias) && conv_direct_shape_ok(batches, height_in, width_in, Ho, Wo)) {
+        (per_channel || !conv->bias) &&
+        conv_direct_shape_ok(batches, conv->Cin, conv->Cout, conv->kh, conv->kw, height_in, width_in, Ho, Wo)) {
         rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, batches * conv->Cin * height_in * width_in, st, "the NHWC copy of the input");
         if (rc != LTQ_OK) return rc;
         LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));

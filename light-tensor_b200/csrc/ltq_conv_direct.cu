@@ -36,19 +36,20 @@ namespace ltq {
 
 namespace {
 
-constexpr int THREADS = 192;            // warp 0 producer, warp 1 MMA issuer, warps 2..5 epilogue
+constexpr int THREADS = 320;            // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue (two per TMEM lane quarter)
 constexpr int CCH = 64;                 // channels per K chunk = bytes per row of an operand tile (64-byte swizzle)
-constexpr int STAGE_BYTES = 128 * CCH;  // one ring stage: up to 128 positions x 64 bytes
-constexpr int MAX_STAGES = 12;
+constexpr int MAX_STAGES = 8;
+constexpr uint32_t MAX_STAGE_BYTES = 48 * 1024;
 constexpr int EXTRA = 16;               // weight rows appended behind the output channels (row 0 of them: all ones)
 constexpr uint32_t TMEM_COLS = 256;     // two accumulators of up to 128 columns
 constexpr size_t SMEM_BUDGET = 200 * 1024;
 
 struct DirectGeom {
     uint32_t B, Ho, Wo, rpt, tiles_per_image, tiles;
-    uint32_t taps, kw, ph, pw, cchunks;   // kh * kw, kernel width, padding, Cin / 64
+    uint32_t P;                           // pixel slots per row of a stage: a power of two >= Wo + kw - 1; rpt = 128 / P
+    uint32_t kh, kw, ph, pw, cchunks;     // kernel size, padding, Cin / 64
     uint32_t Cout, Npad;                  // output channels, Cout + 16
-    uint32_t stages;
+    uint32_t stages, stage_bytes;         // ring depth; (rpt + kh - 1) * P * 64 rounded up to 1 KB
 };
 
 // Shared-memory matrix descriptor for a K-major operand tile with rows of 64 bytes laid out by TMA with the 64-byte
@@ -73,40 +74,48 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
-// NCHW -> NHWC for `batches` images: one CTA per (image, row), the row's C x W bytes staged in shared memory.
+// NCHW -> NHWC for `batches` images: one CTA per (image, row).  The row's C x W bytes are staged in shared memory as
+// 32-bit words (four pixels of one channel each); a thread then takes the words of four consecutive channels, transposes
+// the 4 x 4 bytes in registers and writes four words (four channels of one pixel each), so that a warp's stores are runs
+// of 64 contiguous bytes.
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xt, uint32_t C,
                                                            uint32_t H, uint32_t W)
 {
     griddep_launch_dependents();
-    extern __shared__ uint8_t s[];                       // [C][pitch]
-    const uint32_t h = blockIdx.x, b = blockIdx.y, pitch = W | 1u;   // odd: the transposed reads below hit distinct banks
+    extern __shared__ uint32_t s32[];                    // [C][pitch] words
+    const uint32_t h = blockIdx.x, b = blockIdx.y;
+    const uint32_t ww = (W + 3) / 4, pitch = ww | 1u;    // odd pitch: the column reads below spread over the banks
     griddep_wait();
     const uint8_t *src = x + ((size_t)b * C * H + h) * W;
     if ((W & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0) {
-        const uint32_t ww = W / 4;
         for (uint32_t i = threadIdx.x; i < C * ww; i += blockDim.x) {
-            const uint32_t c = i / ww, w4 = (i - c * ww) * 4;
-            const uint32_t v = *reinterpret_cast<const uint32_t *>(src + (size_t)c * H * W + w4);
-            uint8_t *d = s + c * pitch + w4;
-            d[0] = (uint8_t)v;
-            d[1] = (uint8_t)(v >> 8);
-            d[2] = (uint8_t)(v >> 16);
-            d[3] = (uint8_t)(v >> 24);
+            const uint32_t c = i / ww, w4 = i - c * ww;
+            s32[c * pitch + w4] = *reinterpret_cast<const uint32_t *>(src + (size_t)c * H * W + 4 * w4);
         }
     } else {
-        for (uint32_t i = threadIdx.x; i < C * W; i += blockDim.x) {
-            const uint32_t c = i / W, w = i - c * W;
-            s[c * pitch + w] = src[(size_t)c * H * W + w];
+        for (uint32_t i = threadIdx.x; i < C * ww; i += blockDim.x) {
+            const uint32_t c = i / ww, w4 = i - c * ww;
+            const uint8_t *r = src + (size_t)c * H * W + 4 * w4;
+            uint32_t v = 0;
+            for (uint32_t k = 0; k < 4 && 4 * w4 + k < W; k++) v |= (uint32_t)r[k] << (8 * k);
+            s32[c * pitch + w4] = v;
         }
     }
     __syncthreads();
     uint32_t *dst = reinterpret_cast<uint32_t *>(xt + ((size_t)b * H + h) * W * C);   // C % 64 == 0: word aligned
     const uint32_t cw = C / 4;
-    for (uint32_t j = threadIdx.x; j < W * cw; j += blockDim.x) {
-        const uint32_t w = j / cw, c4 = (j - w * cw) * 4;
-        const uint32_t v = (uint32_t)s[c4 * pitch + w] | ((uint32_t)s[(c4 + 1) * pitch + w] << 8) |
-                           ((uint32_t)s[(c4 + 2) * pitch + w] << 16) | ((uint32_t)s[(c4 + 3) * pitch + w] << 24);
-        dst[j] = v;
+    for (uint32_t j = threadIdx.x; j < ww * cw; j += blockDim.x) {
+        const uint32_t w4 = j / cw, c4 = j - w4 * cw;    // consecutive threads: consecutive channel groups of one pixel group
+        const uint32_t r0 = s32[(4 * c4) * pitch + w4], r1 = s32[(4 * c4 + 1) * pitch + w4];
+        const uint32_t r2 = s32[(4 * c4 + 2) * pitch + w4], r3 = s32[(4 * c4 + 3) * pitch + w4];
+        // rK = channel 4*c4+K, bytes = pixels 4*w4 .. +3  ->  oP = pixel 4*w4+P, bytes = channels 4*c4 .. +3
+        const uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r0, r1, 0x7362);   // (r0.b0 r1.b0 r0.b1 r1.b1), (b2, b3)
+        const uint32_t u0 = __byte_perm(r2, r3, 0x5140), u1 = __byte_perm(r2, r3, 0x7362);
+        const uint32_t o[4] = {__byte_perm(t0, u0, 0x5410), __byte_perm(t0, u0, 0x7632), __byte_perm(t1, u1, 0x5410),
+                               __byte_perm(t1, u1, 0x7632)};
+#pragma unroll
+        for (uint32_t k = 0; k < 4; k++)
+            if (4 * w4 + k < W) dst[(size_t)(4 * w4 + k) * cw + c4] = o[k];
     }
 }
 
@@ -140,9 +149,9 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     griddep_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw0 = smem_u32(smem_raw);
-    const uint32_t ring = (raw0 + 1023u) & ~1023u;                             // [stages][128 positions][64 B]
-    const uint32_t wsm = ring + g.stages * STAGE_BYTES;                        // [taps * cchunks][Npad rows][64 B]
-    const uint32_t nchunks = g.taps * g.cchunks, wtile = g.Npad * CCH;
+    const uint32_t ring = (raw0 + 1023u) & ~1023u;                             // [stages][rpt + kh - 1 rows][P pixels][64 B]
+    const uint32_t wsm = ring + g.stages * g.stage_bytes;                      // [kh * kw * cchunks][Npad rows][64 B]
+    const uint32_t taps = g.kh * g.kw, nchunks = taps * g.cchunks, wtile = g.Npad * CCH;
     uint8_t *after = smem_raw + (wsm - raw0) + nchunks * wtile;
     uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                     // [128] column terms
     uint64_t *bars = reinterpret_cast<uint64_t *>(after + 128 * 4);            // full[S] empty[S] tfull[2] tempty[2] wfull
@@ -159,7 +168,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
         for (int s = 0; s < 2; s++) {
             mbar_init(tfull0 + 8 * s, 1);
-            mbar_init(tempty0 + 8 * s, 4);  // one arrival per epilogue warp
+            mbar_init(tempty0 + 8 * s, 8);  // one arrival per epilogue warp
         }
         mbar_init(wfull, 1);
         s_misc[1] = 0;
@@ -180,7 +189,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     tc_fence_after();
     griddep_wait();   // the transposed input comes from the kernel in front
     const uint32_t tmem_base = s_misc[0];
-    const uint32_t box_bytes = g.rpt * g.Wo * CCH;   // a copy always delivers its whole box (zeros outside the image)
+    const uint32_t box_bytes = (g.rpt + g.kh - 1) * g.P * CCH;   // a copy always delivers its whole box (zeros outside the image)
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -189,15 +198,15 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < g.tiles; t += gridDim.x) {
                 const uint32_t b = t / g.tiles_per_image, ho0 = (t - b * g.tiles_per_image) * g.rpt;
-                for (uint32_t tap = 0; ok && tap < g.taps; tap++) {
-                    const int32_t y = (int32_t)(ho0 + tap / g.kw) - (int32_t)g.ph, x0 = (int32_t)(tap % g.kw) - (int32_t)g.pw;
-                    for (uint32_t cc = 0; cc < g.cchunks; cc++) {
-                        ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
-                        if (!ok) break;
-                        mbar_expect_tx(full0 + 8 * st, box_bytes);
-                        tma_load_4d(ring + st * STAGE_BYTES, &map_x, full0 + 8 * st, (int32_t)(cc * CCH), x0, y, (int32_t)b);
-                        if (++st == g.stages) { st = 0; ph ^= 1; }
-                    }
+                // one copy per 64-channel chunk: the rpt + kh - 1 input rows the tile's output rows touch, P pixels wide
+                // from the left padding on (whatever lies outside the image arrives as zeros)
+                for (uint32_t cc = 0; cc < g.cchunks; cc++) {
+                    ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
+                    if (!ok) break;
+                    mbar_expect_tx(full0 + 8 * st, box_bytes);
+                    tma_load_4d(ring + st * g.stage_bytes, &map_x, full0 + 8 * st, (int32_t)(cc * CCH), -(int32_t)g.pw,
+                                (int32_t)ho0 - (int32_t)g.ph, (int32_t)b);
+                    if (++st == g.stages) { st = 0; ph ^= 1; }
                 }
             }
         }
@@ -212,14 +221,22 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + as * 128;
-            for (uint32_t ch = 0; ch < nchunks; ch++) {
+            for (uint32_t cc = 0; cc < g.cchunks; cc++) {
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait(full0 + 8 * st, ph, abort_flag, status, 0x300u | st));
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t a_desc = make_smem_desc_sw64(ring + st * STAGE_BYTES), b_desc = make_smem_desc_sw64(wsm + ch * wtile);
                 if (elect_one()) {
-                    umma_i8(d_tmem, a_desc, b_desc, idesc, ch != 0u);
-                    umma_i8(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);   // the second 32 bytes of K of the 64-byte rows
+                    // Output position p = (row hh, column ww) sits in slot hh * P + ww, and for kernel tap (i, j) it reads the
+                    // pixel in slot (hh + i) * P + ww + j: the same 128 rows of 64 bytes, started (i * P + j) slots further on.
+                    // The swizzle is a function of the shared-memory address, so a shifted start needs nothing else.
+                    const uint32_t stage = ring + st * g.stage_bytes;
+                    for (uint32_t tap = 0; tap < taps; tap++) {
+                        const uint32_t i = tap / g.kw, j = tap - i * g.kw;
+                        const uint64_t a_desc = make_smem_desc_sw64(stage + (i * g.P + j) * CCH);
+                        const uint64_t b_desc = make_smem_desc_sw64(wsm + (tap * g.cchunks + cc) * wtile);
+                        umma_i8(d_tmem, a_desc, b_desc, idesc, (cc | tap) != 0u);
+                        umma_i8(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);   // the second 32 bytes of K of the 64-byte rows
+                    }
                     umma_commit(empty0 + 8 * st);
                 }
                 __syncwarp();
@@ -231,47 +248,55 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             if (++as == 2) { as = 0; aph ^= 1; }
         }
     } else {
-        // ---------------- epilogue (warps 2..5 = 128 threads): thread = output position ----------------
-        const uint32_t q = (uint32_t)warp & 3u;
+        // ---------------- epilogue (warps 2..9 = 256 threads): thread = output position x half of the channels ----------------
+        // A lone warp per scheduler cannot hide its own latencies (measured with four warps: 4.4 us per tile, issue slots
+        // 19 % busy), so two warps share each TMEM lane quarter and split the channels.
+        const uint32_t q = (uint32_t)warp & 3u, half = (uint32_t)(warp - 2) >> 2;
         const uint32_t et = threadIdx.x - 64;
         const EpilogueConsts c = epilogue_consts(epi);
         const bool relu = epi.flags & LTQ_FLAG_RELU, sat = epi.flags & LTQ_FLAG_SATURATE;
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
         OutT *o = static_cast<OutT *>(out);
         // column terms (-zA * wsum[channel] + bias[channel]): the same for every tile
-        for (uint32_t j = et; j < 128u; j += 128) s_col[j] = j < g.Cout ? epilogue_col_term(epi, c, j) : 0u;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const uint32_t p = q * 32 + lane;                 // position inside the tile
+        for (uint32_t j = et; j < 128u; j += 256) s_col[j] = j < g.Cout ? epilogue_col_term(epi, c, j) : 0u;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const uint32_t p = q * 32 + lane;                 // slot inside the tile: output row p / P, column p % P
+        const uint32_t hh = p / g.P, wcol = p - hh * g.P;
         const size_t plane = (size_t)g.Ho * g.Wo;
+        const uint32_t split = ((g.Cout / 2 + 15) / 16) * 16;
+        const uint32_t cb = half ? split : 0u, ce = half ? g.Cout : split;   // this warp's channels
         uint32_t as = 0, aph = 0;
         bool ok = true;
         for (uint32_t t = blockIdx.x; t < g.tiles; t += gridDim.x) {
             const uint32_t b = t / g.tiles_per_image, ho0 = (t - b * g.tiles_per_image) * g.rpt;
-            const uint32_t rows = g.Ho - ho0 < g.rpt ? g.Ho - ho0 : g.rpt;
-            const bool valid = p < rows * g.Wo;
+            const bool valid = wcol < g.Wo && ho0 + hh < g.Ho;
             if (ok) ok = mbar_wait(tfull0 + 8 * as, aph, abort_flag, status, 0x400u | as);
             if (ok) {
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((q * 32u) << 16) + as * 128;
-                uint32_t v[16];
+                uint32_t v[16], vn[16];
                 tmem_ld16(taddr + g.Cout, v);             // the all-ones weight row: v[0] = sum of this position's patch bytes
+                if (cb < ce) tmem_ld16(taddr + cb, vn);
                 tmem_ld_wait();
                 const uint32_t rt = c.neg_zB * v[0] + c.bc;
-                OutT *dst = o + (size_t)b * g.Cout * plane + (size_t)ho0 * g.Wo + p;
+                OutT *d = o + (size_t)b * g.Cout * plane + (size_t)(ho0 + hh) * g.Wo + wcol + (size_t)cb * plane;
 #pragma unroll 1
-                for (uint32_t ch = 0; ch < g.Cout; ch += 16) {
-                    tmem_ld16(taddr + ch, v);
-                    tmem_ld_wait();
+                for (uint32_t ch = cb; ch < ce; ch += 16) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = vn[j];
+                    if (ch + 16 < ce) tmem_ld16(taddr + ch + 16, vn);   // the next chunk travels while this one is converted
                     uint32_t res[16];
                     epilogue_convert<OUT, 16>(v, rt, s_col + ch, c, relu, sat, res);
                     if (valid) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
-                            if (OUT == 0) dst[(size_t)(ch + j) * plane] = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
-                            else if (OUT == 1) dst[(size_t)(ch + j) * plane] = (OutT)__uint_as_float(res[j]);
-                            else dst[(size_t)(ch + j) * plane] = (OutT)(int32_t)res[j];
+                            if (OUT == 0) *d = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                            else if (OUT == 1) *d = (OutT)__uint_as_float(res[j]);
+                            else *d = (OutT)(int32_t)res[j];
+                            d += plane;
                         }
                     }
+                    tmem_ld_wait();
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -317,16 +342,25 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-size_t direct_smem(uint32_t stages, uint32_t nchunks, uint32_t Npad)
+size_t direct_smem(uint32_t stages, uint32_t stage_bytes, uint32_t nchunks, uint32_t Npad)
 {
-    return 1024 + (size_t)stages * STAGE_BYTES + (size_t)nchunks * Npad * CCH + 128 * 4 + (2 * MAX_STAGES + 5) * 8 + 16;
+    return 1024 + (size_t)stages * stage_bytes + (size_t)nchunks * Npad * CCH + 128 * 4 + (2 * MAX_STAGES + 5) * 8 + 16;
 }
+
+// Pixel slots per row of a stage (a power of two that holds an output row and the kernel's overhang) and the stage size.
+uint32_t slots_per_row(uint64_t Wo, uint64_t kw)
+{
+    uint32_t P = 8;
+    while (P < Wo + kw - 1) P *= 2;
+    return P;
+}
+uint32_t stage_bytes_for(uint32_t P, uint64_t kh) { return (uint32_t)(((128 / P + kh - 1) * P * CCH + 1023) & ~1023ull); }
 
 template <int OUT>
 cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const DirectGeom &g, const Epilogue &epi, void *out,
                           uint32_t *status, int sms, cudaStream_t stream)
 {
-    const size_t smem = direct_smem(g.stages, g.taps * g.cchunks, g.Npad);
+    const size_t smem = direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad);
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -340,7 +374,7 @@ cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const Di
     const unsigned grid = g.tiles < (uint32_t)sms ? g.tiles : (unsigned)sms;
     e = launch_chained(conv_direct_kernel<OUT>, dim3(grid), dim3(THREADS), smem, stream, mx, mw, g, epi, out, status);
     count_launch();
-    note_kernel("conv_direct_kernel<%s> (%u tiles of %u rows x %u)", out_mode_name(OUT), g.tiles, g.rpt, g.Wo);
+    note_kernel("conv_direct_kernel<%s> (%u tiles of %u rows x %u slots)", out_mode_name(OUT), g.tiles, g.rpt, g.P);
     return e;
 }
 
@@ -350,8 +384,10 @@ bool conv_direct_weights_ok(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t k
 {
     if (sh != 1 || sw != 1 || Cin % CCH != 0 || Cout % 16 != 0 || Cout + EXTRA > 128) return false;
     const uint64_t nchunks = kh * kw * (Cin / CCH);
-    // the weights of all taps stay in shared memory beside a ring of at least 4 stages
-    return nchunks < (1u << 16) && direct_smem(4, (uint32_t)nchunks, (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET && encode_fn() != nullptr;
+    // the weights of all taps stay in shared memory beside a ring of at least 2 of the smallest stages (whether the
+    // stages of a given image width fit is decided per call)
+    return nchunks < (1u << 16) && direct_smem(2, stage_bytes_for(8, kh), (uint32_t)nchunks, (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET &&
+           encode_fn() != nullptr;
 }
 
 size_t conv_direct_weight_bytes(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw) { return (Cout + EXTRA) * Cin * kh * kw; }
@@ -380,15 +416,20 @@ cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, TcOperand
     return cudaSuccess;
 }
 
-bool conv_direct_shape_ok(uint64_t batches, uint64_t H, uint64_t W, uint64_t Ho, uint64_t Wo)
+bool conv_direct_shape_ok(uint64_t batches, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W, uint64_t Ho,
+                          uint64_t Wo)
 {
-    return Wo >= 1 && Wo <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31);
+    if (!(Wo >= 1 && Wo + kw - 1 <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31)))
+        return false;
+    const uint32_t P = slots_per_row(Wo, kw), sb = stage_bytes_for(P, kh);
+    return 128 / P + kh - 1 <= 256 && sb <= MAX_STAGE_BYTES &&
+           direct_smem(2, sb, (uint32_t)(kh * kw * (Cin / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
 }
 
 cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream)
 {
     // one CTA per (row, image); the grid's y extent holds 65535 images per launch
-    const size_t pitch = W | 1u, smem = C * pitch;
+    const size_t pitch = ((W + 3) / 4) | 1u, smem = C * pitch * 4;
     if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
     static bool attr_done = false;
     if (!attr_done) {
@@ -414,26 +455,27 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uin
     g.B = (uint32_t)batches;
     g.Ho = (uint32_t)Ho;
     g.Wo = (uint32_t)Wo;
-    g.rpt = (uint32_t)(128 / Wo);
-    if (g.rpt > Ho) g.rpt = (uint32_t)Ho;
-    if (g.rpt > 256) g.rpt = 256;
+    g.P = slots_per_row(Wo, kw);
+    g.rpt = 128 / g.P;
     g.tiles_per_image = (uint32_t)((Ho + g.rpt - 1) / g.rpt);
     if ((uint64_t)g.tiles_per_image * batches >= (1ull << 31)) return cudaErrorInvalidConfiguration;
     g.tiles = g.tiles_per_image * g.B;
-    g.taps = (uint32_t)(kh * kw);
+    g.kh = (uint32_t)kh;
     g.kw = (uint32_t)kw;
     g.ph = (uint32_t)ph;
     g.pw = (uint32_t)pw;
     g.cchunks = (uint32_t)(Cin / CCH);
     g.Cout = (uint32_t)Cout;
     g.Npad = (uint32_t)Cout + EXTRA;
+    g.stage_bytes = stage_bytes_for(g.P, kh);
     g.stages = MAX_STAGES;
-    while (g.stages > 4 && direct_smem(g.stages, g.taps * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;
-    // the input as {channel, x, y, image}; a box is 64 channels of rpt output rows' worth of pixels
+    while (g.stages > 2 && direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;
+    if (direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) return cudaErrorInvalidConfiguration;
+    // the input as {channel, x, y, image}; a box is 64 channels of the rpt + kh - 1 input rows a tile touches, P pixels wide
     alignas(64) CUtensorMap mx;
     cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batches};
     cuuint64_t strides[3] = {(cuuint64_t)Cin, (cuuint64_t)(W * Cin), (cuuint64_t)(H * W * Cin)};
-    cuuint32_t box[4] = {(cuuint32_t)CCH, (cuuint32_t)Wo, g.rpt, 1};
+    cuuint32_t box[4] = {(cuuint32_t)CCH, g.P, g.rpt + g.kh - 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(xt), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

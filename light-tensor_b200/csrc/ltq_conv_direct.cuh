@@ -13,8 +13,10 @@ size_t conv_direct_weight_bytes(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64
 // Reorders w [Cout][Cin][kh][kw] into wr [Cout + 16][kh][kw][Cin] (the extra rows: ones, then zeros) and encodes its map.
 cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, TcOperandMap *map, uint64_t Cin, uint64_t Cout, uint64_t kh,
                                         uint64_t kw, cudaStream_t stream);
-// Per-call eligibility: an output row fits one tile (Wo <= 128).
-bool conv_direct_shape_ok(uint64_t batches, uint64_t H, uint64_t W, uint64_t Ho, uint64_t Wo);
+// Per-call eligibility: an output row and the kernel's overhang fit the 128 rows of one tile, and a ring of the tile's
+// input regions fits beside the weights.
+bool conv_direct_shape_ok(uint64_t batches, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W, uint64_t Ho,
+                          uint64_t Wo);
 // x [B][C][H][W] -> xt [B][H][W][C].
 cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream);
 // out [B][Cout][Ho][Wo] from the transposed input.  `epi`: A = input (patch sums come from the kernel itself: asum

@@ -77,12 +77,12 @@ def test_conv_matches_oracle(cuda, oracle, shape):
 
 @pytest.mark.parametrize("shape", [
     # B, Cin, H, W, Cout, kh, kw, ph, pw
-    (2, 64, 12, 20, 32, 3, 3, 1, 1),       # 6 output rows per tile, two tiles per image
-    (3, 64, 56, 56, 64, 3, 3, 1, 1),       # the benchmark's geometry: 2 rows of 56 per tile
-    (1, 128, 9, 9, 48, 3, 3, 0, 0),        # two channel chunks per tap, no padding, 7 x 7 output in one tile
+    (2, 64, 12, 20, 32, 3, 3, 1, 1),       # 32 slots per row: 4 output rows per tile, three tiles per image
+    (3, 64, 56, 56, 64, 3, 3, 1, 1),       # the benchmark's geometry: 2 rows of 56 (64 slots each) per tile
+    (1, 128, 9, 9, 48, 3, 3, 0, 0),        # two channel chunks, no padding, 7 x 7 output in one tile of 8 rows x 16 slots
     (5, 64, 7, 7, 16, 1, 1, 0, 0),         # 1 x 1 kernel
     (2, 64, 30, 30, 32, 5, 5, 2, 2),       # 25 taps (77 KB of reordered weights resident)
-    (1, 64, 5, 130, 16, 3, 3, 1, 0),       # Wo = 128: one output row per tile; padding in y only
+    (1, 64, 5, 128, 16, 3, 3, 1, 0),       # Wo = 126: one output row per tile of 128 slots; padding in y only
 ])
 @pytest.mark.parametrize("mode", ["u8", "f32", "i32"])
 def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
