@@ -74,40 +74,42 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
-// NCHW -> NHWC for `batches` images: one CTA per (image, row).  The row's C x W bytes are staged in shared memory as
-// 32-bit words (four pixels of one channel each); a thread then takes the words of four consecutive channels, transposes
-// the 4 x 4 bytes in registers and writes four words (four channels of one pixel each), so that a warp's stores are runs
-// of 64 contiguous bytes.
+// NCHW -> NHWC for `batches` images: one CTA per (image, NHWC_ROWS rows).  The rows' C x W bytes are staged in
+// shared memory as 32-bit words (four pixels of one channel each); a thread then takes the words of four consecutive
+// channels, transposes the 4 x 4 bytes in registers and writes four words (four channels of one pixel each), so that a
+// warp's stores are runs of 64 contiguous bytes.
+constexpr uint32_t NHWC_ROWS = 1;        // rows per CTA (measured on 32 x 64 x 56 x 56: 1 row per CTA 9 us, 4 rows per CTA 17 us - the
+                                         // kernel lives on the number of warps in flight)
+constexpr size_t NHWC_SMEM = 160 * 1024;
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xt, uint32_t C,
-                                                           uint32_t H, uint32_t W)
+                                                           uint32_t H, uint32_t W, uint32_t rows)
 {
     griddep_launch_dependents();
-    extern __shared__ uint32_t s32[];                    // [C][pitch] words
-    const uint32_t h = blockIdx.x, b = blockIdx.y;
+    extern __shared__ uint32_t s32[];                    // [rows][C][pitch] words
+    const uint32_t h0 = blockIdx.x * rows, b = blockIdx.y;
+    const uint32_t nr = H - h0 < rows ? H - h0 : rows;
     const uint32_t ww = (W + 3) / 4, pitch = ww | 1u;    // odd pitch: the column reads below spread over the banks
     griddep_wait();
-    const uint8_t *src = x + ((size_t)b * C * H + h) * W;
-    if ((W & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0) {
-        for (uint32_t i = threadIdx.x; i < C * ww; i += blockDim.x) {
-            const uint32_t c = i / ww, w4 = i - c * ww;
-            s32[c * pitch + w4] = *reinterpret_cast<const uint32_t *>(src + (size_t)c * H * W + 4 * w4);
+    const uint8_t *src = x + ((size_t)b * C * H + h0) * W;
+    const bool words = (W & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0;
+    for (uint32_t i = threadIdx.x; i < nr * C * ww; i += blockDim.x) {
+        const uint32_t rc = i / ww, w4 = i - rc * ww, r = rc / C, c = rc - r * C;
+        const uint8_t *p = src + ((size_t)c * H + r) * W + 4 * w4;
+        uint32_t v = 0;
+        if (words) {
+            v = *reinterpret_cast<const uint32_t *>(p);
+        } else {
+            for (uint32_t k = 0; k < 4 && 4 * w4 + k < W; k++) v |= (uint32_t)p[k] << (8 * k);
         }
-    } else {
-        for (uint32_t i = threadIdx.x; i < C * ww; i += blockDim.x) {
-            const uint32_t c = i / ww, w4 = i - c * ww;
-            const uint8_t *r = src + (size_t)c * H * W + 4 * w4;
-            uint32_t v = 0;
-            for (uint32_t k = 0; k < 4 && 4 * w4 + k < W; k++) v |= (uint32_t)r[k] << (8 * k);
-            s32[c * pitch + w4] = v;
-        }
+        s32[rc * pitch + w4] = v;
     }
     __syncthreads();
-    uint32_t *dst = reinterpret_cast<uint32_t *>(xt + ((size_t)b * H + h) * W * C);   // C % 64 == 0: word aligned
+    uint32_t *dst = reinterpret_cast<uint32_t *>(xt + ((size_t)b * H + h0) * W * C);   // C % 64 == 0: word aligned
     const uint32_t cw = C / 4;
-    for (uint32_t j = threadIdx.x; j < ww * cw; j += blockDim.x) {
-        const uint32_t w4 = j / cw, c4 = j - w4 * cw;    // consecutive threads: consecutive channel groups of one pixel group
-        const uint32_t r0 = s32[(4 * c4) * pitch + w4], r1 = s32[(4 * c4 + 1) * pitch + w4];
-        const uint32_t r2 = s32[(4 * c4 + 2) * pitch + w4], r3 = s32[(4 * c4 + 3) * pitch + w4];
+    for (uint32_t j = threadIdx.x; j < nr * ww * cw; j += blockDim.x) {
+        const uint32_t rw = j / cw, c4 = j - rw * cw, r = rw / ww, w4 = rw - r * ww;   // consecutive threads: channel groups of one pixel group
+        const uint32_t *col = s32 + (r * C + 4 * c4) * pitch + w4;
+        const uint32_t r0 = col[0], r1 = col[pitch], r2 = col[2 * pitch], r3 = col[3 * pitch];
         // rK = channel 4*c4+K, bytes = pixels 4*w4 .. +3  ->  oP = pixel 4*w4+P, bytes = channels 4*c4 .. +3
         const uint32_t t0 = __byte_perm(r0, r1, 0x5140), t1 = __byte_perm(r0, r1, 0x7362);   // (r0.b0 r1.b0 r0.b1 r1.b1), (b2, b3)
         const uint32_t u0 = __byte_perm(r2, r3, 0x5140), u1 = __byte_perm(r2, r3, 0x7362);
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__rest
                                __byte_perm(t1, u1, 0x7632)};
 #pragma unroll
         for (uint32_t k = 0; k < 4; k++)
-            if (4 * w4 + k < W) dst[(size_t)(4 * w4 + k) * cw + c4] = o[k];
+            if (4 * w4 + k < W) dst[((size_t)r * W + 4 * w4 + k) * cw + c4] = o[k];
     }
 }
 
@@ -422,25 +424,29 @@ bool conv_direct_shape_ok(uint64_t batches, uint64_t Cin, uint64_t Cout, uint64_
     if (!(Wo >= 1 && Wo + kw - 1 <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31)))
         return false;
     const uint32_t P = slots_per_row(Wo, kw), sb = stage_bytes_for(P, kh);
+    if (Cin * ((((W + 3) / 4) | 1u) * 4) > NHWC_SMEM) return false;   // one image row of the transposition in shared memory
     return 128 / P + kh - 1 <= 256 && sb <= MAX_STAGE_BYTES &&
            direct_smem(2, sb, (uint32_t)(kh * kw * (Cin / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
 }
 
 cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream)
 {
-    // one CTA per (row, image); the grid's y extent holds 65535 images per launch
-    const size_t pitch = ((W + 3) / 4) | 1u, smem = C * pitch * 4;
-    if (smem > 160 * 1024) return cudaErrorInvalidConfiguration;
+    // one CTA per (group of rows, image); the grid's y extent holds 65535 images per launch
+    const size_t pitch = ((W + 3) / 4) | 1u, row_bytes = C * pitch * 4;
+    if (row_bytes > NHWC_SMEM) return cudaErrorInvalidConfiguration;
+    uint32_t rows = (uint32_t)(NHWC_SMEM / row_bytes);
+    rows = rows > NHWC_ROWS ? NHWC_ROWS : rows;
+    const size_t smem = rows * row_bytes;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(nchw_to_nhwc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(nchw_to_nhwc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
     for (uint64_t b0 = 0; b0 < batches; b0 += 65535) {
         const uint64_t nb = batches - b0 < 65535 ? batches - b0 : 65535;
-        cudaError_t e = launch_chained(nchw_to_nhwc_kernel, dim3((unsigned)H, (unsigned)nb), dim3(256), smem, stream,
-                                       x + b0 * C * H * W, xt + b0 * C * H * W, (uint32_t)C, (uint32_t)H, (uint32_t)W);
+        cudaError_t e = launch_chained(nchw_to_nhwc_kernel, dim3((unsigned)((H + rows - 1) / rows), (unsigned)nb), dim3(256), smem, stream,
+                                       x + b0 * C * H * W, xt + b0 * C * H * W, (uint32_t)C, (uint32_t)H, (uint32_t)W, rows);
         if (e != cudaSuccess) return e;
         count_launch();
     }
