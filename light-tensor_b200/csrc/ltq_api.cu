@@ -579,7 +579,7 @@ struct ltq_conv2d {
     // The path without a patch buffer (ltq_conv_direct.cu), where the geometry allows it: the weights reordered to
     // (kernel row, kernel column, channel) with their tensor map, and the NHWC copy of the input, which grows like `col`.
     uint8_t *w_direct = nullptr;
-    ltq::TcOperandMap map_w_direct;
+    ltq::ConvDirectPlan direct;
     bool direct_ready = false;
     uint8_t *x_nhwc = nullptr;
     uint64_t x_nhwc_cap = 0;
@@ -619,8 +619,8 @@ int ltq_conv2d_create(ltq_conv2d **conv, int device, uint64_t channels_in, uint6
     c->dev = dev;
     cudaError_t e = cudaMalloc(&c->wsum, channels_out * sizeof(int32_t));
     if (e == cudaSuccess && c->Kp != c->K) e = cudaMalloc(&c->w_pad, channels_out * c->Kp);
-    if (e == cudaSuccess && conv_direct_weights_ok(channels_in, channels_out, kernel_h, kernel_w, stride_h, stride_w))
-        e = cudaMalloc(&c->w_direct, conv_direct_weight_bytes(channels_in, channels_out, kernel_h, kernel_w));
+    if (e == cudaSuccess && conv_direct_plan(&c->direct, channels_in, channels_out, kernel_h, kernel_w, stride_h, stride_w))
+        e = cudaMalloc(&c->w_direct, conv_direct_weight_bytes(c->direct, channels_in, kernel_h, kernel_w));
     if (e != cudaSuccess) {
         cudaFree(c->w_pad);
         cudaFree(c->wsum);
@@ -662,8 +662,7 @@ int ltq_conv2d_set_weights(ltq_conv2d *conv, const uint8_t *w_dev, const int32_t
     LTQ_CUDA_TRY(launch_row_sums(conv->w, conv->Cout, conv->Kp, conv->wsum, st));
     conv->direct_ready = false;
     if (conv->w_direct) {
-        LTQ_CUDA_TRY(conv_direct_prepare_weights(w_dev, conv->w_direct, &conv->map_w_direct, conv->Cin, conv->Cout, conv->kh,
-                                                 conv->kw, st));
+        LTQ_CUDA_TRY(conv_direct_prepare_weights(w_dev, conv->w_direct, &conv->direct, conv->Cin, conv->kh, conv->kw, st));
         conv->direct_ready = true;
     }
     LTQ_CUDA_TRY(cudaStreamSynchronize(st));
@@ -722,13 +721,13 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     // transpose the input to NHWC, then one kernel for the whole batch.
     if (conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
         (per_channel || !conv->bias) &&
-        conv_direct_shape_ok(batches, conv->Cin, conv->Cout, conv->kh, conv->kw, height_in, width_in, Ho, Wo)) {
+        conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, height_in, width_in, Ho, Wo)) {
         rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, batches * conv->Cin * height_in * width_in, st, "the NHWC copy of the input");
         if (rc != LTQ_OK) return rc;
         LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));
         // positions are the rows here: A = input (its patch sums come out of the kernel), B = weights
         Epilogue epi = make_epilogue(conv->wsum, nullptr, conv->bias, conv->qp_in, conv->qp_wt, conv->qp_out, K, out_mode, flags);
-        LTQ_CUDA_TRY(launch_conv_direct(conv->x_nhwc, conv->map_w_direct, batches, conv->Cin, height_in, width_in, conv->Cout,
+        LTQ_CUDA_TRY(launch_conv_direct(conv->x_nhwc, conv->direct, batches, conv->Cin, height_in, width_in, conv->Cout,
                                         conv->kh, conv->kw, conv->ph, conv->pw, Ho, Wo, epi, out_dev, conv->dev->status,
                                         conv->dev->sms, st));
         return LTQ_OK;

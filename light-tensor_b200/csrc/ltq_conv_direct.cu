@@ -21,8 +21,9 @@
 //    through the shared helpers, stores straight into NCHW (for one channel the 32 positions of a warp are consecutive
 //    addresses).  Accumulators are double buffered in TMEM; one persistent CTA per SM; every wait is bounded.
 //
-// Everything else (other strides, channel counts, wide rows, the reference's position-indexed bias) keeps the patch-buffer
-// path in ltq_conv.cu.
+// More than 112 output channels run as several launches over blocks of channels (each with its own ones row).
+// Everything else (other strides, input channel counts, wide rows, the reference's position-indexed bias) keeps the
+// patch-buffer path in ltq_conv.cu.
 #include <cuda.h>
 
 #include <type_traits>
@@ -48,7 +49,7 @@ struct DirectGeom {
     uint32_t B, Ho, Wo, rpt, tiles_per_image, tiles;
     uint32_t P;                           // pixel slots per row of a stage: a power of two >= Wo + kw - 1; rpt = 128 / P
     uint32_t kh, kw, ph, pw, cchunks;     // kernel size, padding, Cin / 64
-    uint32_t Cout, Npad;                  // output channels, Cout + 16
+    uint32_t Cout, Npad, CoutTotal;       // output channels of this launch, Cout + 16, output channels of the layer
     uint32_t stages, stage_bytes;         // ring depth; (rpt + kh - 1) * P * 64 rounded up to 1 KB
 };
 
@@ -121,7 +122,8 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__rest
     }
 }
 
-// wr[n][(i * kw + j) * C + c] = w[n][(c * kh + i) * kw + j] for n < Cout; row Cout: all ones; rows Cout+1 .. Cout+15: zero.
+// One block of output channels: wr[n][(i * kw + j) * C + c] = w[n][(c * kh + i) * kw + j] for n < Cout (w points at the
+// block's first channel); row Cout: all ones; rows Cout+1 .. Cout+15: zero.
 __global__ void reorder_weights_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ wr, uint32_t Cout, uint32_t C,
                                        uint32_t kh, uint32_t kw)
 {
@@ -281,7 +283,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 if (cb < ce) tmem_ld16(taddr + cb, vn);
                 tmem_ld_wait();
                 const uint32_t rt = c.neg_zB * v[0] + c.bc;
-                OutT *d = o + (size_t)b * g.Cout * plane + (size_t)(ho0 + hh) * g.Wo + wcol + (size_t)cb * plane;
+                OutT *d = o + (size_t)b * g.CoutTotal * plane + (size_t)(ho0 + hh) * g.Wo + wcol + (size_t)cb * plane;
 #pragma unroll 1
                 for (uint32_t ch = cb; ch < ce; ch += 16) {
 #pragma unroll
@@ -382,45 +384,76 @@ cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const Di
 
 }  // namespace
 
-bool conv_direct_weights_ok(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw)
+bool conv_direct_plan(ConvDirectPlan *plan, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw)
 {
-    if (sh != 1 || sw != 1 || Cin % CCH != 0 || Cout % 16 != 0 || Cout + EXTRA > 128) return false;
+    plan->blocks = 0;
+    if (sh != 1 || sw != 1 || Cin % CCH != 0 || Cout % 16 != 0 || encode_fn() == nullptr) return false;
     const uint64_t nchunks = kh * kw * (Cin / CCH);
-    // the weights of all taps stay in shared memory beside a ring of at least 2 of the smallest stages (whether the
-    // stages of a given image width fit is decided per call)
-    return nchunks < (1u << 16) && direct_smem(2, stage_bytes_for(8, kh), (uint32_t)nchunks, (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET &&
-           encode_fn() != nullptr;
+    if (nchunks >= (1u << 16)) return false;
+    // Output channels in blocks of at most 112 (+ 16 extra weight rows = the MMA's 128 columns per accumulator), as equal as
+    // multiples of 16 allow; a block's weights of all taps stay in shared memory beside a ring of at least 2 of the
+    // smallest stages (whether the stages of a given image width fit is decided per call).
+    for (uint32_t blocks = (uint32_t)((Cout + 111) / 112); blocks <= (uint32_t)ConvDirectPlan::MAX_BLOCKS; blocks++) {
+        const uint32_t nb = (uint32_t)((Cout / 16 + blocks - 1) / blocks) * 16;
+        if (direct_smem(2, stage_bytes_for(8, kh), (uint32_t)nchunks, nb + EXTRA) > SMEM_BUDGET) continue;
+        uint32_t c0 = 0;
+        plan->blocks = 0;
+        while (c0 < Cout) {
+            const uint32_t n = Cout - c0 < nb ? (uint32_t)(Cout - c0) : nb;
+            plan->cout0[plan->blocks] = c0;
+            plan->nb[plan->blocks] = n;
+            plan->blocks++;
+            c0 += n;
+        }
+        return true;
+    }
+    return false;
 }
 
-size_t conv_direct_weight_bytes(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw) { return (Cout + EXTRA) * Cin * kh * kw; }
-
-cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, TcOperandMap *map, uint64_t Cin, uint64_t Cout, uint64_t kh,
-                                        uint64_t kw, cudaStream_t stream)
+size_t conv_direct_weight_bytes(const ConvDirectPlan &plan, uint64_t Cin, uint64_t kh, uint64_t kw)
 {
-    reorder_weights_kernel<<<256, 256, 0, stream>>>(w, wr, (uint32_t)Cout, (uint32_t)Cin, (uint32_t)kh, (uint32_t)kw);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    count_launch();
-    const uint64_t K = Cin * kh * kw, Npad = Cout + EXTRA;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Npad};
-    cuuint64_t strides[1] = {(cuuint64_t)K};
-    cuuint32_t box[2] = {(cuuint32_t)CCH, (cuuint32_t)Npad};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode_fn()(reinterpret_cast<CUtensorMap *>(map->opaque), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, wr, dims, strides, box,
-                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    map->base = wr;
-    map->rows = Npad;
-    map->K = K;
-    map->box_rows = (int)Npad;
-    map->box_lines = 0;
+    size_t rows = 0;
+    for (uint32_t i = 0; i < plan.blocks; i++) rows += plan.nb[i] + EXTRA;
+    return rows * Cin * kh * kw;
+}
+
+cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirectPlan *plan, uint64_t Cin, uint64_t kh, uint64_t kw,
+                                        cudaStream_t stream)
+{
+    const uint64_t K = Cin * kh * kw;
+    size_t row0 = 0;
+    for (uint32_t i = 0; i < plan->blocks; i++) {
+        uint8_t *dst = wr + row0 * K;
+        const uint64_t Npad = plan->nb[i] + EXTRA;
+        reorder_weights_kernel<<<256, 256, 0, stream>>>(w + (size_t)plan->cout0[i] * K, dst, plan->nb[i], (uint32_t)Cin, (uint32_t)kh,
+                                                        (uint32_t)kw);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        count_launch();
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Npad};
+        cuuint64_t strides[1] = {(cuuint64_t)K};
+        cuuint32_t box[2] = {(cuuint32_t)CCH, (cuuint32_t)Npad};
+        cuuint32_t estr[2] = {1, 1};
+        TcOperandMap *map = &plan->maps[i];
+        CUresult r = encode_fn()(reinterpret_cast<CUtensorMap *>(map->opaque), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dst, dims, strides,
+                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        map->base = dst;
+        map->rows = Npad;
+        map->K = K;
+        map->box_rows = (int)Npad;
+        map->box_lines = 0;
+        row0 += Npad;
+    }
     return cudaSuccess;
 }
 
-bool conv_direct_shape_ok(uint64_t batches, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W, uint64_t Ho,
-                          uint64_t Wo)
+bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W,
+                          uint64_t Ho, uint64_t Wo)
 {
+    if (plan.blocks == 0) return false;
+    const uint64_t Cout = plan.nb[0];   // the widest block
     if (!(Wo >= 1 && Wo + kw - 1 <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31)))
         return false;
     const uint32_t P = slots_per_row(Wo, kw), sb = stage_bytes_for(P, kh);
@@ -453,7 +486,7 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches,
     return cudaSuccess;
 }
 
-cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
+cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
                                uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
                                const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
 {
@@ -471,12 +504,8 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uin
     g.ph = (uint32_t)ph;
     g.pw = (uint32_t)pw;
     g.cchunks = (uint32_t)(Cin / CCH);
-    g.Cout = (uint32_t)Cout;
-    g.Npad = (uint32_t)Cout + EXTRA;
+    g.CoutTotal = (uint32_t)Cout;
     g.stage_bytes = stage_bytes_for(g.P, kh);
-    g.stages = MAX_STAGES;
-    while (g.stages > 2 && direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;
-    if (direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) return cudaErrorInvalidConfiguration;
     // the input as {channel, x, y, image}; a box is 64 channels of the rpt + kh - 1 input rows a tile touches, P pixels wide
     alignas(64) CUtensorMap mx;
     cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batches};
@@ -487,12 +516,28 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uin
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
-    const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(map_w.opaque);
-    switch (epi.out_mode) {
-        case LTQ_OUT_U8: return launch_direct<0>(mx, mw, g, epi, out, status, sms, stream);
-        case LTQ_OUT_F32: return launch_direct<1>(mx, mw, g, epi, out, status, sms, stream);
-        default: return launch_direct<2>(mx, mw, g, epi, out, status, sms, stream);
+    const size_t esize = epi.out_mode == LTQ_OUT_U8 ? 1 : 4, plane = (size_t)Ho * Wo;
+    // one launch per block of output channels (each reads the input tiles again, out of L2)
+    for (uint32_t i = 0; i < plan.blocks; i++) {
+        g.Cout = plan.nb[i];
+        g.Npad = g.Cout + EXTRA;
+        g.stages = MAX_STAGES;
+        while (g.stages > 2 && direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;
+        if (direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) return cudaErrorInvalidConfiguration;
+        Epilogue e = epi;                       // the block's own channel sums and biases
+        e.bsum = epi.bsum + plan.cout0[i];
+        if (epi.bias) e.bias = epi.bias + plan.cout0[i];
+        void *o = static_cast<uint8_t *>(out) + (size_t)plan.cout0[i] * plane * esize;
+        const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(plan.maps[i].opaque);
+        cudaError_t ce;
+        switch (epi.out_mode) {
+            case LTQ_OUT_U8: ce = launch_direct<0>(mx, mw, g, e, o, status, sms, stream); break;
+            case LTQ_OUT_F32: ce = launch_direct<1>(mx, mw, g, e, o, status, sms, stream); break;
+            default: ce = launch_direct<2>(mx, mw, g, e, o, status, sms, stream);
+        }
+        if (ce != cudaSuccess) return ce;
     }
+    return cudaSuccess;
 }
 
 }  // namespace ltq

@@ -5,23 +5,33 @@
 
 namespace ltq {
 
-// Static eligibility (known when the layer is created): stride 1, input channels a multiple of 64, output channels a
-// multiple of 16 and at most 112, and the reordered weights of all kernel taps fit in shared memory beside the ring.
-bool conv_direct_weights_ok(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw);
-// Bytes of the reordered weight buffer: (Cout + 16) rows of Cin * kh * kw.
-size_t conv_direct_weight_bytes(uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw);
-// Reorders w [Cout][Cin][kh][kw] into wr [Cout + 16][kh][kw][Cin] (the extra rows: ones, then zeros) and encodes its map.
-cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, TcOperandMap *map, uint64_t Cin, uint64_t Cout, uint64_t kh,
-                                        uint64_t kw, cudaStream_t stream);
+// The layer's output channels in blocks of at most 112 (one launch each), with the tensor map of every block's reordered
+// weights.
+struct ConvDirectPlan {
+    static constexpr int MAX_BLOCKS = 8;
+    uint32_t blocks = 0;
+    uint32_t cout0[MAX_BLOCKS] = {0}, nb[MAX_BLOCKS] = {0};
+    TcOperandMap maps[MAX_BLOCKS];
+};
+// Static eligibility (known when the layer is created) and the block split: stride 1, input channels a multiple of 64,
+// output channels a multiple of 16 (at most 8 blocks), and a block's reordered weights of all kernel taps fit in shared
+// memory beside the ring.  plan->blocks == 0 and false otherwise.
+bool conv_direct_plan(ConvDirectPlan *plan, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw);
+// Bytes of the reordered weight buffer: per block (channels + 16) rows of Cin * kh * kw.
+size_t conv_direct_weight_bytes(const ConvDirectPlan &plan, uint64_t Cin, uint64_t kh, uint64_t kw);
+// Reorders w [Cout][Cin][kh][kw] block by block into wr [channels + 16][kh][kw][Cin] (the extra rows: ones, then zeros) and
+// encodes the blocks' maps.
+cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirectPlan *plan, uint64_t Cin, uint64_t kh, uint64_t kw,
+                                        cudaStream_t stream);
 // Per-call eligibility: an output row and the kernel's overhang fit the 128 rows of one tile, and a ring of the tile's
 // input regions fits beside the weights.
-bool conv_direct_shape_ok(uint64_t batches, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W, uint64_t Ho,
-                          uint64_t Wo);
+bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W,
+                          uint64_t Ho, uint64_t Wo);
 // x [B][C][H][W] -> xt [B][H][W][C].
 cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream);
 // out [B][Cout][Ho][Wo] from the transposed input.  `epi`: A = input (patch sums come from the kernel itself: asum
 // unused), B = weights (bsum = their sums per output channel, bias per output channel or nullptr).
-cudaError_t launch_conv_direct(const uint8_t *xt, const TcOperandMap &map_w, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
+cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
                                uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
                                const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream);
 

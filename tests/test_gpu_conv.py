@@ -83,6 +83,8 @@ def test_conv_matches_oracle(cuda, oracle, shape):
     (5, 64, 7, 7, 16, 1, 1, 0, 0),         # 1 x 1 kernel
     (2, 64, 30, 30, 32, 5, 5, 2, 2),       # 25 taps (77 KB of reordered weights resident)
     (1, 64, 5, 128, 16, 3, 3, 1, 0),       # Wo = 126: one output row per tile of 128 slots; padding in y only
+    (2, 64, 14, 14, 256, 3, 3, 1, 1),      # 256 output channels: three launches (96 + 96 + 64 channels)
+    (1, 128, 10, 12, 128, 3, 3, 1, 1),     # 128 -> 128 channels: two channel chunks, two launches of 64 channels
 ])
 @pytest.mark.parametrize("mode", ["u8", "f32", "i32"])
 def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
