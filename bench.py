@@ -909,6 +909,18 @@ def run_conv(args):
     launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
     kernel = ltq.last_kernel()
 
+    # the same layer inside a channels-last chain (input and output [B, H, W, C]: no transposition pass)
+    xs_cl = [x.permute(0, 2, 3, 1).contiguous() for x in xs]
+    outs_cl = [torch.empty((B, H, W, Cout), dtype=torch.uint8, device=dev) for _ in range(sets)]
+    cl = ltq.FLAG_RELU | ltq.FLAG_NHWC_IN | ltq.FLAG_NHWC_OUT
+
+    def step_cl(i):
+        convs[i % sets].forward(xs_cl[i % sets], ltq.OUT_U8, cl, out=outs_cl[i % sets])
+    for i in range(sets):
+        step_cl(i)
+    ms_cl = h.timed(step_cl, args.steps, 3, graph=not args.no_graph)
+    same = bool(torch.equal(outs_cl[0].permute(0, 3, 1, 2), convs[0].forward(xs[0], ltq.OUT_U8, ltq.FLAG_RELU)))
+
     # the same layer through the patch buffer (the form every geometry can take), for comparison
     def step_patches(i):
         convs[i % sets].forward(xs[i % sets], ltq.OUT_U8, ltq.FLAG_RELU | ltq.FLAG_FORCE_TC, out=outs[i % sets])
@@ -925,6 +937,8 @@ def run_conv(args):
            "timing": "CUDA graph replay" if not args.no_graph else "eager launches"}
     h.finish(base_line(h, args, ops / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
                        samples_per_s=B * world / (ms_step * 1e-3), gpu_launches=int(launches), kernel=kernel,
+                       channels_last={"ms": ms_cl, "equals_nchw_result": same,
+                                      "step": "the kernel alone: input and output [B, H, W, C] (LTQ_FLAG_NHWC_IN | LTQ_FLAG_NHWC_OUT)"},
                        through_patch_buffer={"ms": ms_patches, "kernel": kernel_patches,
                                              "step": "patch gather of the batch + patch sums + one GEMM over all images"},
                        clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))

@@ -65,6 +65,8 @@ typedef enum ltq_out_mode {
 #define LTQ_FLAG_FORCE_TC_SINGLE 0x1000u/* with the tcgen05 path: the single-CTA kernel */
 #define LTQ_FLAG_FORCE_SKINNY 0x400u/* weight-streaming kernel (needs M <= 16, K % 128 == 0) */
 #define LTQ_FLAG_MULTICAST_DEST 0x2000u /* ltq_layer_forward_scatter only: dests[0] is an NVLink multicast address */
+#define LTQ_FLAG_NHWC_IN 0x4000u   /* ltq_conv2d_forward only: x_dev is [batches, height, width, channels] */
+#define LTQ_FLAG_NHWC_OUT 0x8000u  /* ltq_conv2d_forward only: out_dev is [batches, height_out, width_out, channels_out] */
 
 int ltq_version(void);
 const char *ltq_last_error(void);
@@ -365,7 +367,13 @@ int ltq_conv2d_output_size(const ltq_conv2d *conv, uint64_t height_in, uint64_t 
  * Bias: the reference adds bias[j] with j the output POSITION (math_fns.cpp:1469-1472) although the tensor holds
  * channels_out values; that is reproduced as long as Ho*Wo <= channels_out and refused (LTQ_ERR_UNSUPPORTED) beyond,
  * where the reference reads past the tensor.  LTQ_FLAG_BIAS_PER_CHANNEL adds bias[c] per output channel instead.
- * LTQ_FLAG_RELU / LTQ_FLAG_SATURATE / LTQ_FLAG_FORCE_* act as in ltq_layer_forward. */
+ * LTQ_FLAG_RELU / LTQ_FLAG_SATURATE / LTQ_FLAG_FORCE_* act as in ltq_layer_forward.
+ * Layout, additive: the reference knows NCHW only.  Layers with stride 1, a multiple of 64 input channels and a multiple
+ * of 16 output channels are computed from a channels-last copy of the input; LTQ_FLAG_NHWC_IN hands that layout in
+ * directly (no transposition pass; x_dev 16-byte aligned) and LTQ_FLAG_NHWC_OUT writes it (out_dev 16-byte aligned), so
+ * that a chain of such layers never leaves it.  The values are the same, only their place in memory differs.  For
+ * any other geometry, a forced kernel or the reference's position-indexed bias the two flags give
+ * LTQ_ERR_UNSUPPORTED. */
 int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches, uint64_t height_in, uint64_t width_in,
                        int out_mode, unsigned flags, void *out_dev, void *stream);
 

@@ -719,16 +719,27 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
 
     // Without a patch buffer where the geometry allows (and no kernel is forced, and the bias is per channel or absent):
     // transpose the input to NHWC, then one kernel for the whole batch.
-    if (conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
-        (per_channel || !conv->bias) &&
-        conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, height_in, width_in, Ho, Wo)) {
-        rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, batches * conv->Cin * height_in * width_in, st, "the NHWC copy of the input");
-        if (rc != LTQ_OK) return rc;
-        LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));
+    const bool nhwc_in = (flags & LTQ_FLAG_NHWC_IN) != 0, nhwc_out = (flags & LTQ_FLAG_NHWC_OUT) != 0;
+    const bool direct = conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
+                        (per_channel || !conv->bias) &&
+                        conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, height_in, width_in, Ho, Wo);
+    LTQ_REQUIRE(direct || !(nhwc_in || nhwc_out), LTQ_ERR_UNSUPPORTED,
+                "channels-last input / output is only available for the layers computed without a patch buffer (stride 1, "
+                "input channels a multiple of 64, output channels a multiple of 16, no forced kernel, bias absent or per channel)");
+    LTQ_REQUIRE(!nhwc_in || ((uintptr_t)x_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last input must be 16-byte aligned");
+    LTQ_REQUIRE(!nhwc_out || ((uintptr_t)out_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last output must be 16-byte aligned");
+    if (direct) {
+        const uint8_t *x_cl = x_dev;
+        if (!nhwc_in) {
+            rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, batches * conv->Cin * height_in * width_in, st, "the NHWC copy of the input");
+            if (rc != LTQ_OK) return rc;
+            LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));
+            x_cl = conv->x_nhwc;
+        }
         // positions are the rows here: A = input (its patch sums come out of the kernel), B = weights
         Epilogue epi = make_epilogue(conv->wsum, nullptr, conv->bias, conv->qp_in, conv->qp_wt, conv->qp_out, K, out_mode, flags);
-        LTQ_CUDA_TRY(launch_conv_direct(conv->x_nhwc, conv->direct, batches, conv->Cin, height_in, width_in, conv->Cout,
-                                        conv->kh, conv->kw, conv->ph, conv->pw, Ho, Wo, epi, out_dev, conv->dev->status,
+        LTQ_CUDA_TRY(launch_conv_direct(x_cl, conv->direct, batches, conv->Cin, height_in, width_in, conv->Cout, conv->kh,
+                                        conv->kw, conv->ph, conv->pw, Ho, Wo, epi, out_dev, nhwc_out, conv->dev->status,
                                         conv->dev->sms, st));
         return LTQ_OK;
     }

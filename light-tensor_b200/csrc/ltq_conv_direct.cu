@@ -51,6 +51,7 @@ struct DirectGeom {
     uint32_t kh, kw, ph, pw, cchunks;     // kernel size, padding, Cin / 64
     uint32_t Cout, Npad, CoutTotal;       // output channels of this launch, Cout + 16, output channels of the layer
     uint32_t stages, stage_bytes;         // ring depth; (rpt + kh - 1) * P * 64 rounded up to 1 KB
+    uint32_t nhwc_out;                    // output as [image][row][column][channel] instead of [image][channel][row][column]
 };
 
 // Shared-memory matrix descriptor for a K-major operand tile with rows of 64 bytes laid out by TMA with the 64-byte
@@ -283,7 +284,8 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 if (cb < ce) tmem_ld16(taddr + cb, vn);
                 tmem_ld_wait();
                 const uint32_t rt = c.neg_zB * v[0] + c.bc;
-                OutT *d = o + (size_t)b * g.CoutTotal * plane + (size_t)(ho0 + hh) * g.Wo + wcol + (size_t)cb * plane;
+                OutT *d = g.nhwc_out ? o + (((size_t)b * g.Ho + ho0 + hh) * g.Wo + wcol) * g.CoutTotal + cb
+                                     : o + (size_t)b * g.CoutTotal * plane + (size_t)(ho0 + hh) * g.Wo + wcol + (size_t)cb * plane;
 #pragma unroll 1
                 for (uint32_t ch = cb; ch < ce; ch += 16) {
 #pragma unroll
@@ -291,7 +293,17 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     if (ch + 16 < ce) tmem_ld16(taddr + ch + 16, vn);   // the next chunk travels while this one is converted
                     uint32_t res[16];
                     epilogue_convert<OUT, 16>(v, rt, s_col + ch, c, relu, sat, res);
-                    if (valid) {
+                    if (valid && g.nhwc_out) {
+                        // channels-last: the 16 channels of the chunk are consecutive bytes / words of this position
+                        uint4 *d4 = reinterpret_cast<uint4 *>(d);
+                        if (OUT == 0) {
+                            d4[0] = make_uint4(res[0], res[1], res[2], res[3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) d4[j] = make_uint4(res[4 * j], res[4 * j + 1], res[4 * j + 2], res[4 * j + 3]);
+                        }
+                        d += 16;
+                    } else if (valid) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
                             if (OUT == 0) *d = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
@@ -488,9 +500,10 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches,
 
 cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
                                uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
-                               const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream)
+                               const Epilogue &epi, void *out, bool nhwc_out, uint32_t *status, int sms, cudaStream_t stream)
 {
     DirectGeom g;
+    g.nhwc_out = nhwc_out ? 1u : 0u;
     g.B = (uint32_t)batches;
     g.Ho = (uint32_t)Ho;
     g.Wo = (uint32_t)Wo;
@@ -527,7 +540,7 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
         Epilogue e = epi;                       // the block's own channel sums and biases
         e.bsum = epi.bsum + plan.cout0[i];
         if (epi.bias) e.bias = epi.bias + plan.cout0[i];
-        void *o = static_cast<uint8_t *>(out) + (size_t)plan.cout0[i] * plane * esize;
+        void *o = static_cast<uint8_t *>(out) + (size_t)plan.cout0[i] * (nhwc_out ? 1 : plane) * esize;
         const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(plan.maps[i].opaque);
         cudaError_t ce;
         switch (epi.out_mode) {

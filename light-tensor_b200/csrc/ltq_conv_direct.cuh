@@ -29,10 +29,10 @@ bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t
                           uint64_t Ho, uint64_t Wo);
 // x [B][C][H][W] -> xt [B][H][W][C].
 cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream);
-// out [B][Cout][Ho][Wo] from the transposed input.  `epi`: A = input (patch sums come from the kernel itself: asum
+// out [B][Cout][Ho][Wo] (or [B][Ho][Wo][Cout] with nhwc_out, 16-byte aligned) from the transposed input.  `epi`: A = input (patch sums come from the kernel itself: asum
 // unused), B = weights (bsum = their sums per output channel, bias per output channel or nullptr).
 cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
                                uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
-                               const Epilogue &epi, void *out, uint32_t *status, int sms, cudaStream_t stream);
+                               const Epilogue &epi, void *out, bool nhwc_out, uint32_t *status, int sms, cudaStream_t stream);
 
 }  // namespace ltq

@@ -26,6 +26,7 @@ FLAG_RELU, FLAG_SATURATE, FLAG_BIAS_PER_CHANNEL = 1, 2, 4
 FLAG_FORCE_SIMT, FLAG_FORCE_TC, FLAG_FORCE_SKINNY = 0x100, 0x200, 0x400
 FLAG_FORCE_TC_PAIR, FLAG_FORCE_TC_SINGLE = 0x800, 0x1000
 FLAG_MULTICAST_DEST = 0x2000
+FLAG_NHWC_IN, FLAG_NHWC_OUT = 0x4000, 0x8000
 
 _u64, _vp, _int = C.c_uint64, C.c_void_p, C.c_int
 _qp = C.POINTER(QParams)

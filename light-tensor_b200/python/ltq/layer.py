@@ -4,7 +4,7 @@ import ctypes as C
 
 import torch
 
-from ._binding import (OUT_F32, OUT_I32, OUT_U8, FLAG_BIAS_PER_CHANNEL, FLAG_RELU, FLAG_SATURATE, QParams, check,
+from ._binding import (OUT_F32, OUT_I32, OUT_U8, FLAG_BIAS_PER_CHANNEL, FLAG_NHWC_IN, FLAG_NHWC_OUT, FLAG_RELU, FLAG_SATURATE, QParams, check,
                        lib)
 
 _OUT_DTYPE = {OUT_U8: torch.uint8, OUT_F32: torch.float32, OUT_I32: torch.int32}
@@ -272,12 +272,18 @@ class ConvHandle:
         return ho.value, wo.value
 
     def forward(self, x, out_mode=OUT_U8, flags=0, out=None):
-        """x: uint8 CUDA NCHW (contiguous).  Returns [B, Cout, Ho, Wo] in the dtype of out_mode."""
-        assert x.is_cuda and x.dtype == torch.uint8 and x.is_contiguous() and x.dim() == 4 and x.shape[1] == self.Cin
-        B, _, H, W = x.shape
+        """x: uint8 CUDA NCHW (contiguous), or [B, H, W, Cin] with FLAG_NHWC_IN.  Returns [B, Cout, Ho, Wo] - with
+        FLAG_NHWC_OUT [B, Ho, Wo, Cout] - in the dtype of out_mode."""
+        assert x.is_cuda and x.dtype == torch.uint8 and x.is_contiguous() and x.dim() == 4
+        if flags & FLAG_NHWC_IN:
+            B, H, W, C = x.shape
+        else:
+            B, C, H, W = x.shape
+        assert C == self.Cin
         ho, wo = self.output_size(H, W)
         if out is None:
-            out = torch.empty((B, self.Cout, ho, wo), dtype=_OUT_DTYPE[out_mode], device=x.device)
+            shape = (B, ho, wo, self.Cout) if flags & FLAG_NHWC_OUT else (B, self.Cout, ho, wo)
+            out = torch.empty(shape, dtype=_OUT_DTYPE[out_mode], device=x.device)
         check(lib().ltq_conv2d_forward(self._h, x.data_ptr(), B, H, W, out_mode, flags, out.data_ptr(), self._stream()))
         return out
 

@@ -115,6 +115,39 @@ def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
     assert ltq.lib().ltq_device_check(0, None) == 0
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 12, 20, 32, 3, 3, 1, 1), (1, 128, 10, 12, 128, 3, 3, 1, 1), (2, 64, 14, 14, 256, 1, 1, 0, 0)])
+@pytest.mark.parametrize("mode", ["u8", "f32", "i32"])
+def test_conv_channels_last_in_and_out(cuda, shape, mode):
+    """LTQ_FLAG_NHWC_IN / LTQ_FLAG_NHWC_OUT: the same values as the NCHW call, only placed channels-last, in every
+    combination of the two flags; refused where the layer is not computed from a channels-last copy."""
+    import ltq
+    B, Cin, H, W, Cout, kh, kw, ph, pw = shape
+    rng = np.random.default_rng(sum(shape))
+    x = cuda.from_numpy(rng.integers(0, 256, (B, Cin, H, W), dtype=np.uint8)).cuda()
+    w = cuda.from_numpy(rng.integers(0, 256, (Cout, Cin * kh * kw), dtype=np.uint8)).cuda()
+    bias = cuda.from_numpy(rng.integers(-30000, 30000, Cout, dtype=np.int32)).cuda()
+    h = ltq.ConvHandle(0, Cin, Cout, kh, kw, ph, pw, 1, 1)
+    h.set_weights(w, bias)
+    h.set_qparams(ltq.QParams(0.02, 128), ltq.QParams(0.005, 127), ltq.QParams(4.0, 3))
+    out_mode = {"u8": ltq.OUT_U8, "f32": ltq.OUT_F32, "i32": ltq.OUT_I32}[mode]
+    base = ltq.FLAG_BIAS_PER_CHANNEL | ltq.FLAG_RELU
+    ref = h.forward(x, out_mode, base)
+    x_cl = x.permute(0, 2, 3, 1).contiguous()
+    for fin, fout in ((True, False), (False, True), (True, True)):
+        flags = base | (ltq.FLAG_NHWC_IN if fin else 0) | (ltq.FLAG_NHWC_OUT if fout else 0)
+        y = h.forward(x_cl if fin else x, out_mode, flags)
+        assert ltq.last_kernel().startswith("conv_direct_kernel<")
+        want = ref.permute(0, 2, 3, 1).contiguous() if fout else ref
+        assert cuda.equal(y, want), (fin, fout)
+    with pytest.raises(ltq.LtqError, match="channels-last"):
+        h.forward(x, out_mode, base | ltq.FLAG_NHWC_OUT | ltq.FLAG_FORCE_SIMT)
+    odd = ltq.ConvHandle(0, 3, 16, 3, 3, 1, 1, 1, 1)           # 3 input channels: patch-buffer path only
+    odd.set_weights(cuda.zeros((16, 27), dtype=cuda.uint8, device="cuda"))
+    with pytest.raises(ltq.LtqError, match="channels-last"):
+        odd.forward(cuda.zeros((1, 8, 8, 3), dtype=cuda.uint8, device="cuda"), out_mode, ltq.FLAG_NHWC_IN)
+    assert ltq.lib().ltq_device_check(0, None) == 0
+
+
 def test_reference_bias_indexing_is_refused_beyond_its_tensor(cuda):
     import ltq
     h = ltq.ConvHandle(0, 2, 4, 3, 3)
