@@ -657,8 +657,18 @@ def run_sections(h, args, pk):
             return d
         return run
 
+    def conv():
+        r = measure_conv(h, args)
+        return {"config": conv_workload_name(r) + " (Conv2d_q, the next layer type on the path; per GPU)",
+                "us_per_batch": r["ms_step"] * 1e3, "tops": r["ops"] / (r["ms_step"] * 1e-3) / 1e12, "kernel": r["kernel"],
+                "channels_last_us": r["channels_last"]["ms"] * 1e3,
+                "channels_last_equals_nchw_result": r["channels_last"]["equals_nchw_result"],
+                "through_patch_buffer_us": r["through_patch_buffer"]["ms"] * 1e3,
+                "through_patch_buffer_kernel": r["through_patch_buffer"]["kernel"]}
+
     guarded("skinny", skinny)
     guarded("mlp_mnist", mnist)
+    guarded("conv2d_q", conv)
     guarded("mlp_block_rows", block("rows"))
     if h.world > 1:
         guarded("mlp_block_cols", block("cols"))
@@ -879,13 +889,13 @@ def run_mlp_mnist(args):
                        clocks=r["clocks"], kernels=r["kernels"], e2e=None, roofline=None, cpu_baseline=None))
 
 
-def run_conv(args):
+def measure_conv(h, args, sample_clocks=False):
     """Conv2d_q on a ResNet-like layer: batch 32, 64 -> 64 channels, 56 x 56, 3 x 3, pad 1 (not one of the configs the
     metric is quoted on; it gives the convolution path a measured number).  A step = one Conv2d_q::forward on uint8
-    NCHW input; this geometry takes the kernel without a patch buffer, and the patch-buffer form is timed beside it."""
+    NCHW input; this geometry takes the kernel without a patch buffer.  Timed beside it: the same layer inside a
+    channels-last chain, and through the patch buffer."""
     import ltq
-    h = Harness(args)
-    torch, dev, world = h.torch, h.dev, h.world
+    torch, dev = h.torch, h.dev
     B, Cin, H, W, Cout, k = 32, 64, 56, 56, 64, 3
     sets = 4                                          # 4 x (6.4 MB input + 58 MB patches + 6.4 MB output)
     g = torch.Generator(device=dev).manual_seed(4321 + h.rank)
@@ -902,10 +912,10 @@ def run_conv(args):
     def step(i):
         convs[i % sets].forward(xs[i % sets], ltq.OUT_U8, ltq.FLAG_RELU, out=outs[i % sets])
 
-    for i in range(sets):      # every handle allocates its patch buffer on first use, which must not happen in a capture
+    for i in range(sets):      # every handle allocates its buffers on first use, which must not happen in a capture
         step(i)
     launches0 = ltq.kernel_launches()
-    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
+    ms_step = h.timed(step, args.steps, args.warmup, graph=not args.no_graph, sample_clocks=sample_clocks)
     launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
     kernel = ltq.last_kernel()
 
@@ -928,19 +938,31 @@ def run_conv(args):
         step_patches(i)
     ms_patches = h.timed(step_patches, args.steps, 3, graph=not args.no_graph)
     kernel_patches = ltq.last_kernel()
-    ops = 2.0 * B * H * W * Cout * Cin * k * k
-    cfg = {"workload": f"conv2d_q: batch {B}, {Cin}->{Cout} channels, {H}x{W}, {k}x{k} kernel, pad 1, uint8 NCHW in/out, "
-                       "fused ReLU", "sharding": "independent replicas, one batch stream per GPU",
-           "l2": f"rotating {sets} distinct input / patch-buffer / output sets",
+    return dict(B=B, Cin=Cin, H=H, W=W, Cout=Cout, k=k, sets=sets, ms_step=ms_step, launches=int(launches), kernel=kernel,
+                ops=2.0 * B * H * W * Cout * Cin * k * k,
+                channels_last={"ms": ms_cl, "equals_nchw_result": same,
+                               "step": "the kernel alone: input and output [B, H, W, C] (LTQ_FLAG_NHWC_IN | LTQ_FLAG_NHWC_OUT)"},
+                through_patch_buffer={"ms": ms_patches, "kernel": kernel_patches,
+                                      "step": "patch gather of the batch + patch sums + one GEMM over all images"})
+
+
+def conv_workload_name(r):
+    return (f"conv2d_q: batch {r['B']}, {r['Cin']}->{r['Cout']} channels, {r['H']}x{r['W']}, {r['k']}x{r['k']} kernel, pad 1, "
+            "uint8 NCHW in/out, fused ReLU")
+
+
+def run_conv(args):
+    h = Harness(args)
+    r = measure_conv(h, args, sample_clocks=True)
+    ms_step, world = r["ms_step"], h.world
+    cfg = {"workload": conv_workload_name(r), "sharding": "independent replicas, one batch stream per GPU",
+           "l2": f"rotating {r['sets']} distinct input / output sets",
            "step": "one Conv2d_q forward of the batch: NCHW -> NHWC transposition + the kernel that reads its patch slices "
                    "straight from the image (no patch buffer)",
            "timing": "CUDA graph replay" if not args.no_graph else "eager launches"}
-    h.finish(base_line(h, args, ops / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
-                       samples_per_s=B * world / (ms_step * 1e-3), gpu_launches=int(launches), kernel=kernel,
-                       channels_last={"ms": ms_cl, "equals_nchw_result": same,
-                                      "step": "the kernel alone: input and output [B, H, W, C] (LTQ_FLAG_NHWC_IN | LTQ_FLAG_NHWC_OUT)"},
-                       through_patch_buffer={"ms": ms_patches, "kernel": kernel_patches,
-                                             "step": "patch gather of the batch + patch sums + one GEMM over all images"},
+    h.finish(base_line(h, args, r["ops"] / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
+                       samples_per_s=r["B"] * world / (ms_step * 1e-3), gpu_launches=r["launches"], kernel=r["kernel"],
+                       channels_last=r["channels_last"], through_patch_buffer=r["through_patch_buffer"],
                        clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))
 
 
