@@ -346,6 +346,48 @@ Tensor FullyConnected_q::forward(Tensor &input)
     return result;
 }
 
+// ---- FusedChain_q -----------------------------------------------------------------------------------------------------
+FusedChain_q::FusedChain_q(const std::vector<FullyConnected_q *> &layers) : layers_(layers)
+{
+    std::vector<ltq_layer *> hs;
+    for (FullyConnected_q *l : layers_) {
+        if (!l || !l->handle_) LTEN_ERR("FusedChain_q: every layer must be on the GPU (call to(GPU, index) first)");
+        hs.push_back(l->handle_);
+    }
+    LTQ_CALL(ltq_mlp_create(&handle_, hs.data(), (int)hs.size()));
+}
+
+FusedChain_q::~FusedChain_q() { ltq_mlp_destroy(handle_); }
+
+Tensor FusedChain_q::forward(Tensor &input)
+{
+    const int ndims = input.get_ndims();
+    if (ndims < 3) LTEN_ERR("FullyConnected_q requires tensors with at least 3 dimensions");
+    FullyConnected_q *first = layers_.front(), *last = layers_.back();
+    if (input.get_device() != GPU || input.get_data_type() != FLOAT32 ||
+        input.get_device_index() != first->weight_ptr_->get_device_index())
+        LTEN_ERR("FusedChain_q: FLOAT32 input on the layers' GPU expected");
+    uint64_t dims[MAX_DIMS];
+    memcpy(dims, input.get_sizes(), sizeof(uint64_t) * ndims);
+    if (dims[ndims - 1] != first->input_features_) LTEN_ERR("Last dimension must be equal to the number of input features");
+    dims[ndims - 1] = last->output_features_;
+    uint64_t rows = 1;
+    for (int d = 0; d < ndims - 1; d++) rows *= dims[d];
+    TensorOps options;
+    options.data_type = last->out_mode_ == LTQ_OUT_U8 ? UINT8 : (last->out_mode_ == LTQ_OUT_F32 ? FLOAT32 : INT32);
+    options.device_type = GPU;
+    options.device_index = input.get_device_index();
+    Tensor result = AllocateTensor(dims, ndims, &options);
+    std::vector<unsigned> flags;
+    for (FullyConnected_q *l : layers_) {   // the parameters may have been set after the chain was built
+        LTQ_CALL(ltq_layer_set_qparams(l->handle_, &l->qparams_in_, &l->qparams_wt_, &l->qparams_out_));
+        flags.push_back(l->flags_);
+    }
+    LTQ_CALL(ltq_mlp_forward(handle_, static_cast<const float *>(input.get_data_ptr()), rows, flags.data(), last->out_mode_,
+                             result.get_data_ptr(), stream_));
+    return result;
+}
+
 // ---- DeviceGroup -------------------------------------------------------------------------------------------------------
 DeviceGroup::DeviceGroup(const std::vector<int> &device_indices) : devices_(device_indices)
 {

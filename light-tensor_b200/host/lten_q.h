@@ -152,6 +152,7 @@ public:
 
 private:
     friend class DeviceGroup;
+    friend class FusedChain_q;
     // Result (and, for uint8 results, row-sum) tensors of the shape asked for: the ones handed out by the previous
     // forward when the caller has dropped them by now, fresh ones otherwise.
     Tensor take_output(const uint64_t *dims, int ndims, const TensorOps &ops, Tensor *cache);
@@ -164,6 +165,28 @@ private:
     unsigned flags_ = 0;
     void *stream_ = nullptr;
     Tensor cached_result_, cached_sums_;
+};
+
+// A chain of 2-4 FullyConnected_q layers run as ONE kernel launch per batch, input quantisation included (additive: the
+// reference's QNet::forward, tests/nn_tests.cpp:630-640, quantises the input and calls layer after layer, which for a
+// small network is all launch latency).  The layers stay owned by the caller, must be on the same GPU, and keep their
+// parameters and output settings: layer i's ReLU / saturate flags apply to it, the LAST layer's output mode is the
+// chain's.  forward() takes the FLOAT32 GPU input {.., rows, in_features of the first layer} and returns what the last
+// layer's forward() would return after Quantize(input) and the layers in turn, bit for bit.  Throws where the chain
+// does not fit one cluster's shared memory (then run the layers one by one).
+class FusedChain_q {
+public:
+    explicit FusedChain_q(const std::vector<FullyConnected_q *> &layers);
+    ~FusedChain_q();
+    FusedChain_q(const FusedChain_q &) = delete;
+    FusedChain_q &operator=(const FusedChain_q &) = delete;
+    Tensor forward(Tensor &input);
+    void set_stream(void *stream) { stream_ = stream; }
+
+private:
+    std::vector<FullyConnected_q *> layers_;
+    ltq_mlp *handle_ = nullptr;
+    void *stream_ = nullptr;
 };
 
 // One host thread driving a quantized layer over several GPUs (additive: l-ten has no multi-device code on this path,

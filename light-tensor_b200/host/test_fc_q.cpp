@@ -234,6 +234,14 @@ int main()
     }
     layers[0]->set_next(nullptr);
     layers[1]->set_next(nullptr);
+    {   // the same three layers as one launch: float input in, the last layer's bytes out
+        FusedChain_q chain({layers[0], layers[1], layers[2]});
+        Tensor y = chain.forward(input);
+        CHECK(y.get_ndims() == 3 && y.get_sizes()[1] == (uint64_t)B && y.get_sizes()[2] == (uint64_t)dims[3], "fused chain: output shape");
+        CHECK(download<uint8_t>(y) == h, "fused chain (one launch) equals the layer-by-layer result and the oracle");
+        Tensor y2 = chain.forward(input);
+        CHECK(download<uint8_t>(y2) == h, "fused chain, second call");
+    }
     TensorOps of;
     of.device_type = GPU;
     Tensor output = AllocateTensor({1, (uint64_t)B, 10}, &of);
