@@ -60,7 +60,8 @@ __device__ __forceinline__ uint32_t quant4_u8(float4 x, float scale, float zpf, 
         const float b2 = __fadd_rn(v2, 8388608.f), b3 = __fadd_rn(v3, 8388608.f);
         const float d0 = __fsub_rn(v0, __fadd_rn(b0, -8388608.f)), d1 = __fsub_rn(v1, __fadd_rn(b1, -8388608.f));
         const float d2 = __fsub_rn(v2, __fadd_rn(b2, -8388608.f)), d3 = __fsub_rn(v3, __fadd_rn(b3, -8388608.f));
-        const bool near = fabsf(d0) > 0.4996f || fabsf(d1) > 0.4996f || fabsf(d2) > 0.4996f || fabsf(d3) > 0.4996f;
+        // one comparison on the largest distance (four short-circuited comparisons are four branches)
+        const bool near = fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))) > 0.4996f;
         if (!near) {
             const uint32_t lo = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x0040);  // bytes b0[0], b1[0]
             const uint32_t hi = __byte_perm(__float_as_uint(b2), __float_as_uint(b3), 0x0040);
