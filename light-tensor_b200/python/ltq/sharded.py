@@ -252,8 +252,10 @@ class ColShardedLinear:
             # one destination: the multicast address (this rank's own buffer is behind it too)
             self.layer.forward_scatter(x_q, [buf.mc_ptr], self.N, self.n0, out_mode, flags | FLAG_MULTICAST_DEST)
         else:
-            # this rank's pointer first (the kernel's primary destination), then the peers'
-            ptrs = [buf.ptrs[self.rank]] + [p for r, p in enumerate(buf.ptrs) if r != self.rank]
+            # this rank's pointer first (the kernel's primary destination), then the peers' starting with the next rank:
+            # at any moment the ranks then store to different peers instead of all to the same one
+            world = len(buf.ptrs)
+            ptrs = [buf.ptrs[self.rank]] + [buf.ptrs[(self.rank + k) % world] for k in range(1, world)]
             self.layer.forward_scatter(x_q, ptrs, self.N, self.n0, out_mode, flags)
         self._barrier(x_q.device)
         return buf.local[:M * self.N * self._esize].view(_OUT_DTYPE[out_mode]).view(M, self.N)
