@@ -558,7 +558,7 @@ void Conv2d_q::set_qparams_params(QuantizationParams *qparams, int count)
 void Conv2d_q::set_output(ltq_out_mode mode, bool relu, bool saturate, bool bias_per_channel)
 {
     out_mode_ = mode;
-    flags_ = (relu ? LTQ_FLAG_RELU : 0u) | (saturate ? LTQ_FLAG_SATURATE : 0u) |
+    flags_ = (flags_ & (LTQ_FLAG_NHWC_IN | LTQ_FLAG_NHWC_OUT)) | (relu ? LTQ_FLAG_RELU : 0u) | (saturate ? LTQ_FLAG_SATURATE : 0u) |
              (bias_per_channel ? LTQ_FLAG_BIAS_PER_CHANNEL : 0u);
 }
 
@@ -578,6 +578,12 @@ void Conv2d_q::to(device target_device, int target_device_index)
     }
 }
 
+void Conv2d_q::set_layout(bool channels_last_in, bool channels_last_out)
+{
+    flags_ = (flags_ & ~(LTQ_FLAG_NHWC_IN | LTQ_FLAG_NHWC_OUT)) | (channels_last_in ? LTQ_FLAG_NHWC_IN : 0u) |
+             (channels_last_out ? LTQ_FLAG_NHWC_OUT : 0u);
+}
+
 Tensor Conv2d_q::forward(Tensor &input)
 {
     // the reference's checks, messages and order: l-ten/conv2d.cpp:285-301
@@ -588,16 +594,19 @@ Tensor Conv2d_q::forward(Tensor &input)
     if (input.get_ndims() != 4) LTEN_ERR("Conv2d_q requires tensors with exactly 4 dimensions (NCHW)");
     if (input.get_device() != GPU) LTEN_ERR("Conv2d_q: this build computes on GPU tensors only; call to(GPU, index) first");
     const uint64_t *in = input.get_sizes();
+    const bool cl_in = (flags_ & LTQ_FLAG_NHWC_IN) != 0, cl_out = (flags_ & LTQ_FLAG_NHWC_OUT) != 0;
+    const uint64_t h_in = cl_in ? in[1] : in[2], w_in = cl_in ? in[2] : in[3];
+    if ((cl_in ? in[3] : in[1]) != channels_in_) LTEN_ERR("Conv2d_q: the input's channel count is not the layer's");
     uint64_t ho = 0, wo = 0;
-    LTQ_CALL(ltq_conv2d_output_size(handle_, in[2], in[3], &ho, &wo));
+    LTQ_CALL(ltq_conv2d_output_size(handle_, h_in, w_in, &ho, &wo));
 
     TensorOps options;
     options.data_type = out_mode_ == LTQ_OUT_U8 ? UINT8 : (out_mode_ == LTQ_OUT_F32 ? FLOAT32 : INT32);
     options.device_type = GPU;
     options.device_index = input.get_device_index();
-    Tensor result = AllocateTensor({in[0], channels_out_, ho, wo}, &options);
+    Tensor result = cl_out ? AllocateTensor({in[0], ho, wo, channels_out_}, &options) : AllocateTensor({in[0], channels_out_, ho, wo}, &options);
     LTQ_CALL(ltq_conv2d_set_qparams(handle_, &qparams_in_, &qparams_wt_, &qparams_out_));
-    LTQ_CALL(ltq_conv2d_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), in[0], in[2], in[3], out_mode_,
+    LTQ_CALL(ltq_conv2d_forward(handle_, static_cast<const uint8_t *>(input.get_data_ptr()), in[0], h_in, w_in, out_mode_,
                                 flags_, result.get_data_ptr(), nullptr));
     return result;
 }

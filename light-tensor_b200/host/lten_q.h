@@ -258,6 +258,10 @@ public:
     // Additive.  bias_per_channel adds bias[c] per output channel; the default applies the bias the way the reference's
     // GEMM does, per output position, which it only defines while Ho*Wo <= channels_out.
     void set_output(ltq_out_mode mode, bool relu = false, bool saturate = false, bool bias_per_channel = false);
+    // Additive: channels-last placement ({N, H, W, C}) of the input and / or the output, for chains of layers that are
+    // computed from a channels-last copy anyway (stride 1, input channels a multiple of 64, output channels a multiple
+    // of 16); forward() throws for other layers.  The values are those of the NCHW call.
+    void set_layout(bool channels_last_in, bool channels_last_out);
 
 private:
     uint64_t channels_in_, channels_out_, kernel_h_, kernel_w_, pad_h_, pad_w_, stride_h_, stride_w_;

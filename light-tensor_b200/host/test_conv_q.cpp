@@ -237,6 +237,46 @@ int main()
               g_conv->forward(t);
           }), "image smaller than the kernel rejected");
 
+    // ---- a 64 -> 32 channel 3 x 3 layer (computed without a patch buffer): NCHW against the oracle, then the same layer
+    //      with channels-last input and output, which must hold the same values in the other order ----
+    {
+        const int B2 = 2, C2 = 64, H2 = 9, W2 = 12, O2 = 32;
+        std::vector<uint8_t> x2((size_t)B2 * C2 * H2 * W2), w2((size_t)O2 * C2 * 9);
+        uint32_t seed = 12345;
+        for (auto &v : x2) { seed = seed * 1664525u + 1013904223u; v = (uint8_t)(seed >> 24); }
+        for (auto &v : w2) { seed = seed * 1664525u + 1013904223u; v = (uint8_t)(seed >> 24); }
+        Conv2d_q big(C2, O2, false, 3, 3, 1, 1);
+        big.init();
+        memcpy(big.get_weights()->get_data_ptr(), w2.data(), w2.size());
+        QuantizationParams qi{0.02f, 128}, qw{0.005f, 127}, qo{4.0f, 3};
+        big.set_qparams_in(qi);
+        big.set_qparams_out(qo);
+        big.set_qparams_params(&qw, 1);
+        big.to(GPU, 0);
+        Tensor xin = upload(x2, {(uint64_t)B2, (uint64_t)C2, (uint64_t)H2, (uint64_t)W2}, UINT8);
+        Tensor y = big.forward(xin);
+        std::vector<uint8_t> got = download<uint8_t>(y), want(got.size());
+        oracle_qparams oi{qi.scale, qi.zero_point}, ow{qw.scale, qw.zero_point}, oo{qo.scale, qo.zero_point};
+        CHECK(oracle_conv2d_q(x2.data(), B2, C2, H2, W2, w2.data(), nullptr, 0, O2, 3, 3, 1, 1, 1, 1, &oi, &ow, &oo, want.data()) == 0,
+              "oracle conv");
+        CHECK(got == want, "64-channel Conv2d_q (no patch buffer) vs oracle");
+        std::vector<uint8_t> x_cl(x2.size());
+        for (int b = 0; b < B2; b++)
+            for (int c = 0; c < C2; c++)
+                for (int i = 0; i < H2 * W2; i++) x_cl[((size_t)b * H2 * W2 + i) * C2 + c] = x2[((size_t)b * C2 + c) * H2 * W2 + i];
+        big.set_layout(true, true);
+        Tensor xcl = upload(x_cl, {(uint64_t)B2, (uint64_t)H2, (uint64_t)W2, (uint64_t)C2}, UINT8);
+        Tensor ycl = big.forward(xcl);
+        CHECK(ycl.get_sizes()[1] == (uint64_t)H2 && ycl.get_sizes()[3] == (uint64_t)O2, "channels-last output shape");
+        std::vector<uint8_t> gcl = download<uint8_t>(ycl);
+        bool same = gcl.size() == want.size();
+        for (int b = 0; same && b < B2; b++)
+            for (int o = 0; same && o < O2; o++)
+                for (int i = 0; i < H2 * W2; i++)
+                    if (gcl[((size_t)b * H2 * W2 + i) * O2 + o] != want[((size_t)b * O2 + o) * H2 * W2 + i]) { same = false; break; }
+        CHECK(same, "channels-last in / out holds the NCHW result's values");
+    }
+
     delete conv1;
     delete fc1;
     delete fc2;

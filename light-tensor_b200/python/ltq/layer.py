@@ -374,8 +374,15 @@ class Conv2d_q:
 
     def set_output(self, out_mode=OUT_U8, relu=False, saturate=False, bias_per_channel=False):
         self._out_mode = out_mode
-        self._flags = ((FLAG_RELU if relu else 0) | (FLAG_SATURATE if saturate else 0) |
-                       (FLAG_BIAS_PER_CHANNEL if bias_per_channel else 0))
+        self._flags = ((self._flags & (FLAG_NHWC_IN | FLAG_NHWC_OUT)) | (FLAG_RELU if relu else 0) |
+                       (FLAG_SATURATE if saturate else 0) | (FLAG_BIAS_PER_CHANNEL if bias_per_channel else 0))
+
+    def set_layout(self, channels_last_in=False, channels_last_out=False):
+        """Additive: channels-last placement ([N, H, W, C]) of the input and / or the output, for chains of layers that
+        are computed from a channels-last copy anyway (stride 1, input channels a multiple of 64, output channels a
+        multiple of 16); forward raises for other layers.  The values are those of the NCHW call."""
+        self._flags = ((self._flags & ~(FLAG_NHWC_IN | FLAG_NHWC_OUT)) | (FLAG_NHWC_IN if channels_last_in else 0) |
+                       (FLAG_NHWC_OUT if channels_last_out else 0))
 
     def _push_qparams(self):
         if self._handle is not None:

@@ -139,6 +139,19 @@ def test_conv_channels_last_in_and_out(cuda, shape, mode):
         assert ltq.last_kernel().startswith("conv_direct_kernel<")
         want = ref.permute(0, 2, 3, 1).contiguous() if fout else ref
         assert cuda.equal(y, want), (fin, fout)
+    if mode == "u8":
+        # the same through the layer class with the reference's surface
+        conv = ltq.Conv2d_q(Cin, Cout, True, kh, kw, ph, pw)
+        conv.init()
+        conv.get_all_weights()[0].copy_(w.view(Cout, Cin, kh * kw).cpu())
+        conv.get_all_weights()[1].copy_(bias.view(1, Cout, 1, 1).cpu())
+        conv.set_qparams_in(ltq.QParams(0.02, 128))
+        conv.set_qparams_out(ltq.QParams(4.0, 3))
+        conv.set_qparams_params([ltq.QParams(0.005, 127)], 1)
+        conv.set_output(ltq.OUT_U8, relu=True, bias_per_channel=True)
+        conv.to("cuda", 0)
+        conv.set_layout(True, True)
+        assert cuda.equal(conv.forward(x_cl), ref.permute(0, 2, 3, 1).contiguous())
     with pytest.raises(ltq.LtqError, match="channels-last"):
         h.forward(x, out_mode, base | ltq.FLAG_NHWC_OUT | ltq.FLAG_FORCE_SIMT)
     odd = ltq.ConvHandle(0, 3, 16, 3, 3, 1, 1, 1, 1)           # 3 input channels: patch-buffer path only
