@@ -47,6 +47,14 @@ __device__ __forceinline__ uint32_t quant_u8(float x, float scale, float zpf, fl
     return __float_as_uint(big) & 0xFFu;
 }
 
+// The reference's sequence for four elements.  Rarely taken (a few warps in a hundred): kept out of line so that its four
+// divisions cost the callers' hot loops neither registers nor instruction-cache room.
+static __device__ __noinline__ uint32_t quant4_u8_exact(float4 x, float scale, float zpf)
+{
+    return quant_u8_exact(x.x, scale, zpf) | (quant_u8_exact(x.y, scale, zpf) << 8) |
+           (quant_u8_exact(x.z, scale, zpf) << 16) | (quant_u8_exact(x.w, scale, zpf) << 24);
+}
+
 // Four elements at once, packed little-endian into one word.  The screening value may come from a fused multiply-add
 // (it only has to be within 1.3e-4 of the reference's v, and an FMA is closer than separate roundings); the bytes are
 // taken from the low mantissa bytes of v + 2^23 with three byte permutes.  If any of the four lies within 4e-4 of a
@@ -68,8 +76,7 @@ __device__ __forceinline__ uint32_t quant4_u8(float4 x, float scale, float zpf, 
             return __byte_perm(lo, hi, 0x5410);
         }
     }
-    return quant_u8_exact(x.x, scale, zpf) | (quant_u8_exact(x.y, scale, zpf) << 8) |
-           (quant_u8_exact(x.z, scale, zpf) << 16) | (quant_u8_exact(x.w, scale, zpf) << 24);
+    return quant4_u8_exact(x, scale, zpf);
 }
 
 }  // namespace ltq
