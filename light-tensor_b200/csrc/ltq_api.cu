@@ -723,7 +723,7 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     const bool direct = conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
                         (per_channel || !conv->bias) &&
                         conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, height_in, width_in, Ho, Wo);
-    LTQ_REQUIRE(direct || !(nhwc_in || nhwc_out), LTQ_ERR_UNSUPPORTED,
+    LTQ_REQUIRE(!(nhwc_in || nhwc_out) || (direct && conv->Cin % 64 == 0 && conv->Cout % 16 == 0), LTQ_ERR_UNSUPPORTED,
                 "channels-last input / output is only available for the layers computed without a patch buffer (stride 1, "
                 "input channels a multiple of 64, output channels a multiple of 16, no forced kernel, bias absent or per channel)");
     LTQ_REQUIRE(!nhwc_in || ((uintptr_t)x_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last input must be 16-byte aligned");
@@ -731,7 +731,8 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     if (direct) {
         const uint8_t *x_cl = x_dev;
         if (!nhwc_in) {
-            rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, batches * conv->Cin * height_in * width_in, st, "the NHWC copy of the input");
+            rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, conv_direct_input_bytes(batches, conv->Cin, height_in, width_in), st,
+                      "the NHWC copy of the input");
             if (rc != LTQ_OK) return rc;
             LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));
             x_cl = conv->x_nhwc;

@@ -1,6 +1,7 @@
 // Conv2d_q without a patch buffer (l-ten/conv2d.cpp:352-367 gathers every patch into a [K, Ho*Wo] buffer per image,
 // l-ten/im_col.h:5-33, and multiplies; the first GPU form here did the same for the whole batch: 58 MB written and read
-// again for 6.4 MB of input).  For stride 1 and a channel count that is a multiple of 64 the patches never exist:
+// again for 6.4 MB of input).  For stride 1 the patches never exist (input channels are padded to a multiple of 64 in the
+// channels-last copy and in the reordered weights, output channels to a multiple of 16; zero channels add nothing):
 //
 //  * the product does not care in which order K is walked as long as both operands agree, so K is taken as
 //    (kernel row, kernel column, channel) instead of the reference's (channel, kernel row, kernel column).  The weights
@@ -22,7 +23,7 @@
 //    addresses).  Accumulators are double buffered in TMEM; one persistent CTA per SM; every wait is bounded.
 //
 // More than 112 output channels run as several launches over blocks of channels (each with its own ones row).
-// Everything else (other strides, input channel counts, wide rows, the reference's position-indexed bias) keeps the
+// Everything else (other strides, rows wider than 128 - kw + 1 pixels, the reference's position-indexed bias) keeps the
 // patch-buffer path in ltq_conv.cu.
 #include <cuda.h>
 
@@ -49,7 +50,8 @@ struct DirectGeom {
     uint32_t B, Ho, Wo, rpt, tiles_per_image, tiles;
     uint32_t P;                           // pixel slots per row of a stage: a power of two >= Wo + kw - 1; rpt = 128 / P
     uint32_t kh, kw, ph, pw, cchunks;     // kernel size, padding, Cin / 64
-    uint32_t Cout, Npad, CoutTotal;       // output channels of this launch, Cout + 16, output channels of the layer
+    uint32_t Cout, Npad, CoutTotal;       // channels of this launch's block (a multiple of 16), Cout + 16, channels of the layer
+    uint32_t CoutValid;                   // channels of the block that exist (the last block may be padded)
     uint32_t stages, stage_bytes;         // ring depth; (rpt + kh - 1) * P * 64 rounded up to 1 KB
     uint32_t nhwc_out;                    // output as [image][row][column][channel] instead of [image][channel][row][column]
 };
@@ -83,25 +85,27 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
 constexpr uint32_t NHWC_ROWS = 1;        // rows per CTA (measured on 32 x 64 x 56 x 56: 1 row per CTA 9 us, 4 rows per CTA 17 us - the
                                          // kernel lives on the number of warps in flight)
 constexpr size_t NHWC_SMEM = 160 * 1024;
-__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xt, uint32_t C,
-                                                           uint32_t H, uint32_t W, uint32_t rows)
-{
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xt, uint32_t Cin,
+                                                           uint32_t C, uint32_t H, uint32_t W, uint32_t rows)
+{   // C = Cin rounded up to a multiple of 64: the channels-last copy is padded with zero channels
     griddep_launch_dependents();
     extern __shared__ uint32_t s32[];                    // [rows][C][pitch] words
     const uint32_t h0 = blockIdx.x * rows, b = blockIdx.y;
     const uint32_t nr = H - h0 < rows ? H - h0 : rows;
     const uint32_t ww = (W + 3) / 4, pitch = ww | 1u;    // odd pitch: the column reads below spread over the banks
     griddep_wait();
-    const uint8_t *src = x + ((size_t)b * C * H + h0) * W;
+    const uint8_t *src = x + ((size_t)b * Cin * H + h0) * W;
     const bool words = (W & 3u) == 0 && (reinterpret_cast<uintptr_t>(x) & 3) == 0;
     for (uint32_t i = threadIdx.x; i < nr * C * ww; i += blockDim.x) {
         const uint32_t rc = i / ww, w4 = i - rc * ww, r = rc / C, c = rc - r * C;
-        const uint8_t *p = src + ((size_t)c * H + r) * W + 4 * w4;
         uint32_t v = 0;
-        if (words) {
-            v = *reinterpret_cast<const uint32_t *>(p);
-        } else {
-            for (uint32_t k = 0; k < 4 && 4 * w4 + k < W; k++) v |= (uint32_t)p[k] << (8 * k);
+        if (c < Cin) {
+            const uint8_t *p = src + ((size_t)c * H + r) * W + 4 * w4;
+            if (words) {
+                v = *reinterpret_cast<const uint32_t *>(p);
+            } else {
+                for (uint32_t k = 0; k < 4 && 4 * w4 + k < W; k++) v |= (uint32_t)p[k] << (8 * k);
+            }
         }
         s32[rc * pitch + w4] = v;
     }
@@ -123,21 +127,22 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__rest
     }
 }
 
-// One block of output channels: wr[n][(i * kw + j) * C + c] = w[n][(c * kh + i) * kw + j] for n < Cout (w points at the
-// block's first channel); row Cout: all ones; rows Cout+1 .. Cout+15: zero.
-__global__ void reorder_weights_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ wr, uint32_t Cout, uint32_t C,
-                                       uint32_t kh, uint32_t kw)
+// One block of output channels: wr[n][(i * kw + j) * Cp + c] = w[n][(c * kh + i) * kw + j] for n < valid and c < Cin (w points
+// at the block's first channel; Cp = Cin rounded up to 64, the padded channels are zero); rows valid .. Cout-1 (padding of
+// the last block): zero; row Cout: all ones; rows Cout+1 .. Cout+15: zero.
+__global__ void reorder_weights_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ wr, uint32_t Cout, uint32_t valid,
+                                       uint32_t Cin, uint32_t Cp, uint32_t kh, uint32_t kw)
 {
-    const uint32_t K = C * kh * kw;
-    const uint64_t total = (uint64_t)(Cout + EXTRA) * K;
+    const uint32_t K = Cin * kh * kw, Kp = Cp * kh * kw;
+    const uint64_t total = (uint64_t)(Cout + EXTRA) * Kp;
     for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (uint64_t)gridDim.x * blockDim.x) {
-        const uint32_t n = (uint32_t)(idx / K), k = (uint32_t)(idx - (uint64_t)n * K);
-        uint8_t v;
-        if (n < Cout) {
-            const uint32_t tap = k / C, c = k - tap * C, i = tap / kw, j = tap - i * kw;
-            v = w[(size_t)n * K + ((size_t)c * kh + i) * kw + j];
-        } else {
-            v = n == Cout ? 1 : 0;
+        const uint32_t n = (uint32_t)(idx / Kp), k = (uint32_t)(idx - (uint64_t)n * Kp);
+        uint8_t v = 0;
+        if (n < valid) {
+            const uint32_t tap = k / Cp, c = k - tap * Cp, i = tap / kw, j = tap - i * kw;
+            if (c < Cin) v = w[(size_t)n * K + ((size_t)c * kh + i) * kw + j];
+        } else if (n == Cout) {
+            v = 1;
         }
         wr[idx] = v;
     }
@@ -263,7 +268,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         using OutT = typename std::conditional<OUT == 0, uint8_t, typename std::conditional<OUT == 1, float, int32_t>::type>::type;
         OutT *o = static_cast<OutT *>(out);
         // column terms (-zA * wsum[channel] + bias[channel]): the same for every tile
-        for (uint32_t j = et; j < 128u; j += 256) s_col[j] = j < g.Cout ? epilogue_col_term(epi, c, j) : 0u;
+        for (uint32_t j = et; j < 128u; j += 256) s_col[j] = j < g.CoutValid ? epilogue_col_term(epi, c, j) : 0u;
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const uint32_t p = q * 32 + lane;                 // slot inside the tile: output row p / P, column p % P
         const uint32_t hh = p / g.P, wcol = p - hh * g.P;
@@ -306,9 +311,11 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                     } else if (valid) {
 #pragma unroll
                         for (int j = 0; j < 16; j++) {
-                            if (OUT == 0) *d = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
-                            else if (OUT == 1) *d = (OutT)__uint_as_float(res[j]);
-                            else *d = (OutT)(int32_t)res[j];
+                            if (ch + j < g.CoutValid) {   // (the last block of channels may be padded)
+                                if (OUT == 0) *d = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                                else if (OUT == 1) *d = (OutT)__uint_as_float(res[j]);
+                                else *d = (OutT)(int32_t)res[j];
+                            }
                             d += plane;
                         }
                     }
@@ -396,24 +403,29 @@ cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const Di
 
 }  // namespace
 
+static uint64_t padded_channels(uint64_t Cin) { return (Cin + CCH - 1) / CCH * CCH; }
+
 bool conv_direct_plan(ConvDirectPlan *plan, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw)
 {
     plan->blocks = 0;
-    if (sh != 1 || sw != 1 || Cin % CCH != 0 || Cout % 16 != 0 || encode_fn() == nullptr) return false;
-    const uint64_t nchunks = kh * kw * (Cin / CCH);
+    if (sh != 1 || sw != 1 || encode_fn() == nullptr) return false;
+    const uint64_t nchunks = kh * kw * (padded_channels(Cin) / CCH);
     if (nchunks >= (1u << 16)) return false;
-    // Output channels in blocks of at most 112 (+ 16 extra weight rows = the MMA's 128 columns per accumulator), as equal as
-    // multiples of 16 allow; a block's weights of all taps stay in shared memory beside a ring of at least 2 of the
-    // smallest stages (whether the stages of a given image width fit is decided per call).
-    for (uint32_t blocks = (uint32_t)((Cout + 111) / 112); blocks <= (uint32_t)ConvDirectPlan::MAX_BLOCKS; blocks++) {
-        const uint32_t nb = (uint32_t)((Cout / 16 + blocks - 1) / blocks) * 16;
+    // Output channels (rounded up to a multiple of 16) in blocks of at most 112 (+ 16 extra weight rows = the MMA's 128
+    // columns per accumulator), as equal as multiples of 16 allow; a block's weights of all taps stay in shared memory
+    // beside a ring of at least 2 of the smallest stages (whether the stages of a given image width fit is decided per call).
+    const uint64_t units = (Cout + 15) / 16;
+    for (uint32_t blocks = (uint32_t)((units * 16 + 111) / 112); blocks <= (uint32_t)ConvDirectPlan::MAX_BLOCKS; blocks++) {
+        const uint32_t nb = (uint32_t)((units + blocks - 1) / blocks) * 16;
         if (direct_smem(2, stage_bytes_for(8, kh), (uint32_t)nchunks, nb + EXTRA) > SMEM_BUDGET) continue;
         uint32_t c0 = 0;
         plan->blocks = 0;
         while (c0 < Cout) {
-            const uint32_t n = Cout - c0 < nb ? (uint32_t)(Cout - c0) : nb;
+            const uint32_t left = (uint32_t)(Cout - c0);
+            const uint32_t n = left < nb ? (left + 15) / 16 * 16 : nb;
             plan->cout0[plan->blocks] = c0;
             plan->nb[plan->blocks] = n;
+            plan->valid[plan->blocks] = left < n ? left : n;
             plan->blocks++;
             c0 += n;
         }
@@ -426,24 +438,26 @@ size_t conv_direct_weight_bytes(const ConvDirectPlan &plan, uint64_t Cin, uint64
 {
     size_t rows = 0;
     for (uint32_t i = 0; i < plan.blocks; i++) rows += plan.nb[i] + EXTRA;
-    return rows * Cin * kh * kw;
+    return rows * padded_channels(Cin) * kh * kw;
 }
+
+size_t conv_direct_input_bytes(uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W) { return batches * H * W * padded_channels(Cin); }
 
 cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirectPlan *plan, uint64_t Cin, uint64_t kh, uint64_t kw,
                                         cudaStream_t stream)
 {
-    const uint64_t K = Cin * kh * kw;
+    const uint64_t K = Cin * kh * kw, Cp = padded_channels(Cin), Kp = Cp * kh * kw;
     size_t row0 = 0;
     for (uint32_t i = 0; i < plan->blocks; i++) {
-        uint8_t *dst = wr + row0 * K;
+        uint8_t *dst = wr + row0 * Kp;
         const uint64_t Npad = plan->nb[i] + EXTRA;
-        reorder_weights_kernel<<<256, 256, 0, stream>>>(w + (size_t)plan->cout0[i] * K, dst, plan->nb[i], (uint32_t)Cin, (uint32_t)kh,
-                                                        (uint32_t)kw);
+        reorder_weights_kernel<<<256, 256, 0, stream>>>(w + (size_t)plan->cout0[i] * K, dst, plan->nb[i], plan->valid[i], (uint32_t)Cin,
+                                                        (uint32_t)Cp, (uint32_t)kh, (uint32_t)kw);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
         count_launch();
-        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)Npad};
-        cuuint64_t strides[1] = {(cuuint64_t)K};
+        cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)Npad};
+        cuuint64_t strides[1] = {(cuuint64_t)Kp};
         cuuint32_t box[2] = {(cuuint32_t)CCH, (cuuint32_t)Npad};
         cuuint32_t estr[2] = {1, 1};
         TcOperandMap *map = &plan->maps[i];
@@ -453,7 +467,7 @@ cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirec
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
         map->base = dst;
         map->rows = Npad;
-        map->K = K;
+        map->K = Kp;
         map->box_rows = (int)Npad;
         map->box_lines = 0;
         row0 += Npad;
@@ -469,13 +483,14 @@ bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t
     if (!(Wo >= 1 && Wo + kw - 1 <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31)))
         return false;
     const uint32_t P = slots_per_row(Wo, kw), sb = stage_bytes_for(P, kh);
-    if (Cin * ((((W + 3) / 4) | 1u) * 4) > NHWC_SMEM) return false;   // one image row of the transposition in shared memory
+    if (padded_channels(Cin) * ((((W + 3) / 4) | 1u) * 4) > NHWC_SMEM) return false;   // one image row of the transposition in shared memory
     return 128 / P + kh - 1 <= 256 && sb <= MAX_STAGE_BYTES &&
-           direct_smem(2, sb, (uint32_t)(kh * kw * (Cin / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
+           direct_smem(2, sb, (uint32_t)(kh * kw * (padded_channels(Cin) / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
 }
 
-cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream)
+cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W, cudaStream_t stream)
 {
+    const uint64_t C = padded_channels(Cin);
     // one CTA per (group of rows, image); the grid's y extent holds 65535 images per launch
     const size_t pitch = ((W + 3) / 4) | 1u, row_bytes = C * pitch * 4;
     if (row_bytes > NHWC_SMEM) return cudaErrorInvalidConfiguration;
@@ -491,7 +506,7 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches,
     for (uint64_t b0 = 0; b0 < batches; b0 += 65535) {
         const uint64_t nb = batches - b0 < 65535 ? batches - b0 : 65535;
         cudaError_t e = launch_chained(nchw_to_nhwc_kernel, dim3((unsigned)((H + rows - 1) / rows), (unsigned)nb), dim3(256), smem, stream,
-                                       x + b0 * C * H * W, xt + b0 * C * H * W, (uint32_t)C, (uint32_t)H, (uint32_t)W, rows);
+                                       x + b0 * Cin * H * W, xt + b0 * C * H * W, (uint32_t)Cin, (uint32_t)C, (uint32_t)H, (uint32_t)W, rows);
         if (e != cudaSuccess) return e;
         count_launch();
     }
@@ -516,13 +531,14 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
     g.kw = (uint32_t)kw;
     g.ph = (uint32_t)ph;
     g.pw = (uint32_t)pw;
-    g.cchunks = (uint32_t)(Cin / CCH);
+    const uint64_t Cp = padded_channels(Cin);
+    g.cchunks = (uint32_t)(Cp / CCH);
     g.CoutTotal = (uint32_t)Cout;
     g.stage_bytes = stage_bytes_for(g.P, kh);
     // the input as {channel, x, y, image}; a box is 64 channels of the rpt + kh - 1 input rows a tile touches, P pixels wide
     alignas(64) CUtensorMap mx;
-    cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batches};
-    cuuint64_t strides[3] = {(cuuint64_t)Cin, (cuuint64_t)(W * Cin), (cuuint64_t)(H * W * Cin)};
+    cuuint64_t dims[4] = {(cuuint64_t)Cp, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batches};
+    cuuint64_t strides[3] = {(cuuint64_t)Cp, (cuuint64_t)(W * Cp), (cuuint64_t)(H * W * Cp)};
     cuuint32_t box[4] = {(cuuint32_t)CCH, g.P, g.rpt + g.kh - 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(xt), dims, strides, box, estr,
@@ -533,6 +549,7 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
     // one launch per block of output channels (each reads the input tiles again, out of L2)
     for (uint32_t i = 0; i < plan.blocks; i++) {
         g.Cout = plan.nb[i];
+        g.CoutValid = plan.valid[i];
         g.Npad = g.Cout + EXTRA;
         g.stages = MAX_STAGES;
         while (g.stages > 2 && direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;

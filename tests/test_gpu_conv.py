@@ -66,6 +66,8 @@ def test_conv_matches_oracle(cuda, oracle, shape):
     want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], ph=ph, pw=pw, sh=sh,
                                 sw=sw)
     got = _conv(cuda, ltq, c, [ltq_qp(r) for r in rows])
+    # stride 1 takes the kernel without a patch buffer whatever the channel counts (they are padded), stride 2 the patch buffer
+    assert ltq.last_kernel().startswith("conv_direct_kernel<") == (sh == 1 and sw == 1), ltq.last_kernel()
     np.testing.assert_array_equal(got, want)
     # one bias per output channel (the library's option; the oracle restates the same arithmetic)
     bias = rng.integers(-30000, 30000, Cout, dtype=np.int32)
