@@ -722,8 +722,10 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     const bool nhwc_in = (flags & LTQ_FLAG_NHWC_IN) != 0, nhwc_out = (flags & LTQ_FLAG_NHWC_OUT) != 0;
     const bool direct = conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
                         (per_channel || !conv->bias) &&
-                        conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, height_in, width_in, Ho, Wo);
-    LTQ_REQUIRE(!(nhwc_in || nhwc_out) || (direct && conv->Cin % 64 == 0 && conv->Cout % 16 == 0), LTQ_ERR_UNSUPPORTED,
+                        conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, conv->ph, conv->pw, height_in,
+                                             width_in, Ho, Wo);
+    LTQ_REQUIRE(!(nhwc_in || nhwc_out) || (direct && conv->Cin % 64 == 0 && conv->Cout % 16 == 0 && (!nhwc_in || (conv->sh == 1 && conv->sw == 1))),
+                LTQ_ERR_UNSUPPORTED,
                 "channels-last input / output is only available for the layers computed without a patch buffer (stride 1, "
                 "input channels a multiple of 64, output channels a multiple of 16, no forced kernel, bias absent or per channel)");
     LTQ_REQUIRE(!nhwc_in || ((uintptr_t)x_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last input must be 16-byte aligned");
@@ -731,10 +733,10 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     if (direct) {
         const uint8_t *x_cl = x_dev;
         if (!nhwc_in) {
-            rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, conv_direct_input_bytes(batches, conv->Cin, height_in, width_in), st,
+            rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, conv_direct_input_bytes(conv->direct, batches, conv->Cin, height_in, width_in), st,
                       "the NHWC copy of the input");
             if (rc != LTQ_OK) return rc;
-            LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, batches, conv->Cin, height_in, width_in, st));
+            LTQ_CUDA_TRY(launch_nchw_to_nhwc(x_dev, conv->x_nhwc, conv->direct, batches, conv->Cin, height_in, width_in, st));
             x_cl = conv->x_nhwc;
         }
         // positions are the rows here: A = input (its patch sums come out of the kernel), B = weights

@@ -1,7 +1,8 @@
 // Conv2d_q without a patch buffer (l-ten/conv2d.cpp:352-367 gathers every patch into a [K, Ho*Wo] buffer per image,
 // l-ten/im_col.h:5-33, and multiplies; the first GPU form here did the same for the whole batch: 58 MB written and read
-// again for 6.4 MB of input).  For stride 1 the patches never exist (input channels are padded to a multiple of 64 in the
-// channels-last copy and in the reordered weights, output channels to a multiple of 16; zero channels add nothing):
+// again for 6.4 MB of input).  Here the patches never exist (input channels are padded to a multiple of 64 in the
+// channels-last copy and in the reordered weights, output channels to a multiple of 16; zero channels add nothing; the
+// description is for stride 1, strides are at the end):
 //
 //  * the product does not care in which order K is walked as long as both operands agree, so K is taken as
 //    (kernel row, kernel column, channel) instead of the reference's (channel, kernel row, kernel column).  The weights
@@ -22,9 +23,14 @@
 //    through the shared helpers, stores straight into NCHW (for one channel the 32 positions of a warp are consecutive
 //    addresses).  Accumulators are double buffered in TMEM; one persistent CTA per SM; every wait is bounded.
 //
+// Strides: the channels-last copy is kept as sh * sw PLANES, plane (y mod sh, x mod sw) holding the pixels of that residue
+// as a dense image.  For output position (ho, wo) kernel tap (i, j) reads pixel (sh * ho + i - pad, sw * wo + j - pad), i.e.
+// pixel (ho + floor((i - pad) / sh), wo + floor((j - pad) / sw)) of plane ((i - pad) mod sh, (j - pad) mod sw): again a
+// constant shift per tap, so a tile loads one region per plane in use (a 5-D tensor copy, the plane being the fifth
+// coordinate) and every tap is an MMA over its plane's region with a shifted start.
 // More than 112 output channels run as several launches over blocks of channels (each with its own ones row).
-// Everything else (other strides, rows wider than 128 - kw + 1 pixels, the reference's position-indexed bias) keeps the
-// patch-buffer path in ltq_conv.cu.
+// Everything else (rows wider than the 128 slots of a tile, regions or weights too large for shared memory, the
+// reference's position-indexed bias) keeps the patch-buffer path in ltq_conv.cu.
 #include <cuda.h>
 
 #include <type_traits>
@@ -41,18 +47,25 @@ namespace {
 constexpr int THREADS = 320;            // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue (two per TMEM lane quarter)
 constexpr int CCH = 64;                 // channels per K chunk = bytes per row of an operand tile (64-byte swizzle)
 constexpr int MAX_STAGES = 8;
-constexpr uint32_t MAX_STAGE_BYTES = 48 * 1024;
+constexpr uint32_t MAX_STAGE_BYTES = 96 * 1024;
 constexpr int EXTRA = 16;               // weight rows appended behind the output channels (row 0 of them: all ones)
 constexpr uint32_t TMEM_COLS = 256;     // two accumulators of up to 128 columns
 constexpr size_t SMEM_BUDGET = 200 * 1024;
+constexpr uint32_t MAX_TAPS = 256;      // kernel positions (their region offsets are tabulated in shared memory)
 
 struct DirectGeom {
     uint32_t B, Ho, Wo, rpt, tiles_per_image, tiles;
-    uint32_t P;                           // pixel slots per row of a stage: a power of two >= Wo + kw - 1; rpt = 128 / P
-    uint32_t kh, kw, ph, pw, cchunks;     // kernel size, padding, Cin / 64
+    uint32_t P;                           // pixel slots per row of a region: a power of two >= Wo + dx_span; rpt = 128 / P
+    uint32_t kh, kw, ph, pw, cchunks;     // kernel size, padding, padded Cin / 64
+    // Strides: the channels-last copy is split into sh * sw PLANES, plane (y mod sh, x mod sw) holding the pixels of that
+    // residue as a dense image.  Kernel tap (i, j) then reads plane ((i - ph) mod sh, (j - pw) mod sw) shifted by
+    // (floor((i - ph) / sh), floor((j - pw) / sw)) pixels, for every output position alike - stride 1 is the one-plane case.
+    uint32_t sh, sw, plane_mask;          // strides; bit p set: plane p is read by some tap
+    int32_t dy_min, dx_min;               // smallest shifts (<= 0 with padding)
+    uint32_t rows_box, plane_bytes;       // rows of a region (rpt + dy span); rows_box * P * 64 rounded up to 1 KB
     uint32_t Cout, Npad, CoutTotal;       // channels of this launch's block (a multiple of 16), Cout + 16, channels of the layer
     uint32_t CoutValid;                   // channels of the block that exist (the last block may be padded)
-    uint32_t stages, stage_bytes;         // ring depth; (rpt + kh - 1) * P * 64 rounded up to 1 KB
+    uint32_t stages, stage_bytes;         // ring depth; planes * plane_bytes
     uint32_t nhwc_out;                    // output as [image][row][column][channel] instead of [image][channel][row][column]
 };
 
@@ -69,14 +82,17 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw64(uint32_t smem_addr)
     return d;
 }
 
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1,
-                                            int32_t c2, int32_t c3)
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1,
+                                            int32_t c2, int32_t c3, int32_t c4)
 {
     asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
+// floor(a / b) and a - b * floor(a / b) for b > 0
+__host__ __device__ __forceinline__ int32_t floordiv(int32_t a, int32_t b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+__host__ __device__ __forceinline__ int32_t floormod(int32_t a, int32_t b) { return a - b * floordiv(a, b); }
 
 // NCHW -> NHWC for `batches` images: one CTA per (image, NHWC_ROWS rows).  The rows' C x W bytes are staged in
 // shared memory as 32-bit words (four pixels of one channel each); a thread then takes the words of four consecutive
@@ -85,9 +101,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
 constexpr uint32_t NHWC_ROWS = 1;        // rows per CTA (measured on 32 x 64 x 56 x 56: 1 row per CTA 9 us, 4 rows per CTA 17 us - the
                                          // kernel lives on the number of warps in flight)
 constexpr size_t NHWC_SMEM = 160 * 1024;
+template <bool PLANES>   // PLANES = false: strides 1, one plane, none of the residue arithmetic
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__restrict__ x, uint8_t *__restrict__ xt, uint32_t Cin,
-                                                           uint32_t C, uint32_t H, uint32_t W, uint32_t rows)
-{   // C = Cin rounded up to a multiple of 64: the channels-last copy is padded with zero channels
+                                                           uint32_t C, uint32_t H, uint32_t W, uint32_t rows, uint32_t sh, uint32_t sw,
+                                                           uint32_t b_first, uint32_t b_total)
+{   // C = Cin rounded up to a multiple of 64: the channels-last copy is padded with zero channels.  With strides the copy
+    // is split into sh * sw planes [plane][image][ceil(H / sh)][ceil(W / sw)][C], plane = (y mod sh) * sw + (x mod sw).
     griddep_launch_dependents();
     extern __shared__ uint32_t s32[];                    // [rows][C][pitch] words
     const uint32_t h0 = blockIdx.x * rows, b = blockIdx.y;
@@ -110,8 +129,8 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__rest
         s32[rc * pitch + w4] = v;
     }
     __syncthreads();
-    uint32_t *dst = reinterpret_cast<uint32_t *>(xt + ((size_t)b * H + h0) * W * C);   // C % 64 == 0: word aligned
-    const uint32_t cw = C / 4;
+    uint32_t *dst = reinterpret_cast<uint32_t *>(xt);   // C % 64 == 0: word aligned
+    const uint32_t cw = C / 4, Hp = (H + sh - 1) / sh, Wp = (W + sw - 1) / sw;
     for (uint32_t j = threadIdx.x; j < nr * ww * cw; j += blockDim.x) {
         const uint32_t rw = j / cw, c4 = j - rw * cw, r = rw / ww, w4 = rw - r * ww;   // consecutive threads: channel groups of one pixel group
         const uint32_t *col = s32 + (r * C + 4 * c4) * pitch + w4;
@@ -122,8 +141,17 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const uint8_t *__rest
         const uint32_t o[4] = {__byte_perm(t0, u0, 0x5410), __byte_perm(t0, u0, 0x7632), __byte_perm(t1, u1, 0x5410),
                                __byte_perm(t1, u1, 0x7632)};
 #pragma unroll
-        for (uint32_t k = 0; k < 4; k++)
-            if (4 * w4 + k < W) dst[((size_t)r * W + 4 * w4 + k) * cw + c4] = o[k];
+        for (uint32_t k = 0; k < 4; k++) {
+            const uint32_t xx = 4 * w4 + k, yy = h0 + r;
+            if (xx < W) {
+                if (!PLANES) {   // one plane: no residues to take (the divisions below cost a third of the kernel's time)
+                    dst[(((size_t)(b_first + b) * H + yy) * W + xx) * cw + c4] = o[k];
+                } else {
+                    const uint32_t plane = (yy % sh) * sw + (xx % sw);
+                    dst[((((size_t)plane * b_total + b_first + b) * Hp + yy / sh) * Wp + xx / sw) * cw + c4] = o[k];
+                }
+            }
+        }
     }
 }
 
@@ -159,12 +187,13 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
     griddep_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw0 = smem_u32(smem_raw);
-    const uint32_t ring = (raw0 + 1023u) & ~1023u;                             // [stages][rpt + kh - 1 rows][P pixels][64 B]
+    const uint32_t ring = (raw0 + 1023u) & ~1023u;                             // [stages][planes][rows_box][P pixels][64 B]
     const uint32_t wsm = ring + g.stages * g.stage_bytes;                      // [kh * kw * cchunks][Npad rows][64 B]
     const uint32_t taps = g.kh * g.kw, nchunks = taps * g.cchunks, wtile = g.Npad * CCH;
     uint8_t *after = smem_raw + (wsm - raw0) + nchunks * wtile;
     uint32_t *s_col = reinterpret_cast<uint32_t *>(after);                     // [128] column terms
-    uint64_t *bars = reinterpret_cast<uint64_t *>(after + 128 * 4);            // full[S] empty[S] tfull[2] tempty[2] wfull
+    uint32_t *s_tap = s_col + 128;                                             // [MAX_TAPS] byte offset of every tap's window in a stage
+    uint64_t *bars = reinterpret_cast<uint64_t *>(after + (128 + MAX_TAPS) * 4);   // full[S] empty[S] tfull[2] tempty[2] wfull
     uint32_t *s_misc = reinterpret_cast<uint32_t *>(bars + 2 * MAX_STAGES + 5);  // [0] tmem base, [1] abort flag
     volatile uint32_t *abort_flag = s_misc + 1;
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * MAX_STAGES;
@@ -194,12 +223,23 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         tmem_alloc(smem_u32(s_misc), TMEM_COLS);
         tmem_relinquish();
     }
+    // Where every kernel tap's window starts inside a stage: its plane's slot, then (dy * P + dx) pixel slots further on
+    // (dy, dx counted from the region's first row and column).  Tabulated once: the MMA-issuing thread is the kernel's
+    // critical path and should not divide.
+    for (uint32_t tap = threadIdx.x; tap < taps; tap += blockDim.x) {
+        const uint32_t i = tap / g.kw, j = tap - i * g.kw;
+        const int32_t ti = (int32_t)i - (int32_t)g.ph, tj = (int32_t)j - (int32_t)g.pw;
+        const uint32_t pl = (uint32_t)floormod(ti, (int32_t)g.sh) * g.sw + (uint32_t)floormod(tj, (int32_t)g.sw);
+        const uint32_t dy = (uint32_t)(floordiv(ti, (int32_t)g.sh) - g.dy_min), dx = (uint32_t)(floordiv(tj, (int32_t)g.sw) - g.dx_min);
+        s_tap[tap] = (uint32_t)__popc(g.plane_mask & ((1u << pl) - 1u)) * g.plane_bytes + (dy * g.P + dx) * CCH;
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     griddep_wait();   // the transposed input comes from the kernel in front
     const uint32_t tmem_base = s_misc[0];
-    const uint32_t box_bytes = (g.rpt + g.kh - 1) * g.P * CCH;   // a copy always delivers its whole box (zeros outside the image)
+    const uint32_t box_bytes = g.rows_box * g.P * CCH;   // a copy always delivers its whole box (zeros outside the image)
+    const uint32_t planes = g.sh * g.sw;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -208,14 +248,16 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < g.tiles; t += gridDim.x) {
                 const uint32_t b = t / g.tiles_per_image, ho0 = (t - b * g.tiles_per_image) * g.rpt;
-                // one copy per 64-channel chunk: the rpt + kh - 1 input rows the tile's output rows touch, P pixels wide
-                // from the left padding on (whatever lies outside the image arrives as zeros)
+                // per 64-channel chunk one copy per plane in use: the rows_box rows of the plane that the tile's output rows
+                // touch, P pixels wide from the leftmost shift on (whatever lies outside the image arrives as zeros)
                 for (uint32_t cc = 0; cc < g.cchunks; cc++) {
                     ok = mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x100u | st);
                     if (!ok) break;
-                    mbar_expect_tx(full0 + 8 * st, box_bytes);
-                    tma_load_4d(ring + st * g.stage_bytes, &map_x, full0 + 8 * st, (int32_t)(cc * CCH), -(int32_t)g.pw,
-                                (int32_t)ho0 - (int32_t)g.ph, (int32_t)b);
+                    mbar_expect_tx(full0 + 8 * st, box_bytes * (uint32_t)__popc(g.plane_mask));
+                    for (uint32_t pl = 0; pl < planes; pl++)
+                        if (g.plane_mask >> pl & 1u)   // planes in use sit back to back in the stage
+                            tma_load_5d(ring + st * g.stage_bytes + (uint32_t)__popc(g.plane_mask & ((1u << pl) - 1u)) * g.plane_bytes,
+                                        &map_x, full0 + 8 * st, (int32_t)(cc * CCH), g.dx_min, (int32_t)ho0 + g.dy_min, (int32_t)b, (int32_t)pl);
                     if (++st == g.stages) { st = 0; ph ^= 1; }
                 }
             }
@@ -236,13 +278,13 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 if (!ok) break;
                 tc_fence_after();
                 if (elect_one()) {
-                    // Output position p = (row hh, column ww) sits in slot hh * P + ww, and for kernel tap (i, j) it reads the
-                    // pixel in slot (hh + i) * P + ww + j: the same 128 rows of 64 bytes, started (i * P + j) slots further on.
-                    // The swizzle is a function of the shared-memory address, so a shifted start needs nothing else.
+                    // Output position p = (row hh, column ww) sits in slot hh * P + ww, and for kernel tap (i, j) it reads, from
+                    // the tap's plane, the pixel in slot (hh + dy) * P + ww + dx: the same 128 rows of 64 bytes, started
+                    // (dy * P + dx) slots further on (dy, dx counted from the region's first row and column).  The swizzle is
+                    // a function of the shared-memory address, so a shifted start needs nothing else.
                     const uint32_t stage = ring + st * g.stage_bytes;
                     for (uint32_t tap = 0; tap < taps; tap++) {
-                        const uint32_t i = tap / g.kw, j = tap - i * g.kw;
-                        const uint64_t a_desc = make_smem_desc_sw64(stage + (i * g.P + j) * CCH);
+                        const uint64_t a_desc = make_smem_desc_sw64(stage + s_tap[tap]);
                         const uint64_t b_desc = make_smem_desc_sw64(wsm + (tap * g.cchunks + cc) * wtile);
                         umma_i8(d_tmem, a_desc, b_desc, idesc, (cc | tap) != 0u);
                         umma_i8(d_tmem, a_desc + 2u, b_desc + 2u, idesc, 1u);   // the second 32 bytes of K of the 64-byte rows
@@ -367,17 +409,37 @@ EncodeTiledFn encode_fn()
 
 size_t direct_smem(uint32_t stages, uint32_t stage_bytes, uint32_t nchunks, uint32_t Npad)
 {
-    return 1024 + (size_t)stages * stage_bytes + (size_t)nchunks * Npad * CCH + 128 * 4 + (2 * MAX_STAGES + 5) * 8 + 16;
+    return 1024 + (size_t)stages * stage_bytes + (size_t)nchunks * Npad * CCH + (128 + MAX_TAPS) * 4 + (2 * MAX_STAGES + 5) * 8 + 16;
 }
 
-// Pixel slots per row of a stage (a power of two that holds an output row and the kernel's overhang) and the stage size.
-uint32_t slots_per_row(uint64_t Wo, uint64_t kw)
+// What a tile loads: per plane in use a region of rows_box rows x P pixel slots (P a power of two that holds an output
+// row and the spread of the kernel's column shifts).  ok = false when a row does not fit the 128 rows of a tile.
+struct RegionGeom {
+    uint32_t P, rpt, rows_box, plane_bytes, stage_bytes, plane_mask;
+    int32_t dy_min, dx_min;
+    bool ok;
+};
+RegionGeom region_geom(uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t sh, uint64_t sw, uint64_t Wo)
 {
-    uint32_t P = 8;
-    while (P < Wo + kw - 1) P *= 2;
-    return P;
+    RegionGeom r{};
+    r.dy_min = floordiv(-(int32_t)ph, (int32_t)sh);
+    r.dx_min = floordiv(-(int32_t)pw, (int32_t)sw);
+    const int32_t dy_max = floordiv((int32_t)kh - 1 - (int32_t)ph, (int32_t)sh), dx_max = floordiv((int32_t)kw - 1 - (int32_t)pw, (int32_t)sw);
+    const uint64_t need = Wo + (uint64_t)(dx_max - r.dx_min);
+    r.P = 8;
+    while (r.P < need && r.P < 256) r.P *= 2;
+    r.ok = need <= 128;
+    if (!r.ok) return r;
+    r.rpt = 128 / r.P;
+    r.rows_box = r.rpt + (uint32_t)(dy_max - r.dy_min);
+    r.plane_bytes = (uint32_t)(((uint64_t)r.rows_box * r.P * CCH + 1023) & ~1023ull);
+    for (uint64_t i = 0; i < kh; i++)
+        for (uint64_t j = 0; j < kw; j++)
+            r.plane_mask |= 1u << (floormod((int32_t)i - (int32_t)ph, (int32_t)sh) * (int32_t)sw + floormod((int32_t)j - (int32_t)pw, (int32_t)sw));
+    r.stage_bytes = (uint32_t)__builtin_popcount(r.plane_mask) * r.plane_bytes;
+    r.ok = r.rows_box <= 256;
+    return r;
 }
-uint32_t stage_bytes_for(uint32_t P, uint64_t kh) { return (uint32_t)(((128 / P + kh - 1) * P * CCH + 1023) & ~1023ull); }
 
 template <int OUT>
 cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const DirectGeom &g, const Epilogue &epi, void *out,
@@ -408,8 +470,11 @@ static uint64_t padded_channels(uint64_t Cin) { return (Cin + CCH - 1) / CCH * C
 bool conv_direct_plan(ConvDirectPlan *plan, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw)
 {
     plan->blocks = 0;
-    if (sh != 1 || sw != 1 || encode_fn() == nullptr) return false;
+    if (sh < 1 || sw < 1 || sh * sw > 16 || kh * kw > MAX_TAPS || encode_fn() == nullptr) return false;
+    plan->sh = (uint32_t)sh;
+    plan->sw = (uint32_t)sw;
     const uint64_t nchunks = kh * kw * (padded_channels(Cin) / CCH);
+    const uint32_t min_stage = region_geom(kh, kw, 0, 0, sh, sw, 1).stage_bytes;   // the smallest a stage can be
     if (nchunks >= (1u << 16)) return false;
     // Output channels (rounded up to a multiple of 16) in blocks of at most 112 (+ 16 extra weight rows = the MMA's 128
     // columns per accumulator), as equal as multiples of 16 allow; a block's weights of all taps stay in shared memory
@@ -417,7 +482,7 @@ bool conv_direct_plan(ConvDirectPlan *plan, uint64_t Cin, uint64_t Cout, uint64_
     const uint64_t units = (Cout + 15) / 16;
     for (uint32_t blocks = (uint32_t)((units * 16 + 111) / 112); blocks <= (uint32_t)ConvDirectPlan::MAX_BLOCKS; blocks++) {
         const uint32_t nb = (uint32_t)((units + blocks - 1) / blocks) * 16;
-        if (direct_smem(2, stage_bytes_for(8, kh), (uint32_t)nchunks, nb + EXTRA) > SMEM_BUDGET) continue;
+        if (direct_smem(2, min_stage, (uint32_t)nchunks, nb + EXTRA) > SMEM_BUDGET) continue;
         uint32_t c0 = 0;
         plan->blocks = 0;
         while (c0 < Cout) {
@@ -441,7 +506,10 @@ size_t conv_direct_weight_bytes(const ConvDirectPlan &plan, uint64_t Cin, uint64
     return rows * padded_channels(Cin) * kh * kw;
 }
 
-size_t conv_direct_input_bytes(uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W) { return batches * H * W * padded_channels(Cin); }
+size_t conv_direct_input_bytes(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W)
+{
+    return (size_t)plan.sh * plan.sw * batches * ((H + plan.sh - 1) / plan.sh) * ((W + plan.sw - 1) / plan.sw) * padded_channels(Cin);
+}
 
 cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirectPlan *plan, uint64_t Cin, uint64_t kh, uint64_t kw,
                                         cudaStream_t stream)
@@ -475,22 +543,29 @@ cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirec
     return cudaSuccess;
 }
 
-bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W,
-                          uint64_t Ho, uint64_t Wo)
+bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw,
+                          uint64_t H, uint64_t W, uint64_t Ho, uint64_t Wo)
 {
     if (plan.blocks == 0) return false;
     const uint64_t Cout = plan.nb[0];   // the widest block
-    if (!(Wo >= 1 && Wo + kw - 1 <= 128 && W <= (1u << 20) && H <= (1u << 20) && batches < (1ull << 31) && Ho < (1ull << 31)))
+    if (!(Wo >= 1 && W <= (1u << 20) && H <= (1u << 20) && ph <= (1u << 20) && pw <= (1u << 20) && batches < (1ull << 31) &&
+          Ho < (1ull << 31)))
         return false;
-    const uint32_t P = slots_per_row(Wo, kw), sb = stage_bytes_for(P, kh);
+    const RegionGeom r = region_geom(kh, kw, ph, pw, plan.sh, plan.sw, Wo);
+    if (!r.ok || r.stage_bytes > MAX_STAGE_BYTES) return false;
     if (padded_channels(Cin) * ((((W + 3) / 4) | 1u) * 4) > NHWC_SMEM) return false;   // one image row of the transposition in shared memory
-    return 128 / P + kh - 1 <= 256 && sb <= MAX_STAGE_BYTES &&
-           direct_smem(2, sb, (uint32_t)(kh * kw * (padded_channels(Cin) / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
+    return direct_smem(2, r.stage_bytes, (uint32_t)(kh * kw * (padded_channels(Cin) / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
 }
 
-cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W, cudaStream_t stream)
+cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H,
+                                uint64_t W, cudaStream_t stream)
 {
     const uint64_t C = padded_channels(Cin);
+    // planes of different residues have up to one row / column less than ceil(H / sh) x ceil(W / sw): those stay zero
+    if (H % plan.sh != 0 || W % plan.sw != 0) {
+        cudaError_t e = cudaMemsetAsync(xt, 0, conv_direct_input_bytes(plan, batches, Cin, H, W), stream);
+        if (e != cudaSuccess) return e;
+    }
     // one CTA per (group of rows, image); the grid's y extent holds 65535 images per launch
     const size_t pitch = ((W + 3) / 4) | 1u, row_bytes = C * pitch * 4;
     if (row_bytes > NHWC_SMEM) return cudaErrorInvalidConfiguration;
@@ -499,14 +574,21 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches,
     const size_t smem = rows * row_bytes;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(nchw_to_nhwc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(nchw_to_nhwc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(nchw_to_nhwc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
+    const bool one_plane = plan.sh == 1 && plan.sw == 1;
     for (uint64_t b0 = 0; b0 < batches; b0 += 65535) {
         const uint64_t nb = batches - b0 < 65535 ? batches - b0 : 65535;
-        cudaError_t e = launch_chained(nchw_to_nhwc_kernel, dim3((unsigned)((H + rows - 1) / rows), (unsigned)nb), dim3(256), smem, stream,
-                                       x + b0 * Cin * H * W, xt + b0 * C * H * W, (uint32_t)Cin, (uint32_t)C, (uint32_t)H, (uint32_t)W, rows);
+        const dim3 grid((unsigned)((H + rows - 1) / rows), (unsigned)nb);
+        cudaError_t e = one_plane ? launch_chained(nchw_to_nhwc_kernel<false>, grid, dim3(256), smem, stream, x + b0 * Cin * H * W, xt,
+                                                   (uint32_t)Cin, (uint32_t)C, (uint32_t)H, (uint32_t)W, rows, 1u, 1u, (uint32_t)b0,
+                                                   (uint32_t)batches)
+                                  : launch_chained(nchw_to_nhwc_kernel<true>, grid, dim3(256), smem, stream, x + b0 * Cin * H * W, xt,
+                                                   (uint32_t)Cin, (uint32_t)C, (uint32_t)H, (uint32_t)W, rows, plan.sh, plan.sw,
+                                                   (uint32_t)b0, (uint32_t)batches);
         if (e != cudaSuccess) return e;
         count_launch();
     }
@@ -522,8 +604,17 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
     g.B = (uint32_t)batches;
     g.Ho = (uint32_t)Ho;
     g.Wo = (uint32_t)Wo;
-    g.P = slots_per_row(Wo, kw);
-    g.rpt = 128 / g.P;
+    const RegionGeom rg = region_geom(kh, kw, ph, pw, plan.sh, plan.sw, Wo);
+    if (!rg.ok) return cudaErrorInvalidConfiguration;
+    g.P = rg.P;
+    g.rpt = rg.rpt;
+    g.sh = plan.sh;
+    g.sw = plan.sw;
+    g.plane_mask = rg.plane_mask;
+    g.dy_min = rg.dy_min;
+    g.dx_min = rg.dx_min;
+    g.rows_box = rg.rows_box;
+    g.plane_bytes = rg.plane_bytes;
     g.tiles_per_image = (uint32_t)((Ho + g.rpt - 1) / g.rpt);
     if ((uint64_t)g.tiles_per_image * batches >= (1ull << 31)) return cudaErrorInvalidConfiguration;
     g.tiles = g.tiles_per_image * g.B;
@@ -534,14 +625,15 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
     const uint64_t Cp = padded_channels(Cin);
     g.cchunks = (uint32_t)(Cp / CCH);
     g.CoutTotal = (uint32_t)Cout;
-    g.stage_bytes = stage_bytes_for(g.P, kh);
-    // the input as {channel, x, y, image}; a box is 64 channels of the rpt + kh - 1 input rows a tile touches, P pixels wide
+    g.stage_bytes = rg.stage_bytes;
+    // the input as {channel, x, y, image, plane}; a box is 64 channels of the rows of one plane a tile touches, P pixels wide
     alignas(64) CUtensorMap mx;
-    cuuint64_t dims[4] = {(cuuint64_t)Cp, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batches};
-    cuuint64_t strides[3] = {(cuuint64_t)Cp, (cuuint64_t)(W * Cp), (cuuint64_t)(H * W * Cp)};
-    cuuint32_t box[4] = {(cuuint32_t)CCH, g.P, g.rpt + g.kh - 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<uint8_t *>(xt), dims, strides, box, estr,
+    const uint64_t Hp = (H + plan.sh - 1) / plan.sh, Wp = (W + plan.sw - 1) / plan.sw;
+    cuuint64_t dims[5] = {(cuuint64_t)Cp, (cuuint64_t)Wp, (cuuint64_t)Hp, (cuuint64_t)batches, (cuuint64_t)(plan.sh * plan.sw)};
+    cuuint64_t strides[4] = {(cuuint64_t)Cp, (cuuint64_t)(Wp * Cp), (cuuint64_t)(Hp * Wp * Cp), (cuuint64_t)(batches * Hp * Wp * Cp)};
+    cuuint32_t box[5] = {(cuuint32_t)CCH, g.P, g.rows_box, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<uint8_t *>(xt), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;

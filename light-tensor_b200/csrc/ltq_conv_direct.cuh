@@ -10,6 +10,7 @@ namespace ltq {
 struct ConvDirectPlan {
     static constexpr int MAX_BLOCKS = 8;
     uint32_t blocks = 0;
+    uint32_t sh = 1, sw = 1;       // the layer's strides: the channels-last copy is kept as sh * sw planes of equal residues
     uint32_t cout0[MAX_BLOCKS] = {0}, nb[MAX_BLOCKS] = {0}, valid[MAX_BLOCKS] = {0};   // first channel, padded and real count
     TcOperandMap maps[MAX_BLOCKS];
 };
@@ -19,7 +20,7 @@ struct ConvDirectPlan {
 // and false otherwise.
 bool conv_direct_plan(ConvDirectPlan *plan, uint64_t Cin, uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t sh, uint64_t sw);
 // Bytes of the channels-last copy of the input (channels padded to a multiple of 64).
-size_t conv_direct_input_bytes(uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W);
+size_t conv_direct_input_bytes(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W);
 // Bytes of the reordered weight buffer: per block (channels + 16) rows of padded Cin * kh * kw.
 size_t conv_direct_weight_bytes(const ConvDirectPlan &plan, uint64_t Cin, uint64_t kh, uint64_t kw);
 // Reorders w [Cout][Cin][kh][kw] block by block into wr [channels + 16][kh][kw][Cin] (the extra rows: ones, then zeros) and
@@ -28,10 +29,11 @@ cudaError_t conv_direct_prepare_weights(const uint8_t *w, uint8_t *wr, ConvDirec
                                         cudaStream_t stream);
 // Per-call eligibility: an output row and the kernel's overhang fit the 128 rows of one tile, and a ring of the tile's
 // input regions fits beside the weights.
-bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t H, uint64_t W,
-                          uint64_t Ho, uint64_t Wo);
+bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw,
+                          uint64_t H, uint64_t W, uint64_t Ho, uint64_t Wo);
 // x [B][Cin][H][W] -> xt [B][H][W][Cin rounded up to a multiple of 64] (zero channels behind the real ones).
-cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, uint64_t batches, uint64_t C, uint64_t H, uint64_t W, cudaStream_t stream);
+cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H,
+                                uint64_t W, cudaStream_t stream);
 // out [B][Cout][Ho][Wo] (or [B][Ho][Wo][Cout] with nhwc_out, 16-byte aligned) from the transposed input.  `epi`: A = input (patch sums come from the kernel itself: asum
 // unused), B = weights (bsum = their sums per output channel, bias per output channel or nullptr).
 cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,

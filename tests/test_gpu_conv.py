@@ -66,7 +66,8 @@ def test_conv_matches_oracle(cuda, oracle, shape):
     want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], ph=ph, pw=pw, sh=sh,
                                 sw=sw)
     got = _conv(cuda, ltq, c, [ltq_qp(r) for r in rows])
-    # stride 1 takes the kernel without a patch buffer whatever the channel counts (they are padded), stride 2 the patch buffer
+    # these stride-1 layers take the kernel without a patch buffer whatever the channel counts (they are padded); the 7 x 7
+    # stride-2 layer's weights and regions do not fit its shared memory and go through the patch buffer
     assert ltq.last_kernel().startswith("conv_direct_kernel<") == (sh == 1 and sw == 1), ltq.last_kernel()
     np.testing.assert_array_equal(got, want)
     # one bias per output channel (the library's option; the oracle restates the same arithmetic)
@@ -114,6 +115,39 @@ def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
             want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], bias=bias if use_bias else None,
                                         ph=ph, pw=pw, sh=1, sw=1, bias_per_channel=use_bias)
             np.testing.assert_array_equal(got, want)
+    assert ltq.lib().ltq_device_check(0, None) == 0
+
+
+@pytest.mark.parametrize("shape", [
+    # B, Cin, H, W, Cout, kh, kw, ph, pw, sh, sw
+    (2, 64, 16, 16, 32, 3, 3, 1, 1, 2, 2),       # the usual down-sampling layer: four planes of equal residues
+    (1, 32, 15, 17, 48, 3, 3, 1, 1, 2, 2),       # odd image size: the planes differ by a row / a column
+    (2, 64, 14, 14, 64, 1, 1, 0, 0, 2, 2),       # 1 x 1 kernel: only one of the four planes is read
+    (3, 8, 21, 30, 24, 3, 5, 1, 2, 2, 1),        # different strides per direction
+    (1, 64, 56, 56, 64, 3, 3, 1, 1, 2, 2),       # 28 x 28 output
+    (1, 16, 23, 23, 16, 4, 4, 0, 0, 3, 3),       # stride 3, no padding
+])
+def test_strided_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape):
+    """Strides: the channels-last copy is kept as sh * sw planes of equal residues and every kernel tap reads one plane
+    with a constant shift.  Against the oracle and the patch-buffer path, bit for bit."""
+    import ltq
+    B, Cin, H, W, Cout, kh, kw, ph, pw, sh, sw = shape
+    rng = np.random.default_rng(sum(shape))
+    c = dict(Cin=Cin, Cout=Cout, kh=kh, kw=kw, ph=ph, pw=pw, sh=sh, sw=sw,
+             x=rng.integers(0, 256, (B, Cin, H, W), dtype=np.uint8),
+             w=rng.integers(0, 256, (Cout, Cin * kh * kw), dtype=np.uint8))
+    rows = [(0.02, 128), (0.005, 127), (4.0, 3)]
+    qps = [ltq_qp(r) for r in rows]
+    bias = rng.integers(-30000, 30000, Cout, dtype=np.int32)
+    got = _conv(cuda, ltq, c, qps, flags=ltq.FLAG_BIAS_PER_CHANNEL, bias=bias)
+    assert ltq.last_kernel().startswith("conv_direct_kernel<"), ltq.last_kernel()
+    want = oracle.port.conv2d_q(c["x"], c["w"], Cout, kh, kw, *[qp_of(oracle, r) for r in rows], bias=bias, ph=ph, pw=pw, sh=sh,
+                                sw=sw, bias_per_channel=True)
+    np.testing.assert_array_equal(got, want)
+    for mode in (ltq.OUT_I32, ltq.OUT_F32):
+        a = _conv(cuda, ltq, c, qps, flags=ltq.FLAG_RELU, out_mode=mode)
+        b = _conv(cuda, ltq, c, qps, flags=ltq.FLAG_RELU | ltq.FLAG_FORCE_SIMT, out_mode=mode)
+        np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
     assert ltq.lib().ltq_device_check(0, None) == 0
 
 
