@@ -372,8 +372,8 @@ int ltq_conv2d_output_size(const ltq_conv2d *conv, uint64_t height_in, uint64_t 
  * input; where the input channels are a multiple of 64 and the output channels a multiple of 16, LTQ_FLAG_NHWC_IN
  * hands that layout in directly (no transposition pass; x_dev 16-byte aligned) and LTQ_FLAG_NHWC_OUT writes it (out_dev
  * 16-byte aligned; LTQ_FLAG_NHWC_IN needs strides 1), so that a chain of such layers never leaves it.  The values are
- * the same, only their place in memory differs.  For any other geometry, a forced kernel or the reference's
- * position-indexed bias the two flags give LTQ_ERR_UNSUPPORTED. */
+ * the same, only their place in memory differs.  For any other geometry or a forced kernel the two flags give
+ * LTQ_ERR_UNSUPPORTED. */
 int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches, uint64_t height_in, uint64_t width_in,
                        int out_mode, unsigned flags, void *out_dev, void *stream);
 

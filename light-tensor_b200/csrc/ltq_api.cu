@@ -721,13 +721,12 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     // transpose the input to NHWC, then one kernel for the whole batch.
     const bool nhwc_in = (flags & LTQ_FLAG_NHWC_IN) != 0, nhwc_out = (flags & LTQ_FLAG_NHWC_OUT) != 0;
     const bool direct = conv->direct_ready && !(flags & (LTQ_FLAG_FORCE_SIMT | LTQ_FLAG_FORCE_TC | LTQ_FLAG_FORCE_SKINNY)) &&
-                        (per_channel || !conv->bias) &&
                         conv_direct_shape_ok(conv->direct, batches, conv->Cin, conv->kh, conv->kw, conv->ph, conv->pw, height_in,
                                              width_in, Ho, Wo);
     LTQ_REQUIRE(!(nhwc_in || nhwc_out) || (direct && conv->Cin % 64 == 0 && conv->Cout % 16 == 0 && (!nhwc_in || (conv->sh == 1 && conv->sw == 1))),
                 LTQ_ERR_UNSUPPORTED,
-                "channels-last input / output is only available for the layers computed without a patch buffer (stride 1, "
-                "input channels a multiple of 64, output channels a multiple of 16, no forced kernel, bias absent or per channel)");
+                "channels-last input / output is only available for the layers computed without a patch buffer, with input "
+                "channels a multiple of 64 and output channels a multiple of 16 (input: strides 1), and no forced kernel");
     LTQ_REQUIRE(!nhwc_in || ((uintptr_t)x_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last input must be 16-byte aligned");
     LTQ_REQUIRE(!nhwc_out || ((uintptr_t)out_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last output must be 16-byte aligned");
     if (direct) {
@@ -740,7 +739,10 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
             x_cl = conv->x_nhwc;
         }
         // positions are the rows here: A = input (its patch sums come out of the kernel), B = weights
-        Epilogue epi = make_epilogue(conv->wsum, nullptr, conv->bias, conv->qp_in, conv->qp_wt, conv->qp_out, K, out_mode, flags);
+        // (bias per channel = per column here; the reference's indexing by output position = per row)
+        Epilogue epi = make_epilogue(conv->wsum, nullptr, per_channel ? conv->bias : nullptr, conv->qp_in, conv->qp_wt, conv->qp_out, K,
+                                     out_mode, flags);
+        epi.row_bias = per_channel ? nullptr : conv->bias;
         LTQ_CUDA_TRY(launch_conv_direct(x_cl, conv->direct, batches, conv->Cin, height_in, width_in, conv->Cout, conv->kh,
                                         conv->kw, conv->ph, conv->pw, Ho, Wo, epi, out_dev, nhwc_out, conv->dev->status,
                                         conv->dev->sms, st));

@@ -29,8 +29,8 @@
 // constant shift per tap, so a tile loads one region per plane in use (a 5-D tensor copy, the plane being the fifth
 // coordinate) and every tap is an MMA over its plane's region with a shifted start.
 // More than 112 output channels run as several launches over blocks of channels (each with its own ones row).
-// Everything else (rows wider than the 128 slots of a tile, regions or weights too large for shared memory, the
-// reference's position-indexed bias) keeps the patch-buffer path in ltq_conv.cu.
+// Everything else (rows wider than the 128 slots of a tile, regions or weights too large for shared memory) keeps the
+// patch-buffer path in ltq_conv.cu.
 #include <cuda.h>
 
 #include <type_traits>
@@ -330,7 +330,8 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                 tmem_ld16(taddr + g.Cout, v);             // the all-ones weight row: v[0] = sum of this position's patch bytes
                 if (cb < ce) tmem_ld16(taddr + cb, vn);
                 tmem_ld_wait();
-                const uint32_t rt = c.neg_zB * v[0] + c.bc;
+                // (epi.row_bias: the reference's bias indexing, by output position inside the image)
+                const uint32_t rt = c.neg_zB * v[0] + c.bc + (epi.row_bias && valid ? (uint32_t)epi.row_bias[(ho0 + hh) * g.Wo + wcol] : 0u);
                 OutT *d = g.nhwc_out ? o + (((size_t)b * g.Ho + ho0 + hh) * g.Wo + wcol) * g.CoutTotal + cb
                                      : o + (size_t)b * g.CoutTotal * plane + (size_t)(ho0 + hh) * g.Wo + wcol + (size_t)cb * plane;
 #pragma unroll 1

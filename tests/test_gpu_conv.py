@@ -28,6 +28,8 @@ def test_conv_matches_golden(cuda, golden, force):
     flags = ltq.FLAG_FORCE_SIMT if force == "simt" else 0
     for c in iter_conv_cases(g):
         y = _conv(cuda, ltq, c, [ltq_qp(r) for r in c["qp"]], flags=flags, bias=c["bias"])
+        # left to itself the library computes every one of the reference's cases without a patch buffer
+        assert ltq.last_kernel().startswith("conv_direct_kernel<") == (force == "auto"), (c["key"], ltq.last_kernel())
         np.testing.assert_array_equal(y, c["y"], err_msg=c["key"])
     assert ltq.lib().ltq_device_check(0, None) == 0
 
