@@ -337,22 +337,35 @@ def base_line(h, args, value, unit, ms_step, scaling, config, **extra):
     return line
 
 
-def h2d_ceiling_gbs(h, nbytes):
-    """Host->device rate of a copy of `nbytes` out of pinned memory with nothing else running, every rank at the same
-    time (GB/s, this rank; best of 5)."""
+def h2d_ceiling_gbs(h, nbytes, d2h_bytes=0, reps=6):
+    """Host->device rate (GB/s, this rank) of `reps` back-to-back copies of `nbytes` out of pinned memory, every rank
+    starting together after a barrier, so that with N ranks the figure is the rate one rank keeps while the other
+    N - 1 copy too.  With `d2h_bytes` a second stream copies that many bytes device->host at the same time, once per
+    host->device copy: the traffic pattern of the pipelined end-to-end step without any kernel in it."""
     torch = h.torch
     src = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
     dst = torch.empty(nbytes, dtype=torch.uint8, device=h.dev)
-    dst.copy_(src, non_blocking=True)
-    h.sync_all()
+    up = torch.cuda.Stream()
+    if d2h_bytes:
+        back_src = torch.empty(d2h_bytes, dtype=torch.uint8, device=h.dev)
+        back_dst = torch.empty(d2h_bytes, dtype=torch.uint8).pin_memory()
+        down = torch.cuda.Stream()
     best = 0.0
-    for _ in range(5):
+    for trial in range(3):                                   # the first trial also warms the copy engines up
+        h.sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        dst.copy_(src, non_blocking=True)
-        e1.record()
+        with torch.cuda.stream(up):
+            e0.record(up)
+            for _ in range(reps):
+                dst.copy_(src, non_blocking=True)
+            e1.record(up)
+        if d2h_bytes:
+            with torch.cuda.stream(down):
+                for _ in range(reps):
+                    back_dst.copy_(back_src, non_blocking=True)
         torch.cuda.synchronize()
-        best = max(best, nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+        if trial:
+            best = max(best, reps * nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
     return best
 
 
@@ -464,6 +477,7 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
         fc.to("cuda", h.local)
         fc.set_output(out_mode)
         ceiling = h2d_ceiling_gbs(h, M * K * 4)
+        ceiling_both = h2d_ceiling_gbs(h, M * K * 4, d2h_bytes=M * N * res["esize"])
         # Three streams (upload, compute, download) over two buffer sets: the upload of step i+1 and the download of
         # step i-1 run while step i computes, so a step costs what the slower PCIe direction costs.
         host_x = [torch.randn((M, K)).pin_memory() for _ in range(2)]
@@ -499,11 +513,25 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
             for st in (s_up, s_run, s_down):
                 torch.cuda.current_stream().wait_stream(st)
 
-        ms_e2e = h.timed(e2e_step, max(4, steps // 2), 4, graph=False, join=e2e_join)
+        # The host side of the copies (memory, PCIe switch) is shared with the machine's other tenants and its rate moves
+        # on a 100 ms scale: three timed regions of the same K steps, the fastest one is reported and all three are
+        # listed; the copy ceilings are taken again after the regions and the larger reading of each is kept.
+        k_e2e = max(8, steps // 2)
+        regions = [h.timed(e2e_step, k_e2e, 4 if r == 0 else 2, graph=False, join=e2e_join) for r in range(3)]
+        ms_e2e = min(regions)
+        ceiling = max(ceiling, h2d_ceiling_gbs(h, M * K * 4))
+        ceiling_both = max(ceiling_both, h2d_ceiling_gbs(h, M * K * 4, d2h_bytes=M * N * res["esize"]))
         h2d, d2h = M * K * 4, M * N * res["esize"]
-        res["e2e"] = {"ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+        res["e2e"] = {"ms_per_step": ms_e2e, "steps": k_e2e, "ms_per_step_of_each_region": regions,
+                      "timing": f"fastest of 3 regions of {k_e2e} steps each (CUDA events, max over ranks per region)",
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                       "pcie_gbs": {"h2d": h2d / (ms_e2e * 1e-3) / 1e9, "d2h": d2h / (ms_e2e * 1e-3) / 1e9},
                       "h2d_ceiling_gbs": ceiling, "frac_of_h2d_ceiling": h2d / (ms_e2e * 1e-3) / 1e9 / ceiling,
+                      "h2d_ceiling_with_d2h_running_gbs": ceiling_both,
+                      "frac_of_h2d_ceiling_with_d2h_running": h2d / (ms_e2e * 1e-3) / 1e9 / ceiling_both,
+                      "ceiling_method": "6 back-to-back copies of the step's bytes out of pinned memory per rank, all "
+                                        "ranks at once after a barrier, best of 2 trials; second figure with the "
+                                        "step's device->host bytes copied on another stream at the same time",
                       "bound": "host->device copy of the fp32 activations (PCIe); compute is "
                                f"{ms_step / ms_e2e * 100:.1f} % of the step",
                       "host_numa_binding": h.numa}
@@ -633,7 +661,11 @@ def run_sections(h, args, pk):
                 "path": "fused chain: Quantize + 3 layers in one launch (ltq_mlp_forward)",
                 "layer_by_layer": {"us_per_batch": r["ms_layerwise"] * 1e3, "gpu_launches_per_batch": r["launches_layerwise"],
                                    "kernels": r["kernels_layerwise"]},
-                "fused_output_equals_layer_by_layer": r["fused_equals_layerwise"]}
+                "fused_output_equals_layer_by_layer": r["fused_equals_layerwise"],
+                "batch_streams": dict(r["batch_streams"],
+                                      samples_per_s=64 * h.world / (r["batch_streams"]["us_per_batch"] * 1e-6),
+                                      what="the same chain with four independent batch streams in flight per GPU "
+                                           "(four CUDA streams, own buffers each): throughput, not latency")}
 
     def block(shard):
         def run():
@@ -868,8 +900,33 @@ def measure_mlp_mnist(h, args):
     ms_step = h.timed(step_fused, steps, args.warmup, graph=not args.no_graph, sample_clocks=True)
     launches = (ltq.kernel_launches() - launches0) // (steps + args.warmup)
     same = bool(torch.equal(y, y_ref))
+
+    # Throughput with several batches in flight: a chain launch occupies 4 clusters of 8 SMs, so independent batch
+    # streams (a server with several request queues) run side by side on the rest of the device.  Four CUDA streams, each
+    # with its own input and output buffers, batches dealt round robin; one graph holds all of them.
+    S = 4
+    steps_s = (max(steps, 40) + S - 1) // S * S
+    side = [torch.cuda.Stream() for _ in range(S)]
+    xs = [xd.clone() for _ in range(S)]
+    ys = [torch.empty_like(y) for _ in range(S)]
+    warm = max(args.warmup, S)
+
+    def step_streams(i):
+        k, cur, st = i - warm, torch.cuda.current_stream(), side[i % S]
+        if k < S:
+            st.wait_stream(cur)                                  # first batch of this stream in the timed region
+        with torch.cuda.stream(st):
+            mlp.forward(xs[i % S], flags, ltq.OUT_F32, out=ys[i % S])
+        if k < 0 or k == steps_s - 1:
+            for t in side:
+                cur.wait_stream(t)
+
+    ms_streams = h.timed(step_streams, steps_s, warm, graph=not args.no_graph)
+    same_streams = all(bool(torch.equal(t, y_ref)) for t in ys)
     hs[0].check()
     return dict(ms_step=ms_step, launches_per_step=int(launches), steps=steps, kernels=kernels_fused,
+                batch_streams={"streams": S, "us_per_batch": ms_streams * 1e3, "steps": steps_s,
+                               "outputs_equal_single_stream": same_streams},
                 ms_layerwise=ms_layerwise, launches_layerwise=int(launches_layerwise), kernels_layerwise=kernels,
                 fused_equals_layerwise=same, clocks=getattr(h, "clocks", None))
 
@@ -886,7 +943,8 @@ def run_mlp_mnist(args):
     args.steps = r["steps"]
     h.finish(base_line(h, args, ops / (r["ms_step"] * 1e-3) / 1e12 * h.world, "TOPS", r["ms_step"], "weak", cfg,
                        samples_per_s=64 * h.world / (r["ms_step"] * 1e-3), gpu_launches=r["launches_per_step"] * r["steps"],
-                       clocks=r["clocks"], kernels=r["kernels"], e2e=None, roofline=None, cpu_baseline=None))
+                       clocks=r["clocks"], kernels=r["kernels"], batch_streams=r["batch_streams"], e2e=None, roofline=None,
+                       cpu_baseline=None))
 
 
 def measure_conv(h, args, sample_clocks=False):

@@ -573,12 +573,16 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, const ConvDirectP
     uint32_t rows = (uint32_t)(NHWC_SMEM / row_bytes);
     rows = rows > NHWC_ROWS ? NHWC_ROWS : rows;
     const size_t smem = rows * row_bytes;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(nchw_to_nhwc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(nchw_to_nhwc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
+    static bool attr_done[64] = {false};                 // the opt-in shared-memory size is a per-device attribute
+    int dev = 0;
+    cudaError_t ea = cudaGetDevice(&dev);
+    if (ea != cudaSuccess) return ea;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_done[dev]) {
+        ea = cudaFuncSetAttribute(nchw_to_nhwc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
+        if (ea == cudaSuccess) ea = cudaFuncSetAttribute(nchw_to_nhwc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)NHWC_SMEM);
+        if (ea != cudaSuccess) return ea;
+        attr_done[dev] = true;
     }
     const bool one_plane = plan.sh == 1 && plan.sw == 1;
     for (uint64_t b0 = 0; b0 < batches; b0 += 65535) {
