@@ -2,7 +2,7 @@
 """Benchmark of the uint8 quantized fully-connected forward path (libltq, sm_100a).
 
     python bench.py [--gpus N] [--steps K] [--warmup W]          # everything the metric names, one JSON line
-    python bench.py --workload square_4096|skinny|mlp_block|mlp_mnist|conv [--shard rows|cols|cols_fused] ...
+    python bench.py --workload square_4096|skinny|mlp_block|mlp_mnist|conv|helpers [--shard rows|cols|cols_fused] ...
     python bench.py --impl reference ...                          # the reference's own CPU code on the host cores
 
 One JSON line on stdout (rank 0).  The headline (`value`, `ms_per_step`, `roofline`, `e2e`, `cpu_baseline`) is the
@@ -11,7 +11,8 @@ sums, static calibrated qparams as the reference uses them) followed by the quan
 `value` has the inputs resident in HBM; `e2e` is the same work through the FullyConnected_q mirror with pinned host
 buffers, host->device and device->host copies inside the timed region.  The default run also measures the other parts
 of the metric and reports them as sections of the same line: `skinny` (M = 1 / 4 / 16 weight streaming, HBM GB/s),
-`mlp_mnist` (784-512-512-10, samples/s), `mlp_block_rows` (8192-32768-8192 over 65536 tokens, row-sharded over the
+`helpers` (GetMinMax / Quantize / Dequantize and the dynamic activation step, HBM GB/s), `mlp_mnist` (784-512-512-10,
+samples/s, one batch stream and four), `conv2d_q` (the convolution layer), `mlp_block_rows` (8192-32768-8192 over 65536 tokens, row-sharded over the
 ranks, strong scaling) and, with more than one rank, `mlp_block_cols` / `mlp_block_cols_fused` (column-sharded with an
 NCCL all-gather, and with the exchange fused into the GEMM epilogue).
 """
@@ -338,10 +339,12 @@ def base_line(h, args, value, unit, ms_step, scaling, config, **extra):
 
 
 def h2d_ceiling_gbs(h, nbytes, d2h_bytes=0, reps=6):
-    """Host->device rate (GB/s, this rank) of `reps` back-to-back copies of `nbytes` out of pinned memory, every rank
-    starting together after a barrier, so that with N ranks the figure is the rate one rank keeps while the other
-    N - 1 copy too.  With `d2h_bytes` a second stream copies that many bytes device->host at the same time, once per
-    host->device copy: the traffic pattern of the pipelined end-to-end step without any kernel in it."""
+    """Host->device rate (GB/s, this rank) of copies of `nbytes` out of pinned memory, every rank starting together
+    after a barrier, so that with N ranks the figure is the rate one rank keeps while the other N - 1 copy too.  Two
+    ways of issuing them, the better reading counts (which one wins differs from box to box): one copy at a time on
+    the current stream, and `reps` copies back to back on a stream of their own.  With `d2h_bytes` another stream
+    copies that many bytes device->host at the same time, once per host->device copy: the traffic pattern of the
+    pipelined end-to-end step without any kernel in it."""
     torch = h.torch
     src = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
     dst = torch.empty(nbytes, dtype=torch.uint8, device=h.dev)
@@ -351,21 +354,30 @@ def h2d_ceiling_gbs(h, nbytes, d2h_bytes=0, reps=6):
         back_dst = torch.empty(d2h_bytes, dtype=torch.uint8).pin_memory()
         down = torch.cuda.Stream()
     best = 0.0
-    for trial in range(3):                                   # the first trial also warms the copy engines up
+    awake = torch.cuda.Stream() if hasattr(torch.cuda, "_sleep") else None
+    for trial in range(5):                                   # the first trial also warms the copy engines up
+        single = trial % 2 == 1
+        n = 1 if single else reps
         h.sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(up):
-            e0.record(up)
-            for _ in range(reps):
+        st = torch.cuda.current_stream() if single else up
+        if awake is not None:
+            # one CTA spinning for about as long as the copies take: an otherwise idle GPU gave copy rates well below
+            # the ones the end-to-end step reaches with kernels running beside its copies
+            with torch.cuda.stream(awake):
+                torch.cuda._sleep(int(n * nbytes / 20e9 * 1.5e9))
+        with torch.cuda.stream(st):
+            e0.record(st)
+            for _ in range(n):
                 dst.copy_(src, non_blocking=True)
-            e1.record(up)
+            e1.record(st)
         if d2h_bytes:
             with torch.cuda.stream(down):
-                for _ in range(reps):
+                for _ in range(n):
                     back_dst.copy_(back_src, non_blocking=True)
         torch.cuda.synchronize()
         if trial:
-            best = max(best, reps * nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+            best = max(best, n * nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
     return best
 
 
@@ -514,24 +526,26 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
                 torch.cuda.current_stream().wait_stream(st)
 
         # The host side of the copies (memory, PCIe switch) is shared with the machine's other tenants and its rate moves
-        # on a 100 ms scale: three timed regions of the same K steps, the fastest one is reported and all three are
+        # on a 100 ms scale: five timed regions of the same K steps, the fastest one is reported and all five are
         # listed; the copy ceilings are taken again after the regions and the larger reading of each is kept.
         k_e2e = max(8, steps // 2)
-        regions = [h.timed(e2e_step, k_e2e, 4 if r == 0 else 2, graph=False, join=e2e_join) for r in range(3)]
+        regions = [h.timed(e2e_step, k_e2e, 4 if r == 0 else 2, graph=False, join=e2e_join) for r in range(5)]
         ms_e2e = min(regions)
         ceiling = max(ceiling, h2d_ceiling_gbs(h, M * K * 4))
         ceiling_both = max(ceiling_both, h2d_ceiling_gbs(h, M * K * 4, d2h_bytes=M * N * res["esize"]))
         h2d, d2h = M * K * 4, M * N * res["esize"]
         res["e2e"] = {"ms_per_step": ms_e2e, "steps": k_e2e, "ms_per_step_of_each_region": regions,
-                      "timing": f"fastest of 3 regions of {k_e2e} steps each (CUDA events, max over ranks per region)",
+                      "timing": f"fastest of 5 regions of {k_e2e} steps each (CUDA events, max over ranks per region)",
                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                       "pcie_gbs": {"h2d": h2d / (ms_e2e * 1e-3) / 1e9, "d2h": d2h / (ms_e2e * 1e-3) / 1e9},
-                      "h2d_ceiling_gbs": ceiling, "frac_of_h2d_ceiling": h2d / (ms_e2e * 1e-3) / 1e9 / ceiling,
-                      "h2d_ceiling_with_d2h_running_gbs": ceiling_both,
-                      "frac_of_h2d_ceiling_with_d2h_running": h2d / (ms_e2e * 1e-3) / 1e9 / ceiling_both,
-                      "ceiling_method": "6 back-to-back copies of the step's bytes out of pinned memory per rank, all "
-                                        "ranks at once after a barrier, best of 2 trials; second figure with the "
-                                        "step's device->host bytes copied on another stream at the same time",
+                      "h2d_ceiling_gbs": max(ceiling, ceiling_both),
+                      "frac_of_h2d_ceiling": h2d / (ms_e2e * 1e-3) / 1e9 / max(ceiling, ceiling_both),
+                      "h2d_copy_rates_gbs": {"alone": ceiling, "with_d2h_running": ceiling_both},
+                      "ceiling_method": "plain copies of the step's upload out of pinned memory, all ranks at once after "
+                                        "a barrier, singly and 6 back to back, one CTA kept spinning so that the GPU is "
+                                        "not idle, before and after the timed regions; `alone` = nothing else running, "
+                                        "`with_d2h_running` = the step's download bytes copied on another stream at the "
+                                        "same time; the ceiling is the best reading of all",
                       "bound": "host->device copy of the fp32 activations (PCIe); compute is "
                                f"{ms_step / ms_e2e * 100:.1f} % of the step",
                       "host_numa_binding": h.numa}
@@ -615,7 +629,7 @@ def run_linear(args, h=None, sections=False):
                        roofline=roof, cpu_baseline=cpu, e2e=e2e, gpu_launches=r["launches"], clocks=r["clocks"], **extra))
 
 
-def run_sections(h, args, pk):
+def run_sections(h, args, pk, only=None):
     """The parts of the metric beside the headline: skinny M = 1 / 4 / 16 (HBM GB/s), the MNIST-shaped MLP (samples/s)
     and the 8192-32768-8192 block sharded over the ranks.  Each section is timed like the headline (CUDA graph, events,
     max over ranks); a section that fails reports its error instead of taking the line down."""
@@ -698,7 +712,58 @@ def run_sections(h, args, pk):
                 "through_patch_buffer_us": r["through_patch_buffer"]["ms"] * 1e3,
                 "through_patch_buffer_kernel": r["through_patch_buffer"]["kernel"]}
 
+    def helpers():
+        """The per-tensor helpers beside the layers (GetMinMax, Quantize, Dequantize: one streaming pass each) and the
+        dynamic activation step built from them, on the 4096 x 4096 activation block; 6 rotating sets (384 MB of fp32)."""
+        import ltq
+        torch, dev = h.torch, h.dev
+        n, sets = 4096 * 4096, 6
+        xs = [torch.randn((4096, 4096), device=dev) for _ in range(sets)]
+        qs = [torch.empty((4096, 4096), dtype=torch.uint8, device=dev) for _ in range(sets)]
+        sums = torch.empty(4096, dtype=torch.int32, device=dev)
+        mm = torch.empty(2, device=dev)
+        qpd = torch.zeros(8, dtype=torch.uint8, device=dev)
+        qp = ltq.QParams(0.04, 128)
+
+        def f_minmax(i):
+            ltq.GetMinMax(xs[i % sets], out=mm)
+
+        def f_quant(i):
+            ltq.Quantize(xs[i % sets], qp, out=qs[i % sets])
+
+        def f_dequant(i):
+            ltq.Dequantize(qs[i % sets], qp, out=xs[i % sets])
+
+        def f_dynamic(i):   # GetMinMax -> ComputeQuantizationParams (device) -> quantize_rows with the device parameters
+            ltq.GetMinMax(xs[i % sets], out=mm)
+            ltq.compute_qparams_dev(mm, out=qpd)
+            ltq.quantize_rows(xs[i % sets], qp_dev=qpd, q=qs[i % sets], asum=sums)
+
+        c_src = [torch.empty(5 * n // 2, dtype=torch.uint8, device=dev) for _ in range(sets)]
+        c_dst = [torch.empty(5 * n // 2, dtype=torch.uint8, device=dev) for _ in range(sets)]
+
+        def f_copy(i):      # a plain device copy that moves the same 5 bytes per element: what a job of this size can reach
+            c_dst[i % sets].copy_(c_src[i % sets])
+
+        res = {"config": "4096 x 4096 fp32 block (64 MiB), 6 rotating sets; GB/s = algorithmic bytes / time, "
+                         "frac_of_measured against the measured copy rate (taken on buffers of gigabytes); "
+                         "device_copy_same_bytes = torch's device-to-device copy moving the bytes of quantize_u8 / "
+                         "dequantize, timed the same way: the rate a streaming job of this size reaches"}
+        for name, fn, nbytes in (("get_min_max", f_minmax, 4 * n), ("quantize_u8", f_quant, 5 * n),
+                                 ("dynamic_quantize_rows", f_dynamic, 9 * n + 4 * 4096), ("dequantize", f_dequant, 5 * n),
+                                 ("device_copy_same_bytes", f_copy, 5 * n)):
+            ms = h.timed(fn, 24, 3, graph=not args.no_graph)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            res[name] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured": gbs / pk["hbm_gbs"], "algorithmic_bytes": nbytes}
+        res["dynamic_quantize_rows"]["what"] = ("GetMinMax + ComputeQuantizationParams on the device + quantize_rows "
+                                                "reading the parameters from device memory: the fp32 block is read twice")
+        return res
+
+    if only == "helpers":
+        guarded("helpers", helpers)
+        return out
     guarded("skinny", skinny)
+    guarded("helpers", helpers)
     guarded("mlp_mnist", mnist)
     guarded("conv2d_q", conv)
     guarded("mlp_block_rows", block("rows"))
@@ -1024,13 +1089,29 @@ def run_conv(args):
                        clocks=getattr(h, "clocks", None), e2e=None, roofline=None, cpu_baseline=None))
 
 
+def run_helpers(args):
+    """The per-tensor helpers alone (GetMinMax, Quantize, Dequantize, the dynamic activation step): the `helpers` section
+    of the default line as a line of its own, for profiling runs."""
+    h = Harness(args)
+    pk = peaks()
+    r = run_sections(h, args, pk, only="helpers")["helpers"]
+    if "error" in r:
+        raise RuntimeError(r["error"])
+    d = r["dynamic_quantize_rows"]
+    cfg = {"workload": "helpers: GetMinMax / Quantize / Dequantize / dynamic quantize_rows on a 4096 x 4096 fp32 block",
+           "l2": "6 rotating sets (384 MB of fp32)", "timing": "CUDA graph replay" if not args.no_graph else "eager launches"}
+    args.steps = 24
+    h.finish(base_line(h, args, d["gbs"] * h.world, "GB/s", d["us"] * 1e-3, "weak", cfg, helpers=r, gpu_launches=24 * 6,
+                       e2e=None, roofline=None, cpu_baseline=None))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ltq", choices=["ltq", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "square_4096", "skinny", "mlp_block", "mlp_mnist", "conv"],
+    ap.add_argument("--workload", default="all", choices=["all", "square_4096", "skinny", "mlp_block", "mlp_mnist", "conv", "helpers"],
                     help="all (default): the 4096^3 headline plus the skinny / mlp_mnist / mlp_block sections")
     ap.add_argument("--m", type=int, default=16, help="rows for the skinny workload (1, 4 or 16)")
     ap.add_argument("--m-total", type=int, default=65536, help="tokens of the mlp_block workload (all ranks together)")
@@ -1051,6 +1132,8 @@ def main():
         run_mlp_mnist(args)
     elif args.workload == "conv":
         run_conv(args)
+    elif args.workload == "helpers":
+        run_helpers(args)
     else:
         run_linear(args, sections=args.workload == "all")
 

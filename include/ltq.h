@@ -80,7 +80,11 @@ const char *ltq_last_kernel(void);
 
 /* ---- quantisation helpers (replace l-ten/utils.h:23-27 for device data) -------------------------------------- */
 
-/* GetMinMax, l-ten/utils.cpp:198-226.  minmax_dev[0]=min, [1]=max (floats, device).  len >= 1. */
+/* GetMinMax, l-ten/utils.cpp:198-226.  minmax_dev[0]=min, [1]=max (floats, device).  len >= 1.  NaNs behave as in the
+ * reference's compare-and-replace loop: a NaN in data[0] makes both results NaN, NaNs elsewhere are skipped.  When the
+ * minimum or maximum is a zero and the data hold zeros of both signs, the reference returns the one met first; which of
+ * the two this call returns is unspecified (they are equal as numbers, and ComputeQuantizationParams maps both to the
+ * same result). */
 int ltq_get_min_max(const float *data_dev, uint64_t len, float *minmax_dev, int device, void *stream);
 
 /* ComputeQuantizationParams, l-ten/utils.cpp:266-286.  Pure host arithmetic on two scalars.

@@ -40,7 +40,10 @@ __device__ __forceinline__ float ord2f(uint32_t u)
 // single byte-fill initialises them.
 __global__ void __launch_bounds__(256) minmax_reduce_kernel(const float *__restrict__ x, uint64_t len, uint32_t *slot)
 {
-    uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+    griddep_launch_dependents();   // the decoding kernel behind may be scheduled; it waits for this grid to finish
+    // fminf / fmaxf return the other operand when one is NaN: NaNs never replace a minimum or maximum, as in the
+    // reference's compare-and-replace loop.  +inf / -inf as seeds: lo > hi at the end means nothing was comparable.
+    float lo = __int_as_float(0x7F800000), hi = __int_as_float(0xFF800000);
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
     // 16-byte body when the base pointer allows it, scalar head/tail otherwise.
@@ -49,24 +52,27 @@ __global__ void __launch_bounds__(256) minmax_reduce_kernel(const float *__restr
     const uint64_t nvec = (len - head) / 4;
     const float4 *xv = reinterpret_cast<const float4 *>(x + head);
     auto upd = [&](float v) {
-        if (v == v) {  // comparisons with NaN are false in the reference, so NaNs never replace min/max
-            uint32_t o = f2ord(v);
-            lo = o < lo ? o : lo;
-            hi = o > hi ? o : hi;
-        }
+        lo = fminf(lo, v);
+        hi = fmaxf(hi, v);
     };
-    for (uint64_t i = tid; i < nvec; i += nth) {
-        float4 v = __ldg(xv + i);
+    auto upd4 = [&](const float4 &v) {
         upd(v.x); upd(v.y); upd(v.z); upd(v.w);
+    };
+    // four independent 16-byte loads per thread before any arithmetic (the pass lives on bytes in flight), then the rest
+    uint64_t i = tid;
+    for (; i + 3 * nth < nvec; i += 4 * nth) {
+        const float4 a = __ldg(xv + i), b = __ldg(xv + i + nth), c = __ldg(xv + i + 2 * nth), d = __ldg(xv + i + 3 * nth);
+        upd4(a); upd4(b); upd4(c); upd4(d);
     }
-    for (uint64_t i = tid; i < head; i += nth) upd(x[i]);
-    for (uint64_t i = head + nvec * 4 + tid; i < len; i += nth) upd(x[i]);
+    for (; i < nvec; i += nth) upd4(__ldg(xv + i));
+    for (uint64_t k = tid; k < head; k += nth) upd(x[k]);
+    for (uint64_t k = head + nvec * 4 + tid; k < len; k += nth) upd(x[k]);
 
     for (int o = 16; o; o >>= 1) {
-        lo = min(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, o));
-        hi = max(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, o));
+        lo = fminf(lo, __shfl_xor_sync(0xFFFFFFFFu, lo, o));
+        hi = fmaxf(hi, __shfl_xor_sync(0xFFFFFFFFu, hi, o));
     }
-    __shared__ uint32_t slo[8], shi[8];
+    __shared__ float slo[8], shi[8];
     if ((threadIdx.x & 31) == 0) {
         slo[threadIdx.x >> 5] = lo;
         shi[threadIdx.x >> 5] = hi;
@@ -76,38 +82,58 @@ __global__ void __launch_bounds__(256) minmax_reduce_kernel(const float *__restr
         lo = slo[threadIdx.x];
         hi = shi[threadIdx.x];
         for (int o = 4; o; o >>= 1) {
-            lo = min(lo, __shfl_xor_sync(0xFFu, lo, o));
-            hi = max(hi, __shfl_xor_sync(0xFFu, hi, o));
+            lo = fminf(lo, __shfl_xor_sync(0xFFu, lo, o));
+            hi = fmaxf(hi, __shfl_xor_sync(0xFFu, hi, o));
         }
-        if (threadIdx.x == 0) {
-            if (lo != 0xFFFFFFFFu) atomicMin(slot, lo);
-            if (hi != 0u) atomicMin(slot + 1, ~hi);
+        // Everything above only read x, which was complete before the kernel that seeds the slots started; the slots
+        // themselves are ready once that kernel has finished.
+        griddep_wait();
+        if (threadIdx.x == 0 && lo <= hi) {   // something comparable was seen by this CTA
+            atomicMin(slot, f2ord(lo));
+            atomicMin(slot + 1, ~f2ord(hi));
         }
     }
 }
 
-// Decodes the two slots in place into floats {min, max}.  An input with no comparable element (all NaN) keeps the
-// reference's seed, data[0].
+// Seeds the two slots.  A kernel rather than a memset so that the reduction can be its programmatic dependent and stream
+// the data while this one is still being scheduled.
+__global__ void minmax_seed_kernel(uint32_t *slot)
+{
+    griddep_launch_dependents();
+    slot[0] = 0xFFFFFFFFu;
+    slot[1] = 0xFFFFFFFFu;
+}
+
+// Decodes the two slots in place into floats {min, max}.  The reference seeds both with data[0] and replaces them only
+// when a comparison is true: an input with no comparable element (all NaN) keeps the seed, and so does an input whose
+// first element is NaN, whatever follows (every comparison with the NaN seed is false).
 __global__ void minmax_decode_kernel(uint32_t *slot, const float *x)
 {
+    griddep_wait();                // launched as a programmatic dependent of the reduction
     uint32_t a = slot[0], b = slot[1];
-    float mn = (a == 0xFFFFFFFFu) ? x[0] : ord2f(a);
-    float mx = (b == 0xFFFFFFFFu) ? x[0] : ord2f(~b);
+    const float seed = x[0];
+    const bool seed_nan = seed != seed;
+    float mn = (a == 0xFFFFFFFFu || seed_nan) ? seed : ord2f(a);
+    float mx = (b == 0xFFFFFFFFu || seed_nan) ? seed : ord2f(~b);
     reinterpret_cast<float *>(slot)[0] = mn;
     reinterpret_cast<float *>(slot)[1] = mx;
 }
 
 cudaError_t launch_min_max(const float *data, uint64_t len, float *minmax, cudaStream_t stream)
 {
-    cudaError_t e = cudaMemsetAsync(minmax, 0xFF, 8, stream);
-    if (e != cudaSuccess) return e;
     uint64_t want = (len / 4 + 255) / 256;
     uint64_t cap = (uint64_t)sm_count() * 8;
     int blocks = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-    minmax_reduce_kernel<<<blocks, 256, 0, stream>>>(data, len, reinterpret_cast<uint32_t *>(minmax));
-    minmax_decode_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<uint32_t *>(minmax), data);
-    count_launch(2);
-    return cudaGetLastError();
+    // seed (ordinary launch: starts after everything before it in the stream) -> reduction -> decoding, the last two as
+    // programmatic dependents: one launch latency instead of three
+    minmax_seed_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<uint32_t *>(minmax));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    e = launch_chained(minmax_reduce_kernel, dim3(blocks), dim3(256), 0, stream, data, len, reinterpret_cast<uint32_t *>(minmax));
+    if (e != cudaSuccess) return e;
+    e = launch_chained(minmax_decode_kernel, dim3(1), dim3(1), 0, stream, reinterpret_cast<uint32_t *>(minmax), data);
+    count_launch(3);
+    return e;
 }
 
 // ---- qparams from min/max, l-ten/utils.cpp:266-286 -------------------------------------------------------------
@@ -151,9 +177,17 @@ __global__ void __launch_bounds__(256) quantize_u8_kernel(const float *__restric
     const bool aligned = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
     uint64_t nvec = aligned ? len / 4 : 0;
     const float inv = quant_screen_inv(scale);
-    for (uint64_t i = tid; i < nvec; i += nth) {
-        reinterpret_cast<uint32_t *>(q)[i] = quant4_u8(__ldg(reinterpret_cast<const float4 *>(x) + i), scale, zpf, inv);
+    const float4 *xv = reinterpret_cast<const float4 *>(x);
+    uint32_t *qv = reinterpret_cast<uint32_t *>(q);
+    uint64_t i = tid;
+    for (; i + 3 * nth < nvec; i += 4 * nth) {   // four loads in flight per thread, as in quantize_rows_kernel
+        const float4 a = __ldcs(xv + i), b = __ldcs(xv + i + nth), c = __ldcs(xv + i + 2 * nth), d = __ldcs(xv + i + 3 * nth);
+        qv[i] = quant4_u8(a, scale, zpf, inv);
+        qv[i + nth] = quant4_u8(b, scale, zpf, inv);
+        qv[i + 2 * nth] = quant4_u8(c, scale, zpf, inv);
+        qv[i + 3 * nth] = quant4_u8(d, scale, zpf, inv);
     }
+    for (; i < nvec; i += nth) qv[i] = quant4_u8(__ldcs(xv + i), scale, zpf, inv);
     for (uint64_t i = nvec * 4 + tid; i < len; i += nth) q[i] = (uint8_t)quant_u8(x[i], scale, zpf, inv);
 }
 
@@ -172,15 +206,25 @@ __global__ void __launch_bounds__(256) dequantize_kernel(float *__restrict__ x, 
     const uint64_t nth = (uint64_t)gridDim.x * blockDim.x;
     const bool aligned = (((uintptr_t)x & 15) == 0) && (((uintptr_t)q & 3) == 0);
     uint64_t nvec = aligned ? len / 4 : 0;
-    for (uint64_t i = tid; i < nvec; i += nth) {
-        uint32_t p = __ldg(reinterpret_cast<const uint32_t *>(q) + i);
+    auto widen = [&](uint32_t p) {
         float4 v;
         v.x = __fmul_rn(scale, (float)((int)(p & 0xFF) - zp));
         v.y = __fmul_rn(scale, (float)((int)((p >> 8) & 0xFF) - zp));
         v.z = __fmul_rn(scale, (float)((int)((p >> 16) & 0xFF) - zp));
         v.w = __fmul_rn(scale, (float)((int)(p >> 24) - zp));
-        reinterpret_cast<float4 *>(x)[i] = v;
+        return v;
+    };
+    const uint32_t *qv = reinterpret_cast<const uint32_t *>(q);
+    float4 *xv = reinterpret_cast<float4 *>(x);
+    uint64_t i = tid;
+    for (; i + 3 * nth < nvec; i += 4 * nth) {   // loads first: four words in flight per thread
+        const uint32_t a = __ldcs(qv + i), b = __ldcs(qv + i + nth), c = __ldcs(qv + i + 2 * nth), d = __ldcs(qv + i + 3 * nth);
+        xv[i] = widen(a);
+        xv[i + nth] = widen(b);
+        xv[i + 2 * nth] = widen(c);
+        xv[i + 3 * nth] = widen(d);
     }
+    for (; i < nvec; i += nth) xv[i] = widen(__ldcs(qv + i));
     for (uint64_t i = nvec * 4 + tid; i < len; i += nth) x[i] = __fmul_rn(scale, (float)((int)q[i] - zp));
 }
 
@@ -215,7 +259,8 @@ cudaError_t launch_dequantize(float *x, const uint8_t *q, uint64_t len, const lt
 // ---- activation quantise + row sums -------------------------------------------------------------------------------
 // TPR threads cooperate on one row (TPR = 32: a warp; TPR = 256: the whole CTA).  Reads fp32 once, writes uint8 once
 // and one int32 per row: 5 bytes per element of HBM traffic, the minimum for this step.
-template <int TPR>
+// BACK_TO_FRONT: rows are visited last to first (see the loop below).
+template <int TPR, bool BACK_TO_FRONT>
 __global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__restrict__ x, uint64_t M, uint64_t K,
                                                             float scale_h, float zpf_h,
                                                             const ltq_qparams *__restrict__ qp_dev,
@@ -234,9 +279,13 @@ __global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__re
     const int lane = threadIdx.x % TPR;
     const int sub = threadIdx.x / TPR;
     __shared__ int32_t warp_part[8];
-    for (uint64_t row = (uint64_t)blockIdx.x * ROWS_PER_CTA + sub; ; row += (uint64_t)gridDim.x * ROWS_PER_CTA) {
-        // All threads of a CTA leave together when TPR == 256 (row is uniform); with TPR == 32 a warp leaves alone.
-        if (row >= M) break;
+    // BACK_TO_FRONT is chosen when the parameters come from device memory: as a rule they were computed from this very
+    // tensor a moment ago (GetMinMax, then ComputeQuantizationParams), that pass went through the rows front to back,
+    // and its last rows are what L2 still holds; going back to front reads those from L2 instead of HBM.
+    for (uint64_t slot = (uint64_t)blockIdx.x * ROWS_PER_CTA + sub; ; slot += (uint64_t)gridDim.x * ROWS_PER_CTA) {
+        // All threads of a CTA leave together when TPR == 256 (slot is uniform); with TPR == 32 a warp leaves alone.
+        if (slot >= M) break;
+        const uint64_t row = BACK_TO_FRONT ? M - 1 - slot : slot;
         const float *xr = x + row * K;
         uint8_t *qr = q + row * K;
         const bool aligned = (((uintptr_t)xr & 15) == 0) && (((uintptr_t)qr & 3) == 0);
@@ -297,10 +346,12 @@ cudaError_t launch_quantize_rows(const float *x, uint64_t M, uint64_t K, const l
     if (K <= 2048) {
         uint64_t want = (M + 7) / 8;
         int blocks = (int)(want > cap ? cap : want);
-        e = launch_chained(quantize_rows_kernel<32>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
+        e = qp_dev ? launch_chained(quantize_rows_kernel<32, true>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum)
+                   : launch_chained(quantize_rows_kernel<32, false>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
     } else {
         int blocks = (int)(M > cap ? cap : M);
-        e = launch_chained(quantize_rows_kernel<256>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
+        e = qp_dev ? launch_chained(quantize_rows_kernel<256, true>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum)
+                   : launch_chained(quantize_rows_kernel<256, false>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
     }
     count_launch();
     return e;

@@ -29,12 +29,18 @@ __device__ __forceinline__ float quant_screen_inv(float scale)
     return (scale > 1e-30f && scale < 1e30f) ? __fdiv_rn(1.f, scale) : 0.f;
 }
 
+// How far the screened value may lie from the reference's.  With t = x / scale + zpf in exact arithmetic, the reference
+// computes fl(zpf + fl(x / scale)) and the screen fl(x * fl(1 / scale) + zpf) (or the same with one rounding less): each
+// is within (|x / scale| + |t|) * 2^-24 of t, and wherever a rounding boundary of the clamp range [0, 255] is in reach
+// both magnitudes are below 256, so the two values differ by less than 2 * 512 * 2^-24 = 6.2e-5.  A screened value
+// farther than SCREEN_MARGIN (twice that) from every half-integer k + 0.5 therefore rounds to the same byte as the
+// reference's (clamping is monotone and its edges 0 and 255 are themselves 0.5 away from the nearest boundary).
+constexpr float SCREEN_MARGIN = 1.2e-4f;
+constexpr float SCREEN_FAR = 0.5f - SCREEN_MARGIN;   // |v - nearest integer| up to here is safe
+
 // Same result as quant_u8_exact, usually without the division (these kernels are bound by instruction issue, not by
-// HBM, and an IEEE division is half of their instructions).  x * (1/scale) differs from x / scale by at most 2^-22
-// relative; inside the clamp range that is less than 1.3e-4 absolute on v, so whenever the screened v lies farther than
-// 4e-4 from every half-integer k + 0.5 both round to the same byte (clamping is monotone and its edges 0 and 255 are
-// themselves 0.5 away from the nearest rounding boundary).  Elements closer than that, a few in ten thousand, take the
-// exact path.
+// HBM, and an IEEE division is half of their instructions).  Elements within SCREEN_MARGIN of a rounding boundary, a
+// few in ten thousand, take the exact path.
 __device__ __forceinline__ uint32_t quant_u8(float x, float scale, float zpf, float inv)
 {
     if (inv == 0.f) return quant_u8_exact(x, scale, zpf);
@@ -43,22 +49,33 @@ __device__ __forceinline__ uint32_t quant_u8(float x, float scale, float zpf, fl
     const float big = __fadd_rn(v, 8388608.f);
     const float r = __fadd_rn(big, -8388608.f);            // nearest integer, |v - r| <= 0.5
     const float d = fabsf(__fsub_rn(v, r));
-    if (__fsub_rn(0.5f, d) < 4e-4f) return quant_u8_exact(x, scale, zpf);
+    if (d > SCREEN_FAR) return quant_u8_exact(x, scale, zpf);
     return __float_as_uint(big) & 0xFFu;
 }
 
-// The reference's sequence for four elements.  Rarely taken (a few warps in a hundred): kept out of line so that its four
-// divisions cost the callers' hot loops neither registers nor instruction-cache room.
-static __device__ __noinline__ uint32_t quant4_u8_exact(float4 x, float scale, float zpf)
+// The rarely taken branch of quant4_u8 (a warp enters it when any of its 128 elements is within SCREEN_MARGIN of a
+// rounding boundary: two or three warps in a hundred): only the elements that are close get the reference's sequence
+// with its division - as a rule one of the four - the others keep the screened byte.  Out of line so that it costs the
+// callers' hot loops neither registers nor instruction-cache room.  inv == 0 (no screening possible): all four exact.
+static __device__ __noinline__ uint32_t quant4_u8_careful(float4 x, float scale, float zpf, float inv)
 {
-    return quant_u8_exact(x.x, scale, zpf) | (quant_u8_exact(x.y, scale, zpf) << 8) |
-           (quant_u8_exact(x.z, scale, zpf) << 16) | (quant_u8_exact(x.w, scale, zpf) << 24);
+    uint32_t out = 0;
+    const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float v = fmaxf(0.f, fminf(255.f, fmaf(xs[k], inv, zpf)));
+        const float b = __fadd_rn(v, 8388608.f);
+        const float d = fabsf(__fsub_rn(v, __fadd_rn(b, -8388608.f)));
+        uint32_t byte = __float_as_uint(b) & 0xFFu;
+        if (inv == 0.f || d > SCREEN_FAR) byte = quant_u8_exact(xs[k], scale, zpf);
+        out |= byte << (8 * k);
+    }
+    return out;
 }
 
 // Four elements at once, packed little-endian into one word.  The screening value may come from a fused multiply-add
-// (it only has to be within 1.3e-4 of the reference's v, and an FMA is closer than separate roundings); the bytes are
-// taken from the low mantissa bytes of v + 2^23 with three byte permutes.  If any of the four lies within 4e-4 of a
-// rounding boundary, all four are redone with the reference's exact sequence.
+// (one rounding less than separate operations); the bytes are taken from the low mantissa bytes of v + 2^23 with three
+// byte permutes.
 __device__ __forceinline__ uint32_t quant4_u8(float4 x, float scale, float zpf, float inv)
 {
     if (inv != 0.f) {
@@ -69,14 +86,14 @@ __device__ __forceinline__ uint32_t quant4_u8(float4 x, float scale, float zpf, 
         const float d0 = __fsub_rn(v0, __fadd_rn(b0, -8388608.f)), d1 = __fsub_rn(v1, __fadd_rn(b1, -8388608.f));
         const float d2 = __fsub_rn(v2, __fadd_rn(b2, -8388608.f)), d3 = __fsub_rn(v3, __fadd_rn(b3, -8388608.f));
         // one comparison on the largest distance (four short-circuited comparisons are four branches)
-        const bool near = fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))) > 0.4996f;
+        const bool near = fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3))) > SCREEN_FAR;
         if (!near) {
             const uint32_t lo = __byte_perm(__float_as_uint(b0), __float_as_uint(b1), 0x0040);  // bytes b0[0], b1[0]
             const uint32_t hi = __byte_perm(__float_as_uint(b2), __float_as_uint(b3), 0x0040);
             return __byte_perm(lo, hi, 0x5410);
         }
     }
-    return quant4_u8_exact(x, scale, zpf);
+    return quant4_u8_careful(x, scale, zpf, inv);
 }
 
 }  // namespace ltq

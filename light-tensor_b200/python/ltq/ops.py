@@ -18,11 +18,13 @@ def _dev(t):
     return t.device.index if t.device.index is not None else torch.cuda.current_device()
 
 
-def GetMinMax(data):
-    """l-ten/utils.cpp:198-226 on a float32 CUDA tensor.  Returns a 2-element float32 CUDA tensor {min, max}."""
+def GetMinMax(data, out=None):
+    """l-ten/utils.cpp:198-226 on a float32 CUDA tensor.  Returns a 2-element float32 CUDA tensor {min, max} (`out` if
+    given: a loop that must not allocate passes its own)."""
     assert data.dtype == torch.float32
     d = _dev(data)
-    out = torch.empty(2, dtype=torch.float32, device=data.device)
+    if out is None:
+        out = torch.empty(2, dtype=torch.float32, device=data.device)
     check(lib().ltq_get_min_max(data.data_ptr(), data.numel(), out.data_ptr(), d, _stream(data)))
     return out
 
@@ -34,10 +36,12 @@ def ComputeQuantizationParams(min_val, max_val):
     return qp
 
 
-def compute_qparams_dev(minmax):
-    """Same rule evaluated on the device: returns an 8-byte CUDA buffer laid out as QParams."""
+def compute_qparams_dev(minmax, out=None):
+    """Same rule evaluated on the device: returns an 8-byte CUDA buffer laid out as QParams (`out` if given; its padding
+    bytes are left as they are)."""
     d = _dev(minmax)
-    out = torch.zeros(8, dtype=torch.uint8, device=minmax.device)
+    if out is None:
+        out = torch.zeros(8, dtype=torch.uint8, device=minmax.device)
     check(lib().ltq_compute_qparams_dev(minmax.data_ptr(), out.data_ptr(), d, _stream(minmax)))
     return out
 

@@ -71,6 +71,58 @@ def test_unaligned_views(cuda, oracle):
     np.testing.assert_array_equal(ltq.row_sums(m).cpu().numpy(), m.cpu().numpy().astype(np.int64).sum(1))
 
 
+def test_quantize_at_the_rounding_boundaries(cuda, oracle):
+    """The device kernels screen with a multiplication and fall back to the reference's division only near a rounding
+    boundary.  Inputs that sit on, and a few float steps either side of, every boundary k + 0.5 (and the clamp edges)
+    for many scales and zero points must give the reference's bytes (l-ten/utils.cpp:243-254)."""
+    import ltq
+    rng = np.random.default_rng(2024)
+    scales = np.concatenate([rng.uniform(1e-3, 0.3, 40), 10.0 ** rng.uniform(-6, 3, 40), [0.1, 0.25, 1.0, 3.0, 1 / 3]]).astype(np.float32)
+    ks = np.arange(-2, 258, dtype=np.float32) + np.float32(0.5)                   # every boundary, and beyond both clamp edges
+    steps = np.arange(-6, 7)
+    for scale in scales:
+        zp = int(rng.integers(0, 256))
+        x0 = ((ks - np.float32(zp)) * scale).astype(np.float32)
+        xs = [x0]
+        up, down = x0.copy(), x0.copy()
+        for _ in range(6):
+            up = np.nextafter(up, np.float32(np.inf)).astype(np.float32)
+            down = np.nextafter(down, np.float32(-np.inf)).astype(np.float32)
+            xs += [up.copy(), down.copy()]
+        x = np.concatenate(xs + [np.float32([0.0, -0.0, 1e30, -1e30])])
+        x = np.resize(x, (x.size + 127) // 128 * 128).reshape(-1, 128).copy()    # rows of 128 for quantize_rows
+        oq = oracle.qp(scale, zp)
+        want = oracle.port.quantize_u8(x, oq)
+        xd = cuda.from_numpy(x).cuda()
+        qp = ltq.QParams(float(scale), zp)
+        np.testing.assert_array_equal(ltq.Quantize(xd, qp).cpu().numpy(), want, err_msg=f"scale {scale} zp {zp}")
+        np.testing.assert_array_equal(ltq.Quantize(xd.view(-1)[1:], qp).cpu().numpy(), want.ravel()[1:])   # scalar path
+        q, s = ltq.quantize_rows(xd, qp=qp)
+        np.testing.assert_array_equal(q.cpu().numpy(), want)
+        np.testing.assert_array_equal(s.cpu().numpy(), want.astype(np.int64).sum(1).astype(np.int32))
+        wide = xd.view(1, -1) if xd.numel() > 2048 else None                       # one long row: the whole-CTA-per-row form
+        if wide is not None:
+            q2, _ = ltq.quantize_rows(wide.contiguous(), qp=qp)
+            np.testing.assert_array_equal(q2.cpu().numpy().ravel(), want.ravel())
+
+
+def test_min_max_with_nans_follows_the_reference_loop(cuda, oracle):
+    """The reference seeds min and max with data[0] and replaces them when a comparison is true (l-ten/utils.cpp:209-223):
+    NaNs after the first element are skipped, a NaN in the first element stays in both results."""
+    import ltq
+    rng = np.random.default_rng(77)
+    base = (rng.standard_normal(9000) * 3).astype(np.float32)
+    cases = []
+    a = base.copy(); a[[5, 4000, 8999]] = np.nan; cases.append(a)          # NaNs in the middle and at the end
+    b = base.copy(); b[0] = np.nan; cases.append(b)                         # NaN seed
+    cases.append(np.full(300, np.nan, np.float32))                          # nothing comparable
+    c = base.copy(); c[1:] = np.nan; cases.append(c)                        # only the seed is a number
+    for x in cases:
+        got = ltq.GetMinMax(cuda.from_numpy(x).cuda()).cpu().numpy()
+        want = np.array(oracle.port.get_min_max(x), np.float32)
+        np.testing.assert_array_equal(got, want)                            # NaN == NaN for this comparison
+
+
 def test_large_tensor_properties(cuda):
     """Full-size activation block of the 4096^3 configuration: dequantize(quantize(x)) stays within half a step and
     the fused row sums equal the sums of the bytes written."""
