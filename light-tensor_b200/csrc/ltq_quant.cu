@@ -257,7 +257,7 @@ cudaError_t launch_dequantize(float *x, const uint8_t *q, uint64_t len, const lt
 }
 
 // ---- activation quantise + row sums -------------------------------------------------------------------------------
-// TPR threads cooperate on one row (TPR = 32: a warp; TPR = 256: the whole CTA).  Reads fp32 once, writes uint8 once
+// TPR threads cooperate on one row (TPR = 32: a warp; 64: two warps; 256: the whole CTA).  Reads fp32 once, writes uint8 once
 // and one int32 per row: 5 bytes per element of HBM traffic, the minimum for this step.
 // BACK_TO_FRONT: rows are visited last to first (see the loop below).
 template <int TPR, bool BACK_TO_FRONT>
@@ -278,12 +278,13 @@ __global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__re
     constexpr int ROWS_PER_CTA = 256 / TPR;
     const int lane = threadIdx.x % TPR;
     const int sub = threadIdx.x / TPR;
-    __shared__ int32_t warp_part[8];
+    __shared__ int32_t warp_part[2][8];
+    int par = 0;
     // BACK_TO_FRONT is chosen when the parameters come from device memory: as a rule they were computed from this very
     // tensor a moment ago (GetMinMax, then ComputeQuantizationParams), that pass went through the rows front to back,
     // and its last rows are what L2 still holds; going back to front reads those from L2 instead of HBM.
     for (uint64_t slot = (uint64_t)blockIdx.x * ROWS_PER_CTA + sub; ; slot += (uint64_t)gridDim.x * ROWS_PER_CTA) {
-        // All threads of a CTA leave together when TPR == 256 (slot is uniform); with TPR == 32 a warp leaves alone.
+        // All threads that share a row leave together (slot is uniform among them): the CTA, a pair of warps, or a warp.
         if (slot >= M) break;
         const uint64_t row = BACK_TO_FRONT ? M - 1 - slot : slot;
         const float *xr = x + row * K;
@@ -323,15 +324,29 @@ __global__ void __launch_bounds__(256, 8) quantize_rows_kernel(const float *__re
         for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
         if (TPR == 32) {
             if (lane == 0) asum[row] = (int32_t)s;
+        } else if (TPR == 64) {
+            // two warps per row: they meet on a barrier of their own (ids 1-4; 0 is the CTA-wide one), the other three
+            // pairs of the CTA run on.  Partial sums alternate between two buffers, so one barrier per row is enough: a
+            // warp can only write a buffer again after the barrier of the row in between, which its partner reaches
+            // after it has read.
+            if ((threadIdx.x & 31) == 0) warp_part[par][threadIdx.x >> 5] = (int32_t)s;
+            switch (sub) {   // literal ids: with a register operand the compiler reserves all sixteen barriers
+                case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+                default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+            }
+            if (lane == 0) asum[row] = warp_part[par][2 * sub] + warp_part[par][2 * sub + 1];
+            par ^= 1;
         } else {
-            if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = (int32_t)s;
+            if ((threadIdx.x & 31) == 0) warp_part[par][threadIdx.x >> 5] = (int32_t)s;
             __syncthreads();
             if (threadIdx.x == 0) {
                 int32_t t = 0;
-                for (int w = 0; w < 8; w++) t += warp_part[w];
+                for (int w = 0; w < 8; w++) t += warp_part[par][w];
                 asum[row] = t;
             }
-            __syncthreads();
+            par ^= 1;   // the next row writes the other buffer: one barrier per row
         }
     }
 }
@@ -348,6 +363,17 @@ cudaError_t launch_quantize_rows(const float *x, uint64_t M, uint64_t K, const l
         int blocks = (int)(want > cap ? cap : want);
         e = qp_dev ? launch_chained(quantize_rows_kernel<32, true>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum)
                    : launch_chained(quantize_rows_kernel<32, false>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
+    } else if (qp_dev && M * K <= (16ull << 20) && K <= 16384 && (M + 3) / 4 >= (uint64_t)sm_count()) {
+        // Device parameters and at most 64 MB of fp32: the min / max pass that produced the parameters has left the
+        // tensor in L2, the loads return quickly and the work per row (addresses, the sum across lanes, the barrier)
+        // is what counts.  Two warps per row pay it once per four passes of the main loop on a 4096-wide row, a whole CTA
+        // on the row once per pass, and a barrier only stops the two warps it concerns.  Measured on 4096 x 4096 after
+        // GetMinMax: 30.3 us for the whole dynamic step against 32.3 us; on a tensor that comes from HBM the whole-CTA
+        // form is the faster one (16.9 us against 18.3 us alone), so it stays the choice everywhere else.
+        uint64_t want = (M + 3) / 4;
+        int blocks = (int)(want > cap ? cap : want);
+        e = qp_dev ? launch_chained(quantize_rows_kernel<64, true>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum)
+                   : launch_chained(quantize_rows_kernel<64, false>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum);
     } else {
         int blocks = (int)(M > cap ? cap : M);
         e = qp_dev ? launch_chained(quantize_rows_kernel<256, true>, dim3(blocks), dim3(256), 0, stream, x, M, K, scale, zpf, qp_dev, q, asum)

@@ -29,3 +29,13 @@ def test_bench_line_has_the_contract_keys(cuda, extra):
     assert e2e["h2d_bytes_per_step"] > 0 and e2e["d2h_bytes_per_step"] > 0 and 0 < e2e["value"] < line["value"]
     assert line["gpu_launches"] >= 2 * line["steps"]
     assert "sm_mhz" in line["clocks"] and "reasons" in line["clocks"]
+    if not extra:
+        # the default line carries the other parts of the metric as sections; a section that failed would hold "error"
+        for name in ("skinny", "helpers", "mlp_mnist", "conv2d_q", "mlp_block_rows"):
+            assert name in line and "error" not in line[name], (name, line.get(name))
+        assert line["mlp_mnist"]["fused_output_equals_layer_by_layer"] is True
+        assert line["mlp_mnist"]["batch_streams"]["outputs_equal_single_stream"] is True
+        assert line["conv2d_q"]["channels_last_equals_nchw_result"] is True
+        for k in ("get_min_max", "quantize_u8", "dynamic_quantize_rows", "dequantize"):
+            assert 0 < line["helpers"][k]["frac_of_measured"] < 1.5
+        assert 0 < e2e["frac_of_h2d_ceiling"] < 1.3

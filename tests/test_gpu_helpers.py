@@ -35,7 +35,7 @@ def test_explicit_and_bias_quantize(cuda, golden):
 
 
 @pytest.mark.parametrize("shape", [(1, 1), (1, 4096), (3, 17), (16, 4096), (64, 784), (257, 2050), (5, 33000),
-                                   (1000, 48)])
+                                   (1000, 48), (601, 4096), (1000, 4100), (593, 2049)])   # the last three: two warps per row when the parameters are on the device
 def test_quantize_rows_and_sums_vs_oracle(cuda, oracle, shape):
     import ltq
     rng = np.random.default_rng(shape[0] * 1000 + shape[1])
