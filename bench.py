@@ -547,7 +547,9 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
                                         "`with_d2h_running` = the step's download bytes copied on another stream at the "
                                         "same time; the ceiling is the best reading of all",
                       "bound": "host->device copy of the fp32 activations (PCIe); compute is "
-                               f"{ms_step / ms_e2e * 100:.1f} % of the step",
+                               f"{ms_step / ms_e2e * 100:.1f} % of the step" +
+                               ("; with several ranks the copy rates themselves fall (the ranks share host memory and "
+                                "PCIe roots): compare h2d_copy_rates_gbs with the 1-GPU line" if h.world > 1 else ""),
                       "host_numa_binding": h.numa}
     return res
 
