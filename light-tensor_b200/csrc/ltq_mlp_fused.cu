@@ -39,7 +39,10 @@
 // neither changed the time: bytes and sums of a hand-over in ONE copy (7 copies instead of 14 per hand-over), and a
 // conversion-free uint8 epilogue (integer / float bit tricks in place of the two conversion instructions per element).
 // A variant with clusters of 4, the weights streamed through a ring, was built and measured at 18.3 us: with both
-// operands 128 rows tall in one SM's shared memory its MMAs take 140 cycles instead of 70.
+// operands 128 rows tall in one SM's shared memory its MMAs take 140 cycles instead of 70.  Dealing the four 32-byte K
+// steps of every slab over four accumulators (added up in the epilogue) to break the chain of dependent MMAs was also
+// built and measured, bit-exact and slower (10.2 us against 9.3 us on the same box): MMAs issued by one thread do not
+// overlap better for having different accumulators, and the epilogue reads four times the TMEM columns.
 #include <cuda.h>
 
 #include <new>
