@@ -551,6 +551,9 @@ def measure_linear(h, args, wl, m_rows=16, with_e2e=True, steps=None, sustain_s=
                                ("; with several ranks the copy rates themselves fall (the ranks share host memory and "
                                 "PCIe roots): compare h2d_copy_rates_gbs with the 1-GPU line" if h.world > 1 else ""),
                       "host_numa_binding": h.numa}
+        if res["e2e"]["frac_of_h2d_ceiling"] > 1.0:
+            res["e2e"]["ceiling_note"] = ("the plain-copy readings came out below the rate the step itself kept: the host "
+                                          "side (shared with other tenants) was disturbed while they ran")
     return res
 
 
