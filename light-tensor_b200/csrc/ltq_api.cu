@@ -731,7 +731,10 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
     LTQ_REQUIRE(!nhwc_out || ((uintptr_t)out_dev & 15) == 0, LTQ_ERR_INVALID_ARG, "a channels-last output must be 16-byte aligned");
     if (direct) {
         const uint8_t *x_cl = x_dev;
-        if (!nhwc_in) {
+        // an NCHW input with strides 1 and whole words per row is transposed by the kernel itself while it loads
+        const bool gather = !nhwc_in && conv_direct_gather_ok(conv->direct, conv->Cin, conv->kh, conv->kw, conv->ph, conv->pw, width_in,
+                                                              Wo, x_dev);
+        if (!nhwc_in && !gather) {
             rc = grow(&conv->x_nhwc, &conv->x_nhwc_cap, conv_direct_input_bytes(conv->direct, batches, conv->Cin, height_in, width_in), st,
                       "the NHWC copy of the input");
             if (rc != LTQ_OK) return rc;
@@ -745,7 +748,7 @@ int ltq_conv2d_forward(ltq_conv2d *conv, const uint8_t *x_dev, uint64_t batches,
         epi.row_bias = per_channel ? nullptr : conv->bias;
         LTQ_CUDA_TRY(launch_conv_direct(x_cl, conv->direct, batches, conv->Cin, height_in, width_in, conv->Cout, conv->kh,
                                         conv->kw, conv->ph, conv->pw, Ho, Wo, epi, out_dev, nhwc_out, conv->dev->status,
-                                        conv->dev->sms, st));
+                                        conv->dev->sms, st, gather));
         return LTQ_OK;
     }
 

@@ -37,6 +37,8 @@
 
 #include "ltq_common.cuh"
 #include "ltq_conv_direct.cuh"
+#include <string.h>
+
 #include "ltq_gemm_tc.cuh"
 #include "ltq_tcgen05.cuh"
 
@@ -44,7 +46,12 @@ namespace ltq {
 
 namespace {
 
-constexpr int THREADS = 320;            // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue (two per TMEM lane quarter)
+constexpr int GATHER_WARPS = 8;
+constexpr int THREADS = 320 + 32 * GATHER_WARPS;   // warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue (two per TMEM lane
+                                                   // quarter), warps 10.. gather an NCHW input straight into the stages (only launched
+                                                   // when there is something to gather)
+constexpr int GATHER_BUFS = 3;                     // scratch buffers of the gathering warps: copies run GATHER_BUFS - 1 items ahead
+static_assert(GATHER_WARPS == 8, "the gathering code gives 16 lanes to a pixel and 16 pixel groups to a row: 256 threads");
 constexpr int CCH = 64;                 // channels per K chunk = bytes per row of an operand tile (64-byte swizzle)
 constexpr int MAX_STAGES = 8;
 constexpr uint32_t MAX_STAGE_BYTES = 96 * 1024;
@@ -67,6 +74,8 @@ struct DirectGeom {
     uint32_t CoutValid;                   // channels of the block that exist (the last block may be padded)
     uint32_t stages, stage_bytes;         // ring depth; planes * plane_bytes
     uint32_t nhwc_out;                    // output as [image][row][column][channel] instead of [image][channel][row][column]
+    uint32_t gather;                      // 1: the input is NCHW and warps 10 and up transpose it into the stages themselves
+    uint32_t Cin, H, W;                   // input geometry (gather only)
 };
 
 // Shared-memory matrix descriptor for a K-major operand tile with rows of 64 bytes laid out by TMA with the 64-byte
@@ -183,7 +192,7 @@ __global__ void reorder_weights_kernel(const uint8_t *__restrict__ w, uint8_t *_
 template <int OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const DirectGeom g,
-                   const Epilogue epi, void *__restrict__ out, uint32_t *status)
+                   const Epilogue epi, void *__restrict__ out, uint32_t *status, const uint8_t *__restrict__ x_nchw)
 {
     griddep_launch_dependents();
     extern __shared__ uint8_t smem_raw[];
@@ -203,7 +212,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < g.stages; s++) {
-            mbar_init(full0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, g.gather ? GATHER_WARPS : 1);   // one arrival per gathering warp, or the TMA producer's
             mbar_init(empty0 + 8 * s, 1);
         }
         for (int s = 0; s < 2; s++) {
@@ -216,7 +225,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         // the reordered weights are static data: on their way before the kernel in front has finished
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        if (!g.gather) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         mbar_expect_tx(wfull, nchunks * wtile);
         for (uint32_t ch = 0; ch < nchunks; ch++) tma_load_2d(wsm + ch * wtile, &map_w, wfull, (int32_t)(ch * CCH), 0);
     }
@@ -234,17 +243,24 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         const uint32_t dy = (uint32_t)(floordiv(ti, (int32_t)g.sh) - g.dy_min), dx = (uint32_t)(floordiv(tj, (int32_t)g.sw) - g.dx_min);
         s_tap[tap] = (uint32_t)__popc(g.plane_mask & ((1u << pl) - 1u)) * g.plane_bytes + (dy * g.P + dx) * CCH;
     }
+    if (g.gather) {
+        // The gathering warps only ever write pixels that exist; the slots left and right of an image row (the padding
+        // columns and the unused tail of the P slots) are zero for the whole run.
+        uint4 *rz = reinterpret_cast<uint4 *>(smem_raw + (ring - raw0));
+        for (uint32_t i = threadIdx.x; i < g.stages * g.stage_bytes / 16; i += blockDim.x) rz[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // plain stores -> tensor-core reads
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    griddep_wait();   // the transposed input comes from the kernel in front
+    griddep_wait();   // the input comes from the kernel in front
     const uint32_t tmem_base = s_misc[0];
     const uint32_t box_bytes = g.rows_box * g.P * CCH;   // a copy always delivers its whole box (zeros outside the image)
     const uint32_t planes = g.sh * g.sw;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
+        if (lane == 0 && !g.gather) {
             uint32_t st = 0, ph = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < g.tiles; t += gridDim.x) {
@@ -299,6 +315,109 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
             if (elect_one()) umma_commit(tfull0 + 8 * as);
             __syncwarp();
             if (++as == 2) { as = 0; aph ^= 1; }
+        }
+    } else if (warp >= 10) {
+        // ---------------- gather (warps 10 and up, NCHW input, strides 1, W a multiple of 8 up to 64): what the NHWC copy +
+        // the tensor copy do otherwise, in two steps per tile and 64-channel chunk ("item").
+        // (1) The item's image rows - rows_box rows x 64 channels x W bytes, as they lie in the NCHW tensor - are fetched
+        //     into a scratch buffer with 8-byte asynchronous copies (cp.async; 4-byte ones were measured first and their
+        //     sheer number, 3584 per item, set the pace at ~2 us per tile whatever the number of warps and the depth),
+        //     GATHER_BUFS - 1 items ahead of their use: no registers held, memory latency off the critical path.  Rows
+        //     outside the image and channels beyond Cin are not fetched.  A (row, channel) line takes 64 bytes of scratch;
+        //     its 8-byte units are rotated by channel / 4 so that the reads of step 2 spread over the banks.
+        // (2) A thread takes the words (four pixels each) of four consecutive channels at one place of a row from the
+        //     scratch buffer, transposes the 4 x 4 bytes in registers and writes four words - four channels of one pixel
+        //     each - into the stage at the addresses the 64-byte swizzle gives them (16-byte unit index XOR bits 7-8 of
+        //     the byte address).  Sixteen lanes cover the 64 channels of a pixel, so a warp's stores are two runs of 64
+        //     bytes.  Rows outside the image are written as zeros; the columns left and right were zeroed once.
+        // The gathering warps meet once per item (named barrier 2): everybody's copies of the item have landed, and everybody is
+        // done reading the buffer that the copies issued next will overwrite.  The loop always runs its full count so that
+        // the barrier stays matched even after a bounded wait has given up; the work is skipped then.
+        if (g.gather) {
+            const uint32_t lt = threadIdx.x - 320u, c4 = lt & 15u, wsub = lt >> 4;   // wsub: 0 .. GATHER_GROUPS - 1 = 15
+            const uint32_t nw4 = g.W / 4, nw8 = g.W / 8;
+            constexpr uint32_t LINE = 16;                                         // words of scratch per (row, channel)
+            const size_t chan = (size_t)g.H * g.W;
+            uint8_t *ring_ptr = smem_raw + (ring - raw0);
+            uint32_t *scratch = reinterpret_cast<uint32_t *>(s_misc + 4);          // [GATHER_BUFS][rows_box * 64 lines]
+            const uint32_t scratch_words = g.rows_box * CCH * LINE;
+            const uint32_t my_tiles = blockIdx.x < g.tiles ? (g.tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+            const uint32_t items = my_tiles * g.cchunks;
+            // cursor of the copies (runs ahead) and of the transposing step
+            uint32_t f_t = blockIdx.x, f_cc = 0, f_n = 0;
+            // Eight lanes per line; a thread's copies of an item all have the same place in the line and channels a fixed
+            // step apart: one address computation per image row, additions after that.
+            const uint32_t f_w8 = lt & 7u, f_c0 = lt >> 3, f_cstep = (32u * GATHER_WARPS) >> 3;
+            auto fetch_next = [&]() {
+                if (f_n < items && f_w8 < nw8) {
+                    const uint32_t b = f_t / g.tiles_per_image, ho0 = (f_t - b * g.tiles_per_image) * g.rpt;
+                    const uint32_t buf = smem_u32(scratch + (f_n % GATHER_BUFS) * scratch_words);
+                    const uint32_t ch0 = f_cc * CCH + f_c0;                      // first channel of this thread
+                    for (uint32_t r = 0; r < g.rows_box; r++) {
+                        const int32_t y = (int32_t)ho0 + (int32_t)r + g.dy_min;
+                        if (y < 0 || y >= (int32_t)g.H) continue;
+                        const uint8_t *src = x_nchw + ((size_t)b * g.Cin + ch0) * chan + (size_t)y * g.W + 8 * f_w8;
+                        for (uint32_t ch = ch0, c = f_c0; c < (uint32_t)CCH && ch < g.Cin; c += f_cstep, ch += f_cstep) {
+                            const uint32_t dst = buf + ((r * CCH + c) * LINE + 2 * ((f_w8 + (c >> 2)) & 7u)) * 4;
+                            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+                            src += (size_t)f_cstep * chan;
+                        }
+                    }
+                }
+                if (f_n < items) {
+                    f_n++;
+                    if (++f_cc == g.cchunks) { f_cc = 0; f_t += gridDim.x; }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");     // (an empty group when nothing is left: the counting stays uniform)
+            };
+#pragma unroll
+            for (int i = 0; i < GATHER_BUFS - 1; i++) fetch_next();
+            uint32_t st = 0, ph = 0, t = blockIdx.x, cc = 0;
+            bool ok = true;
+            for (uint32_t n = 0; n < items; n++) {
+                asm volatile("cp.async.wait_group %0;" ::"n"(GATHER_BUFS - 2) : "memory");   // this thread's copies of item n are in place
+                asm volatile("bar.sync 2, %0;" ::"n"(32 * GATHER_WARPS) : "memory");   // ... and so are everybody's; item n - 1 has been read by all
+                fetch_next();                                             // item n + GATHER_BUFS - 1, into the buffer item n - 1 used
+                ok = ok && !*abort_flag;
+                if (ok) ok = __all_sync(0xFFFFFFFFu, mbar_wait(empty0 + 8 * st, ph ^ 1, abort_flag, status, 0x700u | st));
+                if (ok) {
+                    const uint32_t b = t / g.tiles_per_image, ho0 = (t - b * g.tiles_per_image) * g.rpt;
+                    (void)b;
+                    uint8_t *stage = ring_ptr + st * g.stage_bytes;
+                    const uint32_t *sc = scratch + (n % GATHER_BUFS) * scratch_words;
+                    const uint32_t c0 = cc * CCH + 4 * c4;                        // this thread's first channel
+                    const uint32_t nch = c0 < g.Cin ? (g.Cin - c0 < 4u ? g.Cin - c0 : 4u) : 0u;
+                    // this thread's place in a row: words wsub of the lines of channels 4 * c4 .. + 3 (their units rotated by c4)
+                    const uint32_t *row = sc + (4 * c4) * LINE + 2 * (((wsub >> 1) + c4) & 7u) + (wsub & 1u);
+                    // byte offset of (slot, this thread's four channels) without the swizzle; slot = r * P + 4 * w4 + k - dx_min
+                    uint32_t off = (uint32_t)(-g.dx_min) * CCH + (c4 & 3u) * 4 + 4 * wsub * CCH;
+                    const uint32_t unit = c4 >> 2;
+                    if (wsub < nw4) {
+                        for (uint32_t r = 0; r < g.rows_box; r++, row += CCH * LINE, off += g.P * CCH) {
+                            const int32_t y = (int32_t)ho0 + (int32_t)r + g.dy_min;
+                            const bool row_in = y >= 0 && y < (int32_t)g.H;
+                            const uint32_t a0 = row_in && nch > 0 ? row[0] : 0u, a1 = row_in && nch > 1 ? row[LINE] : 0u;
+                            const uint32_t a2 = row_in && nch > 2 ? row[2 * LINE] : 0u, a3 = row_in && nch > 3 ? row[3 * LINE] : 0u;
+                            const uint32_t t0 = __byte_perm(a0, a1, 0x5140), t1 = __byte_perm(a0, a1, 0x7362);
+                            const uint32_t u0 = __byte_perm(a2, a3, 0x5140), u1 = __byte_perm(a2, a3, 0x7362);
+                            const uint32_t o[4] = {__byte_perm(t0, u0, 0x5410), __byte_perm(t0, u0, 0x7632), __byte_perm(t1, u1, 0x5410),
+                                                   __byte_perm(t1, u1, 0x7632)};
+#pragma unroll
+                            for (uint32_t k = 0; k < 4; k++) {
+                                const uint32_t o_k = off + k * CCH;                 // = slot * 64 + (c4 & 3) * 4
+                                // the 16-byte unit of the channels, XORed with bits 7-8 of the byte address (= bits 1-2 of the slot)
+                                *reinterpret_cast<uint32_t *>(stage + o_k + ((unit ^ ((o_k >> 7) & 3u)) << 4)) = o[k];
+                            }
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // plain stores -> tensor-core reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full0 + 8 * st);
+                }
+                if (++st == g.stages) { st = 0; ph ^= 1; }
+                if (++cc == g.cchunks) { cc = 0; t += gridDim.x; }
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");              // nothing of this thread's is still on its way
         }
     } else {
         // ---------------- epilogue (warps 2..9 = 256 threads): thread = output position x half of the channels ----------------
@@ -409,10 +528,13 @@ EncodeTiledFn encode_fn()
     return fn;
 }
 
-size_t direct_smem(uint32_t stages, uint32_t stage_bytes, uint32_t nchunks, uint32_t Npad)
+size_t direct_smem(uint32_t stages, uint32_t stage_bytes, uint32_t nchunks, uint32_t Npad, uint32_t scratch_bytes = 0)
 {
-    return 1024 + (size_t)stages * stage_bytes + (size_t)nchunks * Npad * CCH + (128 + MAX_TAPS) * 4 + (2 * MAX_STAGES + 5) * 8 + 16;
+    return 1024 + (size_t)stages * stage_bytes + (size_t)nchunks * Npad * CCH + (128 + MAX_TAPS) * 4 + (2 * MAX_STAGES + 5) * 8 + 16 +
+           scratch_bytes;
 }
+// The gathering warps' scratch buffers: rows_box rows x 64 channels x 64 bytes each.
+uint32_t gather_scratch_bytes(uint32_t rows_box, uint64_t) { return (uint32_t)GATHER_BUFS * rows_box * CCH * 64u; }
 
 // What a tile loads: per plane in use a region of rows_box rows x P pixel slots (P a power of two that holds an output
 // row and the spread of the kernel's column shifts).  ok = false when a row does not fit the 128 rows of a tile.
@@ -445,9 +567,10 @@ RegionGeom region_geom(uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint6
 
 template <int OUT>
 cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const DirectGeom &g, const Epilogue &epi, void *out,
-                          uint32_t *status, int sms, cudaStream_t stream)
+                          uint32_t *status, int sms, cudaStream_t stream, const uint8_t *x_nchw)
 {
-    const size_t smem = direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad);
+    const size_t smem = direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad,
+                                    g.gather ? gather_scratch_bytes(g.rows_box, g.W) : 0u);
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -459,9 +582,12 @@ cudaError_t launch_direct(const CUtensorMap &mx, const CUtensorMap &mw, const Di
         attr_done[dev] = true;
     }
     const unsigned grid = g.tiles < (uint32_t)sms ? g.tiles : (unsigned)sms;
-    e = launch_chained(conv_direct_kernel<OUT>, dim3(grid), dim3(THREADS), smem, stream, mx, mw, g, epi, out, status);
+    // (the gathering warps are only launched when there is something to gather)
+    e = launch_chained(conv_direct_kernel<OUT>, dim3(grid), dim3(g.gather ? THREADS : THREADS - 32 * GATHER_WARPS), smem, stream, mx,
+                       mw, g, epi, out, status, x_nchw);
     count_launch();
-    note_kernel("conv_direct_kernel<%s> (%u tiles of %u rows x %u slots)", out_mode_name(OUT), g.tiles, g.rpt, g.P);
+    note_kernel("conv_direct_kernel<%s> (%u tiles of %u rows x %u slots%s)", out_mode_name(OUT), g.tiles, g.rpt, g.P,
+                g.gather ? ", NCHW input gathered in the kernel" : "");
     return e;
 }
 
@@ -559,6 +685,18 @@ bool conv_direct_shape_ok(const ConvDirectPlan &plan, uint64_t batches, uint64_t
     return direct_smem(2, r.stage_bytes, (uint32_t)(kh * kw * (padded_channels(Cin) / CCH)), (uint32_t)(Cout + EXTRA)) <= SMEM_BUDGET;
 }
 
+bool conv_direct_gather_ok(const ConvDirectPlan &plan, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t W,
+                           uint64_t Wo, const uint8_t *x)
+{
+    // strides 1 (one plane), image rows of whole 8-byte units, at most 64 bytes (one scratch line), an 8-byte aligned input ...
+    if (!(plan.blocks > 0 && plan.sh == 1 && plan.sw == 1 && W % 8 == 0 && W <= 64 && (reinterpret_cast<uintptr_t>(x) & 7) == 0)) return false;
+    // ... and room for the scratch buffers beside the weights and a ring of at least three stages
+    const RegionGeom r = region_geom(kh, kw, ph, pw, 1, 1, Wo);
+    if (!r.ok) return false;
+    return direct_smem(3, r.stage_bytes, (uint32_t)(kh * kw * (padded_channels(Cin) / CCH)), plan.nb[0] + EXTRA,
+                       gather_scratch_bytes(r.rows_box, W)) <= SMEM_BUDGET;
+}
+
 cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H,
                                 uint64_t W, cudaStream_t stream)
 {
@@ -603,10 +741,15 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, const ConvDirectP
 
 cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
                                uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
-                               const Epilogue &epi, void *out, bool nhwc_out, uint32_t *status, int sms, cudaStream_t stream)
+                               const Epilogue &epi, void *out, bool nhwc_out, uint32_t *status, int sms, cudaStream_t stream, bool nchw_in)
 {
     DirectGeom g;
     g.nhwc_out = nhwc_out ? 1u : 0u;
+    g.gather = nchw_in ? 1u : 0u;
+    g.Cin = (uint32_t)Cin;
+    g.H = (uint32_t)H;
+    g.W = (uint32_t)W;
+    if (nchw_in && !conv_direct_gather_ok(plan, Cin, kh, kw, ph, pw, W, Wo, xt)) return cudaErrorInvalidConfiguration;
     g.B = (uint32_t)batches;
     g.Ho = (uint32_t)Ho;
     g.Wo = (uint32_t)Wo;
@@ -639,19 +782,24 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
     cuuint64_t strides[4] = {(cuuint64_t)Cp, (cuuint64_t)(Wp * Cp), (cuuint64_t)(Hp * Wp * Cp), (cuuint64_t)(batches * Hp * Wp * Cp)};
     cuuint32_t box[5] = {(cuuint32_t)CCH, g.P, g.rows_box, 1, 1};
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<uint8_t *>(xt), dims, strides, box, estr,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    if (!nchw_in) {   // (with an NCHW input the kernel reads through plain pointers and the map stays unused)
+        CUresult r = encode_fn()(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<uint8_t *>(xt), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    } else {
+        memset(&mx, 0, sizeof(mx));
+    }
     const size_t esize = epi.out_mode == LTQ_OUT_U8 ? 1 : 4, plane = (size_t)Ho * Wo;
     // one launch per block of output channels (each reads the input tiles again, out of L2)
     for (uint32_t i = 0; i < plan.blocks; i++) {
         g.Cout = plan.nb[i];
         g.CoutValid = plan.valid[i];
         g.Npad = g.Cout + EXTRA;
+        const uint32_t scr = nchw_in ? gather_scratch_bytes(g.rows_box, W) : 0u;
         g.stages = MAX_STAGES;
-        while (g.stages > 2 && direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) g.stages--;
-        if (direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad) > SMEM_BUDGET) return cudaErrorInvalidConfiguration;
+        while (g.stages > 2 && direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad, scr) > SMEM_BUDGET) g.stages--;
+        if (direct_smem(g.stages, g.stage_bytes, g.kh * g.kw * g.cchunks, g.Npad, scr) > SMEM_BUDGET) return cudaErrorInvalidConfiguration;
         Epilogue e = epi;                       // the block's own channel sums and biases
         e.bsum = epi.bsum + plan.cout0[i];
         if (epi.bias) e.bias = epi.bias + plan.cout0[i];
@@ -659,9 +807,9 @@ cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, ui
         const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(plan.maps[i].opaque);
         cudaError_t ce;
         switch (epi.out_mode) {
-            case LTQ_OUT_U8: ce = launch_direct<0>(mx, mw, g, e, o, status, sms, stream); break;
-            case LTQ_OUT_F32: ce = launch_direct<1>(mx, mw, g, e, o, status, sms, stream); break;
-            default: ce = launch_direct<2>(mx, mw, g, e, o, status, sms, stream);
+            case LTQ_OUT_U8: ce = launch_direct<0>(mx, mw, g, e, o, status, sms, stream, nchw_in ? xt : nullptr); break;
+            case LTQ_OUT_F32: ce = launch_direct<1>(mx, mw, g, e, o, status, sms, stream, nchw_in ? xt : nullptr); break;
+            default: ce = launch_direct<2>(mx, mw, g, e, o, status, sms, stream, nchw_in ? xt : nullptr);
         }
         if (ce != cudaSuccess) return ce;
     }

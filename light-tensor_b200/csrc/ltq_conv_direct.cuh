@@ -38,6 +38,12 @@ cudaError_t launch_nchw_to_nhwc(const uint8_t *x, uint8_t *xt, const ConvDirectP
 // unused), B = weights (bsum = their sums per output channel, bias per output channel or nullptr).
 cudaError_t launch_conv_direct(const uint8_t *xt, const ConvDirectPlan &plan, uint64_t batches, uint64_t Cin, uint64_t H, uint64_t W,
                                uint64_t Cout, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t Ho, uint64_t Wo,
-                               const Epilogue &epi, void *out, bool nhwc_out, uint32_t *status, int sms, cudaStream_t stream);
+                               const Epilogue &epi, void *out, bool nhwc_out, uint32_t *status, int sms, cudaStream_t stream,
+                               bool nchw_in = false);
+// nchw_in: `xt` is the caller's NCHW input itself and the kernel transposes it into its stages while it loads (no NHWC
+// copy, no transposition launch).  Possible when conv_direct_gather_ok says so: strides 1, W a multiple of 8 up to 64, an
+// 8-byte aligned input, and shared memory for the gathering warps' scratch buffers beside the weights and three stages.
+bool conv_direct_gather_ok(const ConvDirectPlan &plan, uint64_t Cin, uint64_t kh, uint64_t kw, uint64_t ph, uint64_t pw, uint64_t W,
+                           uint64_t Wo, const uint8_t *x);
 
 }  // namespace ltq

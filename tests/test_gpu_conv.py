@@ -90,9 +90,18 @@ def test_conv_matches_oracle(cuda, oracle, shape):
     (1, 64, 5, 128, 16, 3, 3, 1, 0),       # Wo = 126: one output row per tile of 128 slots; padding in y only
     (2, 64, 14, 14, 256, 3, 3, 1, 1),      # 256 output channels: three launches (96 + 96 + 64 channels)
     (1, 128, 10, 12, 128, 3, 3, 1, 1),     # 128 -> 128 channels: two channel chunks, two launches of 64 channels
+    (2, 64, 9, 16, 32, 3, 3, 1, 1),        # image rows of two 8-byte units: gathered by the kernel itself
+    (1, 100, 10, 24, 24, 3, 3, 0, 1),      # gathered, two channel chunks, the second one 36 channels + padding
+    (3, 3, 11, 64, 16, 3, 3, 1, 1),        # gathered, 64-byte rows (a full scratch line), three channels
+    (2, 64, 6, 8, 16, 1, 1, 0, 0),         # one unit per row, 16 image rows per tile: the scratch lines do not fit, NHWC copy
+    (1, 70, 40, 40, 40, 3, 3, 1, 1),       # gathered, many tiles per CTA-less grid (20 tiles), 70 channels
 ])
 @pytest.mark.parametrize("mode", ["u8", "f32", "i32"])
 def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
+    # the shapes whose NCHW input the kernel transposes itself while it loads (strides 1, rows of whole 8-byte units up to 64
+    # bytes, scratch lines that fit beside the weights); the others go through the NHWC copy
+    GATHERED = {(3, 64, 56, 56, 64, 3, 3, 1, 1), (2, 64, 9, 16, 32, 3, 3, 1, 1), (1, 100, 10, 24, 24, 3, 3, 0, 1),
+                (3, 3, 11, 64, 16, 3, 3, 1, 1), (1, 70, 40, 40, 40, 3, 3, 1, 1)}
     """Stride 1 and a multiple of 64 input channels take the kernel that never builds the patches (K walked as kernel row,
     kernel column, channel; patch sums from an all-ones weight row).  Against the oracle, bit for bit, with and without
     the per-channel bias and ReLU, and against the patch-buffer path on the same device."""
@@ -110,6 +119,8 @@ def test_conv_without_patch_buffer_matches_oracle(cuda, oracle, shape, mode):
         flags = (ltq.FLAG_BIAS_PER_CHANNEL if use_bias else 0) | (ltq.FLAG_RELU if relu else 0)
         got = _conv(cuda, ltq, c, qps, flags=flags, out_mode=out_mode, bias=bias if use_bias else None)
         assert ltq.last_kernel().startswith("conv_direct_kernel<"), ltq.last_kernel()
+        # image rows of whole words are transposed by the kernel itself while it loads; the others go through the NHWC copy
+        assert ("NCHW input gathered" in ltq.last_kernel()) == (shape in GATHERED), ltq.last_kernel()
         old = _conv(cuda, ltq, c, qps, flags=flags | ltq.FLAG_FORCE_SIMT, out_mode=out_mode, bias=bias if use_bias else None)
         assert not ltq.last_kernel().startswith("conv_direct_kernel<")
         np.testing.assert_array_equal(got.view(np.uint32) if mode == "f32" else got, old.view(np.uint32) if mode == "f32" else old)
