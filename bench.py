@@ -1047,7 +1047,7 @@ def measure_conv(h, args, sample_clocks=False):
     launches = (ltq.kernel_launches() - launches0) // (args.steps + args.warmup) * args.steps
     kernel = ltq.last_kernel()
 
-    # the same layer inside a channels-last chain (input and output [B, H, W, C]: no transposition pass)
+    # the same layer inside a channels-last chain (input and output [B, H, W, C]: plain tensor copies, nothing to transpose)
     xs_cl = [x.permute(0, 2, 3, 1).contiguous() for x in xs]
     outs_cl = [torch.empty((B, H, W, Cout), dtype=torch.uint8, device=dev) for _ in range(sets)]
     cl = ltq.FLAG_RELU | ltq.FLAG_NHWC_IN | ltq.FLAG_NHWC_OUT
@@ -1085,8 +1085,9 @@ def run_conv(args):
     ms_step, world = r["ms_step"], h.world
     cfg = {"workload": conv_workload_name(r), "sharding": "independent replicas, one batch stream per GPU",
            "l2": f"rotating {r['sets']} distinct input / output sets",
-           "step": "one Conv2d_q forward of the batch: NCHW -> NHWC transposition + the kernel that reads its patch slices "
-                   "straight from the image (no patch buffer)",
+           "step": "one Conv2d_q forward of the batch: one kernel that gathers its NCHW input tile by tile (8-byte asynchronous "
+                   "copies + a 4 x 4 byte transposition in registers) and reads every patch slice out of that tile (no NHWC copy, "
+                   "no patch buffer)",
            "timing": "CUDA graph replay" if not args.no_graph else "eager launches"}
     h.finish(base_line(h, args, r["ops"] / (ms_step * 1e-3) / 1e12 * world, "TOPS", ms_step, "weak", cfg,
                        samples_per_s=r["B"] * world / (ms_step * 1e-3), gpu_launches=r["launches"], kernel=r["kernel"],
