@@ -372,9 +372,9 @@ int ltq_conv2d_output_size(const ltq_conv2d *conv, uint64_t height_in, uint64_t 
  * channels_out values; that is reproduced as long as Ho*Wo <= channels_out and refused (LTQ_ERR_UNSUPPORTED) beyond,
  * where the reference reads past the tensor.  LTQ_FLAG_BIAS_PER_CHANNEL adds bias[c] per output channel instead.
  * LTQ_FLAG_RELU / LTQ_FLAG_SATURATE / LTQ_FLAG_FORCE_* act as in ltq_layer_forward.
- * Layout, additive: the reference knows NCHW only.  Most layers are computed from a channels-last copy of the
- * input; where the input channels are a multiple of 64 and the output channels a multiple of 16, LTQ_FLAG_NHWC_IN
- * hands that layout in directly (no transposition pass; x_dev 16-byte aligned) and LTQ_FLAG_NHWC_OUT writes it (out_dev
+ * Layout, additive: the reference knows NCHW only.  Most layers are computed from a channels-last form of the
+ * input (made tile by tile inside the kernel, or as a copy by a kernel in front); where the input channels are a multiple of 64 and the output channels a multiple of 16, LTQ_FLAG_NHWC_IN
+ * hands that layout in directly (nothing to transpose; x_dev 16-byte aligned) and LTQ_FLAG_NHWC_OUT writes it (out_dev
  * 16-byte aligned; LTQ_FLAG_NHWC_IN needs strides 1), so that a chain of such layers never leaves it.  The values are
  * the same, only their place in memory differs.  For any other geometry or a forced kernel the two flags give
  * LTQ_ERR_UNSUPPORTED. */
