@@ -472,15 +472,24 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
                         }
                         d += 16;
                     } else if (valid) {
+                        if (ch + 16 <= g.CoutValid) {     // a whole chunk of channels (all but the padded tail of the last block)
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            if (ch + j < g.CoutValid) {   // (the last block of channels may be padded)
-                                if (OUT == 0) *d = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
-                                else if (OUT == 1) *d = (OutT)__uint_as_float(res[j]);
-                                else *d = (OutT)(int32_t)res[j];
+                            for (int j = 0; j < 16; j++) {
+                                if (OUT == 0) d[(size_t)j * plane] = (OutT)__byte_perm(res[j >> 2], 0u, 0x4440 + (j & 3));
+                                else if (OUT == 1) d[(size_t)j * plane] = (OutT)__uint_as_float(res[j]);
+                                else d[(size_t)j * plane] = (OutT)(int32_t)res[j];
                             }
-                            d += plane;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                if (ch + j < g.CoutValid) {
+                                    if (OUT == 0) d[(size_t)j * plane] = (OutT)((res[j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                                    else if (OUT == 1) d[(size_t)j * plane] = (OutT)__uint_as_float(res[j]);
+                                    else d[(size_t)j * plane] = (OutT)(int32_t)res[j];
+                                }
+                            }
                         }
+                        d += 16 * plane;
                     }
                     tmem_ld_wait();
                 }
