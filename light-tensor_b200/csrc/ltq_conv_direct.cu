@@ -321,7 +321,9 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         // the tensor copy do otherwise, in two steps per tile and 64-channel chunk ("item").
         // (1) The item's image rows - rows_box rows x 64 channels x W bytes, as they lie in the NCHW tensor - are fetched
         //     into a scratch buffer with 8-byte asynchronous copies (cp.async; 4-byte ones were measured first and their
-        //     sheer number, 3584 per item, set the pace at ~2 us per tile whatever the number of warps and the depth),
+        //     sheer number, 3584 per item, set the pace at ~2 us per tile whatever the number of warps and the depth; on
+        //     rows of 20 and 28 bytes, which only 4-byte copies can fetch, gathering measured no faster than the NHWC copy
+        //     in front, so those keep it),
         //     GATHER_BUFS - 1 items ahead of their use: no registers held, memory latency off the critical path.  Rows
         //     outside the image and channels beyond Cin are not fetched.  A (row, channel) line takes 64 bytes of scratch;
         //     its 8-byte units are rotated by channel / 4 so that the reads of step 2 spread over the banks.
