@@ -336,7 +336,7 @@ conv_direct_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         // done reading the buffer that the copies issued next will overwrite.  The loop always runs its full count so that
         // the barrier stays matched even after a bounded wait has given up; the work is skipped then.
         if (g.gather) {
-            const uint32_t lt = threadIdx.x - 320u, c4 = lt & 15u, wsub = lt >> 4;   // wsub: 0 .. GATHER_GROUPS - 1 = 15
+            const uint32_t lt = threadIdx.x - 320u, c4 = lt & 15u, wsub = lt >> 4;   // wsub = 0 .. 15: this thread's place (word) in a row
             const uint32_t nw4 = g.W / 4, nw8 = g.W / 8;
             constexpr uint32_t LINE = 16;                                         // words of scratch per (row, channel)
             const size_t chan = (size_t)g.H * g.W;
